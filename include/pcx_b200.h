@@ -1,0 +1,140 @@
+/*
+ * pcx_b200.h — C ABI of the sm_100a kernels behind the compiled probabilistic-circuit
+ * forward / backward / mini-batch-EM path.
+ *
+ * Every entry point replaces one kernel family of PyJuice; the citation after each
+ * declaration names the reference launcher (or Triton kernel) whose work it takes over.
+ * Paths are relative to the PyJuice source tree (src/pyjuice/...).
+ *
+ * Conventions
+ *   - all pointers are DEVICE pointers; sizes and scalars are passed by value;
+ *   - value buffers are row-major [rows, B] fp32 with the batch innermost;
+ *   - index tables are int32 copies of the compiled int64 tables (host checks the range);
+ *     id 0 in a child / parent / parameter table means padding;
+ *   - kernels are enqueued on `stream` (a cudaStream_t passed as void*), never allocate,
+ *     never synchronise, and write in place;
+ *   - return value: 0 on success, a cudaError_t value if the launch was rejected,
+ *     -1 for an argument the kernel family does not support.
+ */
+#ifndef PCX_B200_H
+#define PCX_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Library / build identification: returns the compute capability it was built for (100). */
+int pcx_build_arch(void);
+
+/* p[i] = v  /  p[i] *= v  for i < n.
+ * Replaces the buffer resets of model/tensorcircuit.py:357-359, 528-529, 1761-1773 and the
+ * `param_flows *= flows_memory` of model/tensorcircuit.py:1411-1412, layer/input_layer.py:299-300. */
+int pcx_fill_f32(float* p, int64_t n, float v, void* stream);
+int pcx_scale_f32(float* p, int64_t n, float v, void* stream);
+/* p[i] = exp(p[i]); used to hand linear-space flows to callers that ask for logspace_flows=False. */
+int pcx_exp_f32(float* p, int64_t n, void* stream);
+
+/* Flow-carrying entry points take `logspace`: 1 = flow buffers hold log-flows (the default regime),
+ * 0 = they hold linear flows (PyJuice's logspace_flows=False).  Arithmetic is done in log space either way;
+ * the flag only changes how flows are read and written. */
+
+/* node_flows[root rows, b] = w (linear) or log w (log space), w = weights ? weights[r*B+b] : 1
+ * (model/tensorcircuit.py:537-552). */
+int pcx_set_root_flows(float* node_flows, const float* weights, int64_t root_start, int64_t num_roots,
+                       int B, int logspace, void* stream);
+
+/* Categorical leaves, forward:  node_mars[node_off+n, b] = log params[s_pids[n] + data[vids[n], b]].
+ * data is [V, B], element size data_elsize in {1,2,4,8} (unsigned 8-bit or signed wider).
+ * Replaces InputLayer.forward + Categorical.fw_mar_fn
+ * (layer/input_layer.py:318-380, 1148-1187; nodes/distributions/categorical.py:82-91). */
+int pcx_input_cat_fwd(float* node_mars, const float* params, const void* data, int data_elsize,
+                      const int32_t* vids, const int32_t* s_pids, int64_t n_nodes, int64_t node_off,
+                      int B, void* stream);
+
+/* Categorical leaves, backward:  param_flows[s_pfids[n] + data[vids[n], b]] += flow(node_off+n, b)  (linear value).
+ * Replaces InputLayer.backward + Categorical.bk_flow_fn / cat_backward.cu
+ * (layer/input_layer.py:449-548; nodes/distributions/categorical.py:93-120;
+ *  layer/kernels/c/input_layers/cat_backward.cu:24-52). */
+int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* data, int data_elsize,
+                      const int32_t* vids, const int32_t* s_pfids, int64_t n_nodes, int64_t node_off,
+                      int B, int logspace, void* stream);
+
+/* Product layer forward:  element_mars[nids[i]+j, b] = sum_c node_mars[cids[i,c]+j, b]   (cids == 0 skipped).
+ * Replaces ProdLayer.forward -> _forward_backward_kernel_2d
+ * (layer/prod_layer.py:161-205, 263-369; layer/kernels/prod.py:156-226 with accum=False). */
+int pcx_prod_fwd(float* element_mars, const float* node_mars, const int32_t* nids, const int32_t* cids,
+                 int64_t n_blocks, int n_chs, int block_size, int B, void* stream);
+
+/* Product layer backward:
+ *   node_flows[u_cids[i]+j, b] = logaddexp(node_flows[...], logsumexp_p element_flows[parids[i,p]+j, b])
+ *   (plain sums when logspace == 0).
+ * Replaces ProdLayer.backward (layer/prod_layer.py:207-238; layer/kernels/prod.py:192-226 with
+ * accum=True, prop_logsumexp=True). */
+int pcx_prod_bwd(float* node_flows, const float* element_flows, const int32_t* u_cids, const int32_t* parids,
+                 int64_t n_blocks, int n_pars, int block_size, int B, int logspace, void* stream);
+
+/* Sum layer forward, one partition:
+ *   node_mars[nids[i]+m, b] = log sum_e params[pids[i,e]+m] * exp(element_mars[cids[i,e], b]),  m < block_size.
+ * K is the padded fan-in (table width).  Replaces SumLayer._forward_block_sparse / _forward_sparse and the
+ * kernels they pick (layer/sum_layer.py:551-1056; layer/kernels/sum_forward_block_sparse.py:25-170;
+ * layer/kernels/sum_forward_sparse.py:24-107; layer/kernels/c/tlmm_forward_sum.cu:123-194;
+ * layer/kernels/c/smallbatch_forward_sum.cu:30-73). */
+int pcx_sum_fwd(float* node_mars, const float* element_mars, const float* params,
+                const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                int64_t n_blocks, int K, int block_size, int B, void* stream);
+
+/* Sum layer backward, element flows, one backward partition:
+ *   element_flows[chids[i]+c, b] = element_mars[chids[i]+c, b]
+ *        + log sum_{p, n} params[parpids[i,p] + c*block_size + n] * exp(node_flows[parids[i,p]+n, b] - node_mars[parids[i,p]+n, b])
+ * for c < ch_block_size; P is the padded number of parent blocks.
+ * Replaces SumLayer._backward_block_sparse_ele_flows / _backward_sparse_ele_flows
+ * (layer/sum_layer.py:1369-1719, 2135-2380; layer/kernels/sum_backward_element_block_sparse.py:25-190;
+ *  layer/kernels/c/ele_backward_sum.cu:113-159; layer/kernels/c/smallbatch_ele_backward.cu:47-97). */
+int pcx_sum_bwd_ele(float* element_flows, const float* element_mars, const float* node_flows,
+                    const float* node_mars, const float* params,
+                    const int32_t* chids, const int32_t* parids, const int32_t* parpids,
+                    int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace, void* stream);
+
+/* Sum layer backward, parameter flows, one forward partition:
+ *   param_flows[pfids[i,e]+m] += params[pids[i,e]+m] * sum_b exp(node_flows[nids[i]+m, b] - node_mars[nids[i]+m, b] + element_mars[cids[i,e], b]).
+ * Accumulates (atomically) into param_flows.  Replaces SumLayer._backward_block_sparse_par_flows /
+ * _backward_sparse_par_flows (layer/sum_layer.py:1744-2080, 2380-2620;
+ * layer/kernels/sum_backward_param_block_sparse.py:25-142; layer/kernels/c/par_backward_sum.cu:4-207;
+ * layer/kernels/c/smallbatch_par_backward.cu:31-68). */
+int pcx_sum_bwd_par(float* param_flows, const float* node_flows, const float* node_mars,
+                    const float* element_mars, const float* params,
+                    const int32_t* nids, const int32_t* cids, const int32_t* pids, const int32_t* pfids,
+                    int64_t n_blocks, int K, int block_size, int B, int logspace, void* stream);
+
+/* target[start + j] = sum_c flows[ch_starts[c] + j], j < n  (in place on `flows`; the source's own range is
+ * one of the ch_starts).  Replaces InputLayer._pflow_accum_kernel (layer/input_layer.py:755-783, 1391-1411)
+ * and cum_par_flows_kernel (model/backend/parflow_fusing.py:80-112). */
+int pcx_tied_accum(float* flows, int64_t start, int64_t n, const int64_t* ch_starts, int n_chs, void* stream);
+
+/* EM update of sum parameters.  One descriptor row per node block:
+ *   blk_par[i], blk_flow[i] first parameter / flow of the block, blk_fan[i] real fan-in (child nodes),
+ *   blk_bs[i] block size.  For node m of block i:
+ *     tot = sum_e flows[blk_flow + e*bs + m]
+ *     theta[blk_par + e*bs + m] = (1-step)*theta + step*(flow + pseudo/fan)/(tot + pseudo)
+ *   (keep_zero != 0: parameters < 1e-12 stay 0 and do not receive the pseudocount).
+ * Replaces em_par_update -> cum_pflow_kernel + em_par_update_kernel
+ * (model/backend/par_update.py:173-256, 296-326). */
+int pcx_em_sum(float* params, const float* param_flows, const int64_t* blk_par, const int64_t* blk_flow,
+               const int32_t* blk_fan, const int32_t* blk_bs, int64_t n_blocks, int max_bs,
+               float step, float pseudo, int keep_zero, void* stream);
+
+/* EM update of categorical leaf parameters, one row of node_cats[n] categories per source node n:
+ *   theta[s_pids[n]+c] = (1-step)*theta + step*(flows[s_pfids[n]+c] + pseudo/num_cats)/(sum_c flows + pseudo).
+ * node_cats is indexed by layer-local node id; max_cats only selects the launch shape.
+ * Replaces InputLayer.mini_batch_em -> _em_kernel + Categorical.{small,large}_ncats_em_fn
+ * (layer/input_layer.py:785-813, 1414-1436; nodes/distributions/categorical.py:191-272). */
+int pcx_em_input_cat(float* params, const float* param_flows, const int32_t* source_nids,
+                     const int32_t* s_pids, const int32_t* s_pfids, const int32_t* node_cats,
+                     int64_t n_source, int max_cats, float step, float pseudo, int keep_zero, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PCX_B200_H */

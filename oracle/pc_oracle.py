@@ -1,0 +1,272 @@
+"""CPU oracle for the compiled probabilistic-circuit forward / backward / mini-batch-EM path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this file; it exists so that
+tests, the smoke check and the CPU-baseline leg of the benchmark have an independent statement of
+what the CUDA kernels must compute.  It is a plain PyTorch (CPU, float64 by default) restatement
+of PyJuice's algorithm, driven purely by the compiled index tables:
+
+  * input forward    log p[s_pids[n] + x[vids[n], b]]                nodes/distributions/categorical.py:82-91
+  * product forward  sum of child rows                                layer/prod_layer.py:161-166, layer/kernels/prod.py:156-226
+  * sum forward      log sum_e theta[pids+m] exp(emars[cids])         layer/sum_layer.py:1077-1082, layer/kernels/sum_forward_block_sparse.py:79-124
+  * root flows / driver order                                         model/tensorcircuit.py:355-441, 527-674
+  * element flows    emars + log sum_n theta exp(nflow - nmar)        layer/sum_layer.py:2679-2692, layer/kernels/sum_backward_element_block_sparse.py:86-190
+  * parameter flows  theta * sum_b exp(nflow - nmar + emar)           layer/sum_layer.py:2712-2722, layer/kernels/sum_backward_param_block_sparse.py:64-142
+  * product backward logaddexp-accumulate of parent flows             layer/prod_layer.py:207-238, layer/kernels/prod.py:192-226
+  * input backward   flows[s_pfids[n] + x] += exp(node_flows)         nodes/distributions/categorical.py:93-100
+  * tied accumulate  source range := sum of accumulators              model/backend/parflow_fusing.py:80-99, layer/input_layer.py:1391-1411
+  * EM update        (1-eta) theta + eta (F + alpha/nch)/(sum F + alpha)   model/backend/par_update.py:173-256, categorical.py:191-228
+
+Pinning: the reference cannot execute this path without a GPU (its leaf and product layers are
+Triton-only), so the oracle is pinned (tests/test_oracle_pins.py) against the closed-form dense
+restatements and known-answer values that the reference's own tests assert
+(tests/model/simple_model_test.py:191-528, tests/structures/hmm_correctness_test.py), evaluated on
+tables that are themselves checked bit-for-bit against the reference compiler's output.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+NEG_INF = float("-inf")
+
+
+class OracleState:
+    """All buffers of one forward/backward/EM pass, named as in ``TensorCircuit``."""
+
+    def __init__(self):
+        self.node_mars = self.element_mars = self.node_flows = self.element_flows = None
+        self.param_flows = None
+        self.input_param_flows = []
+
+
+def _tables(pc):
+    """Pull the index tables out of a compiled circuit (ours or the reference's) as CPU tensors."""
+    t = dict(num_nodes=pc.num_nodes, num_elements=pc.num_elements, root=tuple(pc._root_node_range),
+             num_param_flows=pc.num_param_flows, inputs=[], inner=[])
+    for layer in pc.input_layer_group:
+        t["inputs"].append(dict(
+            vids=layer.vids.cpu(), s_pids=layer.s_pids.cpu(), s_pfids=layer.s_pfids.cpu(),
+            source_nids=layer.source_nids.cpu(), metadata=layer.metadata.cpu(), s_mids=layer.s_mids.cpu(),
+            rng=tuple(layer._output_ind_range), num_param_flows=layer.num_param_flows,
+            tied=[(a, b, c.cpu()) for a, b, c in layer.tied2source_nids]))
+    for group in pc.inner_layer_groups:
+        layers = []
+        for layer in group:
+            if group.is_prod():
+                layers.append(dict(kind="prod", bs=layer.block_size,
+                                   nids=[x.cpu() for x in layer.partitioned_nids], cids=[x.cpu() for x in layer.partitioned_cids],
+                                   u_cids=[x.cpu() for x in layer.partitioned_u_cids], parids=[x.cpu() for x in layer.partitioned_parids]))
+            else:
+                layers.append(dict(kind="sum", bs=layer.block_size,
+                                   nids=[x.cpu() for x in layer.partitioned_nids], cids=[x.cpu() for x in layer.partitioned_cids],
+                                   pids=[x.cpu() for x in layer.partitioned_pids], pfids=[x.cpu() for x in layer.partitioned_pfids],
+                                   chids=[x.cpu() for x in layer.partitioned_chids], parids=[x.cpu() for x in layer.partitioned_parids],
+                                   parpids=[x.cpu() for x in layer.partitioned_parpids], cs_block_sizes=list(layer.cs_block_sizes)))
+        t["inner"].append(("prod" if group.is_prod() else "sum", layers))
+    return t
+
+
+def _lse(x, dim):
+    m = x.max(dim=dim, keepdim=True).values
+    m = torch.where(torch.isinf(m) & (m < 0), torch.zeros_like(m), m)
+    return (x - m).exp().sum(dim=dim).log() + m.squeeze(dim)
+
+
+def _prod_forward(layer, node_mars, element_mars):
+    j = torch.arange(layer["bs"])
+    for nids, cids in zip(layer["nids"], layer["cids"]):
+        rows = (cids[:, :, None] + j[None, None, :])                 # [n, C, bs]
+        vals = node_mars[rows]                                       # [n, C, bs, B]
+        vals = torch.where((cids == 0)[:, :, None, None], torch.zeros_like(vals), vals)
+        element_mars[(nids[:, None] + j[None, :]).reshape(-1)] = vals.sum(dim=1).reshape(-1, vals.size(-1))
+
+
+def _row_chunks(n_rows, per_row_elems, budget=32_000_000):
+    step = max(1, budget // max(per_row_elems, 1))
+    for r0 in range(0, n_rows, step):
+        yield r0, min(r0 + step, n_rows)
+
+
+def _neg_inf_like(x):
+    return torch.full_like(x, NEG_INF)
+
+
+def _sum_forward(layer, node_mars, element_mars, params):
+    m = torch.arange(layer["bs"])
+    B = node_mars.size(1)
+    for nids, cids, pids in zip(layer["nids"], layer["cids"], layer["pids"]):
+        K = cids.size(1)
+        for r0, r1 in _row_chunks(nids.numel(), K * (B + layer["bs"])):
+            em = element_mars[cids[r0:r1]]                           # [n, K, B]
+            th = params[pids[r0:r1, :, None] + m[None, None, :]]     # [n, K, bs]
+            mx = em.max(dim=1).values                                # [n, B]
+            dead = torch.isinf(mx) & (mx < 0)
+            mx0 = torch.where(dead, torch.zeros_like(mx), mx)
+            acc = torch.bmm(th.transpose(1, 2), (em - mx0[:, None, :]).exp())   # [n, bs, B]
+            out = acc.log() + mx0[:, None, :]
+            out = torch.where(dead[:, None, :], _neg_inf_like(out), out)
+            node_mars[(nids[r0:r1, None] + m[None, :]).reshape(-1)] = out.reshape(-1, B)
+
+
+def _sum_backward(layer, st, params, compute_param_flows):
+    bs = layer["bs"]
+    n = torch.arange(bs)
+    B = st.node_mars.size(1)
+    # element flows
+    for chids, parids, parpids, cbs in zip(layer["chids"], layer["parids"], layer["parpids"], layer["cs_block_sizes"]):
+        c = torch.arange(cbs)
+        P = parids.size(1)
+        for r0, r1 in _row_chunks(chids.numel(), P * bs * (2 * B + cbs)):
+            pr, pp = parids[r0:r1], parpids[r0:r1]                   # [r, P]
+            rows = (pr[:, :, None] + n[None, None, :]).reshape(pr.size(0), -1)          # [r, P*bs]
+            nf, nm = st.node_flows[rows], st.node_mars[rows]         # [r, P*bs, B]
+            lnf = torch.where(torch.isinf(nm) & (nm < 0), _neg_inf_like(nf), nf - nm)
+            pad = (pr == 0)[:, :, None].expand(-1, -1, bs).reshape(pr.size(0), -1)
+            lnf = torch.where(pad[:, :, None], _neg_inf_like(lnf), lnf)
+            th = params[pp[:, :, None, None] + c[None, None, :, None] * bs + n[None, None, None, :]]   # [r, P, cbs, bs]
+            th = th.permute(0, 2, 1, 3).reshape(pr.size(0), cbs, -1)                    # [r, cbs, P*bs]
+            mx = lnf.max(dim=1).values
+            dead = torch.isinf(mx) & (mx < 0)
+            mx0 = torch.where(dead, torch.zeros_like(mx), mx)
+            acc = torch.bmm(th, (lnf - mx0[:, None, :]).exp())       # [r, cbs, B]
+            tgt = (chids[r0:r1, None] + c[None, :]).reshape(-1)
+            em = st.element_mars[tgt].reshape(pr.size(0), cbs, B)
+            out = acc.log() + mx0[:, None, :] + em
+            kill = dead[:, None, :] | (torch.isinf(em) & (em < 0)) | (acc <= 0)
+            st.element_flows[tgt] = torch.where(kill, _neg_inf_like(out), out).reshape(-1, B)
+    if not compute_param_flows:
+        return
+    # parameter flows
+    for nids, cids, pids, pfids in zip(layer["nids"], layer["cids"], layer["pids"], layer["pfids"]):
+        K = cids.size(1)
+        for r0, r1 in _row_chunks(nids.numel(), (K + 2 * bs) * B + 2 * K * bs):
+            rows = (nids[r0:r1, None] + n[None, :])                  # [r, bs]
+            nf, nm = st.node_flows[rows], st.node_mars[rows]         # [r, bs, B]
+            lnf = torch.where(torch.isinf(nm) & (nm < 0), _neg_inf_like(nf), nf - nm)
+            em = st.element_mars[cids[r0:r1]]                        # [r, K, B]  (padding -> row 0 = -inf)
+            shift = lnf.max(dim=1).values
+            shift = torch.where(torch.isinf(shift), torch.zeros_like(shift), shift)
+            acc = torch.bmm((lnf - shift[:, None, :]).exp(), (em + shift[:, None, :]).exp().transpose(1, 2))   # [r, bs, K]
+            th = params[pids[r0:r1, None, :] + n[None, :, None]]     # [r, bs, K]
+            idx = (pfids[r0:r1, None, :] + n[None, :, None]).reshape(-1)
+            st.param_flows.index_add_(0, idx, (th * acc).reshape(-1))
+
+
+def _prod_backward(layer, st):
+    j = torch.arange(layer["bs"])
+    for u_cids, parids in zip(layer["u_cids"], layer["parids"]):
+        rows = (parids[:, :, None] + j[None, None, :])               # [n, P, bs]
+        ef = st.element_flows[rows]                                  # [n, P, bs, B]
+        ef = torch.where((parids == 0)[:, :, None, None], torch.full_like(ef, NEG_INF), ef)
+        inc = _lse(ef, dim=1)                                        # [n, bs, B]
+        tgt = (u_cids[:, None] + j[None, :]).reshape(-1)
+        st.node_flows[tgt] = torch.logaddexp(st.node_flows[tgt], inc.reshape(tgt.numel(), -1))
+
+
+def forward(pc, x: torch.Tensor, params: torch.Tensor, input_params, dtype=torch.float64, tables=None,
+            state: Optional[OracleState] = None):
+    """Per-sample log-likelihoods ``[B, num_roots]``; fills ``state.node_mars / element_mars``.
+
+    ``x`` is ``[B, V]`` integer, ``params`` the flat sum-parameter vector, ``input_params`` one flat
+    vector per input layer."""
+    t = tables or _tables(pc)
+    st = state or OracleState()
+    B = x.size(0)
+    xt = x.t().long().cpu()
+    st.node_mars = torch.zeros(t["num_nodes"], B, dtype=dtype)
+    st.element_mars = torch.full((t["num_elements"], B), NEG_INF, dtype=dtype)
+    params = params.detach().cpu().to(dtype)
+    for lt, ip in zip(t["inputs"], input_params):
+        ip = ip.detach().cpu().to(dtype)
+        vals = xt[lt["vids"][:, 0]]                                  # [N, B]
+        st.node_mars[lt["rng"][0]:lt["rng"][1]] = ip[lt["s_pids"][:, None] + vals].log()
+    for kind, layers in t["inner"]:
+        for layer in layers:
+            if kind == "prod":
+                _prod_forward(layer, st.node_mars, st.element_mars)
+            else:
+                _sum_forward(layer, st.node_mars, st.element_mars, params)
+    st.tables = t
+    return st.node_mars[t["root"][0]:t["root"][1]].t().clone(), st
+
+
+def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: OracleState,
+             ll_weights: Optional[torch.Tensor] = None, compute_param_flows: bool = True,
+             param_flows: Optional[torch.Tensor] = None, input_param_flows=None):
+    """Log-space node/element flows and (accumulated) parameter flows.  ``st`` comes from
+    :func:`forward` on the same inputs.  Existing ``param_flows`` are added to, as the reference does."""
+    t = st.tables
+    dtype = st.node_mars.dtype
+    B = x.size(0)
+    xt = x.t().long().cpu()
+    params = params.detach().cpu().to(dtype)
+    st.node_flows = torch.full((t["num_nodes"], B), NEG_INF, dtype=dtype)
+    st.element_flows = torch.full((t["num_elements"], B), NEG_INF, dtype=dtype)
+    r0, r1 = t["root"]
+    st.node_flows[r0:r1] = 0.0 if ll_weights is None else ll_weights.to(dtype).reshape(-1, B).log()
+    st.param_flows = torch.zeros(t["num_param_flows"], dtype=dtype) if param_flows is None else param_flows.detach().cpu().to(dtype).clone()
+    inner = t["inner"]
+    for gi in range(len(inner) - 1, -1, -1):
+        kind, layers = inner[gi]
+        if kind == "prod":
+            for layer in layers:
+                _prod_backward(layer, st)
+        else:
+            for layer in inner[gi - 1][1]:                           # recompute the product layer below
+                _prod_forward(layer, st.node_mars, st.element_mars)
+            for layer in layers:
+                _sum_backward(layer, st, params, compute_param_flows)
+    st.input_param_flows = []
+    for li, lt in enumerate(t["inputs"]):
+        pf = torch.zeros(lt["num_param_flows"], dtype=dtype)
+        if input_param_flows is not None and input_param_flows[li] is not None:
+            pf = input_param_flows[li].detach().cpu().to(dtype).clone()
+        if compute_param_flows:
+            vals = xt[lt["vids"][:, 0]]
+            idx = (lt["s_pfids"][:, None] + vals).reshape(-1)
+            pf.index_add_(0, idx, st.node_flows[lt["rng"][0]:lt["rng"][1]].exp().reshape(-1))
+        st.input_param_flows.append(pf)
+    return st
+
+
+def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size: float, pseudocount: float = 0.0):
+    """Returns ``(new_params, [new_input_params])``; flows are taken from ``st``."""
+    dtype = st.param_flows.dtype
+    new_inputs = []
+    for lt, ip, pf in zip(st.tables["inputs"], input_params, st.input_param_flows):
+        ip = ip.detach().cpu().to(dtype).clone()
+        pf = pf.clone()
+        for start, n, ch in lt["tied"]:
+            pf[start:start + n] = sum(pf[int(c):int(c) + n] for c in ch)
+        for nid in lt["source_nids"].tolist():
+            C = int(lt["metadata"][lt["s_mids"][nid]].item())
+            a, f = int(lt["s_pids"][nid]), int(lt["s_pfids"][nid])
+            flow = pf[f:f + C]
+            ip[a:a + C] = (1.0 - step_size) * ip[a:a + C] + step_size * (flow + pseudocount / C) / (flow.sum() + pseudocount)
+        new_inputs.append(ip)
+
+    params = params.detach().cpu().to(dtype).clone()
+    pf = st.param_flows.clone()
+    for tgt, sizes, chs, G, M in pc.parflow_fusing_kwargs:
+        for i in range(tgt.numel()):
+            n = int(sizes[i])
+            # Slots after the first that hold 0 are padding up to the power-of-two group width.  (The
+            # reference kernel's mask `offs >= 0`, parflow_fusing.py:86-87, lets such padding slots add
+            # param_flows[0:n] as well; that is a defect for non-power-of-two accumulator counts and is
+            # deliberately not reproduced.)
+            real = [int(c) for k, c in enumerate(chs[i].tolist()) if k == 0 or c != 0]
+            pf[int(tgt[i]):int(tgt[i]) + n] = sum(pf[c:c + n] for c in real)
+    par_start, pflow_start, blk_sizes, blk_int, gnids, nchs = [a.cpu() for a in pc.par_update_kwargs[:6]]
+    tot = int(gnids.max().item()) + 1
+    j = torch.arange(int(blk_sizes.max().item()))
+    mask = j[None, :] < blk_sizes[:, None]
+    fidx = pflow_start[:, None] + j[None, :] * blk_int[:, None]
+    pidx = par_start[:, None] + j[None, :] * blk_int[:, None]
+    flows = torch.where(mask, pf[torch.where(mask, fidx, torch.zeros_like(fidx))], torch.zeros((), dtype=dtype))
+    node_tot = torch.zeros(tot, dtype=dtype).index_add_(0, gnids, flows.sum(dim=1))
+    new = (flows + pseudocount / nchs[:, None].to(dtype)) / (node_tot[gnids][:, None] + pseudocount)
+    old = params[torch.where(mask, pidx, torch.zeros_like(pidx))]
+    upd = (1.0 - step_size) * old + step_size * new
+    params[pidx[mask]] = upd[mask]
+    return params, new_inputs

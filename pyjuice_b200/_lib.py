@@ -1,0 +1,85 @@
+"""ctypes binding of ``libpcx_b200.so`` (the C ABI declared in ``include/pcx_b200.h``).
+
+There is no fallback: if the library is missing or a GPU entry point is called without it, an
+exception is raised.  Arguments are raw device pointers (``tensor.data_ptr()``) and plain integers;
+the stream is torch's current CUDA stream, so the launches order with torch work and can be captured
+into CUDA graphs.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libpcx_b200.so")
+
+P, I, L, F = c_void_p, c_int, c_int64, c_float
+
+# name -> argument types, in the order of include/pcx_b200.h (the trailing stream is appended below)
+SIGNATURES = {
+    "pcx_fill_f32": [P, L, F],
+    "pcx_scale_f32": [P, L, F],
+    "pcx_exp_f32": [P, L],
+    "pcx_set_root_flows": [P, P, L, L, I, I],
+    "pcx_input_cat_fwd": [P, P, P, I, P, P, L, L, I],
+    "pcx_input_cat_bwd": [P, P, P, I, P, P, L, L, I, I],
+    "pcx_prod_fwd": [P, P, P, P, L, I, I, I],
+    "pcx_prod_bwd": [P, P, P, P, L, I, I, I, I],
+    "pcx_sum_fwd": [P, P, P, P, P, P, L, I, I, I],
+    "pcx_sum_bwd_ele": [P, P, P, P, P, P, P, P, L, I, I, I, I, I],
+    "pcx_sum_bwd_par": [P, P, P, P, P, P, P, P, P, L, I, I, I, I],
+    "pcx_tied_accum": [P, L, L, P, I],
+    "pcx_em_sum": [P, P, P, P, P, P, L, I, F, F, I],
+    "pcx_em_input_cat": [P, P, P, P, P, P, L, I, F, F, I],
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class PcxError(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and declare every prototype."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise PcxError(f"{LIB_PATH} is missing: build it with `python -m pyjuice_b200.csrc.build` "
+                       "(there is no CPU or PyTorch fallback for the circuit kernels)")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.pcx_build_arch.restype = c_int
+    lib.pcx_build_arch.argtypes = []
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = c_int
+        fn.argtypes = list(args) + [c_void_p]
+    _lib = lib
+    return lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def call(name: str, *args) -> None:
+    """Invoke one entry point on the current CUDA stream; tensors are passed as device pointers."""
+    lib = load()
+    conv = []
+    for a in args:
+        if isinstance(a, torch.Tensor):
+            if not a.is_cuda:
+                raise PcxError(f"{name}: tensor argument is not on a CUDA device (no CPU path exists)")
+            conv.append(a.data_ptr())
+        elif a is None:
+            conv.append(None)
+        else:
+            conv.append(a)
+    rc = getattr(lib, name)(*conv, _stream())
+    if rc != 0:
+        raise PcxError(f"{name} failed with status {rc}")

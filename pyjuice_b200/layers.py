@@ -1,0 +1,364 @@
+"""Layer objects of a compiled circuit: index tables plus the launches that evaluate them.
+
+The classes keep PyJuice's per-layer interface — ``layer(node_mars, element_mars[, params])`` and
+``layer.backward(...)`` with the same positional arguments, ``partitioned_*`` table lists,
+``LayerGroup`` iteration (layer/input_layer.py:35-604, layer/prod_layer.py:28-238,
+layer/sum_layer.py:130-543, layer/layer_group.py:14-113) — but every computation is one call into
+the CUDA library per partition; there is no Triton, no autotuning and no CPU path.
+
+Tables live twice: the int64 CPU/any-device tensors that are the (bit-exact) compiler output, and
+int32 device copies that the kernels read.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .compiler import (compile_input, compile_prod, compile_sum_backward, compile_sum_forward,
+                       reorder_input_nodes)
+from .nodes import BitSet, as_bitset
+
+_I32_MAX = 2 ** 31 - 1
+
+
+def _dev_i32(t: torch.Tensor, device) -> torch.Tensor:
+    if t.numel() > 0 and int(t.max()) > _I32_MAX:
+        raise ValueError("index table exceeds the 32-bit range the kernels address with")
+    return t.to(device=device, dtype=torch.int32).contiguous()
+
+
+def _unsupported(**flags):
+    bad = [k for k, v in flags.items() if v]
+    if bad:
+        raise NotImplementedError(f"option(s) {bad} are outside the compiled LL forward/backward/EM path")
+
+
+class Layer:
+    def __init__(self, nodes):
+        self.nodes = nodes
+        self.device = torch.device("cpu")
+
+    def is_input(self):
+        return False
+
+    def is_prod(self):
+        return False
+
+    def is_sum(self):
+        return False
+
+    def provided(self, name):
+        return getattr(self, name, None) is not None
+
+
+class InputLayer(Layer, nn.Module):
+    """All input vectors of one distribution family (categorical only)."""
+
+    def __init__(self, nodes, cum_nodes: int = 0, pc_num_vars: int = 0, max_tied_ns_per_parflow_block: int = 4):
+        nn.Module.__init__(self)
+        nodes = reorder_input_nodes(list(nodes))
+        Layer.__init__(self, nodes)
+        for ns in nodes:
+            if ns.dist.get_signature() != "Categorical":
+                raise NotImplementedError("only Categorical input distributions are on the compiled path")
+        self.pc_num_vars = pc_num_vars
+        self.dist_signature = "Categorical"
+        t = compile_input(nodes, cum_nodes, max_tied_ns_per_parflow_block)
+        for name in ("vids", "s_pids", "s_pfids", "s_mids", "nids", "source_nids", "node_id2source_id", "metadata"):
+            self.register_buffer(name, t[name])
+        self.tied2source_nids = t["tied2source_nids"]
+        self.num_nodes = t["num_nodes"]
+        self.num_parameters = t["num_parameters"]
+        self.num_param_flows = t["num_param_flows"]
+        self._output_ind_range = t["output_ind_range"]
+        self.num_vars_per_node = self.vids.size(1)
+        assert self.num_vars_per_node == 1, "categorical leaves are univariate"
+        self.node_cats = self.metadata[self.s_mids].to(torch.int64)       # categories of every node
+        self.max_cats = int(self.node_cats.max().item())
+        self.params = nn.Parameter(torch.empty([max(self.num_parameters, 1)], dtype=torch.float32), requires_grad=False)
+        self.param_flows = None
+        self._dev = {}
+
+    def is_input(self):
+        return True
+
+    def to(self, device):
+        device = torch.device(f"cuda:{device}") if isinstance(device, int) else torch.device(device)
+        nn.Module.to(self, device)
+        for item in self.tied2source_nids:
+            item[2] = item[2].to(device)
+        if self.param_flows is not None:
+            self.param_flows = self.param_flows.to(device)
+        self.device = device
+        self._dev = {}
+        if device.type == "cuda":
+            self._dev = dict(vids=_dev_i32(self.vids[:, 0], device), s_pids=_dev_i32(self.s_pids, device),
+                             s_pfids=_dev_i32(self.s_pfids, device), source_nids=_dev_i32(self.source_nids, device),
+                             node_cats=_dev_i32(self.node_cats, device))
+        return self
+
+    def _init_parameters(self, perturbation: float):
+        """Copy (or draw) the parameters of every untied vector, in layer order (layer/input_layer.py:1131-1143)."""
+        p0 = 0
+        params = torch.empty_like(self.params.data, device="cpu")
+        for ns in self.nodes:
+            if ns.is_tied():
+                continue
+            p1 = p0 + ns.num_nodes * ns.dist.num_parameters()
+            if not ns.has_params():
+                ns.init_parameters(perturbation=perturbation, recursive=False)
+            params[p0:p1] = ns._params.reshape(-1)
+            p0 = p1
+        self.params.data = params.to(self.device)
+
+    def init_param_flows(self, flows_memory: float = 1.0):
+        if self.param_flows is None or self.param_flows.device != self.device:
+            self.param_flows = torch.zeros([self.num_param_flows], dtype=torch.float32, device=self.device)
+        elif flows_memory == 0.0:
+            _fill(self.param_flows, 0.0)
+        elif flows_memory < 1.0:
+            _scale(self.param_flows, flows_memory)
+
+    def _require_cuda(self):
+        if self.device.type != "cuda":
+            raise NotImplementedError("input layers run on CUDA only (no CPU path)")
+
+    def forward(self, data: torch.Tensor, node_mars: torch.Tensor, params=None, missing_mask=None, **kwargs):
+        """``data`` is ``[num_vars, B]`` (variables outermost), integer."""
+        _unsupported(params=params is not None, missing_mask=missing_mask is not None)
+        self._require_cuda()
+        data = data.contiguous()
+        B = node_mars.size(1)
+        _lib.call("pcx_input_cat_fwd", node_mars, self.params.data, data, data.element_size(),
+                  self._dev["vids"], self._dev["s_pids"], self.num_nodes, self._output_ind_range[0], B)
+
+    def backward(self, data: torch.Tensor, node_flows: torch.Tensor, node_mars: torch.Tensor, params=None,
+                 logspace_flows: bool = False, missing_mask=None, **kwargs):
+        """Adds the (linear) flow of every (node, sample) to the flow of the observed category."""
+        _unsupported(params=params is not None, missing_mask=missing_mask is not None)
+        self._require_cuda()
+        if self.param_flows is None:
+            self.init_param_flows()
+        data = data.contiguous()
+        B = node_flows.size(1)
+        _lib.call("pcx_input_cat_bwd", self.param_flows, node_flows, data, data.element_size(),
+                  self._dev["vids"], self._dev["s_pfids"], self.num_nodes, self._output_ind_range[0], B,
+                  int(bool(logspace_flows)))
+
+    def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False):
+        self._require_cuda()
+        for start, n, ch_pfids in self.tied2source_nids:
+            _lib.call("pcx_tied_accum", self.param_flows, int(start), int(n), ch_pfids, int(ch_pfids.numel()))
+        _lib.call("pcx_em_input_cat", self.params.data, self.param_flows, self._dev["source_nids"],
+                  self._dev["s_pids"], self._dev["s_pfids"], self._dev["node_cats"], int(self.source_nids.numel()), self.max_cats,
+                  float(step_size), float(pseudocount), int(bool(keep_zero_params)))
+
+    def update_parameters(self):
+        params = self.params.detach().cpu()
+        for ns in self.nodes:
+            if not ns.is_tied():
+                s, e = ns._param_range
+                ns._params = params[s:e].clone()
+
+    def __repr__(self):
+        return f"InputLayer(nid_range={self._output_ind_range}, max_cats={self.max_cats})"
+
+
+class ProdLayer(Layer, nn.Module):
+    def __init__(self, nodes, global_nid_start: Optional[int] = None, layer_sparsity_tol=None, max_num_partitions=None, **kwargs):
+        nn.Module.__init__(self)
+        Layer.__init__(self, list(nodes))
+        assert len(nodes) > 0, "No input node."
+        if global_nid_start is None:
+            block_sparse = all((not ns.is_sparse()) and ns.block_size == nodes[0].block_size for ns in nodes)
+            global_nid_start = nodes[0].block_size if block_sparse else 1
+        t = compile_prod(self.nodes, global_nid_start, layer_sparsity_tol, max_num_partitions)
+        self.block_size = t["block_size"]
+        self.use_block_sparse_edges = t["block_sparse"]
+        self.num_nodes, self.num_edges = t["num_nodes"], t["num_edges"]
+        self._layer_nid_range = (global_nid_start, global_nid_start + self.num_nodes)
+        self.partitioned_nids, self.partitioned_cids = t["nids"], t["cids"]
+        self.partitioned_u_cids, self.partitioned_parids = t["u_cids"], t["parids"]
+        self.num_fw_partitions, self.num_bk_partitions = len(t["nids"]), len(t["u_cids"])
+        self._dev = None
+
+    def is_prod(self):
+        return True
+
+    def to(self, device):
+        device = torch.device(f"cuda:{device}") if isinstance(device, int) else torch.device(device)
+        for name in ("partitioned_nids", "partitioned_cids", "partitioned_u_cids", "partitioned_parids"):
+            setattr(self, name, [x.to(device) for x in getattr(self, name)])
+        self.device = device
+        self._dev = None
+        if device.type == "cuda":
+            self._dev = dict(fw=[(_dev_i32(n, device), _dev_i32(c, device)) for n, c in zip(self.partitioned_nids, self.partitioned_cids)],
+                             bk=[(_dev_i32(u, device), _dev_i32(p, device)) for u, p in zip(self.partitioned_u_cids, self.partitioned_parids)])
+        return self
+
+    def forward(self, node_mars: torch.Tensor, element_mars: torch.Tensor, _for_backward: bool = False, **kwargs):
+        if self._dev is None:
+            raise NotImplementedError("product layers run on CUDA only (no CPU path)")
+        B = node_mars.size(1)
+        for nids, cids in self._dev["fw"]:
+            _lib.call("pcx_prod_fwd", element_mars, node_mars, nids, cids, nids.numel(), cids.size(1), self.block_size, B)
+
+    __call__ = forward
+
+    def backward(self, node_flows: torch.Tensor, element_flows: torch.Tensor, logspace_flows: bool = False, **kwargs):
+        if self._dev is None:
+            raise NotImplementedError("product layers run on CUDA only (no CPU path)")
+        B = node_flows.size(1)
+        for u_cids, parids in self._dev["bk"]:
+            _lib.call("pcx_prod_bwd", node_flows, element_flows, u_cids, parids, u_cids.numel(), parids.size(1),
+                      self.block_size, B, int(bool(logspace_flows)))
+
+    def __repr__(self):
+        return f"ProdLayer(nid_range={self._layer_nid_range}, num_nodes={self.num_nodes}, num_edges={self.num_edges})"
+
+
+class SumLayer(Layer, nn.Module):
+    def __init__(self, nodes, global_nid_start: int, global_pid_start: int, global_pfid_start: int, node2tiednodes,
+                 layer_sparsity_tol=None, max_num_partitions=None, max_tied_ns_per_parflow_block: int = 8, **kwargs):
+        nn.Module.__init__(self)
+        Layer.__init__(self, list(nodes))
+        assert len(nodes) > 0, "No input node."
+        for ns in nodes:
+            assert ns.block_size == nodes[0].block_size, "`block_size` of nodes in the same layer must be identical."
+        self.block_size = nodes[0].block_size
+        fw = compile_sum_forward(self.nodes, global_nid_start, global_pid_start, global_pfid_start, node2tiednodes,
+                                 layer_sparsity_tol, max_num_partitions, max_tied_ns_per_parflow_block)
+        self.num_nodes, self.num_edges = fw["num_nodes"], fw["num_edges"]
+        self.partitioned_nids, self.partitioned_cids = fw["nids"], fw["cids"]
+        self.partitioned_pids, self.partitioned_pfids = fw["pids"], fw["pfids"]
+        self.num_fw_partitions = len(fw["nids"])
+        self._layer_nid_range = (global_nid_start, global_nid_start + self.num_nodes)
+        self._layer_pid_range = (global_pid_start, fw["pid_end"])
+        self._layer_pfid_range = (global_pfid_start, fw["pfid_end"])
+        self.num_parameters = fw["pid_end"] - global_pid_start
+        self.num_param_flows = fw["pfid_end"] - global_pfid_start
+        bk = compile_sum_backward(self.nodes, layer_sparsity_tol, max_num_partitions)
+        self.partitioned_chids, self.partitioned_parids = bk["chids"], bk["parids"]
+        self.partitioned_parpids, self.cs_block_sizes = bk["parpids"], bk["cs_block_sizes"]
+        self.num_bk_partitions = len(bk["chids"])
+        self._dev = None
+
+    def is_sum(self):
+        return True
+
+    _TABLES = ("partitioned_nids", "partitioned_cids", "partitioned_pids", "partitioned_pfids",
+               "partitioned_chids", "partitioned_parids", "partitioned_parpids")
+
+    def to(self, device):
+        device = torch.device(f"cuda:{device}") if isinstance(device, int) else torch.device(device)
+        for name in self._TABLES:
+            setattr(self, name, [x.to(device) for x in getattr(self, name)])
+        self.device = device
+        self._dev = None
+        if device.type == "cuda":
+            c = lambda t: _dev_i32(t, device)
+            self._dev = dict(
+                fw=[tuple(map(c, q)) for q in zip(self.partitioned_nids, self.partitioned_cids, self.partitioned_pids, self.partitioned_pfids)],
+                bk=[tuple(map(c, q)) for q in zip(self.partitioned_chids, self.partitioned_parids, self.partitioned_parpids)])
+        return self
+
+    def _require_cuda(self):
+        if self._dev is None:
+            raise NotImplementedError("sum layers run on CUDA only (no CPU path)")
+
+    def forward(self, node_mars: torch.Tensor, element_mars: torch.Tensor, params: torch.Tensor,
+                propagation_alg: str = "LL", pflow_temperature: float = 1.0, **kwargs):
+        self._require_cuda()
+        _unsupported(propagation_alg=propagation_alg != "LL", pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6)
+        B = node_mars.size(1)
+        for nids, cids, pids, _ in self._dev["fw"]:
+            _lib.call("pcx_sum_fwd", node_mars, element_mars, params, nids, cids, pids,
+                      nids.numel(), cids.size(1), self.block_size, B)
+
+    __call__ = forward
+
+    def backward(self, node_flows: torch.Tensor, element_flows: torch.Tensor, node_mars: torch.Tensor,
+                 element_mars: torch.Tensor, params: torch.Tensor, param_flows: Optional[torch.Tensor] = None,
+                 allow_modify_flows: bool = False, propagation_alg: str = "LL", logspace_flows: bool = False,
+                 negate_pflows: bool = False, accumulate_ch_flows: bool = False, allow_neg_flows: bool = False,
+                 pflow_temperature: float = 1.0, temper_eflow: bool = False, **kwargs):
+        self._require_cuda()
+        _unsupported(allow_modify_flows=allow_modify_flows, propagation_alg=propagation_alg != "LL",
+                     negate_pflows=negate_pflows, accumulate_ch_flows=accumulate_ch_flows, allow_neg_flows=allow_neg_flows,
+                     pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6, temper_eflow=temper_eflow)
+        B = node_flows.size(1)
+        ls = int(bool(logspace_flows))
+        for (chids, parids, parpids), cbs in zip(self._dev["bk"], self.cs_block_sizes):
+            _lib.call("pcx_sum_bwd_ele", element_flows, element_mars, node_flows, node_mars, params,
+                      chids, parids, parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
+        if param_flows is not None:
+            for nids, cids, pids, pfids in self._dev["fw"]:
+                _lib.call("pcx_sum_bwd_par", param_flows, node_flows, node_mars, element_mars, params,
+                          nids, cids, pids, pfids, nids.numel(), cids.size(1), self.block_size, B, ls)
+
+    def __repr__(self):
+        return f"SumLayer(nid_range={self._layer_nid_range}, num_nodes={self.num_nodes}, num_edges={self.num_edges})"
+
+
+class LayerGroup(nn.Module):
+    """Layers of one kind at one depth, evaluated one after the other (layer/layer_group.py:14-113)."""
+
+    def __init__(self, layers: Sequence[Layer]):
+        super().__init__()
+        assert len(layers) >= 1, "A `LayerGroup` must contains at least 1 layer."
+        first = layers[0]
+        self.layer_type = "input" if first.is_input() else ("prod" if first.is_prod() else "sum")
+        self.num_layers = len(layers)
+        self.layers = list(layers)
+        for i, layer in enumerate(self.layers):
+            self.add_module(f"layer_{i}", layer)
+
+    def to(self, device):
+        for layer in self.layers:
+            layer.to(device)
+        return self
+
+    def forward(self, *args, **kwargs):
+        for layer in self.layers:
+            layer.forward(*args, **kwargs)
+
+    __call__ = forward
+
+    def backward(self, *args, **kwargs):
+        for layer in self.layers:
+            layer.backward(*args, **kwargs)
+
+    def is_input(self):
+        return self.layer_type == "input"
+
+    def is_prod(self):
+        return self.layer_type == "prod"
+
+    def is_sum(self):
+        return self.layer_type == "sum"
+
+    def __len__(self):
+        return self.num_layers
+
+    def __getitem__(self, idx):
+        return self.layers[idx]
+
+    def __iter__(self):
+        return iter(self.layers)
+
+
+def _fill(t: torch.Tensor, v: float):
+    if t.is_cuda:
+        _lib.call("pcx_fill_f32", t, t.numel(), float(v))
+    else:
+        t.fill_(v)
+
+
+def _scale(t: torch.Tensor, v: float):
+    if t.is_cuda:
+        _lib.call("pcx_scale_f32", t, t.numel(), float(v))
+    else:
+        t.mul_(v)

@@ -1,0 +1,524 @@
+"""``TensorCircuit``: a compiled probabilistic circuit and the driver of its forward / backward / EM passes.
+
+Public surface and semantics follow PyJuice's ``TensorCircuit`` / ``compile``
+(model/tensorcircuit.py:201-471 forward, 473-687 backward, 1346-1387 mini_batch_em,
+1394-1471 flows init / DDP sync, 1479-1654 accessors, 1801-2030 layer construction and parameter
+initialisation).  What differs is underneath: layers launch hand-written CUDA kernels through a C
+ABI, the inner-layer loops of forward and backward are replayed from CUDA graphs, buffers are
+initialised once instead of being memset on every pass, and the DDP synchronisation is a single
+all-reduce over one packed flow arena.
+
+Buffers (fp32, batch innermost):
+    node_mars      [num_nodes, B]     log-values of input and sum nodes; rows < num_dummy_nodes stay 0
+    element_mars   [num_elements, B]  log-values of product nodes, shared by all product layers; dummy rows -inf
+    node_flows     [num_nodes, B]     log-flows; reset to -inf at the start of every backward pass
+    element_flows  [num_elements, B]  log-flows of product nodes
+"""
+from __future__ import annotations
+
+from functools import partial
+from typing import Optional, Sequence, Union
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .compiler import _IdDict, compile_cum_par_flows, compile_par_update, create_node_layers
+from .layers import InputLayer, LayerGroup, ProdLayer, SumLayer, _fill, _scale, _unsupported
+from .nodes import as_bitset
+
+NEG_INF = float("-inf")
+
+
+def _pc_model_backward_hook(grad, pc, inputs, **kwargs):
+    """Autograd hook on the returned log-likelihoods: ``lls.mean().backward()`` (or any other scalar
+    loss) triggers the circuit's own backward pass with per-sample weights grad / sum(grad) * B
+    (model/tensorcircuit.py:28-41)."""
+    grad = grad.permute(1, 0)
+    pc.backward(inputs=inputs, ll_weights=grad / grad.sum() * grad.size(1),
+                compute_param_flows=pc._optim_hyperparams["compute_param_flows"],
+                flows_memory=pc._optim_hyperparams["flows_memory"], **kwargs)
+    return None
+
+
+class TensorCircuit(nn.Module):
+    def __init__(self, root_ns, layer_sparsity_tol: float = 0.5, max_num_partitions: Optional[int] = None,
+                 disable_gpu_compilation: bool = False, force_gpu_compilation: bool = False,
+                 max_tied_ns_per_parflow_block: int = 32, device=None, verbose: bool = True):
+        super().__init__()
+        self.root_ns = root_ns
+        self.device = torch.device("cpu")
+        scope = as_bitset(root_ns.scope).to_list()
+        self.num_vars = (max(scope) + 1) if scope else 0
+
+        self.node_mars = self.element_mars = self.node_flows = self.element_flows = None
+        self.param_flows = None
+        self._init_layers(layer_sparsity_tol, max_num_partitions, max_tied_ns_per_parflow_block)
+
+        self._optim_hyperparams = {"compute_param_flows": True, "flows_memory": 1.0}
+        self._graphs = {}
+        self.use_cuda_graphs = True
+        self.default_propagation_alg = "LL"
+        self._run_params = {}
+        self._cum_flow_host = 0.0
+        self._cum_flow_dev = None
+        self._eflow_mode = 1
+
+    # ------------------------------------------------------------------------------------------
+    # construction
+    # ------------------------------------------------------------------------------------------
+    def _init_layers(self, layer_sparsity_tol, max_num_partitions, max_tied):
+        self.root_ns._clear_tensor_circuit_hooks()
+        pc_num_vars = len(as_bitset(self.root_ns.scope))
+        depth2nodes, num_layers, max_node_bs, max_ele_bs = create_node_layers(self.root_ns)
+
+        self.num_dummy_nodes = max_ele_bs
+        self.num_dummy_eles = max_node_bs
+        self.num_dummy_params = max_node_bs * max_ele_bs
+        num_nodes, num_edges, num_elements = self.num_dummy_nodes, 0, self.num_dummy_eles
+        num_params, num_param_flows = self.num_dummy_params, 0
+        node2tiednodes = _IdDict()
+
+        self.input_layer_group = None
+        self.inner_layer_groups = []
+        layer_id = 0
+        for depth in range(num_layers):
+            if depth == 0:
+                by_sig = {}
+                for ns in depth2nodes[0]["input"]:
+                    by_sig.setdefault(ns.dist.get_signature(), []).append(ns)
+                layers = []
+                for nodes in by_sig.values():
+                    layer = InputLayer(nodes, cum_nodes=num_nodes, pc_num_vars=pc_num_vars,
+                                       max_tied_ns_per_parflow_block=max_tied)
+                    num_nodes += layer.num_nodes
+                    layers.append(layer)
+                self.input_layer_group = LayerGroup(layers)
+                continue
+
+            assert len(depth2nodes[depth]["prod"]) > 0 and len(depth2nodes[depth]["sum"]) > 0, \
+                f"Depth {depth}: (# prod nodes: {len(depth2nodes[depth]['prod'])}, # sum nodes: {len(depth2nodes[depth]['sum'])})"
+
+            by_bs = {}
+            for ns in depth2nodes[depth]["prod"]:
+                by_bs.setdefault(ns.block_size, []).append(ns)
+            layer_num_elements = max_node_bs          # element ids restart at every depth
+            prod_layers = []
+            for nodes in by_bs.values():
+                layer = ProdLayer(nodes, global_nid_start=layer_num_elements, layer_sparsity_tol=layer_sparsity_tol,
+                                  max_num_partitions=max_num_partitions)
+                layer_num_elements += layer.num_nodes
+                num_edges += layer.num_edges
+                prod_layers.append(layer)
+            group = LayerGroup(prod_layers)
+            self.inner_layer_groups.append(group)
+            self.add_module(f"prod_layer_{layer_id}", group)
+            num_elements = max(num_elements, layer_num_elements)
+
+            by_bs = {}
+            for ns in depth2nodes[depth]["sum"]:
+                by_bs.setdefault(ns.block_size, []).append(ns)
+            sum_layers = []
+            for nodes in by_bs.values():
+                layer = SumLayer(nodes, global_nid_start=num_nodes, global_pid_start=num_params,
+                                 global_pfid_start=num_param_flows, node2tiednodes=node2tiednodes,
+                                 layer_sparsity_tol=layer_sparsity_tol, max_num_partitions=max_num_partitions,
+                                 max_tied_ns_per_parflow_block=max_tied)
+                num_nodes += layer.num_nodes
+                num_edges += layer.num_edges
+                num_params += layer.num_parameters
+                num_param_flows += layer.num_param_flows
+                sum_layers.append(layer)
+            group = LayerGroup(sum_layers)
+            self.inner_layer_groups.append(group)
+            self.add_module(f"sum_layer_{layer_id}", group)
+            layer_id += 1
+
+        self.num_nodes, self.num_edges, self.num_elements = num_nodes, num_edges, num_elements
+        self.num_sum_params, self.num_param_flows = num_params, num_param_flows
+        self.parflow_fusing_kwargs = compile_cum_par_flows(node2tiednodes)
+        # (first flow, length, accumulator starts) of every tied sum source that owns more than one accumulator
+        self._tied_sum_groups = [(src._param_flow_range[0], src._param_flow_range[1] - src._param_flow_range[0],
+                                  [c._param_flow_range[0] for c in item[0]])
+                                 for src, item in node2tiednodes.items() if len(item[0]) > 1]
+        self.par_update_kwargs = compile_par_update(self.root_ns)
+        self._em_blocks = self._compile_em_blocks()
+        self.num_root_nodes = self.root_ns.num_nodes
+        self._root_node_range = (self.num_nodes - self.num_root_nodes, self.num_nodes)
+        self._init_parameters()
+
+    def _compile_em_blocks(self):
+        """Per node block of every untied sum vector: first parameter, first flow, real fan-in, block size —
+        the compact form of the per-(node, 32-edge chunk) items of ``par_update_kwargs`` that the EM kernel
+        walks (flows are read through the vector's own flow range, i.e. the source accumulator)."""
+        par, flow, fan, bsz = [], [], [], []
+        for ns in self.root_ns:
+            if not ns.is_sum() or ns.is_tied():
+                continue
+            cnt = torch.bincount(ns.edge_ids[0], minlength=ns.num_node_blocks) * ns.ch_block_size
+            off = torch.cumsum(cnt * ns.block_size, 0) - cnt * ns.block_size
+            par.append(ns._param_range[0] + off)
+            flow.append(ns._param_flow_range[0] + off)
+            fan.append(cnt)
+            bsz.append(torch.full_like(cnt, ns.block_size))
+        cat = lambda lst, dt: torch.cat(lst).to(dt).contiguous()
+        return dict(par=cat(par, torch.int64), flow=cat(flow, torch.int64), fan=cat(fan, torch.int32),
+                    bs=cat(bsz, torch.int32), max_bs=int(max(int(b.max()) for b in bsz)))
+
+    def _init_parameters(self, perturbation: float = 4.0, pseudocount: float = 0.0):
+        """Sum parameters start as exp(-perturbation * U) unless the node vectors carry parameters; then they are
+        normalised per sum node (model/tensorcircuit.py:2008-2030, model/backend/normalize.py:103-154)."""
+        for ns in self.root_ns:
+            if not ns.is_tied() and (ns.is_sum() or ns.is_input()) and not ns.has_params():
+                ns.init_parameters(perturbation=perturbation, recursive=False)
+        params = torch.exp(torch.rand([self.num_sum_params]) * -perturbation)
+        params[:self.num_dummy_params] = 0.0
+        for ns in self.root_ns:
+            if ns.is_sum() and not ns.is_tied() and ns.has_params():
+                ns.gather_parameters(params)
+        self._normalize_parameters(params, pseudocount)
+        self.params = nn.Parameter(params, requires_grad=False)
+        for layer in self.input_layer_group:
+            layer._init_parameters(perturbation)
+
+    def _normalize_parameters(self, params: torch.Tensor, pseudocount: float = 0.0):
+        eb = self._em_blocks
+        for i in range(eb["par"].numel()):
+            p0, fan, bs = int(eb["par"][i]), int(eb["fan"][i]), int(eb["bs"][i])
+            tile = params[p0:p0 + fan * bs].view(fan, bs)
+            tile.copy_((tile + pseudocount / fan) / (tile.sum(dim=0, keepdim=True) + pseudocount))
+
+    # ------------------------------------------------------------------------------------------
+    # device placement and buffers
+    # ------------------------------------------------------------------------------------------
+    def to(self, device):
+        device = torch.device(f"cuda:{device}") if isinstance(device, int) else torch.device(device)
+        if device.type == "cuda":
+            _lib.load()                                   # fail here, loudly, if the kernels are not built
+        nn.Module.to(self, device)
+        self.input_layer_group.to(device)
+        for group in self.inner_layer_groups:
+            group.to(device)
+        self.device = device
+        self.parflow_fusing_kwargs = [[a.to(device), b.to(device), c.to(device), G, M]
+                                      for a, b, c, G, M in self.parflow_fusing_kwargs]
+        self.par_update_kwargs = [t.to(device) if isinstance(t, torch.Tensor) else t for t in self.par_update_kwargs]
+        self._em_dev = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in self._em_blocks.items()}
+        self._fusing_dev = [(start, n, torch.tensor(accs, dtype=torch.int64, device=device))
+                            for start, n, accs in self._tied_sum_groups]
+        for name in ("node_mars", "element_mars", "node_flows", "element_flows", "param_flows"):
+            setattr(self, name, None)
+        self._graphs = {}
+        self._cum_flow_dev = None
+        return self
+
+    def _require_cuda(self):
+        if self.device.type != "cuda":
+            raise NotImplementedError("the compiled circuit runs on CUDA only; call `pc.to('cuda:0')` first "
+                                      "(there is no CPU path)")
+
+    def _ensure_buffers(self, B: int, backward: bool = False):
+        """(Re)allocate the value buffers when the batch size changes.  Dummy rows are written here once:
+        every other row is fully overwritten by the layer that owns it on each pass."""
+        if self.node_mars is None or self.node_mars.size(1) != B:
+            self.node_mars = torch.zeros(self.num_nodes, B, device=self.device)
+            self.element_mars = torch.full((self.num_elements, B), NEG_INF, device=self.device)
+            self.node_flows = self.element_flows = None
+            self._graphs = {}
+        if backward and (self.node_flows is None or self.node_flows.size(1) != B):
+            self.node_flows = torch.empty(self.num_nodes, B, device=self.device)
+            self.element_flows = torch.full((self.num_elements, B), NEG_INF, device=self.device)
+            self._eflow_mode = 1
+            self._graphs = {k: g for k, g in self._graphs.items() if k[0] != "bk"}
+
+    def _init_buffer(self, name: str, shape, set_value: Optional[float] = None):
+        t = getattr(self, name, None)
+        if not isinstance(t, torch.Tensor) or tuple(t.shape) != tuple(shape) or t.device != self.device:
+            t = torch.zeros(shape, device=self.device)
+            setattr(self, name, t)
+        if set_value is not None:
+            _fill(t, set_value)
+
+    # ------------------------------------------------------------------------------------------
+    # forward
+    # ------------------------------------------------------------------------------------------
+    def _prepare_inputs(self, inputs: torch.Tensor) -> torch.Tensor:
+        assert inputs.dim() == 2 and inputs.size(1) >= self.num_vars
+        if inputs.is_floating_point():
+            raise TypeError("categorical inputs must be an integer tensor")
+        if inputs.dtype not in (torch.uint8, torch.int16, torch.int32, torch.int64):
+            inputs = inputs.long()
+        return inputs.to(self.device, non_blocking=True).t().contiguous()       # [V, B]
+
+    def _run_inner(self, key, fn):
+        """Run ``fn`` (a sequence of launches on the current stream) — from a CUDA graph after the first call."""
+        if not self.use_cuda_graphs:
+            return fn()
+        entry = self._graphs.get(key)
+        if entry is None:                      # first call: run eagerly (also warms up every kernel)
+            fn()
+            self._graphs[key] = "warm"
+        elif entry == "warm":
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            self._graphs[key] = g
+            g.replay()
+        else:
+            entry.replay()
+
+    def _forward_inner(self):
+        for group in self.inner_layer_groups:
+            if group.is_prod():
+                group.forward(self.node_mars, self.element_mars)
+            else:
+                group.forward(self.node_mars, self.element_mars, self.params.data)
+
+    def forward(self, inputs: torch.Tensor, input_layer_fn=None, cache=None, return_cache: bool = False,
+                propagation_alg: Optional[str] = None, pflow_temperature: float = 1.0, **kwargs):
+        """Per-sample log-likelihoods ``[B, num_roots]`` of ``inputs`` (``[B, num_vars]``, integer)."""
+        self._require_cuda()
+        _unsupported(input_layer_fn=input_layer_fn is not None, cache=cache is not None, return_cache=return_cache,
+                     propagation_alg=propagation_alg not in (None, "LL"), pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6,
+                     missing_mask=kwargs.get("missing_mask") is not None)
+        origin_inputs = inputs
+        with torch.no_grad():
+            B = inputs.size(0)
+            data = self._prepare_inputs(inputs)
+            self._ensure_buffers(B)
+            self._last_data, self._last_inputs = data, origin_inputs
+            for layer in self.input_layer_group:
+                layer.forward(data, self.node_mars)
+            self._run_inner(("fw", B, self.params.data_ptr()), self._forward_inner)
+            lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
+        if torch.is_grad_enabled():
+            lls.requires_grad = True
+            lls.register_hook(partial(_pc_model_backward_hook, pc=self, inputs=origin_inputs))
+        return lls
+
+    # ------------------------------------------------------------------------------------------
+    # backward
+    # ------------------------------------------------------------------------------------------
+    def _backward_inner(self, compute_param_flows: bool, logspace_flows: bool):
+        pf = self.param_flows if compute_param_flows else None
+        groups = self.inner_layer_groups
+        for gi in range(len(groups) - 1, -1, -1):
+            group = groups[gi]
+            if group.is_prod():
+                group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
+            else:
+                # the shared element buffer holds another depth by now: recompute this depth's products
+                groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
+                group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
+                               self.params.data, param_flows=pf, logspace_flows=logspace_flows)
+
+    def backward(self, inputs: Optional[torch.Tensor] = None, ll_weights: Optional[torch.Tensor] = None,
+                 compute_param_flows: bool = True, flows_memory: float = 1.0, input_layer_fn=None, cache=None,
+                 return_cache: bool = False, allow_modify_flows: bool = False, propagation_alg: str = "LL",
+                 logspace_flows: bool = True, negate_pflows: bool = False, pflow_temperature: float = 1.0, **kwargs):
+        """Node / element flows and (accumulated) parameter flows of the last forward pass.
+
+        ``logspace_flows`` selects whether the flow buffers hold log-flows (default) or linear flows; the
+        parameter flows are the same either way."""
+        self._require_cuda()
+        _unsupported(input_layer_fn=input_layer_fn is not None, cache=cache is not None, return_cache=return_cache,
+                     allow_modify_flows=allow_modify_flows, propagation_alg=propagation_alg != "LL",
+                     negate_pflows=negate_pflows, pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6,
+                     missing_mask=kwargs.get("missing_mask") is not None)
+        assert self.node_mars is not None and self.element_mars is not None, "Should run forward path first."
+        self._run_params = dict(logspace_flows=logspace_flows, propagation_alg=propagation_alg)
+        with torch.no_grad():
+            B = self.node_mars.size(1)
+            if inputs is None or inputs is getattr(self, "_last_inputs", None):
+                data = self._last_data
+            else:
+                assert inputs.dim() == 2 and inputs.size(0) == B
+                data = self._prepare_inputs(inputs)
+            self._ensure_buffers(B, backward=True)
+            ls = int(bool(logspace_flows))
+            _fill(self.node_flows, NEG_INF if logspace_flows else 0.0)
+            if self._eflow_mode != ls:           # dummy / parentless element rows: -inf in log space, 0 linearly
+                _fill(self.element_flows, NEG_INF if logspace_flows else 0.0)
+                self._eflow_mode = ls
+
+            r0, r1 = self._root_node_range
+            if ll_weights is None:
+                _lib.call("pcx_set_root_flows", self.node_flows, None, r0, r1 - r0, B, ls)
+                if compute_param_flows:
+                    self._cum_flow_host += (r1 - r0) * B
+            else:
+                w = ll_weights.to(self.device, torch.float32)
+                w = w.unsqueeze(0) if w.dim() == 1 else w
+                assert w.size(0) == self.num_root_nodes and w.size(1) == B
+                w = w.contiguous()
+                _lib.call("pcx_set_root_flows", self.node_flows, w, r0, r1 - r0, B, ls)
+                if compute_param_flows:
+                    s = w.sum(dtype=torch.float64)
+                    self._cum_flow_dev = s if self._cum_flow_dev is None else self._cum_flow_dev + s
+
+            if compute_param_flows:
+                self.init_param_flows(flows_memory=flows_memory)
+            key = ("bk", B, bool(compute_param_flows), ls, self.params.data_ptr(),
+                   self.param_flows.data_ptr() if compute_param_flows else 0)
+            self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
+
+            if compute_param_flows:
+                for layer in self.input_layer_group:
+                    layer.backward(data, self.node_flows, self.node_mars, logspace_flows=bool(logspace_flows))
+        return None
+
+    @property
+    def _cum_flow(self) -> float:
+        if self._cum_flow_dev is not None:
+            self._cum_flow_host += float(self._cum_flow_dev.item())
+            self._cum_flow_dev = None
+        return self._cum_flow_host
+
+    @_cum_flow.setter
+    def _cum_flow(self, v: float):
+        self._cum_flow_host = float(v)
+        self._cum_flow_dev = None
+
+    # ------------------------------------------------------------------------------------------
+    # parameter flows and EM
+    # ------------------------------------------------------------------------------------------
+    def init_param_flows(self, flows_memory: float = 1.0, batch_size: Optional[int] = None):
+        assert 0.0 <= flows_memory <= 1.0, "`flows_memory` should be in [0.0, 1.0]"
+        _unsupported(batch_size=batch_size is not None)
+        self._require_cuda()
+        if self.param_flows is None or self.param_flows.device != self.device:
+            self.param_flows = torch.zeros(self.num_param_flows, device=self.device)
+        elif flows_memory == 0.0:
+            _fill(self.param_flows, 0.0)
+        elif flows_memory != 1.0:
+            _scale(self.param_flows, flows_memory)
+        for layer in self.input_layer_group:
+            layer.init_param_flows(flows_memory=flows_memory)
+
+    def zero_param_flows(self):
+        self.init_param_flows(flows_memory=0.0)
+
+    def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False,
+                      step_size_rescaling: bool = False, **kwargs):
+        """theta <- (1 - step_size) theta + step_size * (F + pseudocount / nch) / (sum F + pseudocount), for every
+        sum node and every categorical leaf, from the accumulated flows F."""
+        assert 0.0 < step_size <= 1.0, "`step_size` should be between 0 and 1."
+        _unsupported(step_size_rescaling=step_size_rescaling)
+        self._require_cuda()
+        with torch.no_grad():
+            for layer in self.input_layer_group:
+                layer.mini_batch_em(step_size=step_size, pseudocount=pseudocount, keep_zero_params=keep_zero_params)
+            for start, n, chs in self._fusing_dev:
+                _lib.call("pcx_tied_accum", self.param_flows, start, n, chs, int(chs.numel()))
+            e = self._em_dev
+            _lib.call("pcx_em_sum", self.params.data, self.param_flows, e["par"], e["flow"], e["fan"], e["bs"],
+                      int(e["par"].numel()), e["max_bs"], float(step_size), float(pseudocount), int(bool(keep_zero_params)))
+
+    def sync_param_flows(self, dtype: Optional[torch.dtype] = None, op=None, group=None, sync_cum_flow: bool = True):
+        """Sum the parameter flows of all data-parallel ranks (no-op outside an initialised process group)."""
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) <= 1:
+            return None
+        op = dist.ReduceOp.SUM if op is None else op
+        tensors = [t for t in [self.param_flows] + [l.param_flows for l in self.input_layer_group] if t is not None]
+        for pf in tensors:
+            if dtype is not None and pf.dtype != dtype:
+                buf = pf.to(dtype)
+                dist.all_reduce(buf, op=op, group=group)
+                pf.copy_(buf)
+            else:
+                dist.all_reduce(pf, op=op, group=group)
+        if sync_cum_flow:
+            ct = torch.tensor([float(self._cum_flow)], dtype=torch.float64, device=self.device)
+            dist.all_reduce(ct, op=op, group=group)
+            self._cum_flow = ct.item()
+        return None
+
+    # ------------------------------------------------------------------------------------------
+    # accessors
+    # ------------------------------------------------------------------------------------------
+    def update_parameters(self, clone: bool = True):
+        params = self.params.detach().cpu()
+        for ns in self.root_ns:
+            if ns.is_sum() and not ns.is_tied():
+                ns.update_parameters(params, clone=clone)
+        for layer in self.input_layer_group:
+            layer.update_parameters()
+
+    def update_param_flows(self, clone: bool = True, origin_ns_only: bool = True):
+        flows = self.param_flows.detach().cpu()
+        for ns in self.root_ns:
+            if ns.is_sum() and not ns.is_tied():
+                ns.update_param_flows(flows, clone=clone, origin_ns_only=origin_ns_only)
+
+    def _prod_layer_of(self, ns):
+        for gi, group in enumerate(self.inner_layer_groups):
+            if group.is_prod():
+                for layer in group:
+                    if any(n is ns for n in layer.nodes):
+                        return gi
+        raise ValueError("node vector not found in this circuit")
+
+    def get_node_mars(self, ns):
+        s, e = ns._output_ind_range
+        if ns.is_sum() or ns.is_input():
+            return self.node_mars[s:e, :].detach()
+        gi = self._prod_layer_of(ns)
+        self.inner_layer_groups[gi].forward(self.node_mars, self.element_mars)
+        return self.element_mars[s:e, :].detach()
+
+    def get_node_flows(self, ns, **kwargs):
+        s, e = ns._output_ind_range
+        if ns.is_sum() or ns.is_input():
+            return self.node_flows[s:e, :].detach()
+        gi = self._prod_layer_of(ns)
+        self.inner_layer_groups[gi].forward(self.node_mars, self.element_mars, _for_backward=True)
+        self.inner_layer_groups[gi + 1].backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
+                                                 self.params.data, param_flows=None,
+                                                 logspace_flows=self._run_params.get("logspace_flows", True))
+        return self.element_flows[s:e, :].detach()
+
+    def get_node_params(self, ns, clone: bool = True, **kwargs):
+        if not ns.is_sum() or ns.is_tied():
+            return None
+        s, e = ns._param_range
+        flat = self.params[s:e].detach()
+        flat = flat.clone() if clone else flat
+        local = ((ns._param_ids - s) // (ns.block_size * ns.ch_block_size)).to(flat.device)
+        return flat.reshape(local.size(0), ns.ch_block_size, ns.block_size)[local].permute(0, 2, 1)
+
+    def get_node_param_flows(self, ns, clone: bool = True, **kwargs):
+        if not ns.is_sum() or ns.is_tied():
+            return None
+        s, e = ns._param_flow_range
+        flat = self.param_flows[s:e].detach()
+        flat = flat.clone() if clone else flat
+        local = ((ns._param_flow_ids - s) // (ns.block_size * ns.ch_block_size)).to(flat.device)
+        return flat.reshape(local.size(0), ns.ch_block_size, ns.block_size)[local].permute(0, 2, 1)
+
+    def layers(self, reverse: bool = False, ret_layer_groups: bool = False, ignore_input_layers: bool = False):
+        groups = ([] if ignore_input_layers else [self.input_layer_group]) + list(self.inner_layer_groups)
+        if reverse:
+            groups = groups[::-1]
+        for g in groups:
+            if ret_layer_groups:
+                yield g
+            else:
+                for layer in g:
+                    yield layer
+
+    def print_statistics(self):
+        print(f"> Number of nodes: {self.num_nodes}")
+        print(f"> Number of edges: {self.num_edges}")
+        print(f"> Number of sum parameters: {self.num_sum_params}")
+        print(f"> Number of input parameters: {sum(l.params.numel() for l in self.input_layer_group)}")
+
+
+def compile(ns, layer_sparsity_tol: float = 0.5, max_num_partitions: Optional[int] = None,
+            disable_gpu_compilation: bool = False, force_gpu_compilation: bool = False,
+            max_tied_ns_per_parflow_block: int = 32, device=None, verbose: bool = True) -> TensorCircuit:
+    """Compile the node DAG rooted at ``ns`` into a :class:`TensorCircuit` (model/tensorcircuit.py:2138-2175).
+    Table compilation runs on the host; the two ``*_gpu_compilation`` switches are accepted and ignored."""
+    return TensorCircuit(ns, layer_sparsity_tol=layer_sparsity_tol, max_num_partitions=max_num_partitions,
+                         max_tied_ns_per_parflow_block=max_tied_ns_per_parflow_block, device=device, verbose=verbose)
