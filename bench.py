@@ -1,0 +1,365 @@
+"""Benchmark of the compiled probabilistic-circuit training step (forward + backward + mini-batch EM).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg1] [--impl ours|reference]
+
+One "step" is one mini-batch of the named configuration through ``pc(x)``, ``lls.mean().backward()`` and
+``MiniBatchEM.step()``.  Rank 0 prints ONE JSON line:
+
+  value        samples/s over all ranks, inputs already resident in HBM, timed with CUDA events
+  e2e          the same metric with each step's batch copied from pinned host memory inside the timed region
+               and the mean log-likelihood read back to the host
+  roofline     the dominant kernel family, timed per launch with CUDA events in a separate instrumented pass
+  cpu_baseline the CPU oracle (fp32, all host threads) on a bounded sample of the same workload
+
+``--impl reference`` times that CPU oracle alone (the reference has no runnable CPU implementation of this
+path; the oracle is its restatement) and prints the same line with ``"impl": "reference"``.
+
+Under torchrun every rank holds the full circuit and its own shard of the batch (weak scaling: the per-GPU
+batch is fixed); parameter flows are all-reduced once per EM step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import pyjuice_b200 as pj  # noqa: E402
+from pyjuice_b200 import data as pdata  # noqa: E402
+
+STEP_SIZE, PSEUDOCOUNT = 0.1, 0.1
+
+CONFIGS = {
+    # name: (description, per-GPU batch)
+    "cfg0": ("HCLT-32 4cats K=8", 256),
+    "cfg1": ("HCLT-784 grid28x28 256cats K=128", 512),
+    "cfg2": ("PD-28x28 256cats K=64 splits[4,7,14]", 512),
+    "cfg3": ("RAT-SPN-784 256cats depth5 rep16 K=32", 1024),
+    "cfg4": ("HMM 4096 states vocab32768 T=128 tied", 256),
+}
+
+
+def build_workload(name: str, num_samples: int, seed_offset: int = 0):
+    """Returns (root_ns, data[num_samples, V] as a numpy int64 array).  Circuit structure and parameters depend
+    on the configuration's seed only; ``seed_offset`` (the rank) only changes which samples are drawn."""
+    if name == "cfg0":
+        torch.manual_seed(0)
+        x = pdata.tree_bn_samples(4096, 32, 4, seed=0)
+        ns = pj.structures.HCLT(torch.from_numpy(x).float(), num_latents=8, num_cats=4)
+        x = x[(np.arange(num_samples) + seed_offset * num_samples) % 4096]
+    elif name == "cfg1":
+        torch.manual_seed(1)
+        _, tree, root = pdata.grid_gaussian_bn_samples(16, 28, 28, seed=1)
+        ns = pj.structures.tree_to_hidden_circuit(tree, root, num_latents=128, num_cats=256)
+        x, _, _ = pdata.grid_gaussian_bn_samples(num_samples * (seed_offset + 1), 28, 28, seed=1)
+        x = x[-num_samples:]
+    elif name == "cfg2":
+        import random
+        torch.manual_seed(2)
+        random.seed(2)
+        pts = sorted(set(range(4, 28, 4)) | set(range(7, 28, 7)) | set(range(14, 28, 14)))
+        ns = pj.structures.PD((28, 28), num_latents=64, split_points=[pts, pts], num_cats=256)
+        x, _, _ = pdata.grid_gaussian_bn_samples(num_samples * (seed_offset + 1), 28, 28, seed=2)
+        x = x[-num_samples:]
+    elif name == "cfg3":
+        import random
+        torch.manual_seed(3)
+        random.seed(3)
+        ns = pj.structures.RAT_SPN(num_vars=784, num_latents=32, depth=5, num_repetitions=16, num_cats=256)
+        x = pdata.mixture_samples(num_samples * (seed_offset + 1), 784, 256, seed=3)[-num_samples:]
+    elif name == "cfg4":
+        torch.manual_seed(4)
+        ns = pj.structures.HMM(seq_length=128, num_latents=4096, num_emits=32768, homogeneous=True)
+        x = pdata.hmm_samples(num_samples * (seed_offset + 1), 128, 32768, seed=4)[-num_samples:]
+    else:
+        raise ValueError(name)
+    ns.init_parameters()
+    return ns, x
+
+
+def circuit_stats(pc):
+    """Algorithmic work per sample and per step (the figures every roofline number is computed from)."""
+    e_sum = sum(l.num_edges for g in pc.inner_layer_groups if g.is_sum() for l in g)
+    prod_edges = sum(l.num_edges for g in pc.inner_layer_groups if g.is_prod() for l in g)
+    prod_nodes = sum(l.num_nodes for g in pc.inner_layer_groups if g.is_prod() for l in g)
+    n_in = sum(l.num_nodes for l in pc.input_layer_group)
+    p_in = sum(l.num_parameters for l in pc.input_layer_group)
+    f_in = sum(l.num_param_flows for l in pc.input_layer_group)
+    return dict(e_sum=e_sum, prod_edges=prod_edges, prod_nodes=prod_nodes, n_in=n_in, p_in=p_in, f_in=f_in,
+                p_sum=pc.num_sum_params, f_sum=pc.num_param_flows)
+
+
+# algorithmic flops / bytes of one launch family per STEP (batch B); "unit" picks the roofline it is judged by
+def family_work(stats, B, elsize):
+    s = stats
+    return {
+        "pcx_sum_fwd": ("tensor", 2.0 * s["e_sum"] * B),
+        "pcx_sum_bwd_ele": ("tensor", 2.0 * s["e_sum"] * B),
+        "pcx_sum_bwd_par": ("tensor", 2.0 * s["e_sum"] * B),
+        # product layers run twice forward per step (once more inside the backward pass)
+        "pcx_prod_fwd": ("hbm", 2 * 4.0 * (s["prod_edges"] + s["prod_nodes"]) * B),
+        "pcx_prod_bwd": ("hbm", 4.0 * (s["prod_edges"] + 2 * s["prod_nodes"]) * B),
+        "pcx_input_cat_fwd": ("hbm", (4.0 * s["n_in"] + elsize * 0) * B),
+        "pcx_input_cat_bwd": ("hbm", 4.0 * s["n_in"] * B + 8.0 * s["f_in"]),
+        "pcx_em_input_cat": ("hbm", 12.0 * s["p_in"]),
+        "pcx_em_sum": ("hbm", 12.0 * s["p_sum"]),
+        "pcx_fill_f32": ("hbm", 4.0 * (s["f_sum"] + s["f_in"]) + 4.0 * 0),
+    }
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm": p["hbm_gbs"], "tensor": p["bf16_tflops"], "source": "measured"}
+    return {"hbm": 6650.0, "tensor": 1590.0, "source": "fallback"}
+
+
+def oracle_step_time(pc, x_cpu: torch.Tensor, repeats: int = 1):
+    """Seconds per forward + backward + EM step of the fp32 CPU oracle on ``x_cpu``."""
+    from oracle import pc_oracle as orc
+    tables = orc._tables(pc)
+    params = pc.params.data.detach().cpu()
+    iparams = [l.params.data.detach().cpu() for l in pc.input_layer_group]
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        _, st = orc.forward(pc, x_cpu, params, iparams, dtype=torch.float32, tables=tables)
+        orc.backward(pc, x_cpu, params, iparams, st)
+        orc.em_update(pc, params, iparams, st, STEP_SIZE, PSEUDOCOUNT)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def run_reference(args, rank):
+    """CPU arm: the oracle restatement of the reference algorithm on the host cores, one bounded sample per step."""
+    if rank != 0:
+        return
+    desc, B = CONFIGS[args.config]
+    sample = min(B, args.cpu_sample)
+    ns, x = build_workload(args.config, sample)
+    pc = pj.compile(ns)
+    xc = torch.from_numpy(x)
+    cores = torch.get_num_threads()
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        oracle_step_time(pc, xc)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle_step_time(pc, xc)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = sample / dt
+    what = f"{sample} samples per step (of the {B}-sample batch), fwd+bwd+EM, fp32 torch CPU, {cores} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "samples/sec fwd+bwd+EM", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {desc}", "batch_per_gpu": B},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port", "sample": what},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="cfg1", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+
+    import torch.distributed as dist
+    from pyjuice_b200 import _lib
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    W, K = max(args.warmup, 3), args.steps
+    desc, B = CONFIGS[args.config]
+
+    n_batches = 4
+    ns, x = build_workload(args.config, B * n_batches, seed_offset=rank)
+    pc = pj.compile(ns).to(dev)
+    pc.use_cuda_graphs = not args.no_graphs
+    stats = circuit_stats(pc)
+    max_cats = max(l.max_cats for l in pc.input_layer_group)
+    np_dtype, elsize = (np.uint8, 1) if max_cats <= 256 else (np.int32, 4)
+    host = [torch.from_numpy(x[i * B:(i + 1) * B].astype(np_dtype)).pin_memory() for i in range(n_batches)]
+    resident = [h.to(dev) for h in host]
+    opt = pj.optim.MiniBatchEM(pc, step_size=STEP_SIZE, pseudocount=PSEUDOCOUNT, ddp=world > 1)
+
+    def step(xb):
+        lls = pc(xb)
+        lls.mean().backward()
+        opt.step()
+        return lls
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(W):
+        step(resident[i % n_batches])
+    barrier()
+
+    # launches per step, counted on an eager step (graph replays launch the same kernels)
+    pc.use_cuda_graphs = False
+    _lib.COUNT = 0
+    step(resident[0])
+    launches_per_step = _lib.COUNT
+    pc.use_cuda_graphs = not args.no_graphs
+    barrier()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(K):
+        step(resident[i % n_batches])
+    ev1.record()
+    barrier()
+    ms_dev = ev0.elapsed_time(ev1)
+
+    barrier()
+    ev0.record()
+    last = 0.0
+    for i in range(K):
+        xb = host[i % n_batches].to(dev, non_blocking=True)
+        last = step(xb).mean().item()
+    ev1.record()
+    barrier()
+    ms_e2e = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if sampler else None
+
+    t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = t.tolist()
+
+    # instrumented pass: per-family device time with CUDA events around every launch (eager, outside the timed region)
+    fam = {}
+    if rank == 0:
+        pc.use_cuda_graphs = False
+        for rep in range(3):
+            _lib.PROFILE = [] if rep == 2 else None
+            step(resident[0])
+            torch.cuda.synchronize()
+        for name, a, b in _lib.PROFILE:
+            d = fam.setdefault(name, [0, 0.0])
+            d[0] += 1
+            d[1] += a.elapsed_time(b)
+        _lib.PROFILE = None
+        pc.use_cuda_graphs = not args.no_graphs
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    work = family_work(stats, B, elsize)
+    fam_ms = {k: round(v[1], 4) for k, v in sorted(fam.items(), key=lambda kv: -kv[1][1])}
+    top = max(fam, key=lambda k: fam[k][1])
+    bound, amount = work.get(top, ("hbm", 0.0))
+    n_launch, tot_ms = fam[top]
+    achieved = amount / (tot_ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+    roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peaks[bound],
+                "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": achieved / peaks[bound],
+                "traffic": None, "peak_source": peaks["source"], "launches_per_step": n_launch,
+                "ms_per_step_in_kernel": tot_ms, "family_ms_per_step": fam_ms}
+    sum_ms = sum(fam[k][1] for k in ("pcx_sum_fwd", "pcx_sum_bwd_ele", "pcx_sum_bwd_par") if k in fam)
+    sum_tflops = 6.0 * stats["e_sum"] * B / (sum_ms * 1e-3) / 1e12 if sum_ms > 0 else None
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        sample = min(B, args.cpu_sample)
+        sec = oracle_step_time(pc, torch.from_numpy(x[:sample]))
+        cores = torch.get_num_threads()
+        cpu = {"value": sample / sec, "unit": "samples/s", "cores": cores, "kind": "port",
+               "sample": f"one fwd+bwd+EM step on {sample} samples, fp32 torch CPU oracle, {cores} threads, {sec:.2f} s"}
+
+    total = B * world * K
+    out = {
+        "metric": "samples/sec fwd+bwd+EM", "value": total / (ms_dev * 1e-3), "unit": "samples/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev / K, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {desc}", "batch_per_gpu": B, "global_batch": B * world,
+                   "parallelism": f"dp{world}", "em": {"step_size": STEP_SIZE, "pseudocount": PSEUDOCOUNT},
+                   "input_dtype": np.dtype(np_dtype).name, "cuda_graphs": not args.no_graphs,
+                   "l2": "value buffers (%.2f GB) exceed the 126 MB L2; no explicit flush" %
+                         (4.0 * B * 2 * (pc.num_nodes + pc.num_elements) / 1e9),
+                   "circuit": {k: int(v) for k, v in stats.items()}},
+        "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e / K,
+                "h2d_bytes_per_step": int(B * pc.num_vars * elsize), "d2h_bytes_per_step": 4, "last_mean_ll": last},
+        "gpu_launches": launches_per_step * K,
+        "roofline": roofline,
+        "sum_layers": {"tflops": sum_tflops, "ms_per_step": sum_ms, "frac_of_bf16_peak": (sum_tflops or 0) / peaks["tensor"],
+                       "arith": "fp32 FMA (CUDA cores)"},
+        "cpu_baseline": cpu,
+        "clocks": clocks,
+    }
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -239,11 +239,14 @@ def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size
         pf = pf.clone()
         for start, n, ch in lt["tied"]:
             pf[start:start + n] = sum(pf[int(c):int(c) + n] for c in ch)
-        for nid in lt["source_nids"].tolist():
-            C = int(lt["metadata"][lt["s_mids"][nid]].item())
-            a, f = int(lt["s_pids"][nid]), int(lt["s_pfids"][nid])
-            flow = pf[f:f + C]
-            ip[a:a + C] = (1.0 - step_size) * ip[a:a + C] + step_size * (flow + pseudocount / C) / (flow.sum() + pseudocount)
+        src = lt["source_nids"]
+        cats = lt["metadata"][lt["s_mids"][src]].long()
+        for C in torch.unique(cats).tolist():                        # all nodes with C categories at once
+            sel = src[cats == C]
+            c = torch.arange(C)
+            pidx = lt["s_pids"][sel][:, None] + c[None, :]
+            flow = pf[lt["s_pfids"][sel][:, None] + c[None, :]]
+            ip[pidx] = (1.0 - step_size) * ip[pidx] + step_size * (flow + pseudocount / C) / (flow.sum(dim=1, keepdim=True) + pseudocount)
         new_inputs.append(ip)
 
     params = params.detach().cpu().to(dtype).clone()

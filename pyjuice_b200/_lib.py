@@ -39,6 +39,11 @@ SIGNATURES = {
 
 _lib: Optional[ctypes.CDLL] = None
 
+# Launch accounting for benchmarks: COUNT increments on every call; when PROFILE is a list, every launch is
+# bracketed by CUDA events on the launching stream and (name, start, end) is appended to it.
+COUNT = 0
+PROFILE = None
+
 
 class PcxError(RuntimeError):
     pass
@@ -80,6 +85,15 @@ def call(name: str, *args) -> None:
             conv.append(None)
         else:
             conv.append(a)
-    rc = getattr(lib, name)(*conv, _stream())
+    global COUNT
+    COUNT += 1
+    if PROFILE is not None:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = getattr(lib, name)(*conv, _stream())
+        b.record()
+        PROFILE.append((name, a, b))
+    else:
+        rc = getattr(lib, name)(*conv, _stream())
     if rc != 0:
         raise PcxError(f"{name} failed with status {rc}")

@@ -1,0 +1,60 @@
+"""Shared helpers of the GPU parity tests: run the CUDA path and the CPU oracle on the same circuit and inputs."""
+import torch
+
+from oracle import pc_oracle as orc
+
+LL_ATOL = 1e-3          # nats, absolute, per-sample log-likelihood
+REL_TOL = 1e-3          # relative, node flows / parameter flows / post-EM parameters
+
+
+def rel_close(got: torch.Tensor, ref: torch.Tensor, rtol: float = REL_TOL, floor: float = 1e-6):
+    """|got - ref| <= rtol * max(|ref|, floor * scale) elementwise, scale = largest reference magnitude."""
+    got, ref = got.double().cpu(), ref.double().cpu()
+    scale = max(ref.abs().max().item(), 1e-30)
+    err = (got - ref).abs()
+    bound = rtol * torch.clamp(ref.abs(), min=floor * scale)
+    bad = err > bound
+    return not bool(bad.any()), (err / torch.clamp(ref.abs(), min=floor * scale)).max().item()
+
+
+def oracle_step(pc, x, step=None, pseudo=0.0, params=None, input_params=None, ll_weights=None):
+    params = pc.params.data if params is None else params
+    iparams = [l.params.data for l in pc.input_layer_group] if input_params is None else input_params
+    lls, st = orc.forward(pc, x.cpu(), params, iparams)
+    orc.backward(pc, x.cpu(), params, iparams, st, ll_weights=ll_weights)
+    new = orc.em_update(pc, params, iparams, st, step, pseudo) if step is not None else None
+    return lls, st, new
+
+
+def check_against_oracle(pc, x, step=0.1, pseudo=0.1, logspace_flows=True):
+    """One forward + backward + EM step on the GPU, compared with the oracle.  Returns a dict of worst errors."""
+    dev = pc.device
+    p0 = pc.params.data.detach().cpu().clone()
+    ip0 = [l.params.data.detach().cpu().clone() for l in pc.input_layer_group]
+    ref_lls, st, (ref_p, ref_ip) = oracle_step(pc, x, step, pseudo, params=p0, input_params=ip0)
+
+    pc.init_param_flows(flows_memory=0.0)
+    lls = pc(x.to(dev))
+    pc.backward(x.to(dev), logspace_flows=logspace_flows)
+    out = {}
+    out["ll"] = (lls.double().cpu() - ref_lls).abs().max().item()
+    assert out["ll"] <= LL_ATOL, f"log-likelihood off by {out['ll']} nats"
+
+    nf = pc.node_flows.double().cpu()
+    nf = nf.exp() if logspace_flows else nf
+    ok, out["node_flows"] = rel_close(nf[pc.num_dummy_nodes:], st.node_flows.exp()[pc.num_dummy_nodes:])
+    assert ok, f"node flows rel err {out['node_flows']}"
+    ok, out["param_flows"] = rel_close(pc.param_flows, st.param_flows)
+    assert ok, f"sum parameter flows rel err {out['param_flows']}"
+    for layer, ref in zip(pc.input_layer_group, st.input_param_flows):
+        ok, out["input_flows"] = rel_close(layer.param_flows, ref)
+        assert ok, f"input parameter flows rel err {out['input_flows']}"
+
+    pc.mini_batch_em(step_size=step, pseudocount=pseudo)
+    ok, out["params"] = rel_close(pc.params.data[pc.num_dummy_params:], ref_p[pc.num_dummy_params:])
+    assert ok, f"post-EM sum parameters rel err {out['params']}"
+    for layer, ref in zip(pc.input_layer_group, ref_ip):
+        ok, out["input_params"] = rel_close(layer.params.data, ref)
+        assert ok, f"post-EM input parameters rel err {out['input_params']}"
+    torch.cuda.synchronize()
+    return out

@@ -1,0 +1,106 @@
+"""CPU-side checks: the shared library and its header agree, structure generators and data generators behave,
+and unsupported options are rejected instead of being silently ignored."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import pyjuice_b200 as pj
+from pyjuice_b200 import _lib
+from pyjuice_b200.compiler import partition_nodes_by_n_edges
+from pyjuice_b200.structures import Tree, minimum_spanning_tree
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "pcx_b200.h")).read()
+    return sorted(set(re.findall(r"^\s*int\s+(pcx_\w+)\s*\(", text, flags=re.M)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/pcx_b200.h but not exported"
+    assert set(_lib.SIGNATURES) | {"pcx_build_arch"} == set(names), "ctypes prototypes and header disagree"
+    assert lib.pcx_build_arch() == 100
+
+
+def test_chow_liu_matches_networkx():
+    nx = pytest.importorskip("networkx")
+    rng = np.random.default_rng(0)
+    for n in (5, 17, 40):
+        mi = rng.random((n, n)).astype(np.float32)
+        mi = (mi + mi.T) / 2
+        g = nx.Graph()
+        for v in range(n):
+            g.add_node(v)
+            for u in range(v):
+                g.add_edge(u, v, weight=-mi[u, v])
+        t_ref = nx.minimum_spanning_tree(g)
+        t = minimum_spanning_tree(-mi.astype(np.float64))
+        assert [tuple(e) for e in t_ref.edges()] == [tuple(e) for e in _edges_in_nx_order(t)]
+        root = nx.center(t_ref)[0]
+        assert root == t.center()
+        assert list(nx.dfs_postorder_nodes(t_ref, root)) == t.dfs_postorder(root)
+        clt = nx.bfs_tree(t_ref, root)
+        ch = t.rooted_children(root)
+        for v in range(n):
+            assert list(clt.successors(v)) == ch[v]
+
+
+def _edges_in_nx_order(t: Tree):
+    seen, out = set(), []
+    for u in range(t.n):
+        for v in t.adj[u]:
+            if v not in seen:
+                out.append((u, v))
+        seen.add(u)
+    return out
+
+
+def test_partition_examples():
+    # one value -> one group; widely spread values split until the padded work is within (1 + tol) of the real work
+    assert partition_nodes_by_n_edges(np.array([8, 8, 8]), sparsity_tolerance=0.5).tolist() == [8]
+    out = partition_nodes_by_n_edges(np.array([1] * 50 + [64] * 2), sparsity_tolerance=0.1)
+    assert out.tolist() == [1, 64]
+    assert partition_nodes_by_n_edges(np.array([3, 5, 9]), max_num_partitions=1).tolist() == [9]
+
+
+def test_data_generators_are_seeded_and_in_range():
+    from pyjuice_b200 import data
+    a = data.tree_bn_samples(256, 32, 4, seed=0)
+    b = data.tree_bn_samples(256, 32, 4, seed=0)
+    assert np.array_equal(a, b) and a.min() >= 0 and a.max() < 4 and a.shape == (256, 32)
+    x, tree, root = data.grid_gaussian_bn_samples(128, 6, 6, seed=1, num_cats=64)
+    assert x.shape == (128, 36) and x.max() < 64 and len(tree.edges) == 35
+    m = data.mixture_samples(64, 20, 16, seed=3)
+    assert m.shape == (64, 20) and m.max() < 16
+    h = data.hmm_samples(32, 10, vocab=500, seed=4, num_states=16)
+    assert h.shape == (32, 10) and h.max() < 500
+
+
+def test_unsupported_options_raise():
+    ns = pj.structures.HMM(seq_length=4, num_latents=4, num_emits=5)
+    pc = pj.compile(ns)
+    with pytest.raises(NotImplementedError):
+        pc.forward(torch.zeros(2, 4, dtype=torch.long))           # no CPU path
+    with pytest.raises(NotImplementedError):
+        pj.optim.MiniBatchEM(pc, sync_every=4)
+
+
+def test_parameters_are_normalised_after_compile():
+    torch.manual_seed(0)
+    ns = pj.structures.RAT_SPN(num_vars=12, num_latents=8, depth=2, num_repetitions=2, num_cats=5, block_size=4)
+    pc = pj.compile(ns)
+    eb = pc._em_blocks
+    for i in range(eb["par"].numel()):
+        p0, fan, bs = int(eb["par"][i]), int(eb["fan"][i]), int(eb["bs"][i])
+        s = pc.params.data[p0:p0 + fan * bs].view(fan, bs).sum(dim=0)
+        assert torch.allclose(s, torch.ones_like(s), atol=1e-5)
+    assert torch.all(pc.params.data[:pc.num_dummy_params] == 0)
