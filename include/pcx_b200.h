@@ -28,6 +28,14 @@ extern "C" {
 /* Library / build identification: returns the compute capability it was built for (100). */
 int pcx_build_arch(void);
 
+/* Arithmetic of the sum-layer contractions (process-wide): 0 = fp32 CUDA cores everywhere; 1 (default) = tensor
+ * cores (tcgen05, fp32 accumulate) with every fp32 factor split into bf16 hi + lo (three products) wherever the
+ * block sizes allow a 128-row tile, fp32 CUDA cores elsewhere; 2 = as 1 with a single bf16 product.
+ * Takes over the role of the reference's force_use_bf16 / force_use_fp32 switches (layer/sum_layer.py:752-771). */
+int pcx_set_sum_mode(int mode);
+/* 0, or the code of the first tensor-core kernel whose bounded barrier wait ran out (synchronises the device). */
+int pcx_get_status(void);
+
 /* p[i] = v  /  p[i] *= v  for i < n.
  * Replaces the buffer resets of model/tensorcircuit.py:357-359, 528-529, 1761-1773 and the
  * `param_flows *= flows_memory` of model/tensorcircuit.py:1411-1412, layer/input_layer.py:299-300. */

@@ -37,6 +37,9 @@ SIGNATURES = {
     "pcx_em_input_cat": [P, P, P, P, P, P, L, I, F, F, I],
 }
 
+# entry points without a stream argument
+PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": []}
+
 _lib: Optional[ctypes.CDLL] = None
 
 # Launch accounting for benchmarks: COUNT increments on every call; when PROFILE is a list, every launch is
@@ -58,8 +61,10 @@ def load() -> ctypes.CDLL:
         raise PcxError(f"{LIB_PATH} is missing: build it with `python -m pyjuice_b200.csrc.build` "
                        "(there is no CPU or PyTorch fallback for the circuit kernels)")
     lib = ctypes.CDLL(LIB_PATH)
-    lib.pcx_build_arch.restype = c_int
-    lib.pcx_build_arch.argtypes = []
+    for name, args in PLAIN.items():
+        fn = getattr(lib, name)
+        fn.restype = c_int
+        fn.argtypes = list(args)
     for name, args in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = c_int
@@ -97,3 +102,16 @@ def call(name: str, *args) -> None:
         rc = getattr(lib, name)(*conv, _stream())
     if rc != 0:
         raise PcxError(f"{name} failed with status {rc}")
+
+
+def set_sum_mode(mode: int) -> None:
+    """0 = fp32 CUDA cores, 1 = tensor cores with bf16 hi/lo split (default), 2 = tensor cores, single bf16."""
+    if load().pcx_set_sum_mode(int(mode)) != 0:
+        raise PcxError(f"invalid sum mode {mode}")
+
+
+def check_status() -> None:
+    """Raise if a tensor-core kernel reported that one of its bounded barrier waits ran out."""
+    code = load().pcx_get_status()
+    if code != 0:
+        raise PcxError(f"a tensor-core kernel gave up waiting on a barrier (status {code})")

@@ -197,6 +197,19 @@ def hclt_cfg0(api):
     return api.hclt_from_data(x, num_latents=8, num_cats=4), dict()
 
 
+def hclt_b128(api):
+    """Hidden tree with 128-node blocks (the tile shape of the tensor-core kernels), two blocks per vector."""
+    edges, n = _grid_tree(3, 4, 5)
+    from pyjuice_b200.structures import Tree
+    root = Tree(n, edges).center()
+    return api.hclt_from_tree(edges, n, root, num_latents=256, num_cats=12, block_size=128), dict()
+
+
+def hmm_b128(api):
+    """Homogeneous HMM with 256 states in blocks of 128 (dense 256 x 256 tied transitions)."""
+    return api.hmm(seq_length=6, num_latents=256, num_emits=40, homogeneous=True, block_size=128), dict()
+
+
 def pd_small(api):
     """Poon-Domingos over an 8x8 grid with two scales of splits (random block connections included)."""
     _seed(2)
@@ -221,6 +234,8 @@ CASES = {
     "hmm_inhomogeneous": hmm_inhomogeneous,
     "hclt_grid": hclt_grid,
     "hclt_cfg0": hclt_cfg0,
+    "hclt_b128": hclt_b128,
+    "hmm_b128": hmm_b128,
     "pd_small": pd_small,
     "rat_small": rat_small,
 }

@@ -38,6 +38,22 @@ def test_step_matches_oracle(name):
     print(name, errs)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("B", [5, 128, 200])
+@pytest.mark.parametrize("name", ["hclt_b128", "hmm_b128"])
+def test_sum_arithmetic_modes(name, B, mode):
+    """fp32 CUDA-core kernels (mode 0) and the tcgen05 kernels with split-bf16 operands (mode 1) both meet the bar."""
+    from pyjuice_b200 import _lib
+    _lib.set_sum_mode(mode)
+    try:
+        pc = _build(name, seed=7).to(DEV)
+        errs = check_against_oracle(pc, _data_for(pc, B, seed=B))
+        print(name, B, mode, errs)
+        _lib.check_status()
+    finally:
+        _lib.set_sum_mode(1)
+
+
 @pytest.mark.parametrize("B", [1, 3, 33, 100, 256])
 @pytest.mark.parametrize("name", ["simple_model", "simple_model_bs1", "hclt_grid", "hmm_blocks", "pd_small"])
 def test_ragged_batch_sizes(name, B):
@@ -125,6 +141,12 @@ def test_layer_level_calls_and_accessors():
     assert torch.allclose(pc.element_flows[s:e].double().cpu(), pc.node_flows[a:b].double().cpu(), rtol=1e-4, atol=1e-7)
     p = pc.get_node_params(ns0)
     assert p.shape == ns0._params.shape and torch.allclose(p.cpu(), ns0._params, atol=1e-6)
+
+
+def test_no_kernel_reported_a_failed_wait():
+    from pyjuice_b200 import _lib
+    torch.cuda.synchronize()
+    _lib.check_status()
 
 
 def test_cpu_use_fails_loudly():
