@@ -214,6 +214,8 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--sum-mode", type=int, default=1, choices=[0, 1, 2],
+                    help="0 fp32 CUDA cores, 1 tensor cores with split-bf16 operands, 2 tensor cores single bf16")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -231,6 +233,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     W, K = max(args.warmup, 3), args.steps
     desc, B = CONFIGS[args.config]
+    _lib.set_sum_mode(args.sum_mode)
 
     n_batches = 4
     ns, x = build_workload(args.config, B * n_batches, seed_offset=rank)
@@ -352,7 +355,8 @@ def main():
         "gpu_launches": launches_per_step * K,
         "roofline": roofline,
         "sum_layers": {"tflops": sum_tflops, "ms_per_step": sum_ms, "frac_of_bf16_peak": (sum_tflops or 0) / peaks["tensor"],
-                       "arith": "fp32 FMA (CUDA cores)"},
+                       "arith": ["fp32 FMA (CUDA cores)", "tcgen05 bf16 hi/lo split x3, fp32 accumulate (fwd, element flows); fp32 FMA (parameter flows)",
+                                 "tcgen05 single bf16, fp32 accumulate (fwd, element flows); fp32 FMA (parameter flows)"][args.sum_mode]},
         "cpu_baseline": cpu,
         "clocks": clocks,
     }

@@ -93,6 +93,27 @@ int pcx_sum_fwd(float* node_mars, const float* element_mars, const float* params
                 const int32_t* nids, const int32_t* cids, const int32_t* pids,
                 int64_t n_blocks, int K, int block_size, int B, void* stream);
 
+/* Pre-split parameter tiles for the tensor-core kernels.  The parameter operand of the forward and element-flow
+ * contractions only changes at EM updates, so it is converted once per update into bf16 hi/lo tile images of
+ * 32 KB (one per 128-row tile and 64-deep slice of the contraction) that the kernels copy straight into shared
+ * memory.  mode 0 = forward (kids = cids, kpar = pids, par_block ignored), mode 1 = element flows (kids = parids,
+ * kpar = parpids, row_block = ch_block_size, par_block = block_size).  `pcx_packed_tile_count` * 32768 bytes is the
+ * size of `packed`.  No counterpart in the reference (its kernels convert on the fly:
+ * layer/kernels/c/tlmm_forward_sum.cu:140-166). */
+int64_t pcx_packed_tile_count(int64_t n_rows, int K, int row_block, int par_block, int mode);
+int pcx_pack_sum_params(void* packed, const float* params, const int32_t* kids, const int32_t* kpar,
+                        int64_t n_rows, int K, int row_block, int par_block, int mode, void* stream);
+
+/* pcx_sum_fwd / pcx_sum_bwd_ele on the tensor cores (tcgen05 + TMEM), reading pre-split parameter tiles.
+ * Need block_size % 128 == 0 (forward) or ch_block_size % 128 == 0 and block_size % 8 == 0 (element flows). */
+int pcx_sum_fwd_packed(float* node_mars, const float* element_mars, const void* packed,
+                       const int32_t* nids, const int32_t* cids, int64_t n_blocks, int K, int block_size, int B,
+                       void* stream);
+int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, const float* node_flows,
+                           const float* node_mars, const void* packed, const int32_t* chids, const int32_t* parids,
+                           int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
+                           void* stream);
+
 /* Sum layer backward, element flows, one backward partition:
  *   element_flows[chids[i]+c, b] = element_mars[chids[i]+c, b]
  *        + log sum_{p, n} params[parpids[i,p] + c*block_size + n] * exp(node_flows[parids[i,p]+n, b] - node_mars[parids[i,p]+n, b])

@@ -32,13 +32,18 @@ SIGNATURES = {
     "pcx_sum_fwd": [P, P, P, P, P, P, L, I, I, I],
     "pcx_sum_bwd_ele": [P, P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_sum_bwd_par": [P, P, P, P, P, P, P, P, P, L, I, I, I, I],
+    "pcx_pack_sum_params": [P, P, P, P, L, I, I, I, I],
+    "pcx_sum_fwd_packed": [P, P, P, P, P, L, I, I, I],
+    "pcx_sum_bwd_ele_packed": [P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_tied_accum": [P, L, L, P, I],
     "pcx_em_sum": [P, P, P, P, P, P, L, I, F, F, I],
     "pcx_em_input_cat": [P, P, P, P, P, P, L, I, F, F, I],
 }
 
 # entry points without a stream argument
-PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": []}
+PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": [],
+         "pcx_packed_tile_count": [L, I, I, I, I]}
+SUM_MODE = 1        # mirror of the library's arithmetic mode (see set_sum_mode)
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -63,7 +68,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     for name, args in PLAIN.items():
         fn = getattr(lib, name)
-        fn.restype = c_int
+        fn.restype = c_int64 if name == "pcx_packed_tile_count" else c_int
         fn.argtypes = list(args)
     for name, args in SIGNATURES.items():
         fn = getattr(lib, name)
@@ -106,8 +111,10 @@ def call(name: str, *args) -> None:
 
 def set_sum_mode(mode: int) -> None:
     """0 = fp32 CUDA cores, 1 = tensor cores with bf16 hi/lo split (default), 2 = tensor cores, single bf16."""
+    global SUM_MODE
     if load().pcx_set_sum_mode(int(mode)) != 0:
         raise PcxError(f"invalid sum mode {mode}")
+    SUM_MODE = int(mode)
 
 
 def check_status() -> None:

@@ -537,11 +537,9 @@ sum_par_rows(float* __restrict__ param_flows, const float* __restrict__ node_flo
 
 }  // namespace
 
-// tensor-core dispatch (pcx_sum_tc.cu): return 1 when they took the call, with the launch status in *rc
-int pcx_tc_try_sum_fwd(float*, const float*, const float*, const int32_t*, const int32_t*, const int32_t*,
-                       int64_t, int, int, int, cudaStream_t, int*);
-int pcx_tc_try_sum_ele(float*, const float*, const float*, const float*, const float*, const int32_t*, const int32_t*,
-                       const int32_t*, int64_t, int, int, int, int, int, cudaStream_t, int*);
+// tensor-core dispatch (pcx_sum_tc.cu): returns 1 when it took the call, with the launch status in *rc
+int pcx_tc_try_sum_par(float*, const float*, const float*, const float*, const float*, const int32_t*, const int32_t*,
+                       const int32_t*, const int32_t*, int64_t, int, int, int, int, cudaStream_t, int*);
 
 extern "C" {
 
@@ -551,8 +549,6 @@ int pcx_sum_fwd(float* node_mars, const float* element_mars, const float* params
     if (n_blocks <= 0 || B <= 0) return 0;
     if (block_size <= 0 || (block_size & (block_size - 1)) != 0 || K <= 0) return -1;
     cudaStream_t st = (cudaStream_t)stream;
-    int rc = 0;
-    if (pcx_tc_try_sum_fwd(node_mars, element_mars, params, nids, cids, pids, n_blocks, K, block_size, B, st, &rc)) return rc;
     if (block_size >= 8) {
         dim3 grid(1, (unsigned)pcx_cdiv(B, TB));
         if (block_size >= 64) {
@@ -586,9 +582,6 @@ int pcx_sum_bwd_ele(float* element_flows, const float* element_mars, const float
     if (block_size <= 0 || (block_size & (block_size - 1)) != 0) return -1;
     if (ch_block_size <= 0 || (ch_block_size & (ch_block_size - 1)) != 0 || P <= 0) return -1;
     cudaStream_t st = (cudaStream_t)stream;
-    int rc = 0;
-    if (pcx_tc_try_sum_ele(element_flows, element_mars, node_flows, node_mars, params, chids, parids, parpids,
-                           n_blocks, P, block_size, ch_block_size, B, logspace, st, &rc)) return rc;
 #define PCX_ELE_ARGS element_flows, element_mars, node_flows, node_mars, params, chids, parids, parpids, P, block_size
     if (ch_block_size >= 8) {
         dim3 grid(1, (unsigned)pcx_cdiv(B, TB));
@@ -623,6 +616,9 @@ int pcx_sum_bwd_par(float* param_flows, const float* node_flows, const float* no
     if (n_blocks <= 0 || B <= 0) return 0;
     if (block_size <= 0 || (block_size & (block_size - 1)) != 0 || K <= 0) return -1;
     cudaStream_t st = (cudaStream_t)stream;
+    int rc = 0;
+    if (pcx_tc_try_sum_par(param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids,
+                           n_blocks, K, block_size, B, logspace, st, &rc)) return rc;
 #define PCX_PAR_ARGS param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids
     if (block_size >= 8) {
         int64_t tiles_e = pcx_cdiv(K, TB);

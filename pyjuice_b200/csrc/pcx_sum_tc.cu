@@ -1,81 +1,176 @@
-// Sum-layer forward and element-flow kernels on the Blackwell tensor cores (tcgen05.mma + TMEM).
+// Sum-layer kernels on the Blackwell tensor cores (tcgen05.mma, fp32 accumulators in TMEM).
 //
-// Both are log-sum-exp contractions  out[r, b] = log sum_k A[r, k] * exp(L[k, b])  with A >= 0 the sum
-// parameters and L log-domain values.  One CTA owns a 128 (rows) x 128 (batch columns) output tile:
+// Three contractions share one skeleton (a CTA of 256 threads owns a 128-row output tile, stages 64-deep
+// operand slices in shared memory in the K-major core-matrix layout and lets one thread issue the MMAs):
 //
-//   pass 1   thread t < 128 owns batch column t and scans L[:, t] for its maximum mx_t (no cross-thread
-//            reduction: the batch is the contiguous dimension, so the scan is also perfectly coalesced);
-//   pass 2   per 64-deep K chunk, threads 0..127 turn their column into exp(L - mx_t), threads 128..255
-//            fetch one row of A each; both split every fp32 value into bf16 hi + lo and write the four
-//            operand tiles (A_hi, A_lo, B_hi, B_lo) straight into shared memory in the K-major core-matrix
-//            layout tcgen05.mma consumes; one thread then issues A_hi*B_hi + A_hi*B_lo + A_lo*B_hi into the
-//            fp32 TMEM accumulator.  Two smem stages let chunk c+1 be produced while chunk c multiplies;
-//            tcgen05.commit -> mbarrier tells when a stage may be overwritten;
-//   epilogue warps 0..3 read the accumulator back (tcgen05.ld), apply log(.) + mx_t, transpose through
-//            shared memory and store whole 512-byte rows.
+//   forward        node_mars[r, b]   = log sum_k  theta[r, k] * exp(emars[k, b])            tile 128 x 64 (batch)
+//   element flows  eflows[c, b]      = emars[c, b] + log sum_k theta^T[c, k] * exp(nflow[k, b] - nmar[k, b])
+//   parameter flows pflow[m, e]     += theta[m, e] * sum_b exp(nflow[m, b] - nmar[m, b] - s_b) * exp(emars[e, b] + s_b)
+//                                                                                            tile 128 x 64 (edges)
 //
-// The three-term bf16 split keeps ~16 significant bits per factor (relative product error ~2^-16) with fp32
-// accumulation; `PCX_SUM_BF16X1` drops to a single bf16 product.  Every mbarrier wait is bounded: on expiry
-// the kernel records a status code, stops issuing work, frees its TMEM and returns.
+// Operands produced on CUDA cores (the exponentials) are split into bf16 hi + lo and multiplied as
+// hi*hi + hi*lo + lo*hi, which keeps ~16 significant bits per factor.  The parameter operand of the first two
+// kernels is static between EM updates, so it is pre-split once per update into ready-made 32 KB tile images
+// (pcx_pack_sum_params) that the kernels copy into shared memory with cp.async while the exponentials are
+// being computed.
+//
+// Latency, not throughput, bounds these kernels on deep circuits (hundreds of small dependent layers): every
+// thread therefore issues all global loads of a slice before touching any of them, the batch column of the
+// log-sum-exp kernels is shared by four threads (one 8-row group each per half-slice) so that the column
+// maximum needs a single shared-memory exchange, and tables up to 128 deep keep their values in registers
+// between the maximum pass and the exponential pass.
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a status code, skips its remaining tensor-core
+// work, frees its TMEM and returns.
 #include "pcx_common.cuh"
 #include "pcx_tc.cuh"
 #include "../../include/pcx_b200.h"
+#include <float.h>
 
 namespace {
 
 using namespace pcx_tc;
 
-constexpr int BM = 128;          // rows per tile   (UMMA M)
-constexpr int BN = 128;          // batch columns per tile (UMMA N)
-constexpr int KC = 64;           // contraction depth per smem stage
-constexpr int KG = KC / 8;       // 16-byte K groups per stage
+constexpr int BM = 128;                  // rows per tile (UMMA M)
+constexpr int BN = 64;                   // columns per tile (UMMA N)
+constexpr int KC = 64;                   // contraction depth per shared-memory stage
+constexpr int KG = KC / 8;               // 16-byte K groups per stage
 constexpr int STAGES = 2;
 constexpr int NTH = 256;
-constexpr int TILE_BYTES = KG * BM * 16;                 // one operand tile (BM == BN): 8 KB... x2 below
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;              // A_hi, A_lo, B_hi, B_lo
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
-static_assert(BM == BN, "operand tiles share one size");
+constexpr int A_TILE = KG * BM * 16;     // 16 KB: one bf16 [128 x 64] operand tile
+constexpr int B_TILE = KG * BN * 16;     //  8 KB: one bf16 [ 64 x 64] operand tile
+constexpr int STAGE_BYTES = 2 * A_TILE + 2 * B_TILE;          // A_hi, A_lo, B_hi, B_lo = 48 KB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+// parameter-flow kernel: slabs padded by 16 B so that the 8 lanes that stage one row write 8 different banks
+constexpr int XSLAB = BM * 16 + 16, YSLAB = BN * 16 + 16;
+constexpr int X_TILE = KG * XSLAB, Y_TILE = KG * YSLAB;
+constexpr int PAR_STAGE_BYTES = 2 * X_TILE + 2 * Y_TILE;
+constexpr int PAR_SMEM_BYTES = STAGES * PAR_STAGE_BYTES + 1024;
 static_assert(STAGES * STAGE_BYTES >= BM * (BN + 1) * 4, "epilogue transpose buffer aliases the stages");
 
-__device__ int g_tc_status = 0;      // 0 ok; otherwise the code of the first bounded wait that gave up
+__device__ int g_tc_status = 0;          // 0 ok; otherwise the code of the first bounded wait that gave up
 
+__device__ __forceinline__ uint32_t pack2(uint16_t a, uint16_t b) { return (uint32_t)a | ((uint32_t)b << 16); }
+
+__device__ __forceinline__ void store_split8(uint4* hi, uint4* lo, const float* x) {
+    uint16_t h[8], l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) split_bf16(x[j], h[j], l[j]);
+    *hi = make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
+    *lo = make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// Issue the MMAs of one 64-deep stage: A tiles at `sa` (hi, then lo), B tiles at `sb` (hi, then lo).  A tile is
+// KG slabs of [rows][16 B]; consecutive slabs are ASLAB / BSLAB bytes apart (rows * 16, or that plus padding).
+template <int ASLAB = BM * 16, int BSLAB = BN * 16>
+__device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t sa, uint32_t sb, uint32_t idesc, bool first, int terms) {
+#pragma unroll
+    for (int ks = 0; ks < KC / 16; ++ks) {
+        const uint64_t dAh = smem_desc(sa + ks * 2 * ASLAB, ASLAB, 128);
+        const uint64_t dAl = smem_desc(sa + KG * ASLAB + ks * 2 * ASLAB, ASLAB, 128);
+        const uint64_t dBh = smem_desc(sb + ks * 2 * BSLAB, BSLAB, 128);
+        const uint64_t dBl = smem_desc(sb + KG * BSLAB + ks * 2 * BSLAB, BSLAB, 128);
+        mma_bf16_ss(tmem, dAh, dBh, idesc, (!first || ks > 0) ? 1u : 0u);
+        if (terms == 3) {
+            mma_bf16_ss(tmem, dAh, dBl, idesc, 1u);
+            mma_bf16_ss(tmem, dAl, dBh, idesc, 1u);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Parameter pre-split: ready-made A tiles for the forward (MODE 0) and element-flow (MODE 1) kernels
+// ---------------------------------------------------------------------------------------------------------
+struct PackArgs {
+    uint4* out;                 // [n_rows * tiles_r * n_chunks] tile images of 2 * A_TILE bytes (hi, then lo)
+    const float* params;
+    const int32_t* kids;        // FWD: cids (only to know padding)   ELE: parids
+    const int32_t* kpar;        // FWD: pids                          ELE: parpids
+    int K;                      // table width
+    int row_block;              // rows per table row (multiple of 128)
+    int par_block;              // ELE: parent block size (>= 8)
+    int n_chunks;
+    int64_t n_vec;              // total 16-byte (hi) vectors = n_rows * tiles_r * n_chunks * KG * BM
+};
+
+template <int MODE>
+__global__ void pack_params_kernel(const PackArgs a) {
+    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= a.n_vec) return;
+    const int r = (int)(t % BM);
+    const int g = (int)((t / BM) % KG);
+    int64_t tile = t / (BM * KG);
+    const int chunk = (int)(tile % a.n_chunks);
+    const int64_t rowtile = tile / a.n_chunks;
+    const int tiles_r = a.row_block / BM;
+    const int64_t i = rowtile / tiles_r;
+    const int r0 = (int)(rowtile % tiles_r) * BM;
+    const int kb = chunk * KC + g * 8;
+    float v[8];
+    if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int k = kb + j;
+            v[j] = (k < a.K) ? a.params[(int64_t)a.kpar[i * a.K + k] + r0 + r] : 0.0f;
+        }
+    } else {
+        const int KK = a.K * a.par_block;
+        const int lg = 31 - __clz(a.par_block);
+        int p = kb >> lg, n = kb & (a.par_block - 1);
+        int pr = (kb < KK) ? a.kids[i * a.K + p] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] = (pr != 0) ? a.params[(int64_t)a.kpar[i * a.K + p] + (int64_t)(r0 + r) * a.par_block + n + j] : 0.0f;
+    }
+    uint4* base = a.out + tile * (2 * A_TILE / 16);
+    store_split8(base + g * BM + r, base + A_TILE / 16 + g * BM + r, v);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Forward / element flows
+// ---------------------------------------------------------------------------------------------------------
 enum Mode { FWD = 0, ELE = 1 };
 
-struct Args {
+struct LseArgs {
     float* out;                 // FWD: node_mars            ELE: element_flows
     const float* lsrc;          // FWD: element_mars         ELE: node_flows
     const float* lsrc2;         //                           ELE: node_mars
     const float* emars;         //                           ELE: element_mars (epilogue)
-    const float* params;
+    const uint4* packed;        // pre-split parameter tiles
     const int32_t* rows;        // FWD: nids                 ELE: chids
     const int32_t* kids;        // FWD: cids [n, K]          ELE: parids [n, P]
-    const int32_t* kpar;        // FWD: pids [n, K]          ELE: parpids [n, P]
-    int K;                      // FWD: table width          ELE: P
-    int row_block;              // FWD: block_size           ELE: ch_block_size   (rows per table row, multiple of 128)
-    int par_block;              //                           ELE: block_size of the parents
+    int K;
+    int row_block;
+    int par_block;
     int B;
     int logspace;
-    int terms;                  // 3 = hi*hi + hi*lo + lo*hi, 1 = hi*hi only
+    int terms;
 };
 
-__device__ __forceinline__ uint32_t pack2(uint16_t a, uint16_t b) { return (uint32_t)a | ((uint32_t)b << 16); }
-
-template <int MODE>
-__global__ void __launch_bounds__(NTH, 1) sum_lse_tc_kernel(const Args a) {
+template <int MODE, bool SMALLK>
+__global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t s_bar[STAGES];
     __shared__ uint32_t s_tmem;
+    __shared__ float s_part[4][BN];
     __shared__ float s_max[BN];
     __shared__ int s_fail;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_r = a.row_block / BM;
-    const int64_t i = blockIdx.x / tiles_r;
-    const int r0 = (int)(blockIdx.x % tiles_r) * BM;
+    const int64_t rowtile = blockIdx.x;
+    const int64_t i = rowtile / tiles_r;
+    const int r0 = (int)(rowtile % tiles_r) * BM;
     const int b0 = blockIdx.y * BN;
     const int B = a.B;
-    // contraction length in elements
     const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
     const int lg_pb = (MODE == ELE) ? (31 - __clz(a.par_block)) : 0;
     const int n_chunks = (KK + KC - 1) / KC;
@@ -91,131 +186,141 @@ __global__ void __launch_bounds__(NTH, 1) sum_lse_tc_kernel(const Args a) {
     tc_fence_after_sync();
     const uint32_t tmem = s_tmem;
 
-    // value L[k, col] of this thread's batch column (threads 0..127)
-    const int col = b0 + tid;
-    const bool col_ok = (tid < BN) && (col < B);
-    auto load_l = [&](int k) -> float {
-        if (k >= KK) return PCX_NEG_INF;
-        if (MODE == FWD) {
-            int cid = a.kids[i * a.K + k];
-            return cid != 0 ? a.lsrc[(int64_t)cid * B + col] : PCX_NEG_INF;
-        } else {
-            int p = k >> lg_pb, n = k & (a.par_block - 1);
-            int pr = a.kids[i * a.K + p];
-            if (pr == 0) return PCX_NEG_INF;
-            float nf = a.lsrc[(int64_t)(pr + n) * B + col];
-            float nm = a.lsrc2[(int64_t)(pr + n) * B + col];
-            if (!a.logspace) nf = (nf > 0.0f) ? logf(nf) : PCX_NEG_INF;
-            return (nm == PCX_NEG_INF || nf == PCX_NEG_INF) ? PCX_NEG_INF : nf - nm;
+    // this thread's share of L: batch column `lc`, K groups q and q + 4 of every 64-deep slice
+    const int lc = tid & (BN - 1), q = tid >> 6;
+    const int col = b0 + lc;
+    const bool col_ok = col < B;
+
+    // raw (log-domain) values of one 8-row group
+    auto load_group = [&](int kb, float* v) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = kb + j;
+            float x = PCX_NEG_INF;
+            if (col_ok && k < KK) {
+                if (MODE == FWD) {
+                    const int cid = a.kids[i * a.K + k];
+                    if (cid != 0) x = a.lsrc[(int64_t)cid * B + col];
+                } else {
+                    const int pr = a.kids[i * a.K + (k >> lg_pb)];
+                    if (pr != 0) {
+                        const int64_t row = (int64_t)pr + (k & (a.par_block - 1));
+                        float nf = a.lsrc[row * B + col];
+                        const float nm = a.lsrc2[row * B + col];
+                        if (!a.logspace) nf = (nf > 0.0f) ? logf(nf) : PCX_NEG_INF;
+                        x = (nm == PCX_NEG_INF || nf == PCX_NEG_INF) ? PCX_NEG_INF : nf - nm;
+                    }
+                }
+            }
+            v[j] = x;
         }
     };
+    auto copy_a = [&](int chunk, uint8_t* st) {
+        const uint4* src = a.packed + (rowtile * n_chunks + chunk) * (2 * A_TILE / 16);
+#pragma unroll
+        for (int w = 0; w < 2 * A_TILE / 16 / NTH; ++w) cp_async16(st + (w * NTH + tid) * 16, src + w * NTH + tid);
+    };
 
-    // ---- pass 1: column maxima ----------------------------------------------------------------------
+    // ---- pass 1: column maxima (values kept in registers when the table is at most two slices deep) ----
+    float keep[SMALLK ? 2 : 1][2][8];
     float mx = PCX_NEG_INF;
-    if (col_ok) {
-#pragma unroll 4
-        for (int k = 0; k < KK; ++k) mx = fmaxf(mx, load_l(k));
+    if (SMALLK) {
+        for (int c = 0; c < n_chunks; ++c) copy_a(c, smem + c * STAGE_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (c < n_chunks) load_group(c * KC + (q + 4 * h) * 8, keep[c][h]);
+                else
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) keep[c][h][j] = PCX_NEG_INF;
+            }
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[c][h][j]);
+    } else {
+        for (int c = 0; c < n_chunks; ++c) {
+            float v[2][8];
+            load_group(c * KC + q * 8, v[0]);
+            load_group(c * KC + (q + 4) * 8, v[1]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(v[0][j], v[1][j]));
+        }
     }
-    if (tid < BN) s_max[tid] = mx;
+    s_part[q][lc] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_part[0][lc], s_part[1][lc]), fmaxf(s_part[2][lc], s_part[3][lc]));
+    if (q == 0) s_max[lc] = mx;
 
-    // ---- pass 2: produce operand tiles, multiply -------------------------------------------------------
+    // ---- pass 2: exponentials -> bf16 hi/lo operand tiles, multiply -----------------------------------------
     const uint32_t idesc = idesc_bf16_f32(BM, BN);
     bool failed = false;
-    for (int c = 0; c < n_chunks; ++c) {
-        const int s = c % STAGES, use = c / STAGES;
-        uint8_t* st = smem + s * STAGE_BYTES;
-        if (c >= STAGES && !failed) {
-            if (!mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
-        }
-        const int k0 = c * KC;
-        if (tid < BN) {
-            // B operand: exp(L - mx) of this thread's column, 8 consecutive k per 16-byte store
-            uint4* bhi = reinterpret_cast<uint4*>(st + 2 * TILE_BYTES);
-            uint4* blo = reinterpret_cast<uint4*>(st + 3 * TILE_BYTES);
-#pragma unroll 2
-            for (int g = 0; g < KG; ++g) {
-                float v[8];
+    if (SMALLK) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = col_ok ? load_l(k0 + g * 8 + j) : PCX_NEG_INF;
-                uint16_t h[8], l[8];
+        for (int c = 0; c < 2; ++c) {
+            if (c < n_chunks) {
+                uint8_t* st = smem + c * STAGE_BYTES;
+                uint4* bhi = reinterpret_cast<uint4*>(st + 2 * A_TILE);
+                uint4* blo = reinterpret_cast<uint4*>(st + 2 * A_TILE + B_TILE);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float x = (v[j] == PCX_NEG_INF) ? 0.0f : expf(v[j] - mx);
-                    split_bf16(x, h[j], l[j]);
+                for (int h = 0; h < 2; ++h) {
+                    const int g = q + 4 * h;
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = (keep[c][h][j] == PCX_NEG_INF) ? 0.0f : expf(keep[c][h][j] - mx);
+                    store_split8(bhi + g * BN + lc, blo + g * BN + lc, v);
                 }
-                bhi[g * BN + tid] = make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
-                blo[g * BN + tid] = make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
-            }
-        } else {
-            // A operand: one row of parameters per thread
-            const int r = tid - BN;
-            uint4* ahi = reinterpret_cast<uint4*>(st);
-            uint4* alo = reinterpret_cast<uint4*>(st + TILE_BYTES);
-#pragma unroll 2
-            for (int g = 0; g < KG; ++g) {
-                float v[8];
-                const int kb = k0 + g * 8;
-                if (MODE == FWD) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        int k = kb + j;
-                        v[j] = (k < KK) ? a.params[(int64_t)a.kpar[i * a.K + k] + r0 + r] : 0.0f;
-                    }
-                } else {
-                    // 8 consecutive parent nodes of one parent block: contiguous in memory (block sizes >= 8)
-                    int p = kb >> lg_pb, n = kb & (a.par_block - 1);
-                    int pr = (kb < KK) ? a.kids[i * a.K + p] : 0;
-                    if (pr != 0) {
-                        const float* sp = a.params + (int64_t)a.kpar[i * a.K + p] + (int64_t)(r0 + r) * a.par_block + n;
-                        if ((reinterpret_cast<uintptr_t>(sp) & 15) == 0) {
-                            const float4* src = reinterpret_cast<const float4*>(sp);
-                            float4 q0 = src[0], q1 = src[1];
-                            v[0] = q0.x; v[1] = q0.y; v[2] = q0.z; v[3] = q0.w;
-                            v[4] = q1.x; v[5] = q1.y; v[6] = q1.z; v[7] = q1.w;
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) v[j] = sp[j];
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-                    }
-                }
-                uint16_t h[8], l[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) split_bf16(v[j], h[j], l[j]);
-                ahi[g * BM + r] = make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
-                alo[g * BM + r] = make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
             }
         }
+        cp_async_wait_all();
         fence_async_smem();
         __syncthreads();
-        failed = failed || (s_fail != 0);
-        if (tid == 0 && !failed) {
+        if (tid == 0) {
             tc_fence_after_sync();
-            const uint32_t sa = smem_u32(st);
-#pragma unroll
-            for (int ks = 0; ks < KC / 16; ++ks) {
-                const uint32_t off = (uint32_t)ks * 2 * BM * 16;       // two K groups per MMA
-                const uint64_t dAh = smem_desc(sa + off, BM * 16, 128);
-                const uint64_t dAl = smem_desc(sa + TILE_BYTES + off, BM * 16, 128);
-                const uint64_t dBh = smem_desc(sa + 2 * TILE_BYTES + off, BN * 16, 128);
-                const uint64_t dBl = smem_desc(sa + 3 * TILE_BYTES + off, BN * 16, 128);
-                mma_bf16_ss(tmem, dAh, dBh, idesc, (c > 0 || ks > 0) ? 1u : 0u);
-                if (a.terms == 3) {
-                    mma_bf16_ss(tmem, dAh, dBl, idesc, 1u);
-                    mma_bf16_ss(tmem, dAl, dBh, idesc, 1u);
-                }
+            for (int c = 0; c < n_chunks; ++c) {
+                const uint32_t sa = smem_u32(smem + c * STAGE_BYTES);
+                issue_stage(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
             }
-            mma_commit(&s_bar[s]);
+            mma_commit(&s_bar[0]);
+        }
+    } else {
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % STAGES, use = c / STAGES;
+            uint8_t* st = smem + s * STAGE_BYTES;
+            if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
+            copy_a(c, st);
+            uint4* bhi = reinterpret_cast<uint4*>(st + 2 * A_TILE);
+            uint4* blo = reinterpret_cast<uint4*>(st + 2 * A_TILE + B_TILE);
+            float v[2][8];
+            load_group(c * KC + q * 8, v[0]);
+            load_group(c * KC + (q + 4) * 8, v[1]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int g = q + 4 * h;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[h][j] = (v[h][j] == PCX_NEG_INF) ? 0.0f : expf(v[h][j] - mx);
+                store_split8(bhi + g * BN + lc, blo + g * BN + lc, v[h]);
+            }
+            cp_async_wait_all();
+            fence_async_smem();
+            __syncthreads();
+            failed = failed || (s_fail != 0);
+            if (tid == 0 && !failed) {
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(st);
+                issue_stage(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
+                mma_commit(&s_bar[s]);
+            }
         }
     }
 
-    // ---- epilogue --------------------------------------------------------------------------------------
+    // ---- epilogue ------------------------------------------------------------------------------------------
     {
-        const int cl = n_chunks - 1;
+        const int cl = SMALLK ? 0 : n_chunks - 1;       // the last commit covers every MMA issued before it
         if (!failed && !mbar_wait(&s_bar[cl % STAGES], (uint32_t)((cl / STAGES) & 1))) { failed = true; s_fail = 2; }
-        // every earlier chunk's multiply has completed too: a commit covers all tcgen05 work issued before it
     }
     __syncthreads();
     failed = failed || (s_fail != 0);
@@ -229,7 +334,7 @@ __global__ void __launch_bounds__(NTH, 1) sum_lse_tc_kernel(const Args a) {
             tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cg * 32), v);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                float m = s_max[cg * 32 + j];
+                const float m = s_max[cg * 32 + j];
                 float o;
                 if (MODE == FWD) o = (m == PCX_NEG_INF) ? PCX_NEG_INF : logf(fmaxf(v[j], 1e-24f)) + m;
                 else o = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : logf(v[j]) + m;
@@ -244,11 +349,11 @@ __global__ void __launch_bounds__(NTH, 1) sum_lse_tc_kernel(const Args a) {
         for (int r = warp; r < BM; r += NTH / 32) {
 #pragma unroll
             for (int cc = lane; cc < BN; cc += 32) {
-                int b = b0 + cc;
+                const int b = b0 + cc;
                 if (b >= B) continue;
                 float o = T[r * (BN + 1) + cc];
                 if (MODE == ELE) {
-                    float em = a.emars[(base_row + r) * B + b];
+                    const float em = a.emars[(base_row + r) * B + b];
                     o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
                     if (!a.logspace) o = expf(o);
                 }
@@ -262,46 +367,255 @@ __global__ void __launch_bounds__(NTH, 1) sum_lse_tc_kernel(const Args a) {
     if (warp == 0) tmem_dealloc(tmem, BN);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Parameter flows
+// ---------------------------------------------------------------------------------------------------------
+struct ParArgs {
+    float* param_flows;
+    const float* node_flows;
+    const float* node_mars;
+    const float* element_mars;
+    const float* params;
+    const int32_t* nids;
+    const int32_t* cids;
+    const int32_t* pids;
+    const int32_t* pfids;
+    int K;
+    int block_size;
+    int B;
+    int logspace;
+    int terms;
+    int chunks_per_cta;         // 64-sample slices handled by one CTA (the batch is split across blockIdx.z)
+};
+
+__global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t s_bar[STAGES];
+    __shared__ uint32_t s_tmem;
+    __shared__ float s_part[NTH / 32][KC];
+    __shared__ int s_cid[BN], s_pid[BN], s_pfid[BN];
+    __shared__ int s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_r = a.block_size / BM;
+    const int64_t rowtile = blockIdx.x;
+    const int64_t i = rowtile / tiles_r;
+    const int r0 = (int)(rowtile % tiles_r) * BM;
+    const int e0 = blockIdx.y * BN;
+    const int B = a.B;
+    const int total_chunks = (B + KC - 1) / KC;
+    const int c_begin = blockIdx.z * a.chunks_per_cta;
+    const int c_end = min(total_chunks, c_begin + a.chunks_per_cta);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[s], 1);
+        fence_mbar_init();
+        s_fail = 0;
+    }
+    if (tid < BN) {
+        const int e = e0 + tid;
+        const bool ok = e < a.K;
+        s_cid[tid] = ok ? a.cids[i * a.K + e] : 0;
+        s_pid[tid] = ok ? a.pids[i * a.K + e] : 0;
+        s_pfid[tid] = ok ? a.pfids[i * a.K + e] : 0;
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, BN);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    const int64_t nid = (int64_t)a.nids[i] + r0;
+
+    // staging role: 8-sample group g of the slice, rows rb + 32 j
+    const int g = tid & 7, rb = tid >> 3;
+    const uint32_t idesc = idesc_bf16_f32(BM, BN);
+    bool failed = false;
+
+    for (int c = c_begin; c < c_end; ++c) {
+        const int it = c - c_begin, s = it % STAGES, use = it / STAGES;
+        uint8_t* st = smem + s * PAR_STAGE_BYTES;
+        const int bb = c * KC + g * 8;                 // first sample of this thread's group
+        const bool b_ok = bb < B;                      // B is a multiple of 8: a group is all-in or all-out
+
+        // issue every load of the slice first
+        float x[4][8], y[2][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t off = (nid + rb + 32 * j) * B + bb;
+            if (b_ok) {
+                const float4 f0 = *reinterpret_cast<const float4*>(a.node_flows + off);
+                const float4 f1 = *reinterpret_cast<const float4*>(a.node_flows + off + 4);
+                const float4 m0 = *reinterpret_cast<const float4*>(a.node_mars + off);
+                const float4 m1 = *reinterpret_cast<const float4*>(a.node_mars + off + 4);
+                const float nf[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                const float nm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    float f = nf[t];
+                    if (!a.logspace) f = (f > 0.0f) ? logf(f) : PCX_NEG_INF;
+                    x[j][t] = (nm[t] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[t];
+                }
+            } else {
+#pragma unroll
+                for (int t = 0; t < 8; ++t) x[j][t] = PCX_NEG_INF;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int cid = s_cid[rb + 32 * j];
+            if (b_ok && cid != 0) {
+                const float4 q0 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid * B + bb);
+                const float4 q1 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid * B + bb + 4);
+                y[j][0] = q0.x; y[j][1] = q0.y; y[j][2] = q0.z; y[j][3] = q0.w;
+                y[j][4] = q1.x; y[j][5] = q1.y; y[j][6] = q1.z; y[j][7] = q1.w;
+            } else {
+#pragma unroll
+                for (int t = 0; t < 8; ++t) y[j][t] = PCX_NEG_INF;
+            }
+        }
+        // per-sample shift = max over the 128 rows of the tile of log(flow / value)
+        float pm[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            float m = fmaxf(fmaxf(x[0][t], x[1][t]), fmaxf(x[2][t], x[3][t]));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+            pm[t] = m;
+        }
+        if (lane < 8) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) s_part[warp][lane * 8 + t] = pm[t];
+        }
+        if (it >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
+        __syncthreads();
+        float sh[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            float m = s_part[0][g * 8 + t];
+#pragma unroll
+            for (int w = 1; w < NTH / 32; ++w) m = fmaxf(m, s_part[w][g * 8 + t]);
+            sh[t] = m;
+        }
+        uint8_t* xhi = st;
+        uint8_t* xlo = st + X_TILE;
+        uint8_t* yhi = st + 2 * X_TILE;
+        uint8_t* ylo = st + 2 * X_TILE + Y_TILE;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                x[j][t] = (sh[t] == PCX_NEG_INF || x[j][t] == PCX_NEG_INF) ? 0.0f : expf(x[j][t] - sh[t]);
+            const int o = g * XSLAB + (rb + 32 * j) * 16;
+            store_split8(reinterpret_cast<uint4*>(xhi + o), reinterpret_cast<uint4*>(xlo + o), x[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                y[j][t] = (sh[t] == PCX_NEG_INF || y[j][t] == PCX_NEG_INF) ? 0.0f : fminf(expf(y[j][t] + sh[t]), 3.0e38f);
+            const int o = g * YSLAB + (rb + 32 * j) * 16;
+            store_split8(reinterpret_cast<uint4*>(yhi + o), reinterpret_cast<uint4*>(ylo + o), y[j]);
+        }
+        fence_async_smem();
+        __syncthreads();
+        failed = failed || (s_fail != 0);
+        if (tid == 0 && !failed) {
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(st);
+            issue_stage<XSLAB, YSLAB>(tmem, sa, sa + 2 * X_TILE, idesc, it == 0, a.terms);
+            mma_commit(&s_bar[s]);
+        }
+    }
+
+    const int n_it = c_end - c_begin;
+    if (n_it > 0) {
+        const int il = n_it - 1;
+        if (!failed && !mbar_wait(&s_bar[il % STAGES], (uint32_t)((il / STAGES) & 1))) { failed = true; s_fail = 2; }
+    }
+    __syncthreads();
+    failed = failed || (s_fail != 0);
+    tc_fence_after_sync();
+    if (warp < 4 && !failed && n_it > 0) {
+        const int row = warp * 32 + lane;
+#pragma unroll 1
+        for (int cg = 0; cg < BN / 32; ++cg) {
+            float v[32];
+            tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cg * 32), v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int e = cg * 32 + j;
+                if (s_cid[e] == 0) continue;
+                const float pf = a.params[(int64_t)s_pid[e] + r0 + row] * v[j];
+                if (pf != 0.0f) atomicAdd(a.param_flows + (int64_t)s_pfid[e] + r0 + row, pf);
+            }
+        }
+    }
+    if (failed && tid == 0) atomicCAS(&g_tc_status, 0, 300 + s_fail);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, BN);
+}
+
 int g_sum_mode = 1;      // 0: fp32 CUDA cores only, 1: tensor cores with bf16 hi/lo split, 2: tensor cores, single bf16
 
-template <int MODE>
-int launch_tc(const Args& a, int64_t n_blocks, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(sum_lse_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+template <typename Kern>
+int configure_once(Kern kern, bool* done) {
+    if (!*done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        *done = true;
     }
-    dim3 grid((unsigned)(n_blocks * (a.row_block / BM)), (unsigned)pcx_cdiv(a.B, BN));
-    sum_lse_tc_kernel<MODE><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    return 0;
+}
+
+template <int MODE>
+int launch_lse(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
+    static bool done_small = false, done_big = false;
+    const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
+    dim3 grid((unsigned)(n_rows * (a.row_block / BM)), (unsigned)pcx_cdiv(a.B, BN));
+    if (KK <= 2 * KC) {
+        int rc = configure_once(sum_lse_tc_kernel<MODE, true>, &done_small);
+        if (rc) return rc;
+        sum_lse_tc_kernel<MODE, true><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    } else {
+        int rc = configure_once(sum_lse_tc_kernel<MODE, false>, &done_big);
+        if (rc) return rc;
+        sum_lse_tc_kernel<MODE, false><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    }
     PCX_LAUNCH_CHECK();
     return 0;
 }
 
 }  // namespace
 
-// Internal entry points used by pcx_sum_simt.cu's dispatchers; return 1 if the tensor-core path took the call.
-int pcx_tc_try_sum_fwd(float* node_mars, const float* element_mars, const float* params, const int32_t* nids,
-                       const int32_t* cids, const int32_t* pids, int64_t n_blocks, int K, int block_size, int B,
-                       cudaStream_t st, int* rc) {
-    if (g_sum_mode == 0 || block_size % BM != 0) return 0;
-    Args a{};
-    a.out = node_mars; a.lsrc = element_mars; a.params = params; a.rows = nids; a.kids = cids; a.kpar = pids;
-    a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1; a.terms = (g_sum_mode == 2) ? 1 : 3;
-    *rc = launch_tc<FWD>(a, n_blocks, st);
-    return 1;
-}
+// Used by the dispatchers in pcx_sum_simt.cu.
+int pcx_tc_sum_mode() { return g_sum_mode; }
 
-int pcx_tc_try_sum_ele(float* element_flows, const float* element_mars, const float* node_flows, const float* node_mars,
-                       const float* params, const int32_t* chids, const int32_t* parids, const int32_t* parpids,
-                       int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
+int pcx_tc_try_sum_par(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                       const float* params, const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                       const int32_t* pfids, int64_t n_blocks, int K, int block_size, int B, int logspace,
                        cudaStream_t st, int* rc) {
-    if (g_sum_mode == 0 || ch_block_size % BM != 0 || block_size % 8 != 0) return 0;
-    Args a{};
-    a.out = element_flows; a.lsrc = node_flows; a.lsrc2 = node_mars; a.emars = element_mars; a.params = params;
-    a.rows = chids; a.kids = parids; a.kpar = parpids; a.K = P; a.row_block = ch_block_size; a.par_block = block_size;
-    a.B = B; a.logspace = logspace; a.terms = (g_sum_mode == 2) ? 1 : 3;
-    *rc = launch_tc<ELE>(a, n_blocks, st);
+    if (g_sum_mode == 0 || block_size % BM != 0 || B % 8 != 0) return 0;
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(sum_par_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM_BYTES);
+        if (e != cudaSuccess) { *rc = (int)e; return 1; }
+        done = true;
+    }
+    ParArgs a{param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids,
+              K, block_size, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1};
+    const int64_t base = n_blocks * (block_size / BM) * pcx_cdiv(K, BN);
+    const int total_chunks = (int)pcx_cdiv(B, KC);
+    int64_t splits = pcx_cdiv(2 * 148, base);                  // aim at two CTAs per SM
+    if (splits > total_chunks) splits = total_chunks;
+    if (splits < 1) splits = 1;
+    a.chunks_per_cta = (int)pcx_cdiv(total_chunks, splits);
+    dim3 grid((unsigned)(n_blocks * (block_size / BM)), (unsigned)pcx_cdiv(K, BN),
+              (unsigned)pcx_cdiv(total_chunks, a.chunks_per_cta));
+    sum_par_tc_kernel<<<grid, NTH, PAR_SMEM_BYTES, st>>>(a);
+    cudaError_t e = cudaGetLastError();
+    *rc = (e == cudaSuccess) ? 0 : (int)e;
     return 1;
 }
 
@@ -317,6 +631,55 @@ int pcx_get_status(void) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
     return e == cudaSuccess ? v : -(int)e;
+}
+
+int64_t pcx_packed_tile_count(int64_t n_rows, int K, int row_block, int par_block, int mode) {
+    if (row_block % BM != 0) return 0;
+    const int64_t KK = (mode == 0) ? K : (int64_t)K * par_block;
+    return n_rows * (row_block / BM) * pcx_cdiv(KK, KC);
+}
+
+int pcx_pack_sum_params(void* packed, const float* params, const int32_t* kids, const int32_t* kpar,
+                        int64_t n_rows, int K, int row_block, int par_block, int mode, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (row_block % BM != 0 || (mode != 0 && mode != 1) || (mode == 1 && par_block % 8 != 0)) return -1;
+    PackArgs a{};
+    a.out = reinterpret_cast<uint4*>(packed); a.params = params; a.kids = kids; a.kpar = kpar;
+    a.K = K; a.row_block = row_block; a.par_block = (mode == 1) ? par_block : 1;
+    const int64_t KK = (mode == 0) ? K : (int64_t)K * par_block;
+    a.n_chunks = (int)pcx_cdiv(KK, KC);
+    a.n_vec = n_rows * (row_block / BM) * a.n_chunks * KG * BM;
+    const unsigned grid = (unsigned)pcx_cdiv(a.n_vec, 256);
+    if (mode == 0) pack_params_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    else pack_params_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_sum_fwd_packed(float* node_mars, const float* element_mars, const void* packed,
+                       const int32_t* nids, const int32_t* cids, int64_t n_blocks, int K, int block_size, int B,
+                       void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size % BM != 0 || K <= 0) return -1;
+    LseArgs a{};
+    a.out = node_mars; a.lsrc = element_mars; a.packed = reinterpret_cast<const uint4*>(packed);
+    a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
+    a.terms = (g_sum_mode == 2) ? 1 : 3;
+    return launch_lse<FWD>(a, n_blocks, (cudaStream_t)stream);
+}
+
+int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, const float* node_flows,
+                           const float* node_mars, const void* packed, const int32_t* chids, const int32_t* parids,
+                           int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
+                           void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (ch_block_size % BM != 0 || block_size % 8 != 0 || P <= 0) return -1;
+    LseArgs a{};
+    a.out = element_flows; a.lsrc = node_flows; a.lsrc2 = node_mars; a.emars = element_mars;
+    a.packed = reinterpret_cast<const uint4*>(packed); a.rows = chids; a.kids = parids; a.K = P;
+    a.row_block = ch_block_size; a.par_block = block_size; a.B = B; a.logspace = logspace;
+    a.terms = (g_sum_mode == 2) ? 1 : 3;
+    return launch_lse<ELE>(a, n_blocks, (cudaStream_t)stream);
 }
 
 }  // extern "C"

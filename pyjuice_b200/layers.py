@@ -36,6 +36,46 @@ def _unsupported(**flags):
         raise NotImplementedError(f"option(s) {bad} are outside the compiled LL forward/backward/EM path")
 
 
+class ParamPacker:
+    """Keeps the pre-split (bf16 hi/lo) parameter tiles of the tensor-core sum kernels in step with ``params``.
+
+    Sum layers register the tables they need tiles for; layers whose tables are identical (tied parameters, e.g.
+    the transition layers of a homogeneous HMM) share one buffer.  ``refresh`` re-runs the packing kernels when the
+    parameter tensor was replaced, modified through torch, or updated by an EM step (``invalidate``)."""
+    TILE_BYTES = 32768
+
+    def __init__(self, device):
+        self.device = device
+        self.entries = {}
+        self._stamp = None
+        self._epoch = 0
+
+    def register(self, key, n_rows, K, row_block, par_block, mode, kids, kpar):
+        entry = self.entries.get(key)
+        if entry is None:
+            tiles = int(_lib.load().pcx_packed_tile_count(n_rows, K, row_block, par_block, mode))
+            buf = torch.empty(tiles * self.TILE_BYTES, dtype=torch.uint8, device=self.device)
+            entry = dict(buf=buf, args=(kids, kpar, n_rows, K, row_block, par_block, mode))
+            self.entries[key] = entry
+            self._stamp = None
+        return entry["buf"]
+
+    def invalidate(self):
+        self._epoch += 1
+
+    def refresh(self, params: torch.Tensor):
+        stamp = (params.data_ptr(), params._version, self._epoch)
+        if stamp == self._stamp:
+            return
+        for entry in self.entries.values():
+            _lib.call("pcx_pack_sum_params", entry["buf"], params, *entry["args"])
+        self._stamp = stamp
+
+    @property
+    def nbytes(self):
+        return sum(e["buf"].numel() for e in self.entries.values())
+
+
 class Layer:
     def __init__(self, nodes):
         self.nodes = nodes
@@ -252,18 +292,40 @@ class SumLayer(Layer, nn.Module):
     _TABLES = ("partitioned_nids", "partitioned_cids", "partitioned_pids", "partitioned_pfids",
                "partitioned_chids", "partitioned_parids", "partitioned_parpids")
 
-    def to(self, device):
+    def to(self, device, packer: Optional[ParamPacker] = None):
         device = torch.device(f"cuda:{device}") if isinstance(device, int) else torch.device(device)
+        cpu_tables = {name: [x.cpu() for x in getattr(self, name)] for name in self._TABLES}
         for name in self._TABLES:
             setattr(self, name, [x.to(device) for x in getattr(self, name)])
         self.device = device
         self._dev = None
+        self._packer = None
         if device.type == "cuda":
             c = lambda t: _dev_i32(t, device)
             self._dev = dict(
                 fw=[tuple(map(c, q)) for q in zip(self.partitioned_nids, self.partitioned_cids, self.partitioned_pids, self.partitioned_pfids)],
                 bk=[tuple(map(c, q)) for q in zip(self.partitioned_chids, self.partitioned_parids, self.partitioned_parpids)])
+            self._packed_fw = [None] * self.num_fw_partitions
+            self._packed_bk = [None] * self.num_bk_partitions
+            if packer is not None:
+                self._packer = packer
+                bs = self.block_size
+                if bs % 128 == 0:
+                    for p, (nids, cids, pids, _) in enumerate(self._dev["fw"]):
+                        key = ("fw", bs, tuple(pids.shape), cpu_tables["partitioned_pids"][p].numpy().tobytes())
+                        self._packed_fw[p] = packer.register(key, nids.numel(), cids.size(1), bs, 1, 0, cids, pids)
+                for p, ((chids, parids, parpids), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
+                    if cbs % 128 == 0 and bs % 8 == 0:
+                        key = ("bk", bs, cbs, tuple(parids.shape), cpu_tables["partitioned_parpids"][p].numpy().tobytes(),
+                               (cpu_tables["partitioned_parids"][p] != 0).numpy().tobytes())
+                        self._packed_bk[p] = packer.register(key, chids.numel(), parids.size(1), cbs, bs, 1, parids, parpids)
         return self
+
+    def _use_packed(self, params):
+        if self._packer is None or _lib.SUM_MODE == 0:
+            return False
+        self._packer.refresh(params)
+        return True
 
     def _require_cuda(self):
         if self._dev is None:
@@ -274,9 +336,14 @@ class SumLayer(Layer, nn.Module):
         self._require_cuda()
         _unsupported(propagation_alg=propagation_alg != "LL", pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6)
         B = node_mars.size(1)
-        for nids, cids, pids, _ in self._dev["fw"]:
-            _lib.call("pcx_sum_fwd", node_mars, element_mars, params, nids, cids, pids,
-                      nids.numel(), cids.size(1), self.block_size, B)
+        packed = self._use_packed(params)
+        for p, (nids, cids, pids, _) in enumerate(self._dev["fw"]):
+            if packed and self._packed_fw[p] is not None:
+                _lib.call("pcx_sum_fwd_packed", node_mars, element_mars, self._packed_fw[p], nids, cids,
+                          nids.numel(), cids.size(1), self.block_size, B)
+            else:
+                _lib.call("pcx_sum_fwd", node_mars, element_mars, params, nids, cids, pids,
+                          nids.numel(), cids.size(1), self.block_size, B)
 
     __call__ = forward
 
@@ -291,9 +358,14 @@ class SumLayer(Layer, nn.Module):
                      pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6, temper_eflow=temper_eflow)
         B = node_flows.size(1)
         ls = int(bool(logspace_flows))
-        for (chids, parids, parpids), cbs in zip(self._dev["bk"], self.cs_block_sizes):
-            _lib.call("pcx_sum_bwd_ele", element_flows, element_mars, node_flows, node_mars, params,
-                      chids, parids, parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
+        packed = self._use_packed(params)
+        for p, ((chids, parids, parpids), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
+            if packed and self._packed_bk[p] is not None:
+                _lib.call("pcx_sum_bwd_ele_packed", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p],
+                          chids, parids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
+            else:
+                _lib.call("pcx_sum_bwd_ele", element_flows, element_mars, node_flows, node_mars, params,
+                          chids, parids, parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
         if param_flows is not None:
             for nids, cids, pids, pfids in self._dev["fw"]:
                 _lib.call("pcx_sum_bwd_par", param_flows, node_flows, node_mars, element_mars, params,
@@ -316,9 +388,9 @@ class LayerGroup(nn.Module):
         for i, layer in enumerate(self.layers):
             self.add_module(f"layer_{i}", layer)
 
-    def to(self, device):
+    def to(self, device, **kwargs):
         for layer in self.layers:
-            layer.to(device)
+            layer.to(device, **kwargs)
         return self
 
     def forward(self, *args, **kwargs):

@@ -24,7 +24,7 @@ import torch.nn as nn
 
 from . import _lib
 from .compiler import _IdDict, compile_cum_par_flows, compile_par_update, create_node_layers
-from .layers import InputLayer, LayerGroup, ProdLayer, SumLayer, _fill, _scale, _unsupported
+from .layers import InputLayer, LayerGroup, ParamPacker, ProdLayer, SumLayer, _fill, _scale, _unsupported
 from .nodes import as_bitset
 
 NEG_INF = float("-inf")
@@ -197,8 +197,12 @@ class TensorCircuit(nn.Module):
             _lib.load()                                   # fail here, loudly, if the kernels are not built
         nn.Module.to(self, device)
         self.input_layer_group.to(device)
+        self._packer = ParamPacker(device) if device.type == "cuda" else None
         for group in self.inner_layer_groups:
-            group.to(device)
+            if group.is_sum():
+                group.to(device, packer=self._packer)
+            else:
+                group.to(device)
         self.device = device
         self.parflow_fusing_kwargs = [[a.to(device), b.to(device), c.to(device), G, M]
                                       for a, b, c, G, M in self.parflow_fusing_kwargs]
@@ -290,7 +294,9 @@ class TensorCircuit(nn.Module):
             self._last_data, self._last_inputs = data, origin_inputs
             for layer in self.input_layer_group:
                 layer.forward(data, self.node_mars)
-            self._run_inner(("fw", B, self.params.data_ptr()), self._forward_inner)
+            if _lib.SUM_MODE != 0:
+                self._packer.refresh(self.params.data)       # outside any graph capture
+            self._run_inner(("fw", B, _lib.SUM_MODE, self.params.data_ptr()), self._forward_inner)
             lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
         if torch.is_grad_enabled():
             lls.requires_grad = True
@@ -359,7 +365,9 @@ class TensorCircuit(nn.Module):
 
             if compute_param_flows:
                 self.init_param_flows(flows_memory=flows_memory)
-            key = ("bk", B, bool(compute_param_flows), ls, self.params.data_ptr(),
+            if _lib.SUM_MODE != 0:
+                self._packer.refresh(self.params.data)
+            key = ("bk", B, bool(compute_param_flows), ls, _lib.SUM_MODE, self.params.data_ptr(),
                    self.param_flows.data_ptr() if compute_param_flows else 0)
             self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
 
@@ -414,6 +422,7 @@ class TensorCircuit(nn.Module):
             e = self._em_dev
             _lib.call("pcx_em_sum", self.params.data, self.param_flows, e["par"], e["flow"], e["fan"], e["bs"],
                       int(e["par"].numel()), e["max_bs"], float(step_size), float(pseudocount), int(bool(keep_zero_params)))
+            self._packer.invalidate()
 
     def sync_param_flows(self, dtype: Optional[torch.dtype] = None, op=None, group=None, sync_cum_flow: bool = True):
         """Sum the parameter flows of all data-parallel ranks (no-op outside an initialised process group)."""

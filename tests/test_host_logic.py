@@ -18,7 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _declared_symbols():
     text = open(os.path.join(ROOT, "include", "pcx_b200.h")).read()
-    return sorted(set(re.findall(r"^\s*int\s+(pcx_\w+)\s*\(", text, flags=re.M)))
+    return sorted(set(re.findall(r"^\s*(?:int|int64_t)\s+(pcx_\w+)\s*\(", text, flags=re.M)))
 
 
 def test_library_exports_every_declared_symbol():
