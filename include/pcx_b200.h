@@ -96,13 +96,24 @@ int pcx_sum_fwd(float* node_mars, const float* element_mars, const float* params
 /* Pre-split parameter tiles for the tensor-core kernels.  The parameter operand of the forward and element-flow
  * contractions only changes at EM updates, so it is converted once per update into bf16 hi/lo tile images of
  * 32 KB (one per 128-row tile and 64-deep slice of the contraction) that the kernels copy straight into shared
- * memory.  mode 0 = forward (kids = cids, kpar = pids, par_block ignored), mode 1 = element flows (kids = parids,
- * kpar = parpids, row_block = ch_block_size, par_block = block_size).  `pcx_packed_tile_count` * 32768 bytes is the
- * size of `packed`.  No counterpart in the reference (its kernels convert on the fly:
+ * memory.  One launch serves every table of the circuit: `jobs` is a DEVICE array of n_jobs PcxPackJob records,
+ * n_vec the total number of 16-byte vectors (sum over jobs of tiles * 1024).  `pcx_packed_tile_count` * 32768
+ * bytes is the size of a job's `out`.  No counterpart in the reference (its kernels convert on the fly:
  * layer/kernels/c/tlmm_forward_sum.cu:140-166). */
+typedef struct PcxPackJob {
+    void* out;                /* device: tile images */
+    const int32_t* kids;      /* device: mode 1: parids [n_rows, K] (0 = padding); mode 0: unused */
+    const int32_t* kpar;      /* device: mode 0: pids [n_rows, K]; mode 1: parpids [n_rows, K] */
+    int64_t vec_begin;        /* running sum of tiles * 1024 over the preceding jobs */
+    int32_t K;                /* table width */
+    int32_t row_block;        /* mode 0: block_size; mode 1: ch_block_size (multiple of 128) */
+    int32_t par_block;        /* mode 1: block_size of the parents (multiple of 8); mode 0: 1 */
+    int32_t n_chunks;         /* ceil(contraction length / 64) */
+    int32_t mode;             /* 0 forward, 1 element flows */
+    int32_t pad_;
+} PcxPackJob;
 int64_t pcx_packed_tile_count(int64_t n_rows, int K, int row_block, int par_block, int mode);
-int pcx_pack_sum_params(void* packed, const float* params, const int32_t* kids, const int32_t* kpar,
-                        int64_t n_rows, int K, int row_block, int par_block, int mode, void* stream);
+int pcx_pack_sum_params(const void* jobs, int n_jobs, int64_t n_vec, const float* params, void* stream);
 
 /* pcx_sum_fwd / pcx_sum_bwd_ele on the tensor cores (tcgen05 + TMEM), reading pre-split parameter tiles.
  * Need block_size % 128 == 0 (forward) or ch_block_size % 128 == 0 and block_size % 8 == 0 (element flows). */

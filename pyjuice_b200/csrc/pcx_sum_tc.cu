@@ -88,22 +88,31 @@ __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t sa, uint32_t
 // ---------------------------------------------------------------------------------------------------------
 // Parameter pre-split: ready-made A tiles for the forward (MODE 0) and element-flow (MODE 1) kernels
 // ---------------------------------------------------------------------------------------------------------
-struct PackArgs {
+struct PackJob {                // one table whose parameters are to be pre-split; an array of these lives on the device
     uint4* out;                 // [n_rows * tiles_r * n_chunks] tile images of 2 * A_TILE bytes (hi, then lo)
-    const float* params;
-    const int32_t* kids;        // FWD: cids (only to know padding)   ELE: parids
-    const int32_t* kpar;        // FWD: pids                          ELE: parpids
-    int K;                      // table width
-    int row_block;              // rows per table row (multiple of 128)
-    int par_block;              // ELE: parent block size (>= 8)
-    int n_chunks;
-    int64_t n_vec;              // total 16-byte (hi) vectors = n_rows * tiles_r * n_chunks * KG * BM
+    const int32_t* kids;        // forward: unused                    element flows: parids (0 = padding)
+    const int32_t* kpar;        // forward: pids                      element flows: parpids
+    int64_t vec_begin;          // index of this job's first 16-byte (hi) vector in the launch-wide enumeration
+    int32_t K;                  // table width
+    int32_t row_block;          // rows per table row (multiple of 128)
+    int32_t par_block;          // element flows: parent block size (multiple of 8)
+    int32_t n_chunks;
+    int32_t mode;               // 0 forward, 1 element flows
+    int32_t pad_;
 };
 
-template <int MODE>
-__global__ void pack_params_kernel(const PackArgs a) {
+// One thread per 16-byte vector of every job; the job is found by binary search over vec_begin.
+__global__ void pack_params_kernel(const PackJob* __restrict__ jobs, int n_jobs, int64_t n_vec,
+                                   const float* __restrict__ params) {
     int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= a.n_vec) return;
+    if (t >= n_vec) return;
+    int lo = 0, hi = n_jobs - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (jobs[mid].vec_begin <= t) lo = mid; else hi = mid - 1;
+    }
+    const PackJob a = jobs[lo];
+    t -= a.vec_begin;
     const int r = (int)(t % BM);
     const int g = (int)((t / BM) % KG);
     int64_t tile = t / (BM * KG);
@@ -114,11 +123,11 @@ __global__ void pack_params_kernel(const PackArgs a) {
     const int r0 = (int)(rowtile % tiles_r) * BM;
     const int kb = chunk * KC + g * 8;
     float v[8];
-    if (MODE == 0) {
+    if (a.mode == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             int k = kb + j;
-            v[j] = (k < a.K) ? a.params[(int64_t)a.kpar[i * a.K + k] + r0 + r] : 0.0f;
+            v[j] = (k < a.K) ? params[(int64_t)a.kpar[i * a.K + k] + r0 + r] : 0.0f;
         }
     } else {
         const int KK = a.K * a.par_block;
@@ -127,7 +136,7 @@ __global__ void pack_params_kernel(const PackArgs a) {
         int pr = (kb < KK) ? a.kids[i * a.K + p] : 0;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            v[j] = (pr != 0) ? a.params[(int64_t)a.kpar[i * a.K + p] + (int64_t)(r0 + r) * a.par_block + n + j] : 0.0f;
+            v[j] = (pr != 0) ? params[(int64_t)a.kpar[i * a.K + p] + (int64_t)(r0 + r) * a.par_block + n + j] : 0.0f;
     }
     uint4* base = a.out + tile * (2 * A_TILE / 16);
     store_split8(base + g * BM + r, base + A_TILE / 16 + g * BM + r, v);
@@ -639,19 +648,10 @@ int64_t pcx_packed_tile_count(int64_t n_rows, int K, int row_block, int par_bloc
     return n_rows * (row_block / BM) * pcx_cdiv(KK, KC);
 }
 
-int pcx_pack_sum_params(void* packed, const float* params, const int32_t* kids, const int32_t* kpar,
-                        int64_t n_rows, int K, int row_block, int par_block, int mode, void* stream) {
-    if (n_rows <= 0) return 0;
-    if (row_block % BM != 0 || (mode != 0 && mode != 1) || (mode == 1 && par_block % 8 != 0)) return -1;
-    PackArgs a{};
-    a.out = reinterpret_cast<uint4*>(packed); a.params = params; a.kids = kids; a.kpar = kpar;
-    a.K = K; a.row_block = row_block; a.par_block = (mode == 1) ? par_block : 1;
-    const int64_t KK = (mode == 0) ? K : (int64_t)K * par_block;
-    a.n_chunks = (int)pcx_cdiv(KK, KC);
-    a.n_vec = n_rows * (row_block / BM) * a.n_chunks * KG * BM;
-    const unsigned grid = (unsigned)pcx_cdiv(a.n_vec, 256);
-    if (mode == 0) pack_params_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
-    else pack_params_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+int pcx_pack_sum_params(const void* jobs, int n_jobs, int64_t n_vec, const float* params, void* stream) {
+    if (n_jobs <= 0 || n_vec <= 0) return 0;
+    const unsigned grid = (unsigned)pcx_cdiv(n_vec, 256);
+    pack_params_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const PackJob*>(jobs), n_jobs, n_vec, params);
     PCX_LAUNCH_CHECK();
     return 0;
 }

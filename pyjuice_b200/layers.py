@@ -55,20 +55,39 @@ class ParamPacker:
         if entry is None:
             tiles = int(_lib.load().pcx_packed_tile_count(n_rows, K, row_block, par_block, mode))
             buf = torch.empty(tiles * self.TILE_BYTES, dtype=torch.uint8, device=self.device)
-            entry = dict(buf=buf, args=(kids, kpar, n_rows, K, row_block, par_block, mode))
+            contraction = K if mode == 0 else K * par_block
+            entry = dict(buf=buf, tiles=tiles, kids=kids, kpar=kpar, K=K, row_block=row_block,
+                         par_block=par_block if mode == 1 else 1, n_chunks=(contraction + 63) // 64, mode=mode)
             self.entries[key] = entry
             self._stamp = None
+            self._jobs = None
         return entry["buf"]
 
     def invalidate(self):
         self._epoch += 1
 
+    def _job_table(self):
+        """Device array of PcxPackJob records (include/pcx_b200.h), one per registered table."""
+        import numpy as np
+        dt = np.dtype([("out", "<u8"), ("kids", "<u8"), ("kpar", "<u8"), ("vec_begin", "<i8"), ("K", "<i4"),
+                       ("row_block", "<i4"), ("par_block", "<i4"), ("n_chunks", "<i4"), ("mode", "<i4"), ("pad", "<i4")])
+        rec = np.zeros(len(self.entries), dtype=dt)
+        vec = 0
+        for j, e in enumerate(self.entries.values()):
+            rec[j] = (e["buf"].data_ptr(), e["kids"].data_ptr(), e["kpar"].data_ptr(), vec, e["K"], e["row_block"],
+                      e["par_block"], e["n_chunks"], e["mode"], 0)
+            vec += e["tiles"] * 1024
+        jobs = torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
+        return jobs, len(self.entries), vec
+
     def refresh(self, params: torch.Tensor):
         stamp = (params.data_ptr(), params._version, self._epoch)
-        if stamp == self._stamp:
+        if stamp == self._stamp or not self.entries:
             return
-        for entry in self.entries.values():
-            _lib.call("pcx_pack_sum_params", entry["buf"], params, *entry["args"])
+        if getattr(self, "_jobs", None) is None:
+            self._jobs = self._job_table()
+        jobs, n_jobs, n_vec = self._jobs
+        _lib.call("pcx_pack_sum_params", jobs, n_jobs, n_vec, params)
         self._stamp = stamp
 
     @property
