@@ -125,6 +125,29 @@ int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, cons
                            int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
                            void* stream);
 
+/* Sum layer forward on the tensor cores for hosts that must not allocate.  [No counterpart in the reference.]
+ *
+ * Same result as pcx_sum_fwd_packed, same arguments as pcx_sum_fwd.  Some callers cannot obtain device memory at
+ * the moment they need this kernel: code running inside a stream capture or a real-time loop where cudaMalloc
+ * (which synchronises the device) is forbidden, a plugin living in a process whose memory pool belongs to another
+ * framework, a thin FFI host with no allocator binding at all.  The tensor-core kernel needs the parameters of the
+ * table pre-split into bf16 hi/lo tiles; here that scratch is a fixed array inside the library
+ * (PCX_NOALLOC_MAX_TILES tiles of 32 KB = 8 MiB, held by every GPU that loads the library until the process
+ * exits), filled by a first kernel on `stream` and consumed by the second.  Nothing is allocated or freed.
+ *
+ *   - needs block_size % 128 == 0; n_blocks * (block_size / 128) * ceil(K / 64) tiles must fit, otherwise
+ *     PCX_ERR_SCRATCH_TOO_SMALL is returned and nothing is launched;
+ *   - the first call on each device looks up the array's device address (with that device current); make that
+ *     first call before starting any stream capture;
+ *   - all calls share the one array: calls that may overlap on the GPU (different streams, no ordering) race on
+ *     it and must be serialised by the caller.  Each call rewrites every tile it uses, padding included, so a call
+ *     never depends on what an earlier one left behind. */
+#define PCX_NOALLOC_MAX_TILES 256
+#define PCX_ERR_SCRATCH_TOO_SMALL (-2)
+int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float* params,
+                        const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                        int64_t n_blocks, int K, int block_size, int B, void* stream);
+
 /* Sum layer backward, element flows, one backward partition:
  *   element_flows[chids[i]+c, b] = element_mars[chids[i]+c, b]
  *        + log sum_{p, n} params[parpids[i,p] + c*block_size + n] * exp(node_flows[parids[i,p]+n, b] - node_mars[parids[i,p]+n, b])

@@ -34,6 +34,7 @@ SIGNATURES = {
     "pcx_sum_bwd_par": [P, P, P, P, P, P, P, P, P, L, I, I, I, I],
     "pcx_pack_sum_params": [P, I, L, P],
     "pcx_sum_fwd_packed": [P, P, P, P, P, L, I, I, I],
+    "pcx_sum_fwd_noalloc": [P, P, P, P, P, P, L, I, I, I],
     "pcx_sum_bwd_ele_packed": [P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_tied_accum": [P, L, L, P, I],
     "pcx_em_sum": [P, P, P, P, P, P, L, I, F, F, I],
@@ -105,6 +106,9 @@ def call(name: str, *args) -> None:
         PROFILE.append((name, a, b))
     else:
         rc = getattr(lib, name)(*conv, _stream())
+    if rc == -2:
+        raise PcxError(f"{name}: the table needs more pre-split parameter tiles than the library's built-in scratch "
+                       "holds (256 tiles of 32 KB); use the packed entry points with a caller-owned buffer instead")
     if rc != 0:
         raise PcxError(f"{name} failed with status {rc}")
 

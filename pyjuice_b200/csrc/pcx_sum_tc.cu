@@ -142,6 +142,29 @@ __global__ void pack_params_kernel(const PackJob* __restrict__ jobs, int n_jobs,
     store_split8(base + g * BM + r, base + A_TILE / 16 + g * BM + r, v);
 }
 
+// Same conversion for a single table whose record is passed by value (no device-side job array).
+__global__ void pack_params_one_kernel(const PackJob a, int64_t n_vec, const float* __restrict__ params) {
+    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_vec) return;
+    const int r = (int)(t % BM);
+    const int g = (int)((t / BM) % KG);
+    int64_t tile = t / (BM * KG);
+    const int chunk = (int)(tile % a.n_chunks);
+    const int64_t rowtile = tile / a.n_chunks;
+    const int tiles_r = a.row_block / BM;
+    const int64_t i = rowtile / tiles_r;
+    const int r0 = (int)(rowtile % tiles_r) * BM;
+    const int kb = chunk * KC + g * 8;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int k = kb + j;
+        v[j] = (k < a.K) ? params[(int64_t)a.kpar[i * a.K + k] + r0 + r] : 0.0f;
+    }
+    uint4* base = a.out + tile * (2 * A_TILE / 16);
+    store_split8(base + g * BM + r, base + A_TILE / 16 + g * BM + r, v);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Forward / element flows
 // ---------------------------------------------------------------------------------------------------------
@@ -566,6 +589,12 @@ __global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
     if (warp == 0) tmem_dealloc(tmem, BN);
 }
 
+// Built-in scratch of the allocation-free forward entry point: room for PCX_NOALLOC_MAX_TILES pre-split parameter
+// tiles.  Every GPU that loads the library reserves it until the process exits.
+__device__ __align__(256) unsigned char g_noalloc_tiles[(size_t)PCX_NOALLOC_MAX_TILES * 2 * A_TILE];
+constexpr int kMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};      // device address of the scratch, per device ordinal
+
 int g_sum_mode = 1;      // 0: fp32 CUDA cores only, 1: tensor cores with bf16 hi/lo split, 2: tensor cores, single bf16
 
 template <typename Kern>
@@ -666,6 +695,53 @@ int pcx_sum_fwd_packed(float* node_mars, const float* element_mars, const void* 
     a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
     a.terms = (g_sum_mode == 2) ? 1 : 3;
     return launch_lse<FWD>(a, n_blocks, (cudaStream_t)stream);
+}
+
+int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float* params,
+                        const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                        int64_t n_blocks, int K, int block_size, int B, void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size % BM != 0 || K <= 0) return -1;
+    const int64_t tiles = n_blocks * (block_size / BM) * pcx_cdiv(K, KC);
+    if (tiles > PCX_NOALLOC_MAX_TILES) return PCX_ERR_SCRATCH_TOO_SMALL;
+
+    // Set-up, once per device: in host code the array's name is only a handle, the kernels need its device address.
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return -1;
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_tiles);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
+        static bool done_small = false, done_big = false;
+        int rc = configure_once(sum_lse_tc_kernel<FWD, true>, &done_small);
+        if (rc == 0) rc = configure_once(sum_lse_tc_kernel<FWD, false>, &done_big);
+        if (rc) return rc;
+    }
+    unsigned char* scratch = g_noalloc_ptr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+
+    // 1) split the parameters of this table into the scratch (every byte of the tiles used is rewritten, padding
+    //    included, so nothing depends on what an earlier call left there)
+    PackJob job{};
+    job.out = reinterpret_cast<uint4*>(scratch); job.kids = cids; job.kpar = pids; job.vec_begin = 0;
+    job.K = K; job.row_block = block_size; job.par_block = 1; job.n_chunks = (int)pcx_cdiv(K, KC); job.mode = 0;
+    const int64_t n_vec = tiles * KG * BM;
+    pack_params_one_kernel<<<(unsigned)pcx_cdiv(n_vec, 256), 256, 0, st>>>(job, n_vec, params);
+    PCX_LAUNCH_CHECK();
+
+    // 2) the tensor-core forward kernel, reading the tiles it was just given
+    LseArgs a{};
+    a.out = node_mars; a.lsrc = element_mars; a.packed = reinterpret_cast<const uint4*>(scratch);
+    a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
+    a.terms = (g_sum_mode == 2) ? 1 : 3;
+    dim3 grid((unsigned)(n_blocks * (block_size / BM)), (unsigned)pcx_cdiv(B, BN));
+    if (K <= 2 * KC) sum_lse_tc_kernel<FWD, true><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    else sum_lse_tc_kernel<FWD, false><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    PCX_LAUNCH_CHECK();
+    return 0;
 }
 
 int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, const float* node_flows,
