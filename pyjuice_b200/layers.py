@@ -174,12 +174,15 @@ class InputLayer(Layer, nn.Module):
         self.params.data = params.to(self.device)
 
     def init_param_flows(self, flows_memory: float = 1.0):
+        """Stand-alone use only: inside a `TensorCircuit` the flows are a view into the circuit's flow arena."""
         if self.param_flows is None or self.param_flows.device != self.device:
             self.param_flows = torch.zeros([self.num_param_flows], dtype=torch.float32, device=self.device)
         elif flows_memory == 0.0:
             _fill(self.param_flows, 0.0)
         elif flows_memory < 1.0:
             _scale(self.param_flows, flows_memory)
+        if flows_memory == 0.0:
+            self._tied_folded = False
 
     def _require_cuda(self):
         if self.device.type != "cuda":
@@ -207,10 +210,23 @@ class InputLayer(Layer, nn.Module):
                   self._dev["vids"], self._dev["s_pfids"], self.num_nodes, self._output_ind_range[0], B,
                   int(bool(logspace_flows)))
 
-    def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False):
-        self._require_cuda()
+    @property
+    def num_untied_param_flows(self) -> int:
+        """Flows of the untied vectors: they come first in the layer's flow range, replicas of tied vectors after."""
+        return int(sum(ns.num_nodes * ns.dist.num_param_flows() for ns in self.nodes if not ns.is_tied()))
+
+    def fold_tied_flows(self):
+        """Source range := sum of all accumulators of every tied group (layer/input_layer.py:755-783, 1391-1411).
+        Done at most once per update window; `init_param_flows(0)` re-arms it."""
+        if getattr(self, "_tied_folded", False):
+            return
         for start, n, ch_pfids in self.tied2source_nids:
             _lib.call("pcx_tied_accum", self.param_flows, int(start), int(n), ch_pfids, int(ch_pfids.numel()))
+        self._tied_folded = True
+
+    def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False):
+        self._require_cuda()
+        self.fold_tied_flows()
         _lib.call("pcx_em_input_cat", self.params.data, self.param_flows, self._dev["source_nids"],
                   self._dev["s_pids"], self._dev["s_pfids"], self._dev["node_cats"], int(self.source_nids.numel()), self.max_cats,
                   float(step_size), float(pseudocount), int(bool(keep_zero_params)))

@@ -25,6 +25,7 @@ import torch.nn as nn
 from . import _lib
 from .compiler import _IdDict, compile_cum_par_flows, compile_par_update, create_node_layers
 from .layers import InputLayer, LayerGroup, ParamPacker, ProdLayer, SumLayer, _fill, _scale, _unsupported
+from .flows import FlowArena
 from .nodes import as_bitset
 
 NEG_INF = float("-inf")
@@ -378,6 +379,9 @@ class TensorCircuit(nn.Module):
 
     @property
     def _cum_flow(self) -> float:
+        if getattr(self, "_cum_flow_head", None) is not None:          # total left behind by the last flow sync
+            self._cum_flow_host += FlowArena.decode_total(self._cum_flow_head)
+            self._cum_flow_head = None
         if self._cum_flow_dev is not None:
             self._cum_flow_host += float(self._cum_flow_dev.item())
             self._cum_flow_dev = None
@@ -387,6 +391,7 @@ class TensorCircuit(nn.Module):
     def _cum_flow(self, v: float):
         self._cum_flow_host = float(v)
         self._cum_flow_dev = None
+        self._cum_flow_head = None
 
     # ------------------------------------------------------------------------------------------
     # parameter flows and EM
@@ -396,13 +401,20 @@ class TensorCircuit(nn.Module):
         _unsupported(batch_size=batch_size is not None)
         self._require_cuda()
         if self.param_flows is None or self.param_flows.device != self.device:
-            self.param_flows = torch.zeros(self.num_param_flows, device=self.device)
+            # all accumulators are views into one arena: a single all-reduce synchronises data-parallel ranks
+            self._flow_arena = FlowArena([self.num_param_flows] + [l.num_param_flows for l in self.input_layer_group],
+                                         self.device)
+            self.param_flows = self._flow_arena.views[0]
+            for layer, view in zip(self.input_layer_group, self._flow_arena.views[1:]):
+                layer.param_flows = view
+            self._graphs = {k: g for k, g in self._graphs.items() if k[0] != "bk"}
         elif flows_memory == 0.0:
-            _fill(self.param_flows, 0.0)
+            _fill(self._flow_arena.buf, 0.0)
         elif flows_memory != 1.0:
-            _scale(self.param_flows, flows_memory)
-        for layer in self.input_layer_group:
-            layer.init_param_flows(flows_memory=flows_memory)
+            _scale(self._flow_arena.buf, flows_memory)
+        if flows_memory == 0.0:
+            for layer in self.input_layer_group:
+                layer._tied_folded = False
 
     def zero_param_flows(self):
         self.init_param_flows(flows_memory=0.0)
@@ -425,23 +437,31 @@ class TensorCircuit(nn.Module):
             self._packer.invalidate()
 
     def sync_param_flows(self, dtype: Optional[torch.dtype] = None, op=None, group=None, sync_cum_flow: bool = True):
-        """Sum the parameter flows of all data-parallel ranks (no-op outside an initialised process group)."""
+        """Sum the parameter flows (and the running flow total) of all data-parallel ranks with ONE all-reduce over
+        the flow arena; no-op outside an initialised process group of more than one rank.
+
+        Replica accumulators of tied input vectors are folded into their source range first and left out of the
+        collective when they form the tail of the arena (a homogeneous HMM sends one emission-flow table instead of
+        one per accumulator)."""
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) <= 1:
             return None
-        op = dist.ReduceOp.SUM if op is None else op
-        tensors = [t for t in [self.param_flows] + [l.param_flows for l in self.input_layer_group] if t is not None]
-        for pf in tensors:
-            if dtype is not None and pf.dtype != dtype:
-                buf = pf.to(dtype)
-                dist.all_reduce(buf, op=op, group=group)
-                pf.copy_(buf)
-            else:
-                dist.all_reduce(pf, op=op, group=group)
+        if self.param_flows is None:
+            self.init_param_flows()
+        arena, layers = self._flow_arena, list(self.input_layer_group)
+        reduce_len = None
+        last = layers[-1]
+        if self.device.type == "cuda" and last.tied2source_nids and not getattr(last, "_tied_folded", False):
+            last.fold_tied_flows()
+            reduce_len = arena.segment_end(len(layers), last.num_untied_param_flows)
+        elif getattr(last, "_tied_folded", False):
+            reduce_len = arena.segment_end(len(layers), last.num_untied_param_flows)
+        if getattr(self, "_cum_flow_head", None) is not None:
+            _ = self._cum_flow                              # fold a pending total of an earlier sync into the host part
+        total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host
+        head = arena.all_reduce(total, group=group, dtype=dtype, reduce_len=reduce_len, op=op)
         if sync_cum_flow:
-            ct = torch.tensor([float(self._cum_flow)], dtype=torch.float64, device=self.device)
-            dist.all_reduce(ct, op=op, group=group)
-            self._cum_flow = ct.item()
+            self._cum_flow_host, self._cum_flow_dev, self._cum_flow_head = 0.0, None, head
         return None
 
     # ------------------------------------------------------------------------------------------

@@ -1,0 +1,60 @@
+"""World-size-2 data-parallel logic on CPU (gloo): the flow arena's single all-reduce sums every accumulator and the
+running flow total exactly, leaves the excluded tail alone, and is a no-op without a process group."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    from pyjuice_b200.flows import FlowArena
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        arena = FlowArena([1000, 37, 300], "cpu")
+        for i, v in enumerate(arena.views):
+            v.copy_(torch.arange(v.numel(), dtype=torch.float32) * (rank + 1) + i)
+        before_tail = arena.views[2][100:].clone()
+        reduce_len = arena.segment_end(2, 100)                     # last segment: only its first 100 floats
+        head = arena.all_reduce(5000.0 * (rank + 1) + 0.25, reduce_len=reduce_len)
+        total = FlowArena.decode_total(head)
+        ok = abs(total - (5000.0 * 3 + 0.5)) < 1e-3
+        for i, v in enumerate(arena.views):
+            n = v.numel() if i < 2 else 100
+            exp = torch.arange(v.numel(), dtype=torch.float32)[:n] * 3 + 2 * i
+            ok = ok and torch.equal(v[:n], exp)
+        ok = ok and torch.equal(arena.views[2][100:], before_tail)
+        # device-scalar form of the flow total
+        head = arena.all_reduce(torch.tensor(123456789.0, dtype=torch.float64), reduce_len=64)
+        ok = ok and abs(FlowArena.decode_total(head) - 2 * 123456789.0) < 1.0
+        open(os.path.join(out_dir, f"rank{rank}.txt"), "w").write("ok" if ok else "bad")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_flow_arena_allreduce_world2(tmp_path):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"rank{r}.txt").read() == "ok"
+
+
+def test_sync_is_noop_without_process_group():
+    import pyjuice_b200 as pj
+    ns = pj.structures.HMM(seq_length=4, num_latents=4, num_emits=5)
+    pc = pj.compile(ns)
+    assert pc.sync_param_flows() is None
+
+
+def test_arena_layout():
+    from pyjuice_b200.flows import FlowArena
+    a = FlowArena([10, 70, 5], "cpu")
+    assert a.offsets == [64, 128, 256] and a.total == 320
+    assert all(v.data_ptr() % 256 == a.buf.data_ptr() % 256 for v in a.views)
+    a.views[1].fill_(2.0)
+    assert a.buf[128:198].sum().item() == 140.0 and a.buf[:128].sum().item() == 0.0

@@ -1,0 +1,74 @@
+"""Two data-parallel ranks on two GPUs (NCCL): after `sync_param_flows` every rank holds the flows of the whole
+batch, and the EM update leaves identical parameters on both ranks, equal to a single-GPU step on the full batch.
+Skipped on boxes with fewer than two GPUs."""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _build():
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    from cases import CASES, OursApi
+    api = OursApi()
+    torch.manual_seed(21)
+    ns, kw = CASES["hmm_blocks"](api)             # tied sums and tied leaves with several flow accumulators
+    ns.init_parameters()
+    return api.compile(ns, **kw)
+
+
+def _data(pc, B):
+    g = torch.Generator().manual_seed(5)
+    return (torch.rand(B, pc.num_vars, generator=g) * 12).long()
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device(f"cuda:{rank}"))
+    try:
+        import pyjuice_b200 as pj
+        pc = _build().to(f"cuda:{rank}")
+        x = _data(pc, 64)
+        shard = x[rank * 32:(rank + 1) * 32].to(f"cuda:{rank}")
+        opt = pj.optim.MiniBatchEM(pc, step_size=0.2, pseudocount=0.1, ddp=True)
+        lls = pc(shard)
+        lls.mean().backward()
+        pc.sync_param_flows()
+        flows = pc.param_flows.clone().cpu()
+        opt.ddp = False                                   # already synchronised above
+        opt.step()
+        torch.cuda.synchronize()
+        torch.save(dict(flows=flows, params=pc.params.data.cpu(), iparams=pc.input_layer_group[0].params.data.cpu(),
+                        cum=pc._cum_flow), os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_step_equals_single_gpu_step(tmp_path):
+    import torch.multiprocessing as mp
+    import pyjuice_b200 as pj
+    port = 29700 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(2))
+    assert torch.equal(r0["flows"], r1["flows"]) and torch.equal(r0["params"], r1["params"])
+    assert torch.equal(r0["iparams"], r1["iparams"])
+    assert abs(r0["cum"] - 64.0) < 1e-3
+
+    pc = _build().to("cuda:0")
+    x = _data(pc, 64).to("cuda:0")
+    opt = pj.optim.MiniBatchEM(pc, step_size=0.2, pseudocount=0.1)
+    pc(x).mean().backward()
+    flows = pc.param_flows.clone().cpu()
+    opt.step()
+    assert torch.allclose(r0["flows"], flows, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(r0["params"], pc.params.data.cpu(), rtol=1e-4, atol=1e-7)
+    assert torch.allclose(r0["iparams"], pc.input_layer_group[0].params.data.cpu(), rtol=1e-4, atol=1e-7)
