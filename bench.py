@@ -230,7 +230,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device(f"cuda:{local_rank}")
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     W, K = max(args.warmup, 3), args.steps
     desc, B = CONFIGS[args.config]
     _lib.set_sum_mode(args.sum_mode)
@@ -296,19 +297,20 @@ def main():
     ms_dev, ms_e2e = t.tolist()
 
     # instrumented pass: per-family device time with CUDA events around every launch (eager, outside the timed region)
+    # (every rank takes the steps — they contain the flow all-reduce — but only rank 0 records)
     fam = {}
+    pc.use_cuda_graphs = False
+    for rep in range(3):
+        _lib.PROFILE = [] if (rep == 2 and rank == 0) else None
+        step(resident[0])
+        torch.cuda.synchronize()
     if rank == 0:
-        pc.use_cuda_graphs = False
-        for rep in range(3):
-            _lib.PROFILE = [] if rep == 2 else None
-            step(resident[0])
-            torch.cuda.synchronize()
         for name, a, b in _lib.PROFILE:
             d = fam.setdefault(name, [0, 0.0])
             d[0] += 1
             d[1] += a.elapsed_time(b)
-        _lib.PROFILE = None
-        pc.use_cuda_graphs = not args.no_graphs
+    _lib.PROFILE = None
+    pc.use_cuda_graphs = not args.no_graphs
 
     if world > 1:
         dist.barrier()

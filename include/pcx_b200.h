@@ -125,6 +125,25 @@ int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, cons
                            int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
                            void* stream);
 
+/* Product layer folded into the sum kernels.  In the reference a product layer is its own kernel that writes
+ * element_mars, read back by the sum layer above it and recomputed during the backward pass
+ * (model/tensorcircuit.py:395-411, 590-591; layer/prod_layer.py:161-238).  These variants take, instead of an element
+ * buffer, the child rows of every product node: `fkids` is [n_blocks, K, fc] (forward, parameter flows: the fc
+ * node_mars rows whose sum is the value of table entry (i, k); 0 = none) or [n_blocks, ch_block_size, fc] (element
+ * flows: the children of every output element), fc in {2, 4, 8}.  With direct != 0 the element-flow kernel stores
+ * each element's flow straight into its children's rows of node_flows (valid when every such child has exactly one
+ * parent in the whole circuit), which replaces the product-layer backward kernel as well. */
+int pcx_sum_fwd_fused(float* node_mars, const void* packed, const int32_t* nids, const int32_t* cids,
+                      const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, void* stream);
+int pcx_sum_bwd_ele_fused(float* element_flows, float* node_flows, const float* node_mars, const void* packed,
+                          const int32_t* chids, const int32_t* parids, const int32_t* fkids, int fc, int direct,
+                          int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
+                          void* stream);
+int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const float* node_mars, const float* params,
+                          const int32_t* nids, const int32_t* cids, const int32_t* pids, const int32_t* pfids,
+                          const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, int logspace,
+                          void* stream);
+
 /* Sum layer forward on the tensor cores for hosts that must not allocate.  [No counterpart in the reference.]
  *
  * Same result as pcx_sum_fwd_packed, same arguments as pcx_sum_fwd.  Some callers cannot obtain device memory at

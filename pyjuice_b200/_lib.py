@@ -34,6 +34,9 @@ SIGNATURES = {
     "pcx_sum_bwd_par": [P, P, P, P, P, P, P, P, P, L, I, I, I, I],
     "pcx_pack_sum_params": [P, I, L, P],
     "pcx_sum_fwd_packed": [P, P, P, P, P, L, I, I, I],
+    "pcx_sum_fwd_fused": [P, P, P, P, P, I, L, I, I, I],
+    "pcx_sum_bwd_ele_fused": [P, P, P, P, P, P, P, I, I, L, I, I, I, I, I],
+    "pcx_sum_bwd_par_fused": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I],
     "pcx_sum_fwd_noalloc": [P, P, P, P, P, P, L, I, I, I],
     "pcx_sum_bwd_ele_packed": [P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_tied_accum": [P, L, L, P, I],

@@ -184,9 +184,34 @@ struct LseArgs {
     int B;
     int logspace;
     int terms;
+    // Product layer folded into this kernel (FC > 0): a product node's value is the sum of FC child rows of
+    // node_mars (row 0 = no child), so neither element_mars nor element_flows is touched.
+    const int32_t* fkids;       // FWD: [n, K, FC] child rows of every table entry   ELE: [n, row_block, FC] child rows of every output element
+    const float* nmars;         // node_mars (fused reads)
+    float* nflows_direct;       // ELE: when set, the flow of an element is stored straight to its child rows of node_flows
 };
 
-template <int MODE, bool SMALLK>
+// Sum of up to FC rows of `src` at column `col`; -inf when the entry has no child at all.
+template <int FC>
+__device__ __forceinline__ float fused_value(const int32_t* idx, const float* src, int B, int col) {
+    int r[FC];
+    if (FC == 2) { const int2 t = *reinterpret_cast<const int2*>(idx); r[0] = t.x; r[1] = t.y; }
+    else {
+#pragma unroll
+        for (int c = 0; c < FC; c += 4) {
+            const int4 t = *reinterpret_cast<const int4*>(idx + c);
+            r[c] = t.x; r[c + 1] = t.y; r[c + 2] = t.z; r[c + 3] = t.w;
+        }
+    }
+    float s = 0.0f;
+    bool any = false;
+#pragma unroll
+    for (int c = 0; c < FC; ++c)
+        if (r[c] != 0) { s += src[(int64_t)r[c] * B + col]; any = true; }
+    return any ? s : PCX_NEG_INF;
+}
+
+template <int MODE, bool SMALLK, int FC>
 __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -230,7 +255,9 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             const int k = kb + j;
             float x = PCX_NEG_INF;
             if (col_ok && k < KK) {
-                if (MODE == FWD) {
+                if (MODE == FWD && FC > 0) {
+                    x = fused_value<(FC > 0 ? FC : 2)>(a.fkids + ((int64_t)i * a.K + k) * FC, a.nmars, B, col);
+                } else if (MODE == FWD) {
                     const int cid = a.kids[i * a.K + k];
                     if (cid != 0) x = a.lsrc[(int64_t)cid * B + col];
                 } else {
@@ -385,9 +412,20 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
                 if (b >= B) continue;
                 float o = T[r * (BN + 1) + cc];
                 if (MODE == ELE) {
-                    const float em = a.emars[(base_row + r) * B + b];
+                    const int32_t* ch = (FC > 0) ? a.fkids + ((int64_t)i * a.row_block + r0 + r) * FC : nullptr;
+                    const float em = (FC > 0) ? fused_value<(FC > 0 ? FC : 2)>(ch, a.nmars, B, b)
+                                              : a.emars[(base_row + r) * B + b];
                     o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
                     if (!a.logspace) o = expf(o);
+                    if (FC > 0 && a.nflows_direct != nullptr) {
+                        // every child of this element has it as its only parent: its flow IS the element's flow
+#pragma unroll
+                        for (int c = 0; c < FC; ++c) {
+                            const int cr = ch[c];
+                            if (cr != 0) a.nflows_direct[(int64_t)cr * B + b] = o;
+                        }
+                        continue;
+                    }
                 }
                 a.out[(base_row + r) * B + b] = o;
             }
@@ -418,8 +456,10 @@ struct ParArgs {
     int logspace;
     int terms;
     int chunks_per_cta;         // 64-sample slices handled by one CTA (the batch is split across blockIdx.z)
+    const int32_t* fkids;       // FC > 0: [n, K, FC] child rows of node_mars whose sum is the value of table entry (i, e)
 };
 
+template <int FC>
 __global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -496,7 +536,28 @@ __global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int cid = s_cid[rb + 32 * j];
-            if (b_ok && cid != 0) {
+            if (FC > 0 && b_ok && cid != 0) {
+                // the product node's value is recomputed from its children: no element buffer involved
+                const int32_t* ch = a.fkids + ((int64_t)i * a.K + e0 + rb + 32 * j) * FC;
+                bool any = false;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) y[j][t] = 0.0f;
+#pragma unroll
+                for (int c = 0; c < (FC > 0 ? FC : 1); ++c) {
+                    const int cr = ch[c];
+                    if (cr != 0) {
+                        const float4 q0 = *reinterpret_cast<const float4*>(a.node_mars + (int64_t)cr * B + bb);
+                        const float4 q1 = *reinterpret_cast<const float4*>(a.node_mars + (int64_t)cr * B + bb + 4);
+                        y[j][0] += q0.x; y[j][1] += q0.y; y[j][2] += q0.z; y[j][3] += q0.w;
+                        y[j][4] += q1.x; y[j][5] += q1.y; y[j][6] += q1.z; y[j][7] += q1.w;
+                        any = true;
+                    }
+                }
+                if (!any) {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) y[j][t] = PCX_NEG_INF;
+                }
+            } else if (b_ok && cid != 0) {
                 const float4 q0 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid * B + bb);
                 const float4 q1 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid * B + bb + 4);
                 y[j][0] = q0.x; y[j][1] = q0.y; y[j][2] = q0.z; y[j][3] = q0.w;
@@ -607,22 +668,33 @@ int configure_once(Kern kern, bool* done) {
     return 0;
 }
 
-template <int MODE>
-int launch_lse(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
+template <int MODE, int FC>
+int launch_lse_fc(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
     static bool done_small = false, done_big = false;
     const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
     dim3 grid((unsigned)(n_rows * (a.row_block / BM)), (unsigned)pcx_cdiv(a.B, BN));
     if (KK <= 2 * KC) {
-        int rc = configure_once(sum_lse_tc_kernel<MODE, true>, &done_small);
+        int rc = configure_once(sum_lse_tc_kernel<MODE, true, FC>, &done_small);
         if (rc) return rc;
-        sum_lse_tc_kernel<MODE, true><<<grid, NTH, SMEM_BYTES, st>>>(a);
+        sum_lse_tc_kernel<MODE, true, FC><<<grid, NTH, SMEM_BYTES, st>>>(a);
     } else {
-        int rc = configure_once(sum_lse_tc_kernel<MODE, false>, &done_big);
+        int rc = configure_once(sum_lse_tc_kernel<MODE, false, FC>, &done_big);
         if (rc) return rc;
-        sum_lse_tc_kernel<MODE, false><<<grid, NTH, SMEM_BYTES, st>>>(a);
+        sum_lse_tc_kernel<MODE, false, FC><<<grid, NTH, SMEM_BYTES, st>>>(a);
     }
     PCX_LAUNCH_CHECK();
     return 0;
+}
+
+template <int MODE>
+int launch_lse(const LseArgs& a, int64_t n_rows, int fc, cudaStream_t st) {
+    switch (fc) {
+        case 0: return launch_lse_fc<MODE, 0>(a, n_rows, st);
+        case 2: return launch_lse_fc<MODE, 2>(a, n_rows, st);
+        case 4: return launch_lse_fc<MODE, 4>(a, n_rows, st);
+        case 8: return launch_lse_fc<MODE, 8>(a, n_rows, st);
+        default: return -1;
+    }
 }
 
 }  // namespace
@@ -630,19 +702,25 @@ int launch_lse(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
 // Used by the dispatchers in pcx_sum_simt.cu.
 int pcx_tc_sum_mode() { return g_sum_mode; }
 
-int pcx_tc_try_sum_par(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
-                       const float* params, const int32_t* nids, const int32_t* cids, const int32_t* pids,
-                       const int32_t* pfids, int64_t n_blocks, int K, int block_size, int B, int logspace,
-                       cudaStream_t st, int* rc) {
-    if (g_sum_mode == 0 || block_size % BM != 0 || B % 8 != 0) return 0;
+template <int FC>
+static int launch_par_fc(const ParArgs& a, dim3 grid, cudaStream_t st) {
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(sum_par_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM_BYTES);
-        if (e != cudaSuccess) { *rc = (int)e; return 1; }
+        cudaError_t e = cudaFuncSetAttribute(sum_par_tc_kernel<FC>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
         done = true;
     }
+    sum_par_tc_kernel<FC><<<grid, NTH, PAR_SMEM_BYTES, st>>>(a);
+    cudaError_t e = cudaGetLastError();
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+int pcx_tc_launch_par(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                      const float* params, const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                      const int32_t* pfids, const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size,
+                      int B, int logspace, cudaStream_t st) {
     ParArgs a{param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids,
-              K, block_size, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1};
+              K, block_size, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1, fkids};
     const int64_t base = n_blocks * (block_size / BM) * pcx_cdiv(K, BN);
     const int total_chunks = (int)pcx_cdiv(B, KC);
     int64_t splits = pcx_cdiv(2 * 148, base);                  // aim at two CTAs per SM
@@ -651,9 +729,22 @@ int pcx_tc_try_sum_par(float* param_flows, const float* node_flows, const float*
     a.chunks_per_cta = (int)pcx_cdiv(total_chunks, splits);
     dim3 grid((unsigned)(n_blocks * (block_size / BM)), (unsigned)pcx_cdiv(K, BN),
               (unsigned)pcx_cdiv(total_chunks, a.chunks_per_cta));
-    sum_par_tc_kernel<<<grid, NTH, PAR_SMEM_BYTES, st>>>(a);
-    cudaError_t e = cudaGetLastError();
-    *rc = (e == cudaSuccess) ? 0 : (int)e;
+    switch (fc) {
+        case 0: return launch_par_fc<0>(a, grid, st);
+        case 2: return launch_par_fc<2>(a, grid, st);
+        case 4: return launch_par_fc<4>(a, grid, st);
+        case 8: return launch_par_fc<8>(a, grid, st);
+        default: return -1;
+    }
+}
+
+int pcx_tc_try_sum_par(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                       const float* params, const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                       const int32_t* pfids, int64_t n_blocks, int K, int block_size, int B, int logspace,
+                       cudaStream_t st, int* rc) {
+    if (g_sum_mode == 0 || block_size % BM != 0 || B % 8 != 0) return 0;
+    *rc = pcx_tc_launch_par(param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids,
+                            nullptr, 0, n_blocks, K, block_size, B, logspace, st);
     return 1;
 }
 
@@ -694,7 +785,7 @@ int pcx_sum_fwd_packed(float* node_mars, const float* element_mars, const void* 
     a.out = node_mars; a.lsrc = element_mars; a.packed = reinterpret_cast<const uint4*>(packed);
     a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
     a.terms = (g_sum_mode == 2) ? 1 : 3;
-    return launch_lse<FWD>(a, n_blocks, (cudaStream_t)stream);
+    return launch_lse<FWD>(a, n_blocks, 0, (cudaStream_t)stream);
 }
 
 int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float* params,
@@ -716,8 +807,8 @@ int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float
         if (e != cudaSuccess) return (int)e;
         g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
         static bool done_small = false, done_big = false;
-        int rc = configure_once(sum_lse_tc_kernel<FWD, true>, &done_small);
-        if (rc == 0) rc = configure_once(sum_lse_tc_kernel<FWD, false>, &done_big);
+        int rc = configure_once(sum_lse_tc_kernel<FWD, true, 0>, &done_small);
+        if (rc == 0) rc = configure_once(sum_lse_tc_kernel<FWD, false, 0>, &done_big);
         if (rc) return rc;
     }
     unsigned char* scratch = g_noalloc_ptr[dev];
@@ -738,10 +829,46 @@ int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float
     a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
     a.terms = (g_sum_mode == 2) ? 1 : 3;
     dim3 grid((unsigned)(n_blocks * (block_size / BM)), (unsigned)pcx_cdiv(B, BN));
-    if (K <= 2 * KC) sum_lse_tc_kernel<FWD, true><<<grid, NTH, SMEM_BYTES, st>>>(a);
-    else sum_lse_tc_kernel<FWD, false><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    if (K <= 2 * KC) sum_lse_tc_kernel<FWD, true, 0><<<grid, NTH, SMEM_BYTES, st>>>(a);
+    else sum_lse_tc_kernel<FWD, false, 0><<<grid, NTH, SMEM_BYTES, st>>>(a);
     PCX_LAUNCH_CHECK();
     return 0;
+}
+
+int pcx_sum_fwd_fused(float* node_mars, const void* packed, const int32_t* nids, const int32_t* cids,
+                      const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size % BM != 0 || K <= 0 || (fc != 2 && fc != 4 && fc != 8)) return -1;
+    LseArgs a{};
+    a.out = node_mars; a.nmars = node_mars; a.fkids = fkids; a.packed = reinterpret_cast<const uint4*>(packed);
+    a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
+    a.terms = (g_sum_mode == 2) ? 1 : 3;
+    return launch_lse<FWD>(a, n_blocks, fc, (cudaStream_t)stream);
+}
+
+int pcx_sum_bwd_ele_fused(float* element_flows, float* node_flows, const float* node_mars, const void* packed,
+                          const int32_t* chids, const int32_t* parids, const int32_t* fkids, int fc, int direct,
+                          int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
+                          void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (ch_block_size % BM != 0 || block_size % 8 != 0 || P <= 0 || (fc != 2 && fc != 4 && fc != 8)) return -1;
+    LseArgs a{};
+    a.out = element_flows; a.lsrc = node_flows; a.lsrc2 = node_mars; a.nmars = node_mars; a.fkids = fkids;
+    a.nflows_direct = direct ? node_flows : nullptr;
+    a.packed = reinterpret_cast<const uint4*>(packed); a.rows = chids; a.kids = parids; a.K = P;
+    a.row_block = ch_block_size; a.par_block = block_size; a.B = B; a.logspace = logspace;
+    a.terms = (g_sum_mode == 2) ? 1 : 3;
+    return launch_lse<ELE>(a, n_blocks, fc, (cudaStream_t)stream);
+}
+
+int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const float* node_mars, const float* params,
+                          const int32_t* nids, const int32_t* cids, const int32_t* pids, const int32_t* pfids,
+                          const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, int logspace,
+                          void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size % BM != 0 || B % 8 != 0 || K <= 0 || (fc != 2 && fc != 4 && fc != 8)) return -1;
+    return pcx_tc_launch_par(param_flows, node_flows, node_mars, nullptr, params, nids, cids, pids, pfids, fkids, fc,
+                             n_blocks, K, block_size, B, logspace, (cudaStream_t)stream);
 }
 
 int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, const float* node_flows,
@@ -755,7 +882,7 @@ int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, cons
     a.packed = reinterpret_cast<const uint4*>(packed); a.rows = chids; a.kids = parids; a.K = P;
     a.row_block = ch_block_size; a.par_block = block_size; a.B = B; a.logspace = logspace;
     a.terms = (g_sum_mode == 2) ? 1 : 3;
-    return launch_lse<ELE>(a, n_blocks, (cudaStream_t)stream);
+    return launch_lse<ELE>(a, n_blocks, 0, (cudaStream_t)stream);
 }
 
 }  // extern "C"

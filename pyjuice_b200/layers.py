@@ -382,6 +382,26 @@ class SumLayer(Layer, nn.Module):
 
     __call__ = forward
 
+    # ---- product layer folded in (tables prepared by TensorCircuit._setup_fusion) ------------------------------
+    def forward_fused(self, node_mars: torch.Tensor):
+        B, f = node_mars.size(1), self._fusion
+        for p, (nids, cids, _, _) in enumerate(self._dev["fw"]):
+            _lib.call("pcx_sum_fwd_fused", node_mars, self._packed_fw[p], nids, cids, f["fw"][p], f["fc"],
+                      nids.numel(), cids.size(1), self.block_size, B)
+
+    def backward_ele_fused(self, node_flows, element_flows, node_mars, logspace_flows: bool):
+        B, f = node_flows.size(1), self._fusion
+        for p, ((chids, parids, _), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
+            _lib.call("pcx_sum_bwd_ele_fused", element_flows, node_flows, node_mars, self._packed_bk[p], chids, parids,
+                      f["bk"][p], f["fc"], int(f["direct"]), chids.numel(), parids.size(1), self.block_size, cbs, B,
+                      int(bool(logspace_flows)))
+
+    def backward_par_fused(self, node_flows, node_mars, params, param_flows, logspace_flows: bool):
+        B, f = node_flows.size(1), self._fusion
+        for p, (nids, cids, pids, pfids) in enumerate(self._dev["fw"]):
+            _lib.call("pcx_sum_bwd_par_fused", param_flows, node_flows, node_mars, params, nids, cids, pids, pfids,
+                      f["fw"][p], f["fc"], nids.numel(), cids.size(1), self.block_size, B, int(bool(logspace_flows)))
+
     def backward(self, node_flows: torch.Tensor, element_flows: torch.Tensor, node_mars: torch.Tensor,
                  element_mars: torch.Tensor, params: torch.Tensor, param_flows: Optional[torch.Tensor] = None,
                  allow_modify_flows: bool = False, propagation_alg: str = "LL", logspace_flows: bool = False,

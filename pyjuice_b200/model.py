@@ -213,9 +213,102 @@ class TensorCircuit(nn.Module):
                             for start, n, accs in self._tied_sum_groups]
         for name in ("node_mars", "element_mars", "node_flows", "element_flows", "param_flows"):
             setattr(self, name, None)
+        self._setup_fusion()
+        self._side_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self._graphs = {}
         self._cum_flow_dev = None
         return self
+
+    def _setup_fusion(self):
+        """Decide, per depth, whether the product layer can be folded into the sum kernels above it.
+
+        Folding needs: every sum layer of the depth on the tensor-core path (block size a multiple of 128), at most 8
+        children per product node, and little duplication (an element read by few row tiles — otherwise the product
+        kernel, which computes each element once, is cheaper).  `direct` additionally requires every child row of the
+        depth's products to have exactly one parent product in the whole circuit: then the element-flow kernel can
+        store flows straight into node_flows and the product backward kernel disappears as well."""
+        self._fused = {}
+        self.fuse_product_layers = getattr(self, "fuse_product_layers", True)
+        if self.device.type != "cuda":
+            return
+        dev = self.device
+        parents = torch.zeros(self.num_nodes + 1, dtype=torch.int32)
+        for group in self.inner_layer_groups:
+            if group.is_prod():
+                for layer in group:
+                    j = torch.arange(layer.block_size)
+                    for cids in layer.partitioned_cids:
+                        c = cids.cpu()
+                        rows = (c[c != 0][:, None] + j[None, :]).reshape(-1)
+                        parents.index_add_(0, rows, torch.ones_like(rows, dtype=torch.int32))
+        for gi in range(1, len(self.inner_layer_groups), 2):
+            pgroup, sgroup = self.inner_layer_groups[gi - 1], self.inner_layer_groups[gi]
+            if not all(l.block_size % 128 == 0 and l._packer is not None and all(b is not None for b in l._packed_fw)
+                       and all(b is not None for b in l._packed_bk) for l in sgroup):
+                continue
+            C = max(int((c != 0).sum(dim=1).max()) for l in pgroup for c in l.partitioned_cids)
+            if C > 8:
+                continue
+            fc = 2 if C <= 2 else (4 if C <= 4 else 8)
+            n_ele = max(l._layer_nid_range[1] for l in pgroup)
+            children = torch.zeros(n_ele, fc, dtype=torch.int32)
+            for layer in pgroup:
+                j = torch.arange(layer.block_size)
+                for nids, cids in zip(layer.partitioned_nids, layer.partitioned_cids):
+                    nids, cids = nids.cpu(), cids.cpu()
+                    rows = (nids[:, None] + j[None, :]).reshape(-1)                      # element ids
+                    if cids.size(1) < fc:
+                        cids = torch.nn.functional.pad(cids, (0, fc - cids.size(1)))
+                    ch = (cids[:, None, :fc] + j[None, :, None]) * (cids[:, None, :fc] != 0)
+                    children[rows] = ch.reshape(-1, fc).to(torch.int32)
+            used = (children != 0).any(dim=1).sum().item()
+            reads = sum(int(l.block_size // 128) * int((c != 0).sum()) for l in sgroup for c in l.partitioned_cids)
+            if used == 0 or reads > 2 * used:
+                continue
+            ch_rows = children[children != 0].long()
+            direct = bool((parents[ch_rows] == 1).all())
+            for layer in sgroup:
+                fw = [children[c.cpu()].contiguous().to(dev) for c in layer.partitioned_cids]
+                bk = []
+                for chids, cbs in zip(layer.partitioned_chids, layer.cs_block_sizes):
+                    rows = chids.cpu()[:, None] + torch.arange(cbs)[None, :]
+                    bk.append(children[rows].contiguous().to(dev))
+                layer._fusion = dict(fc=fc, fw=fw, bk=bk, direct=direct)
+            self._fused[gi] = dict(fc=fc, direct=direct,
+                                   child_rows=torch.unique(ch_rows) if not direct else None)
+        # rows of node_flows that still need the -inf / 0 reset each pass: children of every depth that is not
+        # handled by direct stores (those are accumulated into with logaddexp)
+        need = torch.zeros(self.num_nodes + 1, dtype=torch.bool)
+        for gi in range(0, len(self.inner_layer_groups), 2):
+            if self._fused.get(gi + 1, {}).get("direct", False):
+                continue
+            for layer in self.inner_layer_groups[gi]:
+                j = torch.arange(layer.block_size)
+                for u in layer.partitioned_u_cids:
+                    need[(u.cpu()[:, None] + j[None, :]).reshape(-1)] = True
+        idx = torch.nonzero(need).reshape(-1)
+        self._flow_reset_ranges = None
+        if idx.numel() > 0:
+            breaks = torch.nonzero(idx[1:] != idx[:-1] + 1).reshape(-1) + 1
+            starts = torch.cat([idx[:1], idx[breaks]])
+            ends = torch.cat([idx[breaks - 1], idx[-1:]]) + 1
+            if starts.numel() <= 16:
+                self._flow_reset_ranges = list(zip(starts.tolist(), ends.tolist()))
+        else:
+            self._flow_reset_ranges = []
+        covered = torch.zeros(self.num_nodes + 1, dtype=torch.bool)
+        for gi, info in self._fused.items():
+            if info["direct"]:
+                for layer in self.inner_layer_groups[gi]:
+                    for t in layer._fusion["bk"]:
+                        covered[t.cpu().long().reshape(-1)] = True
+        r0, r1 = self._root_node_range
+        covered[r0:r1] = True
+        covered[:self.num_dummy_nodes] = True
+        covered[self.num_nodes] = True
+        # a full reset can only be skipped when every row is either rewritten by a direct store or reset explicitly
+        if self._flow_reset_ranges is not None and not bool((covered | need).all()):
+            self._flow_reset_ranges = None
 
     def _require_cuda(self):
         if self.device.type != "cuda":
@@ -273,10 +366,22 @@ class TensorCircuit(nn.Module):
         else:
             entry.replay()
 
+    def _fusion_on(self, gi: int, backward: bool = False) -> bool:
+        """Whether depth `gi` (a sum group) runs with its product layer folded in.  The folded parameter-flow kernel
+        reads eight samples per vector load, so the backward sweep only folds when the batch is a multiple of 8."""
+        if not (self.fuse_product_layers and _lib.SUM_MODE != 0 and gi in self._fused):
+            return False
+        return (not backward) or self.node_mars.size(1) % 8 == 0
+
     def _forward_inner(self):
-        for group in self.inner_layer_groups:
+        groups = self.inner_layer_groups
+        for gi, group in enumerate(groups):
             if group.is_prod():
-                group.forward(self.node_mars, self.element_mars)
+                if not self._fusion_on(gi + 1):
+                    group.forward(self.node_mars, self.element_mars)
+            elif self._fusion_on(gi):
+                for layer in group:
+                    layer.forward_fused(self.node_mars)
             else:
                 group.forward(self.node_mars, self.element_mars, self.params.data)
 
@@ -297,7 +402,7 @@ class TensorCircuit(nn.Module):
                 layer.forward(data, self.node_mars)
             if _lib.SUM_MODE != 0:
                 self._packer.refresh(self.params.data)       # outside any graph capture
-            self._run_inner(("fw", B, _lib.SUM_MODE, self.params.data_ptr()), self._forward_inner)
+            self._run_inner(("fw", B, _lib.SUM_MODE, self.fuse_product_layers, self.params.data_ptr()), self._forward_inner)
             lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
         if torch.is_grad_enabled():
             lls.requires_grad = True
@@ -308,17 +413,34 @@ class TensorCircuit(nn.Module):
     # backward
     # ------------------------------------------------------------------------------------------
     def _backward_inner(self, compute_param_flows: bool, logspace_flows: bool):
+        """Reverse sweep over the inner layers.  Parameter-flow kernels of fused depths only read node_mars and the
+        node flows of their own layer, so they run on a side stream, off the dependent chain of element-flow kernels."""
         pf = self.param_flows if compute_param_flows else None
         groups = self.inner_layer_groups
+        main = torch.cuda.current_stream()
+        side = self._side_stream
+        forked = False
         for gi in range(len(groups) - 1, -1, -1):
             group = groups[gi]
             if group.is_prod():
-                group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
+                if not (self._fusion_on(gi + 1, True) and self._fused[gi + 1]["direct"]):
+                    group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
+            elif self._fusion_on(gi, True):
+                if pf is not None:
+                    side.wait_stream(main)                 # node flows of this depth are complete on `main`
+                    forked = True
+                    with torch.cuda.stream(side):
+                        for layer in group:
+                            layer.backward_par_fused(self.node_flows, self.node_mars, self.params.data, pf, logspace_flows)
+                for layer in group:
+                    layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
             else:
                 # the shared element buffer holds another depth by now: recompute this depth's products
                 groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
                 group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
                                self.params.data, param_flows=pf, logspace_flows=logspace_flows)
+        if forked:
+            main.wait_stream(side)
 
     def backward(self, inputs: Optional[torch.Tensor] = None, ll_weights: Optional[torch.Tensor] = None,
                  compute_param_flows: bool = True, flows_memory: float = 1.0, input_layer_fn=None, cache=None,
@@ -344,7 +466,13 @@ class TensorCircuit(nn.Module):
                 data = self._prepare_inputs(inputs)
             self._ensure_buffers(B, backward=True)
             ls = int(bool(logspace_flows))
-            _fill(self.node_flows, NEG_INF if logspace_flows else 0.0)
+            reset = NEG_INF if logspace_flows else 0.0
+            ranges = self._flow_reset_ranges if (self.fuse_product_layers and _lib.SUM_MODE != 0 and B % 8 == 0) else None
+            if ranges is None:
+                _fill(self.node_flows, reset)
+            else:                                            # every other row is rewritten by a direct store
+                for a0, a1 in ranges:
+                    _fill(self.node_flows[a0:a1], reset)
             if self._eflow_mode != ls:           # dummy / parentless element rows: -inf in log space, 0 linearly
                 _fill(self.element_flows, NEG_INF if logspace_flows else 0.0)
                 self._eflow_mode = ls
@@ -368,7 +496,7 @@ class TensorCircuit(nn.Module):
                 self.init_param_flows(flows_memory=flows_memory)
             if _lib.SUM_MODE != 0:
                 self._packer.refresh(self.params.data)
-            key = ("bk", B, bool(compute_param_flows), ls, _lib.SUM_MODE, self.params.data_ptr(),
+            key = ("bk", B, bool(compute_param_flows), ls, _lib.SUM_MODE, self.fuse_product_layers, self.params.data_ptr(),
                    self.param_flows.data_ptr() if compute_param_flows else 0)
             self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
 

@@ -143,6 +143,26 @@ def test_layer_level_calls_and_accessors():
     assert p.shape == ns0._params.shape and torch.allclose(p.cpu(), ns0._params, atol=1e-6)
 
 
+@pytest.mark.parametrize("name", ["hclt_b128", "hmm_b128"])
+def test_folded_product_layers_match_separate_kernels(name):
+    """Folding the product layers into the sum kernels (and storing flows straight into node_flows) must not change
+    any result; the two circuits exercise the direct-store case (tree) and shared children (HMM)."""
+    pc = _build(name, seed=9).to(DEV)
+    assert len(pc._fused) > 0, "expected the 128-block depths to be foldable"
+    x = _data_for(pc, 64, seed=2).to(DEV)
+    out = {}
+    for fuse in (True, False):
+        pc.fuse_product_layers = fuse
+        pc.init_param_flows(flows_memory=0.0)
+        lls = pc(x)
+        pc.backward(x)
+        torch.cuda.synchronize()
+        out[fuse] = (lls.clone(), pc.node_flows[pc.num_dummy_nodes:].exp().clone(), pc.param_flows.clone(),
+                     pc.input_layer_group[0].param_flows.clone())
+    for a, b in zip(out[True], out[False]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-6), (a - b).abs().max()
+
+
 def test_no_kernel_reported_a_failed_wait():
     from pyjuice_b200 import _lib
     torch.cuda.synchronize()
