@@ -33,12 +33,16 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     flags = [f for f in FLAGS if not f.startswith("--use_fast_math")]
-    objs = []
-    for src in sources():
+    from concurrent.futures import ThreadPoolExecutor
+
+    def compile_one(src):
         obj = src[:-3] + ".o"
         cmd = [NVCC, *flags, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
         subprocess.run(cmd, check=True)
-        objs.append(obj)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=4) as pool:       # one nvcc per translation unit, side by side
+        objs = list(pool.map(compile_one, sources()))
     subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart"], check=True)
     return LIB
 

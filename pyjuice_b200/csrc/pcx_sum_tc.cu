@@ -46,7 +46,7 @@ constexpr int XSLAB = BM * 16 + 16, YSLAB = BN * 16 + 16;
 constexpr int X_TILE = KG * XSLAB, Y_TILE = KG * YSLAB;
 constexpr int PAR_STAGE_BYTES = 2 * X_TILE + 2 * Y_TILE;
 constexpr int PAR_SMEM_BYTES = STAGES * PAR_STAGE_BYTES + 1024;
-static_assert(STAGES * STAGE_BYTES >= BM * (BN + 1) * 4, "epilogue transpose buffer aliases the stages");
+static_assert(STAGES * STAGE_BYTES >= BM * (64 + 1) * 4, "epilogue transpose buffer aliases the stages");
 
 __device__ int g_tc_status = 0;          // 0 ok; otherwise the code of the first bounded wait that gave up
 
@@ -211,14 +211,21 @@ __device__ __forceinline__ float fused_value(const int32_t* idx, const float* sr
     return any ? s : PCX_NEG_INF;
 }
 
-template <int MODE, bool SMALLK, int FC>
+// One CTA = 128 output rows x TN batch columns.  TN in {16, 32, 64} is chosen per launch so that small layers still
+// spread over the whole GPU: the per-thread instruction stream is the critical path of these kernels, and a
+// narrower tile divides it (256 / TN threads share one column).
+template <int MODE, bool SMALLK, int FC, int TN>
 __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
+    constexpr int TPC = NTH / TN;                      // threads per batch column
+    constexpr int NGS = (16 / TPC) > 0 ? (16 / TPC) : 1;    // SMALLK: 8-row groups per thread (the table has <= 16)
+    constexpr int BSLAB = TN * 16;                     // bytes of one K group of the B tile
+    constexpr int TCOLS = TN < 32 ? 32 : TN;           // TMEM columns to allocate
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t s_bar[STAGES];
     __shared__ uint32_t s_tmem;
-    __shared__ float s_part[4][BN];
-    __shared__ float s_max[BN];
+    __shared__ float s_part[TPC][TN];
+    __shared__ float s_max[TN];
     __shared__ int s_fail;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -226,7 +233,7 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
     const int64_t rowtile = blockIdx.x;
     const int64_t i = rowtile / tiles_r;
     const int r0 = (int)(rowtile % tiles_r) * BM;
-    const int b0 = blockIdx.y * BN;
+    const int b0 = blockIdx.y * TN;
     const int B = a.B;
     const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
     const int lg_pb = (MODE == ELE) ? (31 - __clz(a.par_block)) : 0;
@@ -237,18 +244,18 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
         fence_mbar_init();
         s_fail = 0;
     }
-    if (warp == 0) tmem_alloc(&s_tmem, BN);
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = s_tmem;
 
-    // this thread's share of L: batch column `lc`, K groups q and q + 4 of every 64-deep slice
-    const int lc = tid & (BN - 1), q = tid >> 6;
+    // this thread's share of L: batch column `lc`, 8-row groups q, q + TPC, ... of the table
+    const int lc = tid % TN, q = tid / TN;
     const int col = b0 + lc;
     const bool col_ok = col < B;
 
-    // raw (log-domain) values of one 8-row group
+    // raw (log-domain) values of one 8-row group starting at contraction index kb
     auto load_group = [&](int kb, float* v) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -256,7 +263,7 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             float x = PCX_NEG_INF;
             if (col_ok && k < KK) {
                 if (MODE == FWD && FC > 0) {
-                    x = fused_value<(FC > 0 ? FC : 2)>(a.fkids + ((int64_t)i * a.K + k) * FC, a.nmars, B, col);
+                    x = fused_value<(FC > 0 ? FC : 4)>(a.fkids + ((int64_t)i * a.K + k) * FC, a.nmars, B, col);
                 } else if (MODE == FWD) {
                     const int cid = a.kids[i * a.K + k];
                     if (cid != 0) x = a.lsrc[(int64_t)cid * B + col];
@@ -266,7 +273,7 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
                         const int64_t row = (int64_t)pr + (k & (a.par_block - 1));
                         float nf = a.lsrc[row * B + col];
                         const float nm = a.lsrc2[row * B + col];
-                        if (!a.logspace) nf = (nf > 0.0f) ? logf(nf) : PCX_NEG_INF;
+                        if (!a.logspace) nf = (nf > 0.0f) ? __logf(nf) : PCX_NEG_INF;
                         x = (nm == PCX_NEG_INF || nf == PCX_NEG_INF) ? PCX_NEG_INF : nf - nm;
                     }
                 }
@@ -279,60 +286,51 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
 #pragma unroll
         for (int w = 0; w < 2 * A_TILE / 16 / NTH; ++w) cp_async16(st + (w * NTH + tid) * 16, src + w * NTH + tid);
     };
+    // exp(v - mx) of one group -> bf16 hi/lo, written as row `lc` of K group g of the B tile of stage `st`
+    auto store_group = [&](uint8_t* st, int g, float* v, float mx) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (v[j] == PCX_NEG_INF) ? 0.0f : __expf(v[j] - mx);
+        uint8_t* bt = st + 2 * A_TILE + g * BSLAB + lc * 16;
+        store_split8(reinterpret_cast<uint4*>(bt), reinterpret_cast<uint4*>(bt + KG * BSLAB), v);
+    };
 
-    // ---- pass 1: column maxima (values kept in registers when the table is at most two slices deep) ----
-    float keep[SMALLK ? 2 : 1][2][8];
+    // ---- pass 1: column maxima (values stay in registers when the table is at most two slices deep) ----
+    float keep[SMALLK ? NGS : 1][8];
     float mx = PCX_NEG_INF;
     if (SMALLK) {
         for (int c = 0; c < n_chunks; ++c) copy_a(c, smem + c * STAGE_BYTES);
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int h = 0; h < NGS; ++h) {
+            const int gi = q + TPC * h;                            // group index within the whole table (< 16)
+            if (gi * 8 < KK) load_group(gi * 8, keep[h]);
+            else
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (c < n_chunks) load_group(c * KC + (q + 4 * h) * 8, keep[c][h]);
-                else
+                for (int j = 0; j < 8; ++j) keep[h][j] = PCX_NEG_INF;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) keep[c][h][j] = PCX_NEG_INF;
-            }
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[c][h][j]);
+            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[h][j]);
+        }
     } else {
-        for (int c = 0; c < n_chunks; ++c) {
-            float v[2][8];
-            load_group(c * KC + q * 8, v[0]);
-            load_group(c * KC + (q + 4) * 8, v[1]);
+        for (int gi = q; gi * 8 < KK; gi += TPC) {
+            float v[8];
+            load_group(gi * 8, v);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(v[0][j], v[1][j]));
+            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[j]);
         }
     }
     s_part[q][lc] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(s_part[0][lc], s_part[1][lc]), fmaxf(s_part[2][lc], s_part[3][lc]));
+#pragma unroll
+    for (int t = 0; t < TPC; ++t) mx = fmaxf(mx, s_part[t][lc]);
     if (q == 0) s_max[lc] = mx;
 
     // ---- pass 2: exponentials -> bf16 hi/lo operand tiles, multiply -----------------------------------------
-    const uint32_t idesc = idesc_bf16_f32(BM, BN);
+    const uint32_t idesc = idesc_bf16_f32(BM, TN);
     bool failed = false;
     if (SMALLK) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            if (c < n_chunks) {
-                uint8_t* st = smem + c * STAGE_BYTES;
-                uint4* bhi = reinterpret_cast<uint4*>(st + 2 * A_TILE);
-                uint4* blo = reinterpret_cast<uint4*>(st + 2 * A_TILE + B_TILE);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int g = q + 4 * h;
-                    float v[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = (keep[c][h][j] == PCX_NEG_INF) ? 0.0f : expf(keep[c][h][j] - mx);
-                    store_split8(bhi + g * BN + lc, blo + g * BN + lc, v);
-                }
-            }
+        for (int h = 0; h < NGS; ++h) {
+            const int gi = q + TPC * h;
+            if (gi < n_chunks * KG) store_group(smem + (gi / KG) * STAGE_BYTES, gi % KG, keep[h], mx);
         }
         cp_async_wait_all();
         fence_async_smem();
@@ -341,7 +339,7 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             tc_fence_after_sync();
             for (int c = 0; c < n_chunks; ++c) {
                 const uint32_t sa = smem_u32(smem + c * STAGE_BYTES);
-                issue_stage(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
+                issue_stage<BM * 16, BSLAB>(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
             }
             mma_commit(&s_bar[0]);
         }
@@ -351,17 +349,10 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             uint8_t* st = smem + s * STAGE_BYTES;
             if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
             copy_a(c, st);
-            uint4* bhi = reinterpret_cast<uint4*>(st + 2 * A_TILE);
-            uint4* blo = reinterpret_cast<uint4*>(st + 2 * A_TILE + B_TILE);
-            float v[2][8];
-            load_group(c * KC + q * 8, v[0]);
-            load_group(c * KC + (q + 4) * 8, v[1]);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int g = q + 4 * h;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[h][j] = (v[h][j] == PCX_NEG_INF) ? 0.0f : expf(v[h][j] - mx);
-                store_split8(bhi + g * BN + lc, blo + g * BN + lc, v[h]);
+            for (int g = q; g < KG; g += TPC) {
+                float v[8];
+                load_group(c * KC + g * 8, v);
+                store_group(st, g, v, mx);
             }
             cp_async_wait_all();
             fence_async_smem();
@@ -370,7 +361,7 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             if (tid == 0 && !failed) {
                 tc_fence_after_sync();
                 const uint32_t sa = smem_u32(st);
-                issue_stage(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
+                issue_stage<BM * 16, BSLAB>(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
                 mma_commit(&s_bar[s]);
             }
         }
@@ -384,57 +375,57 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
     __syncthreads();
     failed = failed || (s_fail != 0);
     tc_fence_after_sync();
-    float* T = reinterpret_cast<float*>(smem);            // [BM][BN + 1], aliases the (now idle) stages
-    if (warp < 4 && !failed) {
-        const int row = warp * 32 + lane;
-#pragma unroll 1
-        for (int cg = 0; cg < BN / 32; ++cg) {
-            float v[32];
-            tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cg * 32), v);
+    float* T = reinterpret_cast<float*>(smem);            // [BM][TN + 1], aliases the (now idle) stages
+    if (!failed) {
+        // warps w and w + 4 share the TMEM lane quarter w % 4 and take half of the columns each
+        constexpr int HC = TN / 2;
+        const int lq = warp & 3, c0 = (warp >> 2) * HC;
+        const int row = lq * 32 + lane;
+        float v[HC];
+        tmem_ld<HC>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float m = s_max[cg * 32 + j];
-                float o;
-                if (MODE == FWD) o = (m == PCX_NEG_INF) ? PCX_NEG_INF : logf(fmaxf(v[j], 1e-24f)) + m;
-                else o = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : logf(v[j]) + m;
-                T[row * (BN + 1) + cg * 32 + j] = o;
-            }
+        for (int j = 0; j < HC; ++j) {
+            const float m = s_max[c0 + j];
+            float o;
+            if (MODE == FWD) o = (m == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m;
+            else o = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m;
+            T[row * (TN + 1) + c0 + j] = o;
         }
     }
     tc_fence_before_sync();
     __syncthreads();
     if (!failed) {
         const int64_t base_row = (int64_t)a.rows[i] + r0;
-        for (int r = warp; r < BM; r += NTH / 32) {
+#pragma unroll 4
+        for (int it = 0; it < BM * TN / NTH; ++it) {
+            const int flat = it * NTH + tid;
+            const int r = flat / TN, cc = flat % TN;
+            const int b = b0 + cc;
+            if (b >= B) continue;
+            float o = T[r * (TN + 1) + cc];
+            if (MODE == ELE) {
+                const int32_t* ch = (FC > 0) ? a.fkids + ((int64_t)i * a.row_block + r0 + r) * FC : nullptr;
+                const float em = (FC > 0) ? fused_value<(FC > 0 ? FC : 4)>(ch, a.nmars, B, b)
+                                          : a.emars[(base_row + r) * B + b];
+                o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
+                if (!a.logspace) o = __expf(o);
+                if (FC > 0 && a.nflows_direct != nullptr) {
+                    // every child of this element has it as its only parent: its flow IS the element's flow
 #pragma unroll
-            for (int cc = lane; cc < BN; cc += 32) {
-                const int b = b0 + cc;
-                if (b >= B) continue;
-                float o = T[r * (BN + 1) + cc];
-                if (MODE == ELE) {
-                    const int32_t* ch = (FC > 0) ? a.fkids + ((int64_t)i * a.row_block + r0 + r) * FC : nullptr;
-                    const float em = (FC > 0) ? fused_value<(FC > 0 ? FC : 2)>(ch, a.nmars, B, b)
-                                              : a.emars[(base_row + r) * B + b];
-                    o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
-                    if (!a.logspace) o = expf(o);
-                    if (FC > 0 && a.nflows_direct != nullptr) {
-                        // every child of this element has it as its only parent: its flow IS the element's flow
-#pragma unroll
-                        for (int c = 0; c < FC; ++c) {
-                            const int cr = ch[c];
-                            if (cr != 0) a.nflows_direct[(int64_t)cr * B + b] = o;
-                        }
-                        continue;
+                    for (int c = 0; c < FC; ++c) {
+                        const int cr = ch[c];
+                        if (cr != 0) a.nflows_direct[(int64_t)cr * B + b] = o;
                     }
+                    continue;
                 }
-                a.out[(base_row + r) * B + b] = o;
             }
+            a.out[(base_row + r) * B + b] = o;
         }
     } else if (tid == 0) {
         atomicCAS(&g_tc_status, 0, 100 * (MODE + 1) + s_fail);
     }
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, BN);
+    if (warp == 0) tmem_dealloc(tmem, TCOLS);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -668,29 +659,37 @@ int configure_once(Kern kern, bool* done) {
     return 0;
 }
 
-template <int MODE, int FC>
-int launch_lse_fc(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
+template <int MODE, int FC, int TN>
+int launch_lse_tn(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
     static bool done_small = false, done_big = false;
     const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
-    dim3 grid((unsigned)(n_rows * (a.row_block / BM)), (unsigned)pcx_cdiv(a.B, BN));
+    dim3 grid((unsigned)(n_rows * (a.row_block / BM)), (unsigned)pcx_cdiv(a.B, TN));
     if (KK <= 2 * KC) {
-        int rc = configure_once(sum_lse_tc_kernel<MODE, true, FC>, &done_small);
+        int rc = configure_once(sum_lse_tc_kernel<MODE, true, FC, TN>, &done_small);
         if (rc) return rc;
-        sum_lse_tc_kernel<MODE, true, FC><<<grid, NTH, SMEM_BYTES, st>>>(a);
+        sum_lse_tc_kernel<MODE, true, FC, TN><<<grid, NTH, SMEM_BYTES, st>>>(a);
     } else {
-        int rc = configure_once(sum_lse_tc_kernel<MODE, false, FC>, &done_big);
+        int rc = configure_once(sum_lse_tc_kernel<MODE, false, FC, TN>, &done_big);
         if (rc) return rc;
-        sum_lse_tc_kernel<MODE, false, FC><<<grid, NTH, SMEM_BYTES, st>>>(a);
+        sum_lse_tc_kernel<MODE, false, FC, TN><<<grid, NTH, SMEM_BYTES, st>>>(a);
     }
     PCX_LAUNCH_CHECK();
     return 0;
+}
+
+// Tile width: the widest of 64 / 32 / 16 columns that still gives about one CTA per SM.
+template <int MODE, int FC>
+int launch_lse_fc(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
+    const int64_t row_tiles = n_rows * (a.row_block / BM);
+    if (row_tiles * pcx_cdiv(a.B, 64) >= 148) return launch_lse_tn<MODE, FC, 64>(a, n_rows, st);
+    if (row_tiles * pcx_cdiv(a.B, 32) >= 148) return launch_lse_tn<MODE, FC, 32>(a, n_rows, st);
+    return launch_lse_tn<MODE, FC, 16>(a, n_rows, st);
 }
 
 template <int MODE>
 int launch_lse(const LseArgs& a, int64_t n_rows, int fc, cudaStream_t st) {
     switch (fc) {
         case 0: return launch_lse_fc<MODE, 0>(a, n_rows, st);
-        case 2: return launch_lse_fc<MODE, 2>(a, n_rows, st);
         case 4: return launch_lse_fc<MODE, 4>(a, n_rows, st);
         case 8: return launch_lse_fc<MODE, 8>(a, n_rows, st);
         default: return -1;
@@ -731,7 +730,6 @@ int pcx_tc_launch_par(float* param_flows, const float* node_flows, const float* 
               (unsigned)pcx_cdiv(total_chunks, a.chunks_per_cta));
     switch (fc) {
         case 0: return launch_par_fc<0>(a, grid, st);
-        case 2: return launch_par_fc<2>(a, grid, st);
         case 4: return launch_par_fc<4>(a, grid, st);
         case 8: return launch_par_fc<8>(a, grid, st);
         default: return -1;
@@ -806,10 +804,6 @@ int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float
         e = cudaGetSymbolAddress(&ptr, g_noalloc_tiles);
         if (e != cudaSuccess) return (int)e;
         g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
-        static bool done_small = false, done_big = false;
-        int rc = configure_once(sum_lse_tc_kernel<FWD, true, 0>, &done_small);
-        if (rc == 0) rc = configure_once(sum_lse_tc_kernel<FWD, false, 0>, &done_big);
-        if (rc) return rc;
     }
     unsigned char* scratch = g_noalloc_ptr[dev];
     cudaStream_t st = (cudaStream_t)stream;
@@ -828,17 +822,13 @@ int pcx_sum_fwd_noalloc(float* node_mars, const float* element_mars, const float
     a.out = node_mars; a.lsrc = element_mars; a.packed = reinterpret_cast<const uint4*>(scratch);
     a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
     a.terms = (g_sum_mode == 2) ? 1 : 3;
-    dim3 grid((unsigned)(n_blocks * (block_size / BM)), (unsigned)pcx_cdiv(B, BN));
-    if (K <= 2 * KC) sum_lse_tc_kernel<FWD, true, 0><<<grid, NTH, SMEM_BYTES, st>>>(a);
-    else sum_lse_tc_kernel<FWD, false, 0><<<grid, NTH, SMEM_BYTES, st>>>(a);
-    PCX_LAUNCH_CHECK();
-    return 0;
+    return launch_lse<FWD>(a, n_blocks, 0, st);
 }
 
 int pcx_sum_fwd_fused(float* node_mars, const void* packed, const int32_t* nids, const int32_t* cids,
                       const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
-    if (block_size % BM != 0 || K <= 0 || (fc != 2 && fc != 4 && fc != 8)) return -1;
+    if (block_size % BM != 0 || K <= 0 || (fc != 4 && fc != 8)) return -1;
     LseArgs a{};
     a.out = node_mars; a.nmars = node_mars; a.fkids = fkids; a.packed = reinterpret_cast<const uint4*>(packed);
     a.rows = nids; a.kids = cids; a.K = K; a.row_block = block_size; a.par_block = 1; a.B = B; a.logspace = 1;
@@ -851,7 +841,7 @@ int pcx_sum_bwd_ele_fused(float* element_flows, float* node_flows, const float* 
                           int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace,
                           void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
-    if (ch_block_size % BM != 0 || block_size % 8 != 0 || P <= 0 || (fc != 2 && fc != 4 && fc != 8)) return -1;
+    if (ch_block_size % BM != 0 || block_size % 8 != 0 || P <= 0 || (fc != 4 && fc != 8)) return -1;
     LseArgs a{};
     a.out = element_flows; a.lsrc = node_flows; a.lsrc2 = node_mars; a.nmars = node_mars; a.fkids = fkids;
     a.nflows_direct = direct ? node_flows : nullptr;
@@ -866,7 +856,7 @@ int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const flo
                           const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, int logspace,
                           void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
-    if (block_size % BM != 0 || B % 8 != 0 || K <= 0 || (fc != 2 && fc != 4 && fc != 8)) return -1;
+    if (block_size % BM != 0 || B % 8 != 0 || K <= 0 || (fc != 4 && fc != 8)) return -1;
     return pcx_tc_launch_par(param_flows, node_flows, node_mars, nullptr, params, nids, cids, pids, pfids, fkids, fc,
                              n_blocks, K, block_size, B, logspace, (cudaStream_t)stream);
 }

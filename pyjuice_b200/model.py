@@ -249,7 +249,7 @@ class TensorCircuit(nn.Module):
             C = max(int((c != 0).sum(dim=1).max()) for l in pgroup for c in l.partitioned_cids)
             if C > 8:
                 continue
-            fc = 2 if C <= 2 else (4 if C <= 4 else 8)
+            fc = 4 if C <= 4 else 8
             n_ele = max(l._layer_nid_range[1] for l in pgroup)
             children = torch.zeros(n_ele, fc, dtype=torch.int32)
             for layer in pgroup:
