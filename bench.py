@@ -94,26 +94,55 @@ def circuit_stats(pc):
     n_in = sum(l.num_nodes for l in pc.input_layer_group)
     p_in = sum(l.num_parameters for l in pc.input_layer_group)
     f_in = sum(l.num_param_flows for l in pc.input_layer_group)
+    sum_rows = sum(l.num_nodes for g in pc.inner_layer_groups if g.is_sum() for l in g)
     return dict(e_sum=e_sum, prod_edges=prod_edges, prod_nodes=prod_nodes, n_in=n_in, p_in=p_in, f_in=f_in,
-                p_sum=pc.num_sum_params, f_sum=pc.num_param_flows)
+                p_sum=pc.num_sum_params, f_sum=pc.num_param_flows, sum_rows=sum_rows)
 
 
-# algorithmic flops / bytes of one launch family per STEP (batch B); "unit" picks the roofline it is judged by
+def family_of(name: str) -> str:
+    """Launch family of a C-ABI entry point: the variants of one operator (product layer folded in, pre-split
+    parameter tiles, all layers in one launch, built-in scratch) count as that operator."""
+    for suffix in ("_fused", "_packed", "_batched", "_noalloc"):
+        if name.endswith(suffix):
+            name = name[:-len(suffix)]
+    return name
+
+
+# Algorithmic work of one launch family per STEP (batch B): (binding roofline, amount in bytes or flops, flops).
+# Sum layers: 2 * E_sum * B flops per pass against the minimum bytes of the pass -- every child row read once,
+# every output row written once (fp32), parameters once.  With B in the hundreds that is 15-30 flop/byte, far
+# below the ridge (about 250 flop/byte at the measured peaks) unless a node block is large: HBM binds them, and
+# the tensor-core figure is reported beside it.
 def family_work(stats, B, elsize):
     s = stats
+    flops = 2.0 * s["e_sum"] * B
+    child_rows = s["prod_nodes"] if s["prod_nodes"] else s["sum_rows"]
+    intensity = flops / (4.0 * B * (child_rows + s["sum_rows"]) + 4.0 * s["p_sum"])
+    sum_bound = "tensor" if intensity > 250.0 else "hbm"
+
+    def sum_family(nbytes):
+        return (sum_bound, flops if sum_bound == "tensor" else nbytes, flops)
+
     return {
-        "pcx_sum_fwd": ("tensor", 2.0 * s["e_sum"] * B),
-        "pcx_sum_bwd_ele": ("tensor", 2.0 * s["e_sum"] * B),
-        "pcx_sum_bwd_par": ("tensor", 2.0 * s["e_sum"] * B),
+        "pcx_sum_fwd": sum_family(4.0 * B * (child_rows + s["sum_rows"]) + 4.0 * s["p_sum"]),
+        # reads flows and values of the parents and values of the children, writes the children's flows
+        "pcx_sum_bwd_ele": sum_family(4.0 * B * (2 * s["sum_rows"] + 2 * child_rows) + 4.0 * s["p_sum"]),
+        # reads flows and values of the parents and values of the children; parameters read, flows read-modify-write
+        "pcx_sum_bwd_par": sum_family(4.0 * B * (2 * s["sum_rows"] + child_rows) + 4.0 * s["p_sum"] + 8.0 * s["f_sum"]),
         # product layers run twice forward per step (once more inside the backward pass)
-        "pcx_prod_fwd": ("hbm", 2 * 4.0 * (s["prod_edges"] + s["prod_nodes"]) * B),
-        "pcx_prod_bwd": ("hbm", 4.0 * (s["prod_edges"] + 2 * s["prod_nodes"]) * B),
-        "pcx_input_cat_fwd": ("hbm", (4.0 * s["n_in"] + elsize * 0) * B),
-        "pcx_input_cat_bwd": ("hbm", 4.0 * s["n_in"] * B + 8.0 * s["f_in"]),
-        "pcx_em_input_cat": ("hbm", 12.0 * s["p_in"]),
-        "pcx_em_sum": ("hbm", 12.0 * s["p_sum"]),
-        "pcx_fill_f32": ("hbm", 4.0 * (s["f_sum"] + s["f_in"]) + 4.0 * 0),
+        "pcx_prod_fwd": ("hbm", 2 * 4.0 * (s["prod_edges"] + s["prod_nodes"]) * B, 0.0),
+        "pcx_prod_bwd": ("hbm", 4.0 * (s["prod_edges"] + 2 * s["prod_nodes"]) * B, 0.0),
+        "pcx_input_cat_fwd": ("hbm", 4.0 * s["n_in"] * B, 0.0),
+        "pcx_input_cat_bwd": ("hbm", 4.0 * s["n_in"] * B + 8.0 * s["f_in"], 0.0),
+        "pcx_em_input_cat": ("hbm", 12.0 * s["p_in"], 0.0),
+        "pcx_em_sum": ("hbm", 12.0 * s["p_sum"], 0.0),
+        "pcx_fill_f32": ("hbm", 4.0 * (s["f_sum"] + s["f_in"]), 0.0),
+        "pcx_pack_sum_params": ("hbm", 4.0 * s["p_sum"] + 2 * 4.0 * s["p_sum"], 0.0),
     }
+
+
+# DRAM bytes per step (read + write) of a launch family, from ncu captures of the same kernels; None = not captured
+TRAFFIC_PER_STEP = {}
 
 
 class ClockSampler:
@@ -306,7 +335,7 @@ def main():
         torch.cuda.synchronize()
     if rank == 0:
         for name, a, b in _lib.PROFILE:
-            d = fam.setdefault(name, [0, 0.0])
+            d = fam.setdefault(family_of(name), [0, 0.0])
             d[0] += 1
             d[1] += a.elapsed_time(b)
     _lib.PROFILE = None
@@ -323,13 +352,18 @@ def main():
     work = family_work(stats, B, elsize)
     fam_ms = {k: round(v[1], 4) for k, v in sorted(fam.items(), key=lambda kv: -kv[1][1])}
     top = max(fam, key=lambda k: fam[k][1])
-    bound, amount = work.get(top, ("hbm", 0.0))
+    bound, amount, fam_flops = work.get(top, ("hbm", 0.0, 0.0))
     n_launch, tot_ms = fam[top]
     achieved = amount / (tot_ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peaks[bound],
                 "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": achieved / peaks[bound],
-                "traffic": None, "peak_source": peaks["source"], "launches_per_step": n_launch,
-                "ms_per_step_in_kernel": tot_ms, "family_ms_per_step": fam_ms}
+                "traffic": TRAFFIC_PER_STEP.get((args.config, top)), "peak_source": peaks["source"],
+                "launches_per_step": n_launch, "ms_per_step_in_kernel": tot_ms,
+                "algorithmic_bytes_or_flops_per_step": amount,
+                "tensor_tflops": fam_flops / (tot_ms * 1e-3) / 1e12 if fam_flops else None,
+                "family_ms_per_step": fam_ms,
+                "family_frac": {k: round(work[k][1] / (v[1] * 1e-3) / (1e12 if work[k][0] == "tensor" else 1e9)
+                                         / peaks[work[k][0]], 4) for k, v in fam.items() if k in work and v[1] > 0}}
     sum_ms = sum(fam[k][1] for k in ("pcx_sum_fwd", "pcx_sum_bwd_ele", "pcx_sum_bwd_par") if k in fam)
     sum_tflops = 6.0 * stats["e_sum"] * B / (sum_ms * 1e-3) / 1e12 if sum_ms > 0 else None
 
@@ -357,8 +391,9 @@ def main():
         "gpu_launches": launches_per_step * K,
         "roofline": roofline,
         "sum_layers": {"tflops": sum_tflops, "ms_per_step": sum_ms, "frac_of_bf16_peak": (sum_tflops or 0) / peaks["tensor"],
-                       "arith": ["fp32 FMA (CUDA cores)", "tcgen05 bf16 hi/lo split x3, fp32 accumulate (fwd, element flows); fp32 FMA (parameter flows)",
-                                 "tcgen05 single bf16, fp32 accumulate (fwd, element flows); fp32 FMA (parameter flows)"][args.sum_mode]},
+                       "arith": ["fp32 FMA (CUDA cores)",
+                                 "tcgen05 bf16 hi/lo split x3, fp32 accumulate (fwd, element flows, parameter flows)",
+                                 "tcgen05 single bf16, fp32 accumulate (fwd, element flows, parameter flows)"][args.sum_mode]},
         "cpu_baseline": cpu,
         "clocks": clocks,
     }

@@ -55,19 +55,21 @@ int pcx_set_root_flows(float* node_flows, const float* weights, int64_t root_sta
 
 /* Categorical leaves, forward:  node_mars[node_off+n, b] = log params[s_pids[n] + data[vids[n], b]].
  * data is [V, B], element size data_elsize in {1,2,4,8} (unsigned 8-bit or signed wider).
+ * node_cats[n] = number of categories of node n, max_cats their maximum: when the tables of a few nodes fit in
+ * shared memory (and B % 4 == 0) they are staged there; node_cats may be NULL (always the general kernel).
  * Replaces InputLayer.forward + Categorical.fw_mar_fn
  * (layer/input_layer.py:318-380, 1148-1187; nodes/distributions/categorical.py:82-91). */
 int pcx_input_cat_fwd(float* node_mars, const float* params, const void* data, int data_elsize,
-                      const int32_t* vids, const int32_t* s_pids, int64_t n_nodes, int64_t node_off,
-                      int B, void* stream);
+                      const int32_t* vids, const int32_t* s_pids, const int32_t* node_cats, int max_cats,
+                      int64_t n_nodes, int64_t node_off, int B, void* stream);
 
 /* Categorical leaves, backward:  param_flows[s_pfids[n] + data[vids[n], b]] += flow(node_off+n, b)  (linear value).
  * Replaces InputLayer.backward + Categorical.bk_flow_fn / cat_backward.cu
  * (layer/input_layer.py:449-548; nodes/distributions/categorical.py:93-120;
  *  layer/kernels/c/input_layers/cat_backward.cu:24-52). */
 int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* data, int data_elsize,
-                      const int32_t* vids, const int32_t* s_pfids, int64_t n_nodes, int64_t node_off,
-                      int B, int logspace, void* stream);
+                      const int32_t* vids, const int32_t* s_pfids, const int32_t* node_cats, int max_cats,
+                      int64_t n_nodes, int64_t node_off, int B, int logspace, void* stream);
 
 /* Product layer forward:  element_mars[nids[i]+j, b] = sum_c node_mars[cids[i,c]+j, b]   (cids == 0 skipped).
  * Replaces ProdLayer.forward -> _forward_backward_kernel_2d
@@ -143,6 +145,29 @@ int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const flo
                           const int32_t* nids, const int32_t* cids, const int32_t* pids, const int32_t* pfids,
                           const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, int logspace,
                           void* stream);
+
+/* Parameter flows of MANY tables in one launch (product layers folded in, as pcx_sum_bwd_par_fused).  Tiles of
+ * different layers do not depend on one another, so after the backward sweep has produced every node flow the whole
+ * circuit's parameter flows run as one grid.  `jobs` is a DEVICE array of n_jobs PcxParJob records; a table
+ * contributes n_rows * (block_size / 128) * e_tiles * splits work items, `item_begin` is the running sum over the
+ * preceding jobs, n_items the total.  Every work item handles `chunks_per_cta` 64-sample slices of the batch
+ * (splits = ceil(ceil(B / 64) / chunks_per_cta), the same for every job).  In the reference this is one kernel
+ * launch per layer partition (layer/sum_layer.py:520-541). */
+typedef struct PcxParJob {
+    const int32_t* nids;
+    const int32_t* cids;
+    const int32_t* pids;
+    const int32_t* pfids;
+    const int32_t* fkids;     /* [n_rows, K, fc] */
+    int64_t item_begin;
+    int32_t K;
+    int32_t block_size;
+    int32_t e_tiles;          /* ceil(K / 64) */
+    int32_t splits;
+} PcxParJob;
+int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const float* node_mars, const float* params,
+                            const void* jobs, int n_jobs, int64_t n_items, int fc, int B, int chunks_per_cta,
+                            int logspace, void* stream);
 
 /* Sum layer forward on the tensor cores for hosts that must not allocate.  [No counterpart in the reference.]
  *

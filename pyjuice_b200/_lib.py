@@ -25,8 +25,8 @@ SIGNATURES = {
     "pcx_scale_f32": [P, L, F],
     "pcx_exp_f32": [P, L],
     "pcx_set_root_flows": [P, P, L, L, I, I],
-    "pcx_input_cat_fwd": [P, P, P, I, P, P, L, L, I],
-    "pcx_input_cat_bwd": [P, P, P, I, P, P, L, L, I, I],
+    "pcx_input_cat_fwd": [P, P, P, I, P, P, P, I, L, L, I],
+    "pcx_input_cat_bwd": [P, P, P, I, P, P, P, I, L, L, I, I],
     "pcx_prod_fwd": [P, P, P, P, L, I, I, I],
     "pcx_prod_bwd": [P, P, P, P, L, I, I, I, I],
     "pcx_sum_fwd": [P, P, P, P, P, P, L, I, I, I],
@@ -37,6 +37,7 @@ SIGNATURES = {
     "pcx_sum_fwd_fused": [P, P, P, P, P, I, L, I, I, I],
     "pcx_sum_bwd_ele_fused": [P, P, P, P, P, P, P, I, I, L, I, I, I, I, I],
     "pcx_sum_bwd_par_fused": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I],
+    "pcx_sum_bwd_par_batched": [P, P, P, P, P, I, L, I, I, I, I],
     "pcx_sum_fwd_noalloc": [P, P, P, P, P, P, L, I, I, I],
     "pcx_sum_bwd_ele_packed": [P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_tied_accum": [P, L, L, P, I],

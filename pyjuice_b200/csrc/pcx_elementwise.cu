@@ -44,32 +44,118 @@ __global__ void root_flows_kernel(float* __restrict__ node_flows, const float* _
     node_flows[root_start + i] = logspace ? logf(w) : w;              // root rows are contiguous: [num_roots, B]
 }
 
-// One thread per (node, sample); consecutive threads walk the batch.
+// Categorical leaves, general form: one CTA per node, threads walk the batch.  Used when the batch is not a multiple
+// of four or a node has too many categories to stage its table in shared memory.
 __global__ void input_cat_fwd_kernel(float* __restrict__ node_mars, const float* __restrict__ params,
                                      const void* __restrict__ data, int elsize,
                                      const int32_t* __restrict__ vids, const int32_t* __restrict__ s_pids,
                                      int64_t n_nodes, int64_t node_off, int B) {
-    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= n_nodes * B) return;
-    int64_t n = t / B;
-    int b = (int)(t - n * B);
-    int cat = pcx_load_cat(data, elsize, (int64_t)vids[n] * B + b);
-    node_mars[(node_off + n) * B + b] = logf(params[(int64_t)s_pids[n] + cat]);
+    const int64_t n = blockIdx.x;
+    const int64_t drow = (int64_t)vids[n] * B;
+    const float* prow = params + (int64_t)s_pids[n];
+    float* out = node_mars + (node_off + n) * B;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) out[b] = logf(prow[pcx_load_cat(data, elsize, drow + b)]);
 }
 
 __global__ void input_cat_bwd_kernel(float* __restrict__ param_flows, const float* __restrict__ node_flows,
                                      const void* __restrict__ data, int elsize,
                                      const int32_t* __restrict__ vids, const int32_t* __restrict__ s_pfids,
                                      int64_t n_nodes, int64_t node_off, int B, int logspace) {
-    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= n_nodes * B) return;
-    int64_t n = t / B;
-    int b = (int)(t - n * B);
-    float f = node_flows[(node_off + n) * B + b];
-    f = logspace ? expf(f) : f;
-    if (f == 0.0f) return;
-    int cat = pcx_load_cat(data, elsize, (int64_t)vids[n] * B + b);
-    atomicAdd(param_flows + (int64_t)s_pfids[n] + cat, f);
+    const int64_t n = blockIdx.x;
+    const int64_t drow = (int64_t)vids[n] * B;
+    float* frow = param_flows + (int64_t)s_pfids[n];
+    const float* in = node_flows + (node_off + n) * B;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        float f = in[b];
+        f = logspace ? expf(f) : f;
+        if (f != 0.0f) atomicAdd(frow + pcx_load_cat(data, elsize, drow + b), f);
+    }
+}
+
+// Categorical leaves with the tables of G consecutive nodes staged in shared memory.
+//
+// A CTA owns G nodes.  Forward: it loads their parameter rows with coalesced reads, takes the logarithm once per
+// parameter (not once per sample) and then every thread looks up four consecutive samples per node and writes one
+// float4.  Nodes of one variable are consecutive in a layer, so the four category ids are re-read only when the
+// variable changes.  Backward: the CTA builds the histograms of its G nodes over the whole batch with shared-memory
+// atomics and adds every non-zero bin to the flow accumulators once -- G * num_cats global atomics instead of
+// G * B.  Category ids are clamped to the staged table so that invalid data cannot address outside it.
+constexpr int kStageThreads = 128;
+
+__device__ __forceinline__ void load_cats4(const void* data, int elsize, int64_t idx, int cap, int* c) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] = min(max(pcx_load_cat(data, elsize, idx + k), 0), cap);
+}
+
+__global__ void __launch_bounds__(kStageThreads)
+input_cat_fwd_staged(float* __restrict__ node_mars, const float* __restrict__ params,
+                     const void* __restrict__ data, int elsize,
+                     const int32_t* __restrict__ vids, const int32_t* __restrict__ s_pids,
+                     const int32_t* __restrict__ node_cats, int max_cats, int G,
+                     int64_t n_nodes, int64_t node_off, int B) {
+    extern __shared__ float s_tab[];                       // [G][max_cats] log-parameters
+    const int64_t n0 = (int64_t)blockIdx.x * G;
+    const int g_end = (int)min((int64_t)G, n_nodes - n0);
+    for (int g = 0; g < g_end; ++g) {
+        const float* prow = params + (int64_t)s_pids[n0 + g];
+        const int nc = min(node_cats[n0 + g], max_cats);
+        for (int c = threadIdx.x; c < nc; c += kStageThreads) s_tab[g * max_cats + c] = logf(prow[c]);
+        for (int c = nc + threadIdx.x; c < max_cats; c += kStageThreads) s_tab[g * max_cats + c] = PCX_NEG_INF;
+    }
+    __syncthreads();
+    for (int b = (blockIdx.y * kStageThreads + threadIdx.x) * 4; b < B; b += gridDim.y * kStageThreads * 4) {
+        int cur = -1, c[4];
+        for (int g = 0; g < g_end; ++g) {
+            const int v = vids[n0 + g];
+            if (v != cur) { load_cats4(data, elsize, (int64_t)v * B + b, max_cats - 1, c); cur = v; }
+            const float* t = s_tab + g * max_cats;
+            *reinterpret_cast<float4*>(node_mars + (node_off + n0 + g) * B + b) = make_float4(t[c[0]], t[c[1]], t[c[2]], t[c[3]]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kStageThreads)
+input_cat_bwd_staged(float* __restrict__ param_flows, const float* __restrict__ node_flows,
+                     const void* __restrict__ data, int elsize,
+                     const int32_t* __restrict__ vids, const int32_t* __restrict__ s_pfids,
+                     const int32_t* __restrict__ node_cats, int max_cats, int G,
+                     int64_t n_nodes, int64_t node_off, int B, int logspace) {
+    extern __shared__ float s_tab[];                       // [G][max_cats] flow histograms
+    const int64_t n0 = (int64_t)blockIdx.x * G;
+    const int g_end = (int)min((int64_t)G, n_nodes - n0);
+    for (int k = threadIdx.x; k < G * max_cats; k += kStageThreads) s_tab[k] = 0.0f;
+    __syncthreads();
+    for (int b = threadIdx.x * 4; b < B; b += kStageThreads * 4) {
+        int cur = -1, c[4];
+        for (int g = 0; g < g_end; ++g) {
+            const int v = vids[n0 + g];
+            if (v != cur) { load_cats4(data, elsize, (int64_t)v * B + b, max_cats - 1, c); cur = v; }
+            const float4 q = *reinterpret_cast<const float4*>(node_flows + (node_off + n0 + g) * B + b);
+            float f[4] = {q.x, q.y, q.z, q.w};
+            float* t = s_tab + g * max_cats;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float x = logspace ? expf(f[k]) : f[k];
+                if (x != 0.0f) atomicAdd(t + c[k], x);
+            }
+        }
+    }
+    __syncthreads();
+    for (int g = 0; g < g_end; ++g) {
+        float* frow = param_flows + (int64_t)s_pfids[n0 + g];
+        const int nc = min(node_cats[n0 + g], max_cats);
+        for (int c = threadIdx.x; c < nc; c += kStageThreads) {
+            const float x = s_tab[g * max_cats + c];
+            if (x != 0.0f) atomicAdd(frow + c, x);
+        }
+    }
+}
+
+// Nodes per CTA of the staged kernels: up to 16, limited by 32 KB of shared memory; 0 = table too large to stage.
+inline int stage_group(int max_cats) {
+    if (max_cats <= 0) return 0;
+    int g = (32 * 1024 / 4) / max_cats;
+    return g > 16 ? 16 : g;
 }
 
 // Product forward.  Thread = (row block i, node j of the block, VEC consecutive samples).
@@ -205,23 +291,37 @@ int pcx_set_root_flows(float* node_flows, const float* weights, int64_t root_sta
 }
 
 int pcx_input_cat_fwd(float* node_mars, const float* params, const void* data, int data_elsize,
-                      const int32_t* vids, const int32_t* s_pids, int64_t n_nodes, int64_t node_off,
-                      int B, void* stream) {
+                      const int32_t* vids, const int32_t* s_pids, const int32_t* node_cats, int max_cats,
+                      int64_t n_nodes, int64_t node_off, int B, void* stream) {
     if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
     if (n_nodes <= 0 || B <= 0) return 0;
-    input_cat_fwd_kernel<<<grid_for(n_nodes * B), kThreads, 0, (cudaStream_t)stream>>>(
-        node_mars, params, data, data_elsize, vids, s_pids, n_nodes, node_off, B);
+    const int G = node_cats ? stage_group(max_cats) : 0;
+    if (G >= 1 && B % 4 == 0 && (reinterpret_cast<uintptr_t>(node_mars) & 15) == 0) {
+        dim3 grid((unsigned)pcx_cdiv(n_nodes, G), (unsigned)pcx_cdiv(B, kStageThreads * 4));
+        input_cat_fwd_staged<<<grid, kStageThreads, (size_t)G * max_cats * sizeof(float), (cudaStream_t)stream>>>(
+            node_mars, params, data, data_elsize, vids, s_pids, node_cats, max_cats, G, n_nodes, node_off, B);
+    } else {
+        input_cat_fwd_kernel<<<(unsigned)n_nodes, B >= 256 ? 256 : 128, 0, (cudaStream_t)stream>>>(
+            node_mars, params, data, data_elsize, vids, s_pids, n_nodes, node_off, B);
+    }
     PCX_LAUNCH_CHECK();
     return 0;
 }
 
 int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* data, int data_elsize,
-                      const int32_t* vids, const int32_t* s_pfids, int64_t n_nodes, int64_t node_off,
-                      int B, int logspace, void* stream) {
+                      const int32_t* vids, const int32_t* s_pfids, const int32_t* node_cats, int max_cats,
+                      int64_t n_nodes, int64_t node_off, int B, int logspace, void* stream) {
     if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
     if (n_nodes <= 0 || B <= 0) return 0;
-    input_cat_bwd_kernel<<<grid_for(n_nodes * B), kThreads, 0, (cudaStream_t)stream>>>(
-        param_flows, node_flows, data, data_elsize, vids, s_pfids, n_nodes, node_off, B, logspace);
+    const int G = node_cats ? stage_group(max_cats) : 0;
+    if (G >= 1 && B % 4 == 0 && (reinterpret_cast<uintptr_t>(node_flows) & 15) == 0) {
+        input_cat_bwd_staged<<<(unsigned)pcx_cdiv(n_nodes, G), kStageThreads, (size_t)G * max_cats * sizeof(float),
+                               (cudaStream_t)stream>>>(
+            param_flows, node_flows, data, data_elsize, vids, s_pfids, node_cats, max_cats, G, n_nodes, node_off, B, logspace);
+    } else {
+        input_cat_bwd_kernel<<<(unsigned)n_nodes, B >= 256 ? 256 : 128, 0, (cudaStream_t)stream>>>(
+            param_flows, node_flows, data, data_elsize, vids, s_pfids, n_nodes, node_off, B, logspace);
+    }
     PCX_LAUNCH_CHECK();
     return 0;
 }

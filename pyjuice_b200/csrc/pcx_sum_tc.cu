@@ -451,7 +451,7 @@ struct ParArgs {
 };
 
 template <int FC>
-__global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
+__device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t rowtile, const int etile, const int zsplit) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t s_bar[STAGES];
@@ -462,13 +462,12 @@ __global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_r = a.block_size / BM;
-    const int64_t rowtile = blockIdx.x;
     const int64_t i = rowtile / tiles_r;
     const int r0 = (int)(rowtile % tiles_r) * BM;
-    const int e0 = blockIdx.y * BN;
+    const int e0 = etile * BN;
     const int B = a.B;
     const int total_chunks = (B + KC - 1) / KC;
-    const int c_begin = blockIdx.z * a.chunks_per_cta;
+    const int c_begin = zsplit * a.chunks_per_cta;
     const int c_end = min(total_chunks, c_begin + a.chunks_per_cta);
 
     if (tid == 0) {
@@ -639,6 +638,46 @@ __global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, BN);
+}
+
+template <int FC>
+__global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
+    par_tile_body<FC>(a, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+// Every table of the circuit in ONE launch.  Parameter-flow tiles of different layers are independent of each
+// other (they only read node values / flows and add into disjoint or atomically shared accumulators), so once the
+// chain of element-flow kernels has produced all node flows, the whole circuit's parameter flows form one large
+// grid instead of one small launch per layer.
+struct ParJob {
+    const int32_t* nids;
+    const int32_t* cids;
+    const int32_t* pids;
+    const int32_t* pfids;
+    const int32_t* fkids;
+    int64_t item_begin;         // first work item (CTA) of this table in the launch-wide enumeration
+    int32_t K;
+    int32_t block_size;
+    int32_t e_tiles;            // ceil(K / 64)
+    int32_t splits;             // batch splits per (row tile, edge tile)
+};
+
+template <int FC>
+__global__ void __launch_bounds__(NTH, 2)
+sum_par_tc_batched(const ParJob* __restrict__ jobs, int n_jobs, ParArgs a) {
+    const int64_t w = blockIdx.x;
+    int lo = 0, hi = n_jobs - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (jobs[mid].item_begin <= w) lo = mid; else hi = mid - 1;
+    }
+    const ParJob j = jobs[lo];
+    a.nids = j.nids; a.cids = j.cids; a.pids = j.pids; a.pfids = j.pfids; a.fkids = j.fkids;
+    a.K = j.K; a.block_size = j.block_size;
+    int64_t t = w - j.item_begin;
+    const int z = (int)(t % j.splits); t /= j.splits;
+    const int et = (int)(t % j.e_tiles);
+    par_tile_body<FC>(a, t / j.e_tiles, et, z);
 }
 
 // Built-in scratch of the allocation-free forward entry point: room for PCX_NOALLOC_MAX_TILES pre-split parameter
@@ -859,6 +898,37 @@ int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const flo
     if (block_size % BM != 0 || B % 8 != 0 || K <= 0 || (fc != 4 && fc != 8)) return -1;
     return pcx_tc_launch_par(param_flows, node_flows, node_mars, nullptr, params, nids, cids, pids, pfids, fkids, fc,
                              n_blocks, K, block_size, B, logspace, (cudaStream_t)stream);
+}
+
+int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const float* node_mars, const float* params,
+                            const void* jobs, int n_jobs, int64_t n_items, int fc, int B, int chunks_per_cta,
+                            int logspace, void* stream) {
+    if (n_jobs <= 0 || n_items <= 0 || B <= 0) return 0;
+    if (B % 8 != 0 || chunks_per_cta <= 0 || (fc != 4 && fc != 8)) return -1;
+    ParArgs a{};
+    a.param_flows = param_flows; a.node_flows = node_flows; a.node_mars = node_mars; a.params = params;
+    a.B = B; a.logspace = logspace; a.terms = (g_sum_mode == 2) ? 1 : 3; a.chunks_per_cta = chunks_per_cta;
+    static bool done4 = false, done8 = false;
+    cudaError_t e;
+    if (fc == 4) {
+        if (!done4) {
+            e = cudaFuncSetAttribute(sum_par_tc_batched<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM_BYTES);
+            if (e != cudaSuccess) return (int)e;
+            done4 = true;
+        }
+        sum_par_tc_batched<4><<<(unsigned)n_items, NTH, PAR_SMEM_BYTES, (cudaStream_t)stream>>>(
+            reinterpret_cast<const ParJob*>(jobs), n_jobs, a);
+    } else {
+        if (!done8) {
+            e = cudaFuncSetAttribute(sum_par_tc_batched<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM_BYTES);
+            if (e != cudaSuccess) return (int)e;
+            done8 = true;
+        }
+        sum_par_tc_batched<8><<<(unsigned)n_items, NTH, PAR_SMEM_BYTES, (cudaStream_t)stream>>>(
+            reinterpret_cast<const ParJob*>(jobs), n_jobs, a);
+    }
+    PCX_LAUNCH_CHECK();
+    return 0;
 }
 
 int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, const float* node_flows,

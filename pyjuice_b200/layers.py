@@ -195,7 +195,8 @@ class InputLayer(Layer, nn.Module):
         data = data.contiguous()
         B = node_mars.size(1)
         _lib.call("pcx_input_cat_fwd", node_mars, self.params.data, data, data.element_size(),
-                  self._dev["vids"], self._dev["s_pids"], self.num_nodes, self._output_ind_range[0], B)
+                  self._dev["vids"], self._dev["s_pids"], self._dev["node_cats"], self.max_cats,
+                  self.num_nodes, self._output_ind_range[0], B)
 
     def backward(self, data: torch.Tensor, node_flows: torch.Tensor, node_mars: torch.Tensor, params=None,
                  logspace_flows: bool = False, missing_mask=None, **kwargs):
@@ -207,8 +208,8 @@ class InputLayer(Layer, nn.Module):
         data = data.contiguous()
         B = node_flows.size(1)
         _lib.call("pcx_input_cat_bwd", self.param_flows, node_flows, data, data.element_size(),
-                  self._dev["vids"], self._dev["s_pfids"], self.num_nodes, self._output_ind_range[0], B,
-                  int(bool(logspace_flows)))
+                  self._dev["vids"], self._dev["s_pfids"], self._dev["node_cats"], self.max_cats,
+                  self.num_nodes, self._output_ind_range[0], B, int(bool(logspace_flows)))
 
     @property
     def num_untied_param_flows(self) -> int:

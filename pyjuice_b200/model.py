@@ -19,6 +19,7 @@ from __future__ import annotations
 from functools import partial
 from typing import Optional, Sequence, Union
 
+import numpy as np
 import torch
 import torch.nn as nn
 
@@ -216,6 +217,7 @@ class TensorCircuit(nn.Module):
         self._setup_fusion()
         self._side_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self._graphs = {}
+        self._par_job_cache = {}
         self._cum_flow_dev = None
         return self
 
@@ -412,26 +414,57 @@ class TensorCircuit(nn.Module):
     # ------------------------------------------------------------------------------------------
     # backward
     # ------------------------------------------------------------------------------------------
+    def _par_jobs(self, B: int):
+        """Device job tables (one per child-table width) that let ONE launch compute the parameter flows of every
+        depth whose product layer is folded in; cached per batch size."""
+        key = (B, _lib.SUM_MODE, self.fuse_product_layers)
+        cache = self.__dict__.setdefault("_par_job_cache", {})
+        if key in cache:
+            return cache[key]
+        rec = np.dtype([("nids", "<u8"), ("cids", "<u8"), ("pids", "<u8"), ("pfids", "<u8"), ("fkids", "<u8"),
+                        ("item_begin", "<i8"), ("K", "<i4"), ("block_size", "<i4"), ("e_tiles", "<i4"), ("splits", "<i4")])
+        per_fc = {}
+        for gi, group in enumerate(self.inner_layer_groups):
+            if group.is_sum() and self._fusion_on(gi, True):
+                for layer in group:
+                    f = layer._fusion
+                    for p, (nids, cids, pids, pfids) in enumerate(layer._dev["fw"]):
+                        K = cids.size(1)
+                        per_fc.setdefault(f["fc"], []).append(
+                            (nids, cids, pids, pfids, f["fw"][p], K, layer.block_size,
+                             nids.numel() * (layer.block_size // 128) * ((K + 63) // 64)))
+        total_chunks = (B + 63) // 64
+        out = []
+        for fc, jobs in per_fc.items():
+            base = sum(j[-1] for j in jobs)
+            splits = max(1, min(total_chunks, -(-8 * 148 // base)))          # about four waves of two CTAs per SM
+            chunks_per_cta = -(-total_chunks // splits)
+            splits = -(-total_chunks // chunks_per_cta)
+            table = np.zeros(len(jobs), dtype=rec)
+            begin = 0
+            for r, (nids, cids, pids, pfids, fk, K, bs, items) in zip(table, jobs):
+                r["nids"], r["cids"], r["pids"], r["pfids"], r["fkids"] = (t.data_ptr() for t in (nids, cids, pids, pfids, fk))
+                r["item_begin"], r["K"], r["block_size"], r["e_tiles"], r["splits"] = begin, K, bs, (K + 63) // 64, splits
+                begin += items * splits
+            dev = torch.from_numpy(table.view(np.uint8)).to(self.device)
+            out.append((fc, dev, len(jobs), begin, chunks_per_cta))
+        cache[key] = out
+        return out
+
     def _backward_inner(self, compute_param_flows: bool, logspace_flows: bool):
-        """Reverse sweep over the inner layers.  Parameter-flow kernels of fused depths only read node_mars and the
-        node flows of their own layer, so they run on a side stream, off the dependent chain of element-flow kernels."""
+        """Reverse sweep over the inner layers.  Parameter flows of the depths whose product layer is folded in only
+        read node values and node flows, and tiles of different layers are independent: they all run as ONE launch
+        once the dependent chain of element-flow kernels has produced every node flow."""
         pf = self.param_flows if compute_param_flows else None
         groups = self.inner_layer_groups
-        main = torch.cuda.current_stream()
-        side = self._side_stream
-        forked = False
+        any_fused = False
         for gi in range(len(groups) - 1, -1, -1):
             group = groups[gi]
             if group.is_prod():
                 if not (self._fusion_on(gi + 1, True) and self._fused[gi + 1]["direct"]):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
             elif self._fusion_on(gi, True):
-                if pf is not None:
-                    side.wait_stream(main)                 # node flows of this depth are complete on `main`
-                    forked = True
-                    with torch.cuda.stream(side):
-                        for layer in group:
-                            layer.backward_par_fused(self.node_flows, self.node_mars, self.params.data, pf, logspace_flows)
+                any_fused = True
                 for layer in group:
                     layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
             else:
@@ -439,8 +472,11 @@ class TensorCircuit(nn.Module):
                 groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
                 group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
                                self.params.data, param_flows=pf, logspace_flows=logspace_flows)
-        if forked:
-            main.wait_stream(side)
+        if any_fused and pf is not None:
+            B = self.node_flows.size(1)
+            for fc, jobs, n_jobs, n_items, chunks_per_cta in self._par_jobs(B):
+                _lib.call("pcx_sum_bwd_par_batched", pf, self.node_flows, self.node_mars, self.params.data, jobs,
+                          n_jobs, n_items, fc, B, chunks_per_cta, int(bool(logspace_flows)))
 
     def backward(self, inputs: Optional[torch.Tensor] = None, ll_weights: Optional[torch.Tensor] = None,
                  compute_param_flows: bool = True, flows_memory: float = 1.0, input_layer_fn=None, cache=None,
