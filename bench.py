@@ -243,6 +243,8 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-dataflow", action="store_true", help="per-layer launches instead of one launch per run of layers")
+    ap.add_argument("--chain-tile", type=int, default=None, choices=[16, 32, 64], help="tile width of the dataflow launch")
     ap.add_argument("--sum-mode", type=int, default=1, choices=[0, 1, 2],
                     help="0 fp32 CUDA cores, 1 tensor cores with split-bf16 operands, 2 tensor cores single bf16")
     args = ap.parse_args()
@@ -269,6 +271,8 @@ def main():
     ns, x = build_workload(args.config, B * n_batches, seed_offset=rank)
     pc = pj.compile(ns).to(dev)
     pc.use_cuda_graphs = not args.no_graphs
+    pc.use_dataflow_launch = not args.no_dataflow
+    pc.chain_tile = args.chain_tile
     stats = circuit_stats(pc)
     max_cats = max(l.max_cats for l in pc.input_layer_group)
     np_dtype, elsize = (np.uint8, 1) if max_cats <= 256 else (np.int32, 4)

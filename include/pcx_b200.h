@@ -146,6 +146,32 @@ int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const flo
                           const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, int logspace,
                           void* stream);
 
+/* Forward (mode 0) or element flows (mode 1) of a RUN of consecutive layers in one launch, product layers folded in
+ * (as pcx_sum_fwd_fused / pcx_sum_bwd_ele_fused with direct stores).  Tiles are work items claimed from a device
+ * counter in layer order; a tile of level t starts as soon as the tiles of level t - 1 that cover the same batch
+ * columns are finished, so layers overlap and no launch boundary separates them.  `jobs` is a DEVICE array of
+ * PcxChainJob records ordered by level (level 0 is processed first: the lowest layer for mode 0, the highest for
+ * mode 1); a job holds n_rowtiles * ceil(B / tn) items, `item_begin` is the running sum, `prev_total` the number of
+ * row tiles of the previous level (all its jobs together).  tn in {16, 32, 64} is the tile width in samples.
+ * `ctrl` is caller-owned device scratch of ctrl_len >= 64 + n_levels * ceil(B / tn) ints (8-byte aligned); it is
+ * cleared on the stream by this call.  The reference runs one kernel launch per layer partition
+ * (layer/sum_layer.py:367-412, 414-543). */
+typedef struct PcxChainJob {
+    const void* packed;       /* pre-split parameter tiles of the table (pcx_pack_sum_params) */
+    const int32_t* rows;      /* mode 0: nids      mode 1: chids */
+    const int32_t* kids;      /* mode 0: cids      mode 1: parids */
+    const int32_t* fkids;     /* mode 0: [n, K, fc]   mode 1: [n, ch_block_size, fc] child rows */
+    int64_t item_begin;
+    int32_t K;                /* mode 0: table width      mode 1: parent blocks per child block */
+    int32_t row_block;        /* mode 0: block size       mode 1: child block size */
+    int32_t par_block;        /* mode 0: 1                mode 1: block size of the parents */
+    int32_t n_rowtiles;       /* n_rows * row_block / 128 */
+    int32_t level;
+    int32_t prev_total;
+} PcxChainJob;
+int pcx_sum_chain(int mode, float* node_mars, float* node_flows, const void* jobs, int n_jobs, int64_t n_items,
+                  int n_levels, int tn, int fc, int B, int logspace, int* ctrl, int64_t ctrl_len, void* stream);
+
 /* Parameter flows of MANY tables in one launch (product layers folded in, as pcx_sum_bwd_par_fused).  Tiles of
  * different layers do not depend on one another, so after the backward sweep has produced every node flow the whole
  * circuit's parameter flows run as one grid.  `jobs` is a DEVICE array of n_jobs PcxParJob records; a table

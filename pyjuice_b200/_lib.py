@@ -15,7 +15,8 @@ from typing import Optional
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libpcx_b200.so")
+# PCX_B200_LIB points at another build of the library (e.g. one with development switches compiled in)
+LIB_PATH = os.environ.get("PCX_B200_LIB") or os.path.join(_HERE, "csrc", "libpcx_b200.so")
 
 P, I, L, F = c_void_p, c_int, c_int64, c_float
 
@@ -37,6 +38,7 @@ SIGNATURES = {
     "pcx_sum_fwd_fused": [P, P, P, P, P, I, L, I, I, I],
     "pcx_sum_bwd_ele_fused": [P, P, P, P, P, P, P, I, I, L, I, I, I, I, I],
     "pcx_sum_bwd_par_fused": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I],
+    "pcx_sum_chain": [I, P, P, P, I, L, I, I, I, I, I, P, L],
     "pcx_sum_bwd_par_batched": [P, P, P, P, P, I, L, I, I, I, I],
     "pcx_sum_fwd_noalloc": [P, P, P, P, P, P, L, I, I, I],
     "pcx_sum_bwd_ele_packed": [P, P, P, P, P, P, P, L, I, I, I, I, I],

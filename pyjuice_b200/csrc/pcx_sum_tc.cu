@@ -48,16 +48,39 @@ constexpr int PAR_STAGE_BYTES = 2 * X_TILE + 2 * Y_TILE;
 constexpr int PAR_SMEM_BYTES = STAGES * PAR_STAGE_BYTES + 1024;
 static_assert(STAGES * STAGE_BYTES >= BM * (64 + 1) * 4, "epilogue transpose buffer aliases the stages");
 
+// Optional phase timestamps of the dataflow launch (development builds only: -DPCX_TRACE).
+#ifdef PCX_TRACE
+constexpr int kTraceItems = 1 << 16, kTracePoints = 12;
+__device__ long long g_trace[kTraceItems][kTracePoints];
+#define PCX_T(slot, k)                                                                                     \
+    do {                                                                                                   \
+        if (threadIdx.x == 0 && (slot) >= 0 && (slot) < kTraceItems) {                                     \
+            long long _t;                                                                                  \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                         \
+            g_trace[(slot)][(k)] = _t;                                                                     \
+        }                                                                                                  \
+    } while (0)
+#else
+#define PCX_T(slot, k) do { } while (0)
+#endif
+
 __device__ int g_tc_status = 0;          // 0 ok; otherwise the code of the first bounded wait that gave up
 
 __device__ __forceinline__ uint32_t pack2(uint16_t a, uint16_t b) { return (uint32_t)a | ((uint32_t)b << 16); }
 
+// Eight fp32 values -> eight bf16 "hi" parts and eight bf16 "lo" parts (x ~= hi + lo), two values per conversion.
 __device__ __forceinline__ void store_split8(uint4* hi, uint4* lo, const float* x) {
-    uint16_t h[8], l[8];
+    uint32_t h[4], l[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) split_bf16(x[j], h[j], l[j]);
-    *hi = make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
-    *lo = make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
+    for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 hp = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);      // .x (low half) = x[2j]
+        h[j] = *reinterpret_cast<const uint32_t*>(&hp);
+        const float h0 = __uint_as_float(h[j] << 16), h1 = __uint_as_float(h[j] & 0xffff0000u);
+        const __nv_bfloat162 lp = __floats2bfloat162_rn(x[2 * j] - h0, x[2 * j + 1] - h1);
+        l[j] = *reinterpret_cast<const uint32_t*>(&lp);
+    }
+    *hi = make_uint4(h[0], h[1], h[2], h[3]);
+    *lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -65,6 +88,20 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
 }
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// Bounded wait until *ctr >= target (acquire): about a second at most.
+__device__ __forceinline__ bool poll_counter(const int* ctr, int target) {
+    for (uint32_t n = 0; n < (1u << 21); ++n) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+        if (v >= target) return true;
+        if (n > 64) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void red_release_add(int* ctr, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(ctr), "r"(v) : "memory");
 }
 
 // Issue the MMAs of one 64-deep stage: A tiles at `sa` (hi, then lo), B tiles at `sb` (hi, then lo).  A tile is
@@ -189,96 +226,139 @@ struct LseArgs {
     const int32_t* fkids;       // FWD: [n, K, FC] child rows of every table entry   ELE: [n, row_block, FC] child rows of every output element
     const float* nmars;         // node_mars (fused reads)
     float* nflows_direct;       // ELE: when set, the flow of an element is stored straight to its child rows of node_flows
+    int vec;                    // B % 8 == 0 and 16-byte aligned buffers: the epilogue uses 16-byte accesses
 };
 
-// Sum of up to FC rows of `src` at column `col`; -inf when the entry has no child at all.
+// Child rows of one table entry (row 0 = no child).
 template <int FC>
-__device__ __forceinline__ float fused_value(const int32_t* idx, const float* src, int B, int col) {
-    int r[FC];
-    if (FC == 2) { const int2 t = *reinterpret_cast<const int2*>(idx); r[0] = t.x; r[1] = t.y; }
-    else {
+__device__ __forceinline__ void load_children(const int32_t* idx, int* r) {
 #pragma unroll
-        for (int c = 0; c < FC; c += 4) {
-            const int4 t = *reinterpret_cast<const int4*>(idx + c);
-            r[c] = t.x; r[c + 1] = t.y; r[c + 2] = t.z; r[c + 3] = t.w;
-        }
+    for (int c = 0; c < FC; c += 4) {
+        const int4 t = *reinterpret_cast<const int4*>(idx + c);
+        r[c] = t.x; r[c + 1] = t.y; r[c + 2] = t.z; r[c + 3] = t.w;
     }
-    float s = 0.0f;
-    bool any = false;
+}
+// Values of the FC child rows at column `col`.  The loads are unconditional (row 0 exists and is simply not used),
+// so that a thread can have all loads of several entries in flight at once instead of one per branch.
+template <int FC>
+__device__ __forceinline__ void load_child_values(const int* r, const float* src, int B, int col, float* v) {
 #pragma unroll
-    for (int c = 0; c < FC; ++c)
-        if (r[c] != 0) { s += src[(int64_t)r[c] * B + col]; any = true; }
+    for (int c = 0; c < FC; ++c) v[c] = __ldcg(src + (int64_t)r[c] * B + col);
+}
+// Sum over the children that exist; -inf when the entry has no child at all.
+template <int FC>
+__device__ __forceinline__ float combine_children(const int* r, const float* v) {
+    float s = 0.0f;
+    int any = 0;
+#pragma unroll
+    for (int c = 0; c < FC; ++c) { s += (r[c] != 0) ? v[c] : 0.0f; any |= r[c]; }
     return any ? s : PCX_NEG_INF;
 }
+
+// Shared-memory state of one tile (declared once per kernel so that every instantiation of the body uses the same).
+struct LseShared {
+    uint64_t bar[STAGES];
+    float part[NTH];            // [threads per column][TN] partial column maxima
+    float smax[64];
+    int fail;
+};
 
 // One CTA = 128 output rows x TN batch columns.  TN in {16, 32, 64} is chosen per launch so that small layers still
 // spread over the whole GPU: the per-thread instruction stream is the critical path of these kernels, and a
 // narrower tile divides it (256 / TN threads share one column).
+//
+// `wait_on` (dataflow launches only): a counter that another CTA of the same launch advances when the rows this
+// tile reads are complete; the tile proceeds once it has reached `wait_for`.  Everything that does not depend on
+// those rows (parameter tiles, index tables) is requested before the wait.  The wait is bounded.
+// `ph[s]` counts the completed phases of mbarrier s, so that a CTA can run many tiles on the same barriers.
+// Returns false if a bounded wait gave up (the tile's output is then not written).
 template <int MODE, bool SMALLK, int FC, int TN>
-__global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
+__device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t rowtile, const int coltile,
+                                              const uint32_t tmem, uint8_t* smem, LseShared& sh, uint32_t* ph,
+                                              const int* wait_on, const int wait_for, const int slot = -1) {
     constexpr int TPC = NTH / TN;                      // threads per batch column
     constexpr int NGS = (16 / TPC) > 0 ? (16 / TPC) : 1;    // SMALLK: 8-row groups per thread (the table has <= 16)
     constexpr int BSLAB = TN * 16;                     // bytes of one K group of the B tile
-    constexpr int TCOLS = TN < 32 ? 32 : TN;           // TMEM columns to allocate
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t s_bar[STAGES];
-    __shared__ uint32_t s_tmem;
-    __shared__ float s_part[TPC][TN];
-    __shared__ float s_max[TN];
-    __shared__ int s_fail;
+    constexpr int F = FC > 0 ? FC : 4;
+    constexpr int HC = TN / 2;                         // epilogue: columns per thread
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_r = a.row_block / BM;
-    const int64_t rowtile = blockIdx.x;
     const int64_t i = rowtile / tiles_r;
     const int r0 = (int)(rowtile % tiles_r) * BM;
-    const int b0 = blockIdx.y * TN;
+    const int b0 = coltile * TN;
     const int B = a.B;
     const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
     const int lg_pb = (MODE == ELE) ? (31 - __clz(a.par_block)) : 0;
     const int n_chunks = (KK + KC - 1) / KC;
 
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[s], 1);
-        fence_mbar_init();
-        s_fail = 0;
-    }
-    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = s_tmem;
-
     // this thread's share of L: batch column `lc`, 8-row groups q, q + TPC, ... of the table
     const int lc = tid % TN, q = tid / TN;
     const int col = b0 + lc;
     const bool col_ok = col < B;
+    const int colc = col_ok ? col : 0;
 
-    // raw (log-domain) values of one 8-row group starting at contraction index kb
-    auto load_group = [&](int kb, float* v) {
+    // Loads are unconditional (row 0 exists and is simply not used) and grouped -- every index of a group, then
+    // every value, then the arithmetic -- so that a thread has all loads of a group in flight at once.
+    auto group_index = [&](int kb, int (*r)[F]) {                  // child rows of the 8 entries (FWD, folded)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int k = kb + j;
-            float x = PCX_NEG_INF;
-            if (col_ok && k < KK) {
-                if (MODE == FWD && FC > 0) {
-                    x = fused_value<(FC > 0 ? FC : 4)>(a.fkids + ((int64_t)i * a.K + k) * FC, a.nmars, B, col);
-                } else if (MODE == FWD) {
-                    const int cid = a.kids[i * a.K + k];
-                    if (cid != 0) x = a.lsrc[(int64_t)cid * B + col];
-                } else {
-                    const int pr = a.kids[i * a.K + (k >> lg_pb)];
-                    if (pr != 0) {
-                        const int64_t row = (int64_t)pr + (k & (a.par_block - 1));
-                        float nf = a.lsrc[row * B + col];
-                        const float nm = a.lsrc2[row * B + col];
-                        if (!a.logspace) nf = (nf > 0.0f) ? __logf(nf) : PCX_NEG_INF;
-                        x = (nm == PCX_NEG_INF || nf == PCX_NEG_INF) ? PCX_NEG_INF : nf - nm;
-                    }
-                }
-            }
-            v[j] = x;
+            if (col_ok && k < KK) load_children<F>(a.fkids + ((int64_t)i * a.K + k) * FC, r[j]);
+            else
+#pragma unroll
+                for (int c = 0; c < F; ++c) r[j][c] = 0;
+        }
+    };
+    auto group_values = [&](const int (*r)[F], float* v) {
+        float cv[8][F];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) load_child_values<F>(r[j], a.nmars, B, colc, cv[j]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = combine_children<F>(r[j], cv[j]);
+    };
+    auto parent_of = [&](int kb) -> int {                          // ELE: the parent block of the 8 entries
+        return (col_ok && kb < KK) ? a.kids[i * a.K + (kb >> lg_pb)] : 0;
+    };
+    // ELE: the eight indices of a group lie in one parent block (block sizes are multiples of 8).  The parents'
+    // values do not change during the backward pass; only their flows are produced by other tiles.
+    auto ele_static = [&](int kb, float* nm) -> int {
+        const int pr = parent_of(kb);
+        const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) nm[j] = __ldcg(a.lsrc2 + (row + j) * B + colc);
+        return pr;
+    };
+    auto ele_finish = [&](int kb, int pr, const float* nm, float* v) {
+        const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
+        float nf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) nf[j] = __ldcg(a.lsrc + (row + j) * B + colc);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float f = nf[j];
+            if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
+            v[j] = (pr == 0 || nm[j] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[j];
+        }
+    };
+    // raw (log-domain) values of one 8-row group starting at contraction index kb
+    auto load_group = [&](int kb, float* v) {
+        if (MODE == FWD && FC > 0) {
+            int r[8][F];
+            group_index(kb, r);
+            group_values(r, v);
+        } else if (MODE == FWD) {
+            int cid[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cid[j] = (col_ok && kb + j < KK) ? a.kids[i * a.K + kb + j] : 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(a.lsrc + (int64_t)cid[j] * B + colc);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (cid[j] != 0) ? v[j] : PCX_NEG_INF;
+        } else {
+            float nm[8];
+            const int pr = ele_static(kb, nm);
+            ele_finish(kb, pr, nm, v);
         }
     };
     auto copy_a = [&](int chunk, uint8_t* st) {
@@ -294,15 +374,37 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
         store_split8(reinterpret_cast<uint4*>(bt), reinterpret_cast<uint4*>(bt + KG * BSLAB), v);
     };
 
-    // ---- pass 1: column maxima (values stay in registers when the table is at most two slices deep) ----
+    // ---- before the wait: parameter tiles and the first group's index table -----------------------------
     float keep[SMALLK ? NGS : 1][8];
     float mx = PCX_NEG_INF;
+    int r_first[8][F];
+    float nm_first[8];
+    int pr_first = 0;
+    // epilogue role (see below): this thread finishes HC samples of one output row
+    const int lq = warp & 3, c0 = (warp >> 2) * HC;
+    const int row = lq * 32 + lane;
+    const bool vec = a.vec != 0;
+    int ch[F];
     if (SMALLK) {
         for (int c = 0; c < n_chunks; ++c) copy_a(c, smem + c * STAGE_BYTES);
+        if (MODE == FWD && FC > 0) group_index(q * 8, r_first);
+        if (MODE == ELE) pr_first = ele_static(q * 8, nm_first);
+    }
+    if (MODE == ELE && FC > 0 && vec) load_children<F>(a.fkids + ((int64_t)i * a.row_block + r0 + row) * FC, ch);
+    if (wait_on != nullptr) {
+        if (tid == 0 && !poll_counter(wait_on, wait_for)) sh.fail = 3;
+        __syncthreads();
+    }
+    PCX_T(slot, 2);
+
+    // ---- pass 1: column maxima (values stay in registers when the table is at most two slices deep) ----
+    if (SMALLK) {
 #pragma unroll
         for (int h = 0; h < NGS; ++h) {
             const int gi = q + TPC * h;                            // group index within the whole table (< 16)
-            if (gi * 8 < KK) load_group(gi * 8, keep[h]);
+            if (MODE == FWD && FC > 0 && h == 0) group_values(r_first, keep[0]);
+            else if (MODE == ELE && h == 0) ele_finish(q * 8, pr_first, nm_first, keep[0]);
+            else if (gi * 8 < KK) load_group(gi * 8, keep[h]);
             else
 #pragma unroll
                 for (int j = 0; j < 8; ++j) keep[h][j] = PCX_NEG_INF;
@@ -317,11 +419,14 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[j]);
         }
     }
-    s_part[q][lc] = mx;
+    sh.part[q * TN + lc] = mx;
     __syncthreads();
+    PCX_T(slot, 3);
 #pragma unroll
-    for (int t = 0; t < TPC; ++t) mx = fmaxf(mx, s_part[t][lc]);
-    if (q == 0) s_max[lc] = mx;
+    for (int t = 0; t < TPC; ++t) mx = fmaxf(mx, sh.part[t * TN + lc]);
+    if (q == 0) sh.smax[lc] = mx;
+
+    const int64_t base_row = (int64_t)a.rows[i] + r0;
 
     // ---- pass 2: exponentials -> bf16 hi/lo operand tiles, multiply -----------------------------------------
     const uint32_t idesc = idesc_bf16_f32(BM, TN);
@@ -332,22 +437,24 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             const int gi = q + TPC * h;
             if (gi < n_chunks * KG) store_group(smem + (gi / KG) * STAGE_BYTES, gi % KG, keep[h], mx);
         }
+        PCX_T(slot, 4);
         cp_async_wait_all();
         fence_async_smem();
         __syncthreads();
+        PCX_T(slot, 5);
         if (tid == 0) {
             tc_fence_after_sync();
             for (int c = 0; c < n_chunks; ++c) {
                 const uint32_t sa = smem_u32(smem + c * STAGE_BYTES);
                 issue_stage<BM * 16, BSLAB>(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
             }
-            mma_commit(&s_bar[0]);
+            mma_commit(&sh.bar[0]);
         }
     } else {
         for (int c = 0; c < n_chunks; ++c) {
             const int s = c % STAGES, use = c / STAGES;
             uint8_t* st = smem + s * STAGE_BYTES;
-            if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
+            if (c >= STAGES && !failed && !mbar_wait(&sh.bar[s], (ph[s] + use - 1) & 1)) { failed = true; sh.fail = 1; }
             copy_a(c, st);
             for (int g = q; g < KG; g += TPC) {
                 float v[8];
@@ -357,75 +464,302 @@ __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
             cp_async_wait_all();
             fence_async_smem();
             __syncthreads();
-            failed = failed || (s_fail != 0);
+            failed = failed || (sh.fail != 0);
             if (tid == 0 && !failed) {
                 tc_fence_after_sync();
                 const uint32_t sa = smem_u32(st);
                 issue_stage<BM * 16, BSLAB>(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
-                mma_commit(&s_bar[s]);
+                mma_commit(&sh.bar[s]);
             }
         }
     }
 
     // ---- epilogue ------------------------------------------------------------------------------------------
+    // Warps w and w + 4 share the TMEM lane quarter w % 4 and take half of the columns each: a thread owns HC
+    // consecutive samples of ONE output row.  With B a multiple of 8 it finishes them in registers (one index
+    // load per row, 16-byte loads and stores); the indices and the first child values are requested while the
+    // tensor core is still working.
+    // the values the epilogue adds (children of the output row, their indices were fetched at the start) are
+    // requested while the tensor core works
+    float4 cq[F][2];
+    const int cb0 = (b0 + c0 < B) ? b0 + c0 : 0;       // first column of this thread (clamped for the prefetch)
+    if (MODE == ELE && vec) {
+        if (FC > 0) {
+#pragma unroll
+            for (int c = 0; c < F; ++c) {
+                cq[c][0] = __ldcg(reinterpret_cast<const float4*>(a.nmars + (int64_t)ch[c] * B + cb0));
+                cq[c][1] = __ldcg(reinterpret_cast<const float4*>(a.nmars + (int64_t)ch[c] * B + cb0 + 4));
+            }
+        } else {
+            cq[0][0] = __ldcg(reinterpret_cast<const float4*>(a.emars + (base_row + row) * B + cb0));
+            cq[0][1] = __ldcg(reinterpret_cast<const float4*>(a.emars + (base_row + row) * B + cb0 + 4));
+        }
+    }
+
     {
         const int cl = SMALLK ? 0 : n_chunks - 1;       // the last commit covers every MMA issued before it
-        if (!failed && !mbar_wait(&s_bar[cl % STAGES], (uint32_t)((cl / STAGES) & 1))) { failed = true; s_fail = 2; }
-    }
-    __syncthreads();
-    failed = failed || (s_fail != 0);
-    tc_fence_after_sync();
-    float* T = reinterpret_cast<float*>(smem);            // [BM][TN + 1], aliases the (now idle) stages
-    if (!failed) {
-        // warps w and w + 4 share the TMEM lane quarter w % 4 and take half of the columns each
-        constexpr int HC = TN / 2;
-        const int lq = warp & 3, c0 = (warp >> 2) * HC;
-        const int row = lq * 32 + lane;
-        float v[HC];
-        tmem_ld<HC>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)c0, v);
+        const uint32_t par = SMALLK ? ph[0] : ph[cl % STAGES] + cl / STAGES;
+        if (!failed && !mbar_wait(&sh.bar[cl % STAGES], par & 1)) { failed = true; sh.fail = 2; }
+        if (SMALLK) ph[0] += 1;
+        else
 #pragma unroll
-        for (int j = 0; j < HC; ++j) {
-            const float m = s_max[c0 + j];
-            float o;
-            if (MODE == FWD) o = (m == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m;
-            else o = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m;
-            T[row * (TN + 1) + c0 + j] = o;
-        }
+            for (int s = 0; s < STAGES; ++s) ph[s] += (n_chunks - s + STAGES - 1) / STAGES;
     }
-    tc_fence_before_sync();
     __syncthreads();
-    if (!failed) {
-        const int64_t base_row = (int64_t)a.rows[i] + r0;
-#pragma unroll 4
-        for (int it = 0; it < BM * TN / NTH; ++it) {
-            const int flat = it * NTH + tid;
-            const int r = flat / TN, cc = flat % TN;
-            const int b = b0 + cc;
-            if (b >= B) continue;
-            float o = T[r * (TN + 1) + cc];
-            if (MODE == ELE) {
-                const int32_t* ch = (FC > 0) ? a.fkids + ((int64_t)i * a.row_block + r0 + r) * FC : nullptr;
-                const float em = (FC > 0) ? fused_value<(FC > 0 ? FC : 4)>(ch, a.nmars, B, b)
-                                          : a.emars[(base_row + r) * B + b];
-                o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
-                if (!a.logspace) o = __expf(o);
-                if (FC > 0 && a.nflows_direct != nullptr) {
+    PCX_T(slot, 6);
+    failed = failed || (sh.fail != 0);
+    tc_fence_after_sync();
+    if (vec) {
+        if (!failed) {
+#pragma unroll
+            for (int p = 0; p < HC / 8; ++p) {
+                const int cb = b0 + c0 + 8 * p;                     // B % 8 == 0: a piece is all in or all out
+                float v[8];
+                tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
+                if (cb >= B) continue;
+                if (MODE == ELE && p > 0) {
+                    if (FC > 0) {
+#pragma unroll
+                        for (int c = 0; c < F; ++c) {
+                            cq[c][0] = __ldcg(reinterpret_cast<const float4*>(a.nmars + (int64_t)ch[c] * B + cb));
+                            cq[c][1] = __ldcg(reinterpret_cast<const float4*>(a.nmars + (int64_t)ch[c] * B + cb + 4));
+                        }
+                    } else {
+                        cq[0][0] = __ldcg(reinterpret_cast<const float4*>(a.emars + (base_row + row) * B + cb));
+                        cq[0][1] = __ldcg(reinterpret_cast<const float4*>(a.emars + (base_row + row) * B + cb + 4));
+                    }
+                }
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float m = sh.smax[c0 + 8 * p + j];
+                    if (MODE == FWD) o[j] = (m == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m;
+                    else o[j] = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m;
+                }
+                if (MODE == ELE) {
+                    float em[8];
+                    if (FC > 0) {
+                        int any = 0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) em[j] = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < F; ++c) {
+                            const bool on = ch[c] != 0;
+                            any |= ch[c];
+                            em[0] += on ? cq[c][0].x : 0.0f; em[1] += on ? cq[c][0].y : 0.0f;
+                            em[2] += on ? cq[c][0].z : 0.0f; em[3] += on ? cq[c][0].w : 0.0f;
+                            em[4] += on ? cq[c][1].x : 0.0f; em[5] += on ? cq[c][1].y : 0.0f;
+                            em[6] += on ? cq[c][1].z : 0.0f; em[7] += on ? cq[c][1].w : 0.0f;
+                        }
+                        if (!any) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) em[j] = PCX_NEG_INF;
+                        }
+                    } else {
+                        em[0] = cq[0][0].x; em[1] = cq[0][0].y; em[2] = cq[0][0].z; em[3] = cq[0][0].w;
+                        em[4] = cq[0][1].x; em[5] = cq[0][1].y; em[6] = cq[0][1].z; em[7] = cq[0][1].w;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        o[j] = (o[j] == PCX_NEG_INF || em[j] == PCX_NEG_INF) ? PCX_NEG_INF : o[j] + em[j];
+                        if (!a.logspace) o[j] = __expf(o[j]);
+                    }
+                }
+                const float4 o0 = make_float4(o[0], o[1], o[2], o[3]), o1 = make_float4(o[4], o[5], o[6], o[7]);
+                if (MODE == ELE && FC > 0 && a.nflows_direct != nullptr) {
                     // every child of this element has it as its only parent: its flow IS the element's flow
 #pragma unroll
-                    for (int c = 0; c < FC; ++c) {
-                        const int cr = ch[c];
-                        if (cr != 0) a.nflows_direct[(int64_t)cr * B + b] = o;
+                    for (int c = 0; c < F; ++c) {
+                        if (ch[c] != 0) {
+                            float4* dst = reinterpret_cast<float4*>(a.nflows_direct + (int64_t)ch[c] * B + cb);
+                            dst[0] = o0; dst[1] = o1;
+                        }
                     }
-                    continue;
+                } else {
+                    float4* dst = reinterpret_cast<float4*>(a.out + (base_row + row) * B + cb);
+                    dst[0] = o0; dst[1] = o1;
                 }
             }
-            a.out[(base_row + r) * B + b] = o;
         }
-    } else if (tid == 0) {
-        atomicCAS(&g_tc_status, 0, 100 * (MODE + 1) + s_fail);
+        tc_fence_before_sync();
+    } else {
+        // general batch sizes: through a shared-memory transpose, one sample per thread and step
+        float* T = reinterpret_cast<float*>(smem);            // [BM][TN + 1], aliases the (now idle) stages
+        if (!failed) {
+            float v[HC];
+            tmem_ld<HC>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+            for (int j = 0; j < HC; ++j) {
+                const float m = sh.smax[c0 + j];
+                float o;
+                if (MODE == FWD) o = (m == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m;
+                else o = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m;
+                T[row * (TN + 1) + c0 + j] = o;
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        if (!failed) {
+            constexpr int ITERS = BM * TN / NTH, UB = 4;
+            for (int it0 = 0; it0 < ITERS; it0 += UB) {
+                // four outputs per thread at a time: all their loads first, then the arithmetic and the stores
+                float o[UB], em[UB], cv[UB][F];
+                int chs[UB][F];
+#pragma unroll
+                for (int u = 0; u < UB; ++u) {
+                    const int flat = (it0 + u) * NTH + tid;
+                    const int r = flat / TN, cc = flat % TN;
+                    o[u] = T[r * (TN + 1) + cc];
+                    if (MODE == ELE && FC > 0) load_children<F>(a.fkids + ((int64_t)i * a.row_block + r0 + r) * FC, chs[u]);
+                }
+                if (MODE == ELE) {
+#pragma unroll
+                    for (int u = 0; u < UB; ++u) {
+                        const int flat = (it0 + u) * NTH + tid;
+                        const int r = flat / TN, b = b0 + flat % TN;
+                        const int bc = b < B ? b : 0;
+                        if (FC > 0) load_child_values<F>(chs[u], a.nmars, B, bc, cv[u]);
+                        else em[u] = a.emars[(base_row + r) * B + bc];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UB; ++u) {
+                    const int flat = (it0 + u) * NTH + tid;
+                    const int r = flat / TN, b = b0 + flat % TN;
+                    if (b >= B) continue;
+                    float ov = o[u];
+                    if (MODE == ELE) {
+                        const float e = (FC > 0) ? combine_children<F>(chs[u], cv[u]) : em[u];
+                        ov = (ov == PCX_NEG_INF || e == PCX_NEG_INF) ? PCX_NEG_INF : ov + e;
+                        if (!a.logspace) ov = __expf(ov);
+                        if (FC > 0 && a.nflows_direct != nullptr) {
+#pragma unroll
+                            for (int c = 0; c < F; ++c)
+                                if (chs[u][c] != 0) a.nflows_direct[(int64_t)chs[u][c] * B + b] = ov;
+                            continue;
+                        }
+                    }
+                    a.out[(base_row + r) * B + b] = ov;
+                }
+            }
+        }
+    }
+    if (failed && tid == 0) atomicCAS(&g_tc_status, 0, 100 * (MODE + 1) + sh.fail);
+    PCX_T(slot, 8);
+    return !failed;
+}
+
+// Barriers, status word and TMEM of a CTA; returns the TMEM base address.
+template <int TCOLS>
+__device__ __forceinline__ uint32_t lse_cta_setup(LseShared& sh, uint32_t* s_tmem) {
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&sh.bar[s], 1);
+        fence_mbar_init();
+        sh.fail = 0;
+    }
+    if (threadIdx.x < 32) tmem_alloc(s_tmem, TCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    return *s_tmem;
+}
+
+template <int MODE, bool SMALLK, int FC, int TN>
+__global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
+    constexpr int TCOLS = TN < 32 ? 32 : TN;           // TMEM columns to allocate
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ LseShared sh;
+    __shared__ uint32_t s_tmem;
+    const uint32_t tmem = lse_cta_setup<TCOLS>(sh, &s_tmem);
+    uint32_t ph[STAGES] = {0, 0};
+    lse_tile_body<MODE, SMALLK, FC, TN>(a, blockIdx.x, blockIdx.y, tmem, smem, sh, ph, nullptr, 0);
+    __syncthreads();
+    if (threadIdx.x < 32) tmem_dealloc(tmem, TCOLS);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Dataflow launch: every tile of a run of consecutive layers in ONE launch
+// ---------------------------------------------------------------------------------------------------------
+// Deep, narrow circuits (a tree-shaped model has one layer per level of the tree) spend their time in launch
+// boundaries: a layer with a handful of 128-row blocks cannot fill 148 SMs, and the next layer cannot start before
+// the last tile of this one has drained.  Batch columns are independent of one another, though, so the only true
+// dependency of tile (layer l, rows, columns j) is on the tiles of earlier layers with the same columns j.
+//
+// Work items (table, row tile, column tile) are enumerated layer by layer and claimed from a global counter in that
+// order.  A counter per (level, column tile) counts finished row tiles; an item of level t waits until the counter
+// of (t - 1, j) is complete, which, by induction, means every earlier level is complete for columns j.  An item is
+// only ever claimed after all items it can wait for have been claimed by CTAs that are already running, so the
+// scheme cannot deadlock whatever the number of resident CTAs; each wait is bounded all the same.
+struct ChainJob {
+    const uint4* packed;
+    const int32_t* rows;
+    const int32_t* kids;
+    const int32_t* fkids;
+    int64_t item_begin;
+    int32_t K, row_block, par_block, n_rowtiles;
+    int32_t level, prev_total;
+};
+static_assert(sizeof(ChainJob) == 64, "matches PcxChainJob");
+
+template <int MODE, int FC, int TN>
+__global__ void __launch_bounds__(NTH, 2)
+sum_chain_kernel(LseArgs a, const ChainJob* jobs, int n_jobs, int64_t n_items, int n_ct, int* ctrl) {
+    constexpr int TCOLS = TN < 32 ? 32 : TN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ LseShared sh;
+    __shared__ uint32_t s_tmem;
+    __shared__ int64_t s_item;
+    constexpr int kJobsInSmem = 128;
+    __shared__ __align__(16) ChainJob s_jobs[kJobsInSmem];   // copied with 16-byte accesses                    // small job tables are searched on chip
+    if (n_jobs <= kJobsInSmem) {
+        const uint4* src = reinterpret_cast<const uint4*>(jobs);
+        uint4* dst = reinterpret_cast<uint4*>(s_jobs);
+        for (int k = threadIdx.x; k < n_jobs * (int)(sizeof(ChainJob) / 16); k += NTH) dst[k] = src[k];
+        jobs = s_jobs;
+    }
+    const uint32_t tmem = lse_cta_setup<TCOLS>(sh, &s_tmem);
+    uint32_t ph[STAGES] = {0, 0};
+    int* done = ctrl + 64;                                      // [level][column tile] finished row tiles
+    unsigned long long* queue = reinterpret_cast<unsigned long long*>(ctrl);
+    // thread 0 claims one item ahead: the round trip of the claim overlaps the work on the current item
+    unsigned long long next = 0;
+    if (threadIdx.x == 0) next = atomicAdd(queue, 1ull);
+    for (;;) {
+        if (threadIdx.x == 0) s_item = (int64_t)next;
+        __syncthreads();
+        const int64_t item = s_item;
+        if (item >= n_items) break;
+        if (threadIdx.x == 0) next = atomicAdd(queue, 1ull);
+        PCX_T((int)item, 0);
+        int lo = 0, hi = n_jobs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (jobs[mid].item_begin <= item) lo = mid; else hi = mid - 1;
+        }
+        const ChainJob j = jobs[lo];
+        a.packed = j.packed; a.rows = j.rows; a.kids = j.kids; a.fkids = j.fkids;
+        a.K = j.K; a.row_block = j.row_block; a.par_block = j.par_block;
+        const int64_t t = item - j.item_begin;
+        const int ct = (int)(t / j.n_rowtiles);                 // column-tile major: lane 0 of a level is claimed first
+        const int64_t rt = t % j.n_rowtiles;
+        const int* wait_on = (j.level > 0) ? done + (j.level - 1) * n_ct + ct : nullptr;
+        const int KK = (MODE == FWD) ? j.K : j.K * j.par_block;
+        PCX_T((int)item, 1);
+        if (KK <= 2 * KC) lse_tile_body<MODE, true, FC, TN>(a, rt, ct, tmem, smem, sh, ph, wait_on, j.prev_total, (int)item);
+        else lse_tile_body<MODE, false, FC, TN>(a, rt, ct, tmem, smem, sh, ph, wait_on, j.prev_total, (int)item);
+        // publish: the barrier orders every thread's stores before thread 0's release (a tile that gave up still
+        // counts, so that the launch drains; the status word tells the host)
+        __syncthreads();
+        if (threadIdx.x == 0) red_release_add(done + j.level * n_ct + ct, 1);
+        PCX_T((int)item, 9);
+#ifdef PCX_TRACE
+        if (threadIdx.x == 0 && item < kTraceItems) { g_trace[item][10] = j.level; g_trace[item][11] = blockIdx.x; }
+#endif
     }
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, TCOLS);
+    if (threadIdx.x < 32) tmem_dealloc(tmem, TCOLS);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -494,6 +828,17 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
     const uint32_t idesc = idesc_bf16_f32(BM, BN);
     bool failed = false;
 
+    // child rows of this thread's two table entries: the same for every slice of the batch
+    constexpr int FK = FC > 0 ? FC : 4;
+    int chr[2][FK];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        if (FC > 0 && s_cid[rb + 32 * j] != 0) load_children<FK>(a.fkids + ((int64_t)i * a.K + e0 + rb + 32 * j) * FC, chr[j]);
+        else
+#pragma unroll
+            for (int c = 0; c < FK; ++c) chr[j][c] = 0;
+    }
+
     for (int c = c_begin; c < c_end; ++c) {
         const int it = c - c_begin, s = it % STAGES, use = it / STAGES;
         uint8_t* st = smem + s * PAR_STAGE_BYTES;
@@ -515,7 +860,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
                     float f = nf[t];
-                    if (!a.logspace) f = (f > 0.0f) ? logf(f) : PCX_NEG_INF;
+                    if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
                     x[j][t] = (nm[t] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[t];
                 }
             } else {
@@ -526,22 +871,31 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int cid = s_cid[rb + 32 * j];
-            if (FC > 0 && b_ok && cid != 0) {
-                // the product node's value is recomputed from its children: no element buffer involved
-                const int32_t* ch = a.fkids + ((int64_t)i * a.K + e0 + rb + 32 * j) * FC;
-                bool any = false;
+            if (FC > 0) {
+                // the product node's value is recomputed from its children (no element buffer involved); loads are
+                // unconditional -- row 0 exists and is not used -- so that all of them are in flight together
+                constexpr int F = FC > 0 ? FC : 4;
+                int r[F];
+#pragma unroll
+                for (int c = 0; c < F; ++c) r[c] = b_ok ? chr[j][c] : 0;
+                const int bbc = b_ok ? bb : 0;
+                float4 q[F][2];
+#pragma unroll
+                for (int c = 0; c < F; ++c) {
+                    q[c][0] = __ldcg(reinterpret_cast<const float4*>(a.node_mars + (int64_t)r[c] * B + bbc));
+                    q[c][1] = __ldcg(reinterpret_cast<const float4*>(a.node_mars + (int64_t)r[c] * B + bbc + 4));
+                }
+                int any = 0;
 #pragma unroll
                 for (int t = 0; t < 8; ++t) y[j][t] = 0.0f;
 #pragma unroll
-                for (int c = 0; c < (FC > 0 ? FC : 1); ++c) {
-                    const int cr = ch[c];
-                    if (cr != 0) {
-                        const float4 q0 = *reinterpret_cast<const float4*>(a.node_mars + (int64_t)cr * B + bb);
-                        const float4 q1 = *reinterpret_cast<const float4*>(a.node_mars + (int64_t)cr * B + bb + 4);
-                        y[j][0] += q0.x; y[j][1] += q0.y; y[j][2] += q0.z; y[j][3] += q0.w;
-                        y[j][4] += q1.x; y[j][5] += q1.y; y[j][6] += q1.z; y[j][7] += q1.w;
-                        any = true;
-                    }
+                for (int c = 0; c < F; ++c) {
+                    const bool on = r[c] != 0;
+                    any |= r[c];
+                    y[j][0] += on ? q[c][0].x : 0.0f; y[j][1] += on ? q[c][0].y : 0.0f;
+                    y[j][2] += on ? q[c][0].z : 0.0f; y[j][3] += on ? q[c][0].w : 0.0f;
+                    y[j][4] += on ? q[c][1].x : 0.0f; y[j][5] += on ? q[c][1].y : 0.0f;
+                    y[j][6] += on ? q[c][1].z : 0.0f; y[j][7] += on ? q[c][1].w : 0.0f;
                 }
                 if (!any) {
 #pragma unroll
@@ -588,7 +942,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
         for (int j = 0; j < 4; ++j) {
 #pragma unroll
             for (int t = 0; t < 8; ++t)
-                x[j][t] = (sh[t] == PCX_NEG_INF || x[j][t] == PCX_NEG_INF) ? 0.0f : expf(x[j][t] - sh[t]);
+                x[j][t] = (sh[t] == PCX_NEG_INF || x[j][t] == PCX_NEG_INF) ? 0.0f : __expf(x[j][t] - sh[t]);
             const int o = g * XSLAB + (rb + 32 * j) * 16;
             store_split8(reinterpret_cast<uint4*>(xhi + o), reinterpret_cast<uint4*>(xlo + o), x[j]);
         }
@@ -596,7 +950,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
         for (int j = 0; j < 2; ++j) {
 #pragma unroll
             for (int t = 0; t < 8; ++t)
-                y[j][t] = (sh[t] == PCX_NEG_INF || y[j][t] == PCX_NEG_INF) ? 0.0f : fminf(expf(y[j][t] + sh[t]), 3.0e38f);
+                y[j][t] = (sh[t] == PCX_NEG_INF || y[j][t] == PCX_NEG_INF) ? 0.0f : fminf(__expf(y[j][t] + sh[t]), 3.0e38f);
             const int o = g * YSLAB + (rb + 32 * j) * 16;
             store_split8(reinterpret_cast<uint4*>(yhi + o), reinterpret_cast<uint4*>(ylo + o), y[j]);
         }
@@ -725,12 +1079,42 @@ int launch_lse_fc(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
     return launch_lse_tn<MODE, FC, 16>(a, n_rows, st);
 }
 
+// 16-byte accesses in the epilogue need whole groups of eight samples and aligned buffers.
+inline int lse_vec_ok(const LseArgs& a) {
+    auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    return (a.B % 8 == 0 && al(a.out) && al(a.nmars) && al(a.emars) && al(a.nflows_direct)) ? 1 : 0;
+}
+
 template <int MODE>
-int launch_lse(const LseArgs& a, int64_t n_rows, int fc, cudaStream_t st) {
+int launch_lse(const LseArgs& a_in, int64_t n_rows, int fc, cudaStream_t st) {
+    LseArgs a = a_in;
+    a.vec = lse_vec_ok(a);
     switch (fc) {
         case 0: return launch_lse_fc<MODE, 0>(a, n_rows, st);
         case 4: return launch_lse_fc<MODE, 4>(a, n_rows, st);
         case 8: return launch_lse_fc<MODE, 8>(a, n_rows, st);
+        default: return -1;
+    }
+}
+
+template <int MODE, int FC, int TN>
+int launch_chain_tn(const LseArgs& a, const ChainJob* jobs, int n_jobs, int64_t n_items, int n_ct, int* ctrl,
+                    int n_ctas, cudaStream_t st) {
+    static bool done = false;
+    int rc = configure_once(sum_chain_kernel<MODE, FC, TN>, &done);
+    if (rc) return rc;
+    sum_chain_kernel<MODE, FC, TN><<<n_ctas, NTH, SMEM_BYTES, st>>>(a, jobs, n_jobs, n_items, n_ct, ctrl);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int MODE, int FC>
+int launch_chain_fc(const LseArgs& a, const ChainJob* jobs, int n_jobs, int64_t n_items, int tn, int n_ct, int* ctrl,
+                    int n_ctas, cudaStream_t st) {
+    switch (tn) {
+        case 64: return launch_chain_tn<MODE, FC, 64>(a, jobs, n_jobs, n_items, n_ct, ctrl, n_ctas, st);
+        case 32: return launch_chain_tn<MODE, FC, 32>(a, jobs, n_jobs, n_items, n_ct, ctrl, n_ctas, st);
+        case 16: return launch_chain_tn<MODE, FC, 16>(a, jobs, n_jobs, n_items, n_ct, ctrl, n_ctas, st);
         default: return -1;
     }
 }
@@ -899,6 +1283,43 @@ int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const flo
     return pcx_tc_launch_par(param_flows, node_flows, node_mars, nullptr, params, nids, cids, pids, pfids, fkids, fc,
                              n_blocks, K, block_size, B, logspace, (cudaStream_t)stream);
 }
+
+int pcx_sum_chain(int mode, float* node_mars, float* node_flows, const void* jobs, int n_jobs, int64_t n_items,
+                  int n_levels, int tn, int fc, int B, int logspace, int* ctrl, int64_t ctrl_len, void* stream) {
+    if (n_jobs <= 0 || n_items <= 0 || B <= 0) return 0;
+    if ((mode != 0 && mode != 1) || (fc != 4 && fc != 8) || n_levels <= 0) return -1;
+    const int n_ct = (int)pcx_cdiv(B, tn);
+    const int64_t need = 64 + (int64_t)n_levels * n_ct;
+    if (ctrl == nullptr || ctrl_len < need || (reinterpret_cast<uintptr_t>(ctrl) & 7) != 0) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemsetAsync(ctrl, 0, (size_t)need * sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+    LseArgs a{};
+    a.nmars = node_mars; a.B = B; a.terms = (g_sum_mode == 2) ? 1 : 3;
+    if (mode == 0) { a.out = node_mars; a.logspace = 1; }
+    else { a.lsrc = node_flows; a.lsrc2 = node_mars; a.nflows_direct = node_flows; a.logspace = logspace; }
+    a.vec = lse_vec_ok(a);
+    const int n_ctas = (int)(n_items < 2 * (int64_t)sms ? n_items : 2 * (int64_t)sms);
+    const ChainJob* cj = reinterpret_cast<const ChainJob*>(jobs);
+    if (mode == 0) {
+        return fc == 4 ? launch_chain_fc<FWD, 4>(a, cj, n_jobs, n_items, tn, n_ct, ctrl, n_ctas, st)
+                       : launch_chain_fc<FWD, 8>(a, cj, n_jobs, n_items, tn, n_ct, ctrl, n_ctas, st);
+    }
+    return fc == 4 ? launch_chain_fc<ELE, 4>(a, cj, n_jobs, n_items, tn, n_ct, ctrl, n_ctas, st)
+                   : launch_chain_fc<ELE, 8>(a, cj, n_jobs, n_items, tn, n_ct, ctrl, n_ctas, st);
+}
+
+#ifdef PCX_TRACE
+int pcx_trace_read(long long* host, int n_items) {
+    if (n_items > kTraceItems) n_items = kTraceItems;
+    cudaError_t e = cudaMemcpyFromSymbol(host, g_trace, (size_t)n_items * kTracePoints * sizeof(long long));
+    return (int)e;
+}
+#endif
 
 int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const float* node_mars, const float* params,
                             const void* jobs, int n_jobs, int64_t n_items, int fc, int B, int chunks_per_cta,

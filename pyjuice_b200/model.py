@@ -60,6 +60,8 @@ class TensorCircuit(nn.Module):
         self._optim_hyperparams = {"compute_param_flows": True, "flows_memory": 1.0}
         self._graphs = {}
         self.use_cuda_graphs = True
+        self.use_dataflow_launch = True       # runs of folded depths as one launch (tiles wait on counters)
+        self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
         self.default_propagation_alg = "LL"
         self._run_params = {}
         self._cum_flow_host = 0.0
@@ -218,6 +220,7 @@ class TensorCircuit(nn.Module):
         self._side_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self._graphs = {}
         self._par_job_cache = {}
+        self._chain_cache = {}
         self._cum_flow_dev = None
         return self
 
@@ -375,9 +378,89 @@ class TensorCircuit(nn.Module):
             return False
         return (not backward) or self.node_mars.size(1) % 8 == 0
 
+    def _launch_cfg(self):
+        """Everything that changes which kernels a pass launches (part of the key of a captured graph)."""
+        return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile)
+
+    def _chain_plan(self, B: int, mode: int):
+        """Job table of the dataflow launch (one launch for a run of consecutive depths) for the forward pass
+        (mode 0) or the element flows (mode 1), or None when fewer than two consecutive depths qualify.
+
+        A depth qualifies when its product layer is folded into the sum kernels (for mode 1 also: flows are stored
+        directly into the children's rows); the longest run of qualifying depths with one child-table width is used,
+        the other depths keep their per-layer launches."""
+        key = (B, mode, self._launch_cfg())
+        cache = self.__dict__.setdefault("_chain_cache", {})
+        if key in cache:
+            return cache[key]
+        groups = self.inner_layer_groups
+        plan = None
+        if self.use_dataflow_launch:
+            def ok(gi):
+                return self._fusion_on(gi, backward=(mode == 1)) and (mode == 0 or self._fused[gi]["direct"])
+            runs, cur = [], []
+            for gi in range(1, len(groups), 2):
+                if ok(gi) and (not cur or self._fused[cur[-1]]["fc"] == self._fused[gi]["fc"]):
+                    cur.append(gi)
+                else:
+                    if cur:
+                        runs.append(cur)
+                    cur = [gi] if ok(gi) else []
+            if cur:
+                runs.append(cur)
+            run = max(runs, key=len) if runs else []
+            if len(run) >= 2:
+                fc = self._fused[run[0]]["fc"]
+                levels = run if mode == 0 else run[::-1]
+                jobs = []                                   # (packed, rows, kids, fkids, K, row_block, par_block, n_rowtiles, level)
+                for level, gi in enumerate(levels):
+                    for layer in groups[gi]:
+                        f = layer._fusion
+                        if mode == 0:
+                            for p, (nids, cids, _, _) in enumerate(layer._dev["fw"]):
+                                jobs.append((layer._packed_fw[p], nids, cids, f["fw"][p], cids.size(1), layer.block_size, 1,
+                                             nids.numel() * (layer.block_size // 128), level))
+                        else:
+                            for p, ((chids, parids, _), cbs) in enumerate(zip(layer._dev["bk"], layer.cs_block_sizes)):
+                                jobs.append((layer._packed_bk[p], chids, parids, f["bk"][p], parids.size(1), cbs,
+                                             layer.block_size, chids.numel() * (cbs // 128), level))
+                level_tiles = [0] * len(levels)
+                for j in jobs:
+                    level_tiles[j[8]] += j[7]
+                tn = self.chain_tile
+                if tn is None:                               # widest tile that keeps about two tiles per SM in flight
+                    mean_tiles = sum(level_tiles) / len(levels)
+                    tn = next((t for t in (64, 32) if mean_tiles * (-(-B // t)) >= 296), 16)
+                n_ct = -(-B // tn)
+                rec = np.dtype([("packed", "<u8"), ("rows", "<u8"), ("kids", "<u8"), ("fkids", "<u8"), ("item_begin", "<i8"),
+                                ("K", "<i4"), ("row_block", "<i4"), ("par_block", "<i4"), ("n_rowtiles", "<i4"),
+                                ("level", "<i4"), ("prev_total", "<i4")])
+                table = np.zeros(len(jobs), dtype=rec)
+                begin = 0
+                for r, (packed, rows, kids, fk, K, rb, pb, nrt, level) in zip(table, jobs):
+                    r["packed"], r["rows"], r["kids"], r["fkids"] = (t.data_ptr() for t in (packed, rows, kids, fk))
+                    r["item_begin"], r["K"], r["row_block"], r["par_block"], r["n_rowtiles"] = begin, K, rb, pb, nrt
+                    r["level"], r["prev_total"] = level, (level_tiles[level - 1] if level > 0 else 0)
+                    begin += nrt * n_ct
+                plan = dict(lo=run[0], hi=run[-1], fc=fc, tn=tn, n_levels=len(levels), n_jobs=len(jobs), n_items=begin,
+                            jobs=torch.from_numpy(table.view(np.uint8)).to(self.device),
+                            ctrl=torch.zeros(64 + len(levels) * n_ct, dtype=torch.int32, device=self.device))
+        cache[key] = plan
+        return plan
+
+    def _launch_chain(self, plan, mode: int, logspace_flows: bool = True):
+        _lib.call("pcx_sum_chain", mode, self.node_mars, self.node_flows if mode == 1 else None, plan["jobs"],
+                  plan["n_jobs"], plan["n_items"], plan["n_levels"], plan["tn"], plan["fc"], self.node_mars.size(1),
+                  int(bool(logspace_flows)), plan["ctrl"], plan["ctrl"].numel())
+
     def _forward_inner(self):
         groups = self.inner_layer_groups
+        plan = self._chain_plan(self.node_mars.size(1), 0)
         for gi, group in enumerate(groups):
+            if plan is not None and plan["lo"] - 1 <= gi <= plan["hi"]:
+                if gi == plan["lo"]:
+                    self._launch_chain(plan, 0)
+                continue
             if group.is_prod():
                 if not self._fusion_on(gi + 1):
                     group.forward(self.node_mars, self.element_mars)
@@ -404,7 +487,7 @@ class TensorCircuit(nn.Module):
                 layer.forward(data, self.node_mars)
             if _lib.SUM_MODE != 0:
                 self._packer.refresh(self.params.data)       # outside any graph capture
-            self._run_inner(("fw", B, _lib.SUM_MODE, self.fuse_product_layers, self.params.data_ptr()), self._forward_inner)
+            self._run_inner(("fw", B, self._launch_cfg(), self.params.data_ptr()), self._forward_inner)
             lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
         if torch.is_grad_enabled():
             lls.requires_grad = True
@@ -458,8 +541,14 @@ class TensorCircuit(nn.Module):
         pf = self.param_flows if compute_param_flows else None
         groups = self.inner_layer_groups
         any_fused = False
+        plan = self._chain_plan(self.node_mars.size(1), 1)
         for gi in range(len(groups) - 1, -1, -1):
             group = groups[gi]
+            if plan is not None and plan["lo"] - 1 <= gi <= plan["hi"]:
+                any_fused = True
+                if gi == plan["hi"]:
+                    self._launch_chain(plan, 1, logspace_flows)
+                continue
             if group.is_prod():
                 if not (self._fusion_on(gi + 1, True) and self._fused[gi + 1]["direct"]):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
@@ -532,7 +621,7 @@ class TensorCircuit(nn.Module):
                 self.init_param_flows(flows_memory=flows_memory)
             if _lib.SUM_MODE != 0:
                 self._packer.refresh(self.params.data)
-            key = ("bk", B, bool(compute_param_flows), ls, _lib.SUM_MODE, self.fuse_product_layers, self.params.data_ptr(),
+            key = ("bk", B, bool(compute_param_flows), ls, self._launch_cfg(), self.params.data_ptr(),
                    self.param_flows.data_ptr() if compute_param_flows else 0)
             self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
 

@@ -163,6 +163,31 @@ def test_folded_product_layers_match_separate_kernels(name):
         assert torch.allclose(a, b, rtol=1e-4, atol=1e-6), (a - b).abs().max()
 
 
+@pytest.mark.parametrize("name,batch", [("hclt_b128", 64), ("hclt_b128", 200), ("hmm_b128", 72)])
+@pytest.mark.parametrize("tile", [None, 16, 32, 64])
+def test_dataflow_launch_matches_per_layer_launches(name, batch, tile):
+    """A run of depths executed as ONE launch whose tiles wait on counters must give exactly what the per-layer
+    launches give (same tiles, same arithmetic), for every tile width, with and without CUDA graphs, repeatedly
+    (the counters are cleared by every call)."""
+    pc = _build(name, seed=11).to(DEV)
+    x = _data_for(pc, batch, seed=3).to(DEV)
+    out = {}
+    for dataflow in (False, True):
+        pc.use_dataflow_launch = dataflow
+        pc.chain_tile = tile if dataflow else None
+        for rep in range(3 if dataflow else 1):              # eager, captured, replayed
+            pc.init_param_flows(flows_memory=0.0)
+            lls = pc(x)
+            pc.backward(x)
+            torch.cuda.synchronize()
+        out[dataflow] = (lls.clone(), pc.node_flows[pc.num_dummy_nodes:].exp().clone(), pc.param_flows.clone(),
+                         pc.input_layer_group[0].param_flows.clone())
+    if batch % 8 == 0:
+        assert pc._chain_plan(batch, 0) is not None and pc._chain_plan(batch, 1) is not None
+    for a, b in zip(out[True], out[False]):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-7), (a - b).abs().max()
+
+
 def test_no_kernel_reported_a_failed_wait():
     from pyjuice_b200 import _lib
     torch.cuda.synchronize()
