@@ -102,6 +102,8 @@ def circuit_stats(pc):
 def family_of(name: str) -> str:
     """Launch family of a C-ABI entry point: the variants of one operator (product layer folded in, pre-split
     parameter tiles, all layers in one launch, built-in scratch) count as that operator."""
+    if name.startswith("pcx_sum_chain"):                  # the dataflow launch: forward or element flows of many layers
+        return "pcx_sum_fwd" if name.endswith("_fwd") else "pcx_sum_bwd_ele"
     for suffix in ("_fused", "_packed", "_batched", "_noalloc"):
         if name.endswith(suffix):
             name = name[:-len(suffix)]
@@ -142,19 +144,26 @@ def family_work(stats, B, elsize):
 
 
 # DRAM bytes per step (read + write) of a launch family, from ncu captures of the same kernels; None = not captured
-TRAFFIC_PER_STEP = {}
+TRAFFIC_PER_STEP = {
+    # configs[1], B = 512: one dataflow launch each for the forward pass and the element flows, one batched launch
+    # for the parameter flows (profiles/ncu_full_cfg1_chain_par.md)
+    ("cfg1", "pcx_sum_fwd"): 389.1e6,
+    ("cfg1", "pcx_sum_bwd_ele"): 806.4e6,
+    ("cfg1", "pcx_sum_bwd_par"): 635.0e6,
+}
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi.  It is started well before the timed
+    regions (its start-up disturbs the GPU for a moment); only the samples that fall inside them are reported."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.windows = [], None, []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -163,7 +172,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def window(self, t0: float, t1: float):
+        self.windows.append((t0, t1))
 
     def stop(self):
         if self.proc is None:
@@ -173,10 +185,11 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        ok = [r for t, r in self.rows if len(r) >= 6 and any(a - 0.05 <= t <= b + 0.05 for a, b in self.windows)]
+        sm = [float(r[0]) for r in ok if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in ok if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        reasons = sorted({n for r in ok for n, v in zip(names, r[2:6]) if v.lower() == "active"})
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -215,7 +228,13 @@ def run_reference(args, rank):
     pc = pj.compile(ns)
     xc = torch.from_numpy(x)
     cores = torch.get_num_threads()
-    for _ in range(args.warmup if args.warmup < 2 else 1):
+    # one step at the full sample size tells how long K of them would take; the sample shrinks until the whole
+    # run fits in about two minutes (throughput of this CPU path is close to linear in the number of samples)
+    t_one = oracle_step_time(pc, xc)
+    budget = 120.0
+    if t_one * args.steps > budget and sample > 8:
+        sample = max(8, int(sample * budget / (t_one * args.steps)) // 8 * 8)
+        xc = xc[:sample]
         oracle_step_time(pc, xc)
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -236,8 +255,8 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--config", default="cfg1", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
@@ -267,6 +286,7 @@ def main():
     desc, B = CONFIGS[args.config]
     _lib.set_sum_mode(args.sum_mode)
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None      # started early: see the class comment
     n_batches = 4
     ns, x = build_workload(args.config, B * n_batches, seed_offset=rank)
     pc = pj.compile(ns).to(dev)
@@ -303,17 +323,20 @@ def main():
     pc.use_cuda_graphs = not args.no_graphs
     barrier()
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t0 = time.time()
     ev0.record()
     for i in range(K):
         step(resident[i % n_batches])
     ev1.record()
     barrier()
     ms_dev = ev0.elapsed_time(ev1)
+    if sampler:
+        sampler.window(t0, time.time())
 
     barrier()
+    t0 = time.time()
     ev0.record()
     last = 0.0
     for i in range(K):
@@ -322,6 +345,8 @@ def main():
     ev1.record()
     barrier()
     ms_e2e = ev0.elapsed_time(ev1)
+    if sampler:
+        sampler.window(t0, time.time())
     clocks = sampler.stop() if sampler else None
 
     t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)

@@ -176,8 +176,8 @@ int pcx_sum_chain(int mode, float* node_mars, float* node_flows, const void* job
  * different layers do not depend on one another, so after the backward sweep has produced every node flow the whole
  * circuit's parameter flows run as one grid.  `jobs` is a DEVICE array of n_jobs PcxParJob records; a table
  * contributes n_rows * (block_size / 128) * e_tiles * splits work items, `item_begin` is the running sum over the
- * preceding jobs, n_items the total.  Every work item handles `chunks_per_cta` 64-sample slices of the batch
- * (splits = ceil(ceil(B / 64) / chunks_per_cta), the same for every job).  In the reference this is one kernel
+ * preceding jobs, n_items the total.  Every work item handles `chunks_per_cta` 32-sample slices of the batch
+ * (splits = ceil(ceil(B / 32) / chunks_per_cta), the same for every job).  In the reference this is one kernel
  * launch per layer partition (layer/sum_layer.py:520-541). */
 typedef struct PcxParJob {
     const int32_t* nids;

@@ -41,9 +41,14 @@ constexpr int A_TILE = KG * BM * 16;     // 16 KB: one bf16 [128 x 64] operand t
 constexpr int B_TILE = KG * BN * 16;     //  8 KB: one bf16 [ 64 x 64] operand tile
 constexpr int STAGE_BYTES = 2 * A_TILE + 2 * B_TILE;          // A_hi, A_lo, B_hi, B_lo = 48 KB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
-// parameter-flow kernel: slabs padded by 16 B so that the 8 lanes that stage one row write 8 different banks
+// parameter-flow kernel: 128 threads work on slices of 32 samples, so that four CTAs fit on an SM and hide each
+// other's load latency and barrier waits; slabs are padded by 16 B so that the lanes that stage one row write
+// different banks
+constexpr int PNTH = 128;                // threads
+constexpr int PKC = 32;                  // samples (contraction depth) per shared-memory stage
+constexpr int PKG = PKC / 8;
 constexpr int XSLAB = BM * 16 + 16, YSLAB = BN * 16 + 16;
-constexpr int X_TILE = KG * XSLAB, Y_TILE = KG * YSLAB;
+constexpr int X_TILE = PKG * XSLAB, Y_TILE = PKG * YSLAB;
 constexpr int PAR_STAGE_BYTES = 2 * X_TILE + 2 * Y_TILE;
 constexpr int PAR_SMEM_BYTES = STAGES * PAR_STAGE_BYTES + 1024;
 static_assert(STAGES * STAGE_BYTES >= BM * (64 + 1) * 4, "epilogue transpose buffer aliases the stages");
@@ -96,7 +101,7 @@ __device__ __forceinline__ bool poll_counter(const int* ctr, int target) {
         int v;
         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
         if (v >= target) return true;
-        if (n > 64) __nanosleep(64);
+        if (n > 4096) __nanosleep(256);            // a long wait: stop hammering the counter
     }
     return false;
 }
@@ -106,14 +111,15 @@ __device__ __forceinline__ void red_release_add(int* ctr, int v) {
 
 // Issue the MMAs of one 64-deep stage: A tiles at `sa` (hi, then lo), B tiles at `sb` (hi, then lo).  A tile is
 // KG slabs of [rows][16 B]; consecutive slabs are ASLAB / BSLAB bytes apart (rows * 16, or that plus padding).
-template <int ASLAB = BM * 16, int BSLAB = BN * 16>
+template <int ASLAB = BM * 16, int BSLAB = BN * 16, int DEPTH = KC>
 __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t sa, uint32_t sb, uint32_t idesc, bool first, int terms) {
+    constexpr int GROUPS = DEPTH / 8;                 // 16-byte K groups per tile: the lo tile follows the hi tile
 #pragma unroll
-    for (int ks = 0; ks < KC / 16; ++ks) {
+    for (int ks = 0; ks < DEPTH / 16; ++ks) {
         const uint64_t dAh = smem_desc(sa + ks * 2 * ASLAB, ASLAB, 128);
-        const uint64_t dAl = smem_desc(sa + KG * ASLAB + ks * 2 * ASLAB, ASLAB, 128);
+        const uint64_t dAl = smem_desc(sa + GROUPS * ASLAB + ks * 2 * ASLAB, ASLAB, 128);
         const uint64_t dBh = smem_desc(sb + ks * 2 * BSLAB, BSLAB, 128);
-        const uint64_t dBl = smem_desc(sb + KG * BSLAB + ks * 2 * BSLAB, BSLAB, 128);
+        const uint64_t dBl = smem_desc(sb + GROUPS * BSLAB + ks * 2 * BSLAB, BSLAB, 128);
         mma_bf16_ss(tmem, dAh, dBh, idesc, (!first || ks > 0) ? 1u : 0u);
         if (terms == 3) {
             mma_bf16_ss(tmem, dAh, dBl, idesc, 1u);
@@ -391,6 +397,21 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
         if (MODE == ELE) pr_first = ele_static(q * 8, nm_first);
     }
     if (MODE == ELE && FC > 0 && vec) load_children<F>(a.fkids + ((int64_t)i * a.row_block + r0 + row) * FC, ch);
+    // ELE with 16-column tiles: the values of the 128 output elements (sums of child rows, static during the backward
+    // pass) are gathered now, with coalesced loads in the layout of the operand loads, and parked in the part of
+    // stage 0 that a 16-column B tile leaves unused; the epilogue reads them from there.
+    constexpr bool EMS = (MODE == ELE && FC > 0 && TN == 16);
+    float* em_tile = reinterpret_cast<float*>(smem + 2 * A_TILE + 2 * KG * BSLAB);      // [BM][TN + 1]
+    static_assert(!EMS || BM * (TN + 1) * 4 <= 2 * B_TILE - 2 * KG * BSLAB, "element values fit beside the B tile");
+    if (EMS && vec) {
+        int r[8][F];
+        float ev[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) load_children<F>(a.fkids + ((int64_t)i * a.row_block + r0 + q * 8 + j) * FC, r[j]);
+        group_values(r, ev);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) em_tile[(q * 8 + j) * (TN + 1) + lc] = ev[j];
+    }
     if (wait_on != nullptr) {
         if (tid == 0 && !poll_counter(wait_on, wait_for)) sh.fail = 3;
         __syncthreads();
@@ -483,7 +504,7 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
     // requested while the tensor core works
     float4 cq[F][2];
     const int cb0 = (b0 + c0 < B) ? b0 + c0 : 0;       // first column of this thread (clamped for the prefetch)
-    if (MODE == ELE && vec) {
+    if (MODE == ELE && vec && !EMS) {
         if (FC > 0) {
 #pragma unroll
             for (int c = 0; c < F; ++c) {
@@ -517,7 +538,7 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
                 float v[8];
                 tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
                 if (cb >= B) continue;
-                if (MODE == ELE && p > 0) {
+                if (MODE == ELE && p > 0 && !EMS) {
                     if (FC > 0) {
 #pragma unroll
                         for (int c = 0; c < F; ++c) {
@@ -538,7 +559,10 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
                 }
                 if (MODE == ELE) {
                     float em[8];
-                    if (FC > 0) {
+                    if (EMS) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) em[j] = em_tile[row * (TN + 1) + c0 + 8 * p + j];
+                    } else if (FC > 0) {
                         int any = 0;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) em[j] = 0.0f;
@@ -790,7 +814,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t s_bar[STAGES];
     __shared__ uint32_t s_tmem;
-    __shared__ float s_part[NTH / 32][KC];
+    __shared__ __align__(16) float s_part[PNTH / 32][PKC];
     __shared__ int s_cid[BN], s_pid[BN], s_pfid[BN];
     __shared__ int s_fail;
 
@@ -800,7 +824,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
     const int r0 = (int)(rowtile % tiles_r) * BM;
     const int e0 = etile * BN;
     const int B = a.B;
-    const int total_chunks = (B + KC - 1) / KC;
+    const int total_chunks = (B + PKC - 1) / PKC;
     const int c_begin = zsplit * a.chunks_per_cta;
     const int c_end = min(total_chunks, c_begin + a.chunks_per_cta);
 
@@ -824,7 +848,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
     const int64_t nid = (int64_t)a.nids[i] + r0;
 
     // staging role: 8-sample group g of the slice, rows rb + 32 j
-    const int g = tid & 7, rb = tid >> 3;
+    const int g = tid & (PKG - 1), rb = tid / PKG;
     const uint32_t idesc = idesc_bf16_f32(BM, BN);
     bool failed = false;
 
@@ -842,7 +866,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
     for (int c = c_begin; c < c_end; ++c) {
         const int it = c - c_begin, s = it % STAGES, use = it / STAGES;
         uint8_t* st = smem + s * PAR_STAGE_BYTES;
-        const int bb = c * KC + g * 8;                 // first sample of this thread's group
+        const int bb = c * PKC + g * 8;                 // first sample of this thread's group
         const bool b_ok = bb < B;                      // B is a multiple of 8: a group is all-in or all-out
 
         // issue every load of the slice first
@@ -916,23 +940,29 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
             float m = fmaxf(fmaxf(x[0][t], x[1][t]), fmaxf(x[2][t], x[3][t]));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+#pragma unroll
+            for (int o = PKG; o < 32; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             pm[t] = m;
         }
-        if (lane < 8) {
-#pragma unroll
-            for (int t = 0; t < 8; ++t) s_part[warp][lane * 8 + t] = pm[t];
+        if (lane < PKG) {
+            float4* dst = reinterpret_cast<float4*>(&s_part[warp][lane * 8]);
+            dst[0] = make_float4(pm[0], pm[1], pm[2], pm[3]);
+            dst[1] = make_float4(pm[4], pm[5], pm[6], pm[7]);
         }
         if (it >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
         __syncthreads();
         float sh[8];
+        {
+            const float4 p0 = *reinterpret_cast<const float4*>(&s_part[0][g * 8]);
+            const float4 p1 = *reinterpret_cast<const float4*>(&s_part[0][g * 8 + 4]);
+            sh[0] = p0.x; sh[1] = p0.y; sh[2] = p0.z; sh[3] = p0.w; sh[4] = p1.x; sh[5] = p1.y; sh[6] = p1.z; sh[7] = p1.w;
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
-            float m = s_part[0][g * 8 + t];
-#pragma unroll
-            for (int w = 1; w < NTH / 32; ++w) m = fmaxf(m, s_part[w][g * 8 + t]);
-            sh[t] = m;
+            for (int w = 1; w < PNTH / 32; ++w) {
+                const float4 q0 = *reinterpret_cast<const float4*>(&s_part[w][g * 8]);
+                const float4 q1 = *reinterpret_cast<const float4*>(&s_part[w][g * 8 + 4]);
+                sh[0] = fmaxf(sh[0], q0.x); sh[1] = fmaxf(sh[1], q0.y); sh[2] = fmaxf(sh[2], q0.z); sh[3] = fmaxf(sh[3], q0.w);
+                sh[4] = fmaxf(sh[4], q1.x); sh[5] = fmaxf(sh[5], q1.y); sh[6] = fmaxf(sh[6], q1.z); sh[7] = fmaxf(sh[7], q1.w);
+            }
         }
         uint8_t* xhi = st;
         uint8_t* xlo = st + X_TILE;
@@ -960,7 +990,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
         if (tid == 0 && !failed) {
             tc_fence_after_sync();
             const uint32_t sa = smem_u32(st);
-            issue_stage<XSLAB, YSLAB>(tmem, sa, sa + 2 * X_TILE, idesc, it == 0, a.terms);
+            issue_stage<XSLAB, YSLAB, PKC>(tmem, sa, sa + 2 * X_TILE, idesc, it == 0, a.terms);
             mma_commit(&s_bar[s]);
         }
     }
@@ -995,7 +1025,7 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
 }
 
 template <int FC>
-__global__ void __launch_bounds__(NTH, 2) sum_par_tc_kernel(const ParArgs a) {
+__global__ void __launch_bounds__(PNTH, 4) sum_par_tc_kernel(const ParArgs a) {
     par_tile_body<FC>(a, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
@@ -1017,7 +1047,7 @@ struct ParJob {
 };
 
 template <int FC>
-__global__ void __launch_bounds__(NTH, 2)
+__global__ void __launch_bounds__(PNTH, 4)
 sum_par_tc_batched(const ParJob* __restrict__ jobs, int n_jobs, ParArgs a) {
     const int64_t w = blockIdx.x;
     int lo = 0, hi = n_jobs - 1;
@@ -1132,7 +1162,7 @@ static int launch_par_fc(const ParArgs& a, dim3 grid, cudaStream_t st) {
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    sum_par_tc_kernel<FC><<<grid, NTH, PAR_SMEM_BYTES, st>>>(a);
+    sum_par_tc_kernel<FC><<<grid, PNTH, PAR_SMEM_BYTES, st>>>(a);
     cudaError_t e = cudaGetLastError();
     return (e == cudaSuccess) ? 0 : (int)e;
 }
@@ -1144,8 +1174,8 @@ int pcx_tc_launch_par(float* param_flows, const float* node_flows, const float* 
     ParArgs a{param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids,
               K, block_size, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1, fkids};
     const int64_t base = n_blocks * (block_size / BM) * pcx_cdiv(K, BN);
-    const int total_chunks = (int)pcx_cdiv(B, KC);
-    int64_t splits = pcx_cdiv(2 * 148, base);                  // aim at two CTAs per SM
+    const int total_chunks = (int)pcx_cdiv(B, PKC);
+    int64_t splits = pcx_cdiv(4 * 148, base);                  // aim at four CTAs per SM
     if (splits > total_chunks) splits = total_chunks;
     if (splits < 1) splits = 1;
     a.chunks_per_cta = (int)pcx_cdiv(total_chunks, splits);
@@ -1337,7 +1367,7 @@ int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const f
             if (e != cudaSuccess) return (int)e;
             done4 = true;
         }
-        sum_par_tc_batched<4><<<(unsigned)n_items, NTH, PAR_SMEM_BYTES, (cudaStream_t)stream>>>(
+        sum_par_tc_batched<4><<<(unsigned)n_items, PNTH, PAR_SMEM_BYTES, (cudaStream_t)stream>>>(
             reinterpret_cast<const ParJob*>(jobs), n_jobs, a);
     } else {
         if (!done8) {
@@ -1345,7 +1375,7 @@ int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const f
             if (e != cudaSuccess) return (int)e;
             done8 = true;
         }
-        sum_par_tc_batched<8><<<(unsigned)n_items, NTH, PAR_SMEM_BYTES, (cudaStream_t)stream>>>(
+        sum_par_tc_batched<8><<<(unsigned)n_items, PNTH, PAR_SMEM_BYTES, (cudaStream_t)stream>>>(
             reinterpret_cast<const ParJob*>(jobs), n_jobs, a);
     }
     PCX_LAUNCH_CHECK();

@@ -516,11 +516,11 @@ class TensorCircuit(nn.Module):
                         per_fc.setdefault(f["fc"], []).append(
                             (nids, cids, pids, pfids, f["fw"][p], K, layer.block_size,
                              nids.numel() * (layer.block_size // 128) * ((K + 63) // 64)))
-        total_chunks = (B + 63) // 64
+        total_chunks = (B + 31) // 32                                        # the kernel works on 32-sample slices
         out = []
         for fc, jobs in per_fc.items():
             base = sum(j[-1] for j in jobs)
-            splits = max(1, min(total_chunks, -(-8 * 148 // base)))          # about four waves of two CTAs per SM
+            splits = max(1, min(total_chunks, -(-8 * 148 // base)))          # at least two waves of four CTAs per SM
             chunks_per_cta = -(-total_chunks // splits)
             splits = -(-total_chunks // chunks_per_cta)
             table = np.zeros(len(jobs), dtype=rec)
