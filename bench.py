@@ -147,9 +147,9 @@ def family_work(stats, B, elsize):
 TRAFFIC_PER_STEP = {
     # configs[1], B = 512: one dataflow launch each for the forward pass and the element flows, one batched launch
     # for the parameter flows (profiles/ncu_full_cfg1_chain_par.md)
-    ("cfg1", "pcx_sum_fwd"): 389.1e6,
-    ("cfg1", "pcx_sum_bwd_ele"): 806.4e6,
-    ("cfg1", "pcx_sum_bwd_par"): 635.0e6,
+    ("cfg1", "pcx_sum_fwd"): 389.0e6,
+    ("cfg1", "pcx_sum_bwd_ele"): 801.4e6,
+    ("cfg1", "pcx_sum_bwd_par"): 636.3e6,
 }
 
 
