@@ -215,6 +215,11 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
         else:
             for layer in inner[gi - 1][1]:                           # recompute the product layer below
                 _prod_forward(layer, st.node_mars, st.element_mars)
+            # A product node without a sum parent at this depth has flow zero.  Its row of the shared buffer is not
+            # written below, so clear the buffer per depth (the reference clears it once per pass only,
+            # model/tensorcircuit.py:526-528, and lets such a row keep another depth's flow; that defect is
+            # deliberately not reproduced: the flows here are the true gradients, see tests/test_oracle_pins.py).
+            st.element_flows.fill_(NEG_INF)
             for layer in layers:
                 _sum_backward(layer, st, params, compute_param_flows)
     st.input_param_flows = []

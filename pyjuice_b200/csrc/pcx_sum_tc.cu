@@ -71,7 +71,6 @@ __device__ long long g_trace[kTraceItems][kTracePoints];
 
 __device__ int g_tc_status = 0;          // 0 ok; otherwise the code of the first bounded wait that gave up
 
-__device__ __forceinline__ uint32_t pack2(uint16_t a, uint16_t b) { return (uint32_t)a | ((uint32_t)b << 16); }
 
 // Eight fp32 values -> eight bf16 "hi" parts and eight bf16 "lo" parts (x ~= hi + lo), two values per conversion.
 __device__ __forceinline__ void store_split8(uint4* hi, uint4* lo, const float* x) {
@@ -386,9 +385,8 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
     int r_first[8][F];
     float nm_first[8];
     int pr_first = 0;
-    // epilogue role (see below): this thread finishes HC samples of one output row
-    const int lq = warp & 3, c0 = (warp >> 2) * HC;
-    const int row = lq * 32 + lane;
+    // epilogue role: this thread finishes HC samples of one output row
+    const int erow = (warp & 3) * 32 + lane;
     const bool vec = a.vec != 0;
     int ch[F];
     if (SMALLK) {
@@ -396,7 +394,7 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
         if (MODE == FWD && FC > 0) group_index(q * 8, r_first);
         if (MODE == ELE) pr_first = ele_static(q * 8, nm_first);
     }
-    if (MODE == ELE && FC > 0 && vec) load_children<F>(a.fkids + ((int64_t)i * a.row_block + r0 + row) * FC, ch);
+    if (MODE == ELE && FC > 0 && vec) load_children<F>(a.fkids + ((int64_t)i * a.row_block + r0 + erow) * FC, ch);
     // ELE with 16-column tiles: the values of the 128 output elements (sums of child rows, static during the backward
     // pass) are gathered now, with coalesced loads in the layout of the operand loads, and parked in the part of
     // stage 0 that a 16-column B tile leaves unused; the epilogue reads them from there.
@@ -452,6 +450,31 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
     // ---- pass 2: exponentials -> bf16 hi/lo operand tiles, multiply -----------------------------------------
     const uint32_t idesc = idesc_bf16_f32(BM, TN);
     bool failed = false;
+    // Deep tables: the tensor core adds every product into its fp32 accumulator with truncation, which biases a
+    // sum of hundreds of MMAs low by about 3e-8 per MMA (2e-5 for a 4096-deep table, 2.5e-3 nats after 128 such
+    // layers).  So the sum is taken out of TMEM every kFlush chunks (48 MMAs) and carried in registers, where the
+    // additions round to nearest; two accumulators alternate, so the tensor core never waits for the read-out.
+    constexpr int kFlush = 4;
+    constexpr int ACC_COLS = TN < 32 ? 32 : TN;
+    const int lq = warp & 3, c0 = (warp >> 2) * HC;    // epilogue role: HC samples of output row lq * 32 + lane
+    const int row = lq * 32 + lane;
+    float accr[SMALLK ? 1 : HC];
+    int drained = 0;
+    if (!SMALLK)
+#pragma unroll
+        for (int j = 0; j < HC; ++j) accr[j] = 0.0f;
+    auto drain = [&](int which) {
+        if (!SMALLK) {
+#pragma unroll
+            for (int p = 0; p < HC / 8; ++p) {
+                float v[8];
+                tmem_ld<8>(tmem + which * ACC_COLS + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) accr[8 * p + j] += v[j];
+            }
+            tc_fence_before_sync();
+        }
+    };
     if (SMALLK) {
 #pragma unroll
         for (int h = 0; h < NGS; ++h) {
@@ -476,6 +499,12 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
             const int s = c % STAGES, use = c / STAGES;
             uint8_t* st = smem + s * STAGE_BYTES;
             if (c >= STAGES && !failed && !mbar_wait(&sh.bar[s], (ph[s] + use - 1) & 1)) { failed = true; sh.fail = 1; }
+            // chunk c - 2 is complete: if it closed a group of kFlush chunks, move that group's sum to registers
+            if (c >= STAGES && (c - STAGES + 1) % kFlush == 0 && !failed) {
+                tc_fence_after_sync();
+                drain(((c - STAGES) / kFlush) & 1);
+                ++drained;
+            }
             copy_a(c, st);
             for (int g = q; g < KG; g += TPC) {
                 float v[8];
@@ -489,7 +518,8 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
             if (tid == 0 && !failed) {
                 tc_fence_after_sync();
                 const uint32_t sa = smem_u32(st);
-                issue_stage<BM * 16, BSLAB>(tmem, sa, sa + 2 * A_TILE, idesc, c == 0, a.terms);
+                issue_stage<BM * 16, BSLAB>(tmem + ((c / kFlush) & 1) * ACC_COLS, sa, sa + 2 * A_TILE, idesc,
+                                            c % kFlush == 0, a.terms);
                 mma_commit(&sh.bar[s]);
             }
         }
@@ -530,13 +560,20 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
     PCX_T(slot, 6);
     failed = failed || (sh.fail != 0);
     tc_fence_after_sync();
+    if (!SMALLK && !failed) {                              // groups of chunks whose sum is still in TMEM
+        const int groups = (n_chunks + kFlush - 1) / kFlush;
+        for (int g = drained; g < groups; ++g) drain(g & 1);
+    }
     if (vec) {
         if (!failed) {
 #pragma unroll
             for (int p = 0; p < HC / 8; ++p) {
                 const int cb = b0 + c0 + 8 * p;                     // B % 8 == 0: a piece is all in or all out
                 float v[8];
-                tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
+                if (SMALLK) tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
+                else
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = accr[SMALLK ? 0 : 8 * p + j];
                 if (cb >= B) continue;
                 if (MODE == ELE && p > 0 && !EMS) {
                     if (FC > 0) {
@@ -611,7 +648,10 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
         float* T = reinterpret_cast<float*>(smem);            // [BM][TN + 1], aliases the (now idle) stages
         if (!failed) {
             float v[HC];
-            tmem_ld<HC>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)c0, v);
+            if (SMALLK) tmem_ld<HC>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)c0, v);
+            else
+#pragma unroll
+                for (int j = 0; j < HC; ++j) v[j] = accr[SMALLK ? 0 : j];
 #pragma unroll
             for (int j = 0; j < HC; ++j) {
                 const float m = sh.smax[c0 + j];
@@ -690,7 +730,7 @@ __device__ __forceinline__ uint32_t lse_cta_setup(LseShared& sh, uint32_t* s_tme
 
 template <int MODE, bool SMALLK, int FC, int TN>
 __global__ void __launch_bounds__(NTH, 2) sum_lse_tc_kernel(const LseArgs a) {
-    constexpr int TCOLS = TN < 32 ? 32 : TN;           // TMEM columns to allocate
+    constexpr int TCOLS = 2 * (TN < 32 ? 32 : TN);     // TMEM columns: two accumulators (see kFlush)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ LseShared sh;
@@ -729,7 +769,7 @@ static_assert(sizeof(ChainJob) == 64, "matches PcxChainJob");
 template <int MODE, int FC, int TN>
 __global__ void __launch_bounds__(NTH, 2)
 sum_chain_kernel(LseArgs a, const ChainJob* jobs, int n_jobs, int64_t n_items, int n_ct, int* ctrl) {
-    constexpr int TCOLS = TN < 32 ? 32 : TN;
+    constexpr int TCOLS = 2 * (TN < 32 ? 32 : TN);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ LseShared sh;

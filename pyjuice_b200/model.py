@@ -147,9 +147,45 @@ class TensorCircuit(nn.Module):
                                  for src, item in node2tiednodes.items() if len(item[0]) > 1]
         self.par_update_kwargs = compile_par_update(self.root_ns)
         self._em_blocks = self._compile_em_blocks()
+        self._parentless = self._find_parentless_products()
         self.num_root_nodes = self.root_ns.num_nodes
         self._root_node_range = (self.num_nodes - self.num_root_nodes, self.num_nodes)
         self._init_parameters()
+
+    def _find_parentless_products(self):
+        """Element ranges of the product groups that hold a node without any sum parent in the group above.
+
+        Block-sparse sum vectors (e.g. PD with a cap on connections per block) may list a product vector as a child
+        without connecting every one of its blocks.  Such a product has flow zero, but its row of the shared
+        ``element_flows`` buffer is never written by the element-flow kernels of that depth, and the product backward
+        pass, whose tables list every product of the layer (layer/compilation.py:980-1040), would hand the row's
+        stale content — the flow of another depth's product with the same element id — down to the children.  The
+        reference resets the buffer once per backward pass only (model/tensorcircuit.py:526-528), so it has this
+        defect; here the element range of such a group is reset before the group's element flows are computed, which
+        makes the flows the true gradients (checked against autograd in tests/test_oracle_pins.py)."""
+        out = {}
+        groups = self.inner_layer_groups
+        for gi in range(0, len(groups) - 1, 2):
+            lo = min(l._layer_nid_range[0] for l in groups[gi])
+            hi = max(l._layer_nid_range[1] for l in groups[gi])
+            has_parent = torch.zeros(hi, dtype=torch.bool)
+            for layer in groups[gi + 1]:
+                for chids, cbs in zip(layer.partitioned_chids, layer.cs_block_sizes):
+                    rows = (chids.cpu()[:, None] + torch.arange(cbs)[None, :]).reshape(-1)
+                    has_parent[rows] = True
+            exists = torch.zeros(hi, dtype=torch.bool)
+            for layer in groups[gi]:
+                for nids in layer.partitioned_nids:
+                    rows = (nids.cpu()[:, None] + torch.arange(layer.block_size)[None, :]).reshape(-1)
+                    exists[rows] = True
+            if bool((exists & ~has_parent).any()):
+                out[gi] = (lo, hi)
+        return out
+
+    def _reset_parentless(self, prod_gi: int, logspace_flows: bool):
+        rng = self._parentless.get(prod_gi)
+        if rng is not None:
+            _fill(self.element_flows[rng[0]:rng[1]], NEG_INF if logspace_flows else 0.0)
 
     def _compile_em_blocks(self):
         """Per node block of every untied sum vector: first parameter, first flow, real fan-in, block size —
@@ -554,11 +590,14 @@ class TensorCircuit(nn.Module):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
             elif self._fusion_on(gi, True):
                 any_fused = True
+                if not self._fused[gi]["direct"]:
+                    self._reset_parentless(gi - 1, logspace_flows)
                 for layer in group:
                     layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
             else:
                 # the shared element buffer holds another depth by now: recompute this depth's products
                 groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
+                self._reset_parentless(gi - 1, logspace_flows)
                 group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
                                self.params.data, param_flows=pf, logspace_flows=logspace_flows)
         if any_fused and pf is not None:
@@ -756,6 +795,7 @@ class TensorCircuit(nn.Module):
             return self.node_flows[s:e, :].detach()
         gi = self._prod_layer_of(ns)
         self.inner_layer_groups[gi].forward(self.node_mars, self.element_mars, _for_backward=True)
+        self._reset_parentless(gi, self._run_params.get("logspace_flows", True))
         self.inner_layer_groups[gi + 1].backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
                                                  self.params.data, param_flows=None,
                                                  logspace_flows=self._run_params.get("logspace_flows", True))

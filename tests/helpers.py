@@ -26,7 +26,7 @@ def oracle_step(pc, x, step=None, pseudo=0.0, params=None, input_params=None, ll
     return lls, st, new
 
 
-def check_against_oracle(pc, x, step=0.1, pseudo=0.1, logspace_flows=True):
+def check_against_oracle(pc, x, step=0.1, pseudo=0.1, logspace_flows=True, rtol=REL_TOL):
     """One forward + backward + EM step on the GPU, compared with the oracle.  Returns a dict of worst errors."""
     dev = pc.device
     p0 = pc.params.data.detach().cpu().clone()
@@ -42,19 +42,19 @@ def check_against_oracle(pc, x, step=0.1, pseudo=0.1, logspace_flows=True):
 
     nf = pc.node_flows.double().cpu()
     nf = nf.exp() if logspace_flows else nf
-    ok, out["node_flows"] = rel_close(nf[pc.num_dummy_nodes:], st.node_flows.exp()[pc.num_dummy_nodes:])
+    ok, out["node_flows"] = rel_close(nf[pc.num_dummy_nodes:], st.node_flows.exp()[pc.num_dummy_nodes:], rtol)
     assert ok, f"node flows rel err {out['node_flows']}"
-    ok, out["param_flows"] = rel_close(pc.param_flows, st.param_flows)
+    ok, out["param_flows"] = rel_close(pc.param_flows, st.param_flows, rtol)
     assert ok, f"sum parameter flows rel err {out['param_flows']}"
     for layer, ref in zip(pc.input_layer_group, st.input_param_flows):
-        ok, out["input_flows"] = rel_close(layer.param_flows, ref)
+        ok, out["input_flows"] = rel_close(layer.param_flows, ref, rtol)
         assert ok, f"input parameter flows rel err {out['input_flows']}"
 
     pc.mini_batch_em(step_size=step, pseudocount=pseudo)
-    ok, out["params"] = rel_close(pc.params.data[pc.num_dummy_params:], ref_p[pc.num_dummy_params:])
+    ok, out["params"] = rel_close(pc.params.data[pc.num_dummy_params:], ref_p[pc.num_dummy_params:], rtol)
     assert ok, f"post-EM sum parameters rel err {out['params']}"
     for layer, ref in zip(pc.input_layer_group, ref_ip):
-        ok, out["input_params"] = rel_close(layer.params.data, ref)
+        ok, out["input_params"] = rel_close(layer.params.data, ref, rtol)
         assert ok, f"post-EM input parameters rel err {out['input_params']}"
     torch.cuda.synchronize()
     return out

@@ -188,6 +188,29 @@ def test_dataflow_launch_matches_per_layer_launches(name, batch, tile):
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-7), (a - b).abs().max()
 
 
+@pytest.mark.parametrize("latents", [2, 8, 64])
+def test_products_without_a_parent_receive_no_flow(latents):
+    """Block-sparse sum vectors can leave product blocks without a parent (Poon-Domingos circuits do).  Their rows
+    of the shared element-flow buffer are not written by the element-flow kernels; they must read as "no flow" on
+    every pass — eager, captured and replayed — not as whatever another depth or the previous pass left there."""
+    import random
+    torch.manual_seed(0)
+    random.seed(0)
+    ns = pj.structures.PD((8, 8), num_latents=latents, split_points=[[2, 4, 6], [2, 4, 6]], num_cats=4)
+    ns.init_parameters()
+    pc = pj.compile(ns).to(DEV)
+    x = torch.randint(0, 4, (64, pc.num_vars))
+    if latents == 2:
+        assert len(pc._parentless) > 0
+    for rep in range(4):
+        errs = check_against_oracle(pc, x, step=0.05, pseudo=0.1)
+    layer = pc.input_layer_group[0]
+    s, e = layer._output_ind_range
+    per_var = torch.zeros(pc.num_vars, 64, device=DEV)
+    per_var.index_add_(0, layer.vids[:, 0].to(DEV), pc.node_flows[s:e].exp())
+    assert (per_var - 1.0).abs().max().item() < 1e-4
+
+
 def test_no_kernel_reported_a_failed_wait():
     from pyjuice_b200 import _lib
     torch.cuda.synchronize()

@@ -8,6 +8,7 @@ tests/model/homogeneous_hmm_test.py:98-212 verify).  The tables driving the orac
 bit-for-bit against the reference compiler in test_tables_golden.py.
 """
 import numpy as np
+import pytest
 import torch
 
 import pyjuice_b200 as pj
@@ -204,3 +205,51 @@ def test_flow_invariants_on_cfg0_shape():
             assert torch.allclose(sums, torch.ones_like(sums), atol=1e-6)
     ip = new_inputs[0].reshape(-1, 4).sum(dim=1)
     assert torch.allclose(ip, torch.ones_like(ip), atol=1e-6)
+
+
+@pytest.mark.parametrize("case", ["pd_parentless", "hclt", "hmm", "rat"])
+def test_oracle_flows_are_the_gradients_of_the_log_likelihood(case):
+    """Pin the oracle's backward pass against a second evaluator that shares no code with it: a recursive walk of
+    the node DAG with torch autograd (tests/dag_autograd.py).  Flow of a node = d log p(x) / d log value(node).
+
+    ``pd_parentless`` is a Poon-Domingos circuit in which block-sparse sum vectors leave some product blocks
+    without a parent.  The reference hands the stale content of their rows of the shared element-flow buffer down
+    to the children (it clears the buffer once per backward pass, model/tensorcircuit.py:526-528, while its
+    backward tables skip child blocks without parents, layer/sum_layer.py:273-275); the oracle and the CUDA path
+    deliberately do not: such a product has flow zero.  Also checked: the leaves of every variable receive a total
+    flow of exactly one per sample."""
+    import random
+    from dag_autograd import true_flows
+    torch.manual_seed(0)
+    random.seed(0)
+    if case == "pd_parentless":
+        ns = pj.structures.PD((8, 8), num_latents=2, split_points=[[2, 4, 6], [2, 4, 6]], num_cats=4)
+    elif case == "hclt":
+        x0 = torch.randint(0, 4, (200, 10))
+        ns = pj.structures.HCLT(x0.float(), num_latents=4, num_cats=4)
+    elif case == "hmm":
+        ns = pj.structures.HMM(seq_length=6, num_latents=8, num_emits=5, homogeneous=True)
+    else:
+        ns = pj.structures.RAT_SPN(num_vars=12, num_latents=4, depth=2, num_repetitions=3, num_cats=4)
+    ns.init_parameters()
+    pc = pj.compile(ns)
+    layer = pc.input_layer_group[0]
+    cats = int(layer.node_cats.min())
+    x = torch.randint(0, cats, (3, pc.num_vars))
+    params = pc.params.data.double()
+    iparams = [l.params.data.double() for l in pc.input_layer_group]
+    lls, st = orc.forward(pc, x, params, iparams)
+    orc.backward(pc, x, params, iparams, st)
+
+    ref_lls, flows, order = true_flows(pc, ns, st.node_mars)
+    assert torch.allclose(ref_lls.reshape(-1), lls.reshape(-1).double(), atol=1e-9)
+    if case == "pd_parentless":
+        assert len(pc._parentless) > 0, "the case is meant to contain product blocks without a parent"
+    for n in order:
+        if id(n) in flows:
+            s, e = n._output_ind_range
+            assert torch.allclose(st.node_flows[s:e].exp().double(), flows[id(n)], atol=1e-9), (case, s, e)
+    s, e = layer._output_ind_range
+    per_var = torch.zeros(pc.num_vars, x.size(0), dtype=torch.float64)
+    per_var.index_add_(0, layer.vids[:, 0], st.node_flows[s:e].exp().double())
+    assert torch.allclose(per_var, torch.ones_like(per_var), atol=1e-9)
