@@ -104,7 +104,9 @@ def family_of(name: str) -> str:
     parameter tiles, all layers in one launch, built-in scratch) count as that operator."""
     if name.startswith("pcx_sum_chain"):                  # the dataflow launch: forward or element flows of many layers
         return "pcx_sum_fwd" if name.endswith("_fwd") else "pcx_sum_bwd_ele"
-    for suffix in ("_fused", "_packed", "_batched", "_noalloc"):
+    if name.startswith("pcx_sum_par_dense"):              # operand staging + one product: the parameter flows
+        return "pcx_sum_bwd_par"
+    for suffix in ("_fused", "_packed", "_batched", "_noalloc", "_dense"):
         if name.endswith(suffix):
             name = name[:-len(suffix)]
     return name

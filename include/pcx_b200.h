@@ -146,6 +146,41 @@ int pcx_sum_bwd_par_fused(float* param_flows, const float* node_flows, const flo
                           const int32_t* fkids, int fc, int64_t n_blocks, int K, int block_size, int B, int logspace,
                           void* stream);
 
+/* ---- Dense layers (tables hundreds to thousands deep, e.g. 4096 x 4096 HMM transition layers) ----------------------
+ * Two steps per call: an operand pre-pass (column maxima, exp, bf16 hi/lo split, written as ready-made operand tiles to
+ * `scratch`) and a GEMM over pre-tiled operands (bulk copies global -> shared memory, four-stage ring, tcgen05, eight
+ * TMEM accumulators).  Requirements: block sizes multiples of 128 (parents: of 8), B a multiple of 64, parameters
+ * pre-split with pcx_pack_sum_params.  Rows of the table that list the same children (parents) share one operand:
+ * row_group[i] is the group of table row i, group_row[g] one row of group g.  `scratch` is caller-owned, 256-byte
+ * aligned, at least pcx_dense_scratch_bytes(n_groups, depth, B) bytes (depth = K, or P * block_size for the element
+ * flows).  Same results as pcx_sum_fwd / pcx_sum_bwd_ele (layer/sum_layer.py:551-929, 1369-1719). */
+int64_t pcx_dense_scratch_bytes(int n_groups, int depth, int B);
+int pcx_sum_fwd_dense(float* node_mars, const float* element_mars, const void* packed, const int32_t* nids,
+                      const int32_t* cids, const int32_t* row_group, const int32_t* group_row, int n_groups,
+                      void* scratch, int64_t scratch_bytes, int64_t n_blocks, int K, int block_size, int B,
+                      void* stream);
+int pcx_sum_bwd_ele_dense(float* element_flows, const float* element_mars, const float* node_flows,
+                          const float* node_mars, const void* packed, const int32_t* chids, const int32_t* parids,
+                          const int32_t* row_group, const int32_t* group_row, int n_groups, void* scratch,
+                          int64_t scratch_bytes, int64_t n_blocks, int P, int block_size, int ch_block_size, int B,
+                          int logspace, void* stream);
+
+/* Parameter flows of dense layers (layer/sum_layer.py:1721-2080).  The contraction runs over the batch; layers that
+ * share their parameter and flow tables (tied layers) are contracted in ONE product whose contraction dimension is
+ * the concatenation of their batches.  Step 1, once per layer while element_mars holds that layer's products:
+ * pcx_sum_par_dense_stage writes the layer's operand tiles into chunk columns [slot * cpl, (slot + 1) * cpl),
+ * cpl = ceil(B / 64), of x_tiles ([row tiles][n_chunks_total] tiles of 32 KB) and y_tiles ([ceil(K / 64)]
+ * [n_chunks_total] tiles of 16 KB); every table row must list the same children (cids = the row of table row 0);
+ * `work` holds (ceil(n_blocks * block_size / 64) + 1) * B floats.  Step 2, once per group: pcx_sum_par_dense_gemm adds
+ * params[pids[i,e] + n] * sum_b x[n,b] y[e,b] to param_flows[pfids[i,e] + n]. */
+int pcx_sum_par_dense_stage(void* x_tiles, void* y_tiles, float* work, const float* node_flows,
+                            const float* node_mars, const float* element_mars, const int32_t* nids,
+                            const int32_t* cids, int64_t n_blocks, int K, int block_size, int B, int n_chunks_total,
+                            int slot, int logspace, void* stream);
+int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* x_tiles, const void* y_tiles,
+                           const int32_t* cids, const int32_t* pids, const int32_t* pfids, int64_t n_blocks, int K,
+                           int block_size, int n_chunks_total, void* stream);
+
 /* Forward (mode 0) or element flows (mode 1) of a RUN of consecutive layers in one launch, product layers folded in
  * (as pcx_sum_fwd_fused / pcx_sum_bwd_ele_fused with direct stores).  Tiles are work items claimed from a device
  * counter in layer order; a tile of level t starts as soon as the tiles of level t - 1 that cover the same batch

@@ -94,6 +94,15 @@ class ParamPacker:
     def nbytes(self):
         return sum(e["buf"].numel() for e in self.entries.values())
 
+    def scratch(self, nbytes: int) -> torch.Tensor:
+        """Operand scratch of the dense sum kernels: one buffer, shared by all layers (they run one after the other);
+        ``grown`` counts re-allocations, so that captured CUDA graphs that hold the old address can be dropped."""
+        buf = getattr(self, "_scratch", None)
+        if buf is None or buf.numel() < nbytes:
+            self._scratch = buf = torch.empty(int(nbytes), dtype=torch.uint8, device=self.device)
+            self.grown = getattr(self, "grown", 0) + 1
+        return buf
+
 
 class Layer:
     def __init__(self, nodes):
@@ -355,7 +364,30 @@ class SumLayer(Layer, nn.Module):
                         key = ("bk", bs, cbs, tuple(parids.shape), cpu_tables["partitioned_parpids"][p].numpy().tobytes(),
                                (cpu_tables["partitioned_parids"][p] != 0).numpy().tobytes())
                         self._packed_bk[p] = packer.register(key, chids.numel(), parids.size(1), cbs, bs, 1, parids, parpids)
+            # rows of a table that list the same children (parents) share one tensor-core operand in the dense kernels
+            def groups_of(table):
+                uniq, inverse = torch.unique(table, dim=0, return_inverse=True)
+                first = torch.full((uniq.size(0),), table.size(0), dtype=torch.int64)
+                first.scatter_reduce_(0, inverse, torch.arange(table.size(0)), reduce="amin")
+                return _dev_i32(inverse, device), _dev_i32(first, device), int(uniq.size(0))
+            self._groups_fw = [groups_of(t) for t in cpu_tables["partitioned_cids"]]
+            self._groups_bk = [groups_of(t) for t in cpu_tables["partitioned_parids"]]
         return self
+
+    # Tables at least this deep take the two-step dense path (operand pre-pass + GEMM over pre-tiled operands).
+    DENSE_MIN_DEPTH = 512
+
+    def _dense_ok(self, p: int, B: int, backward: bool) -> bool:
+        if not self.use_dense_kernels or B % 64 != 0 or _lib.SUM_MODE == 0:
+            return False
+        if backward:
+            return self._packed_bk[p] is not None and self._dev["bk"][p][1].size(1) * self.block_size >= self.DENSE_MIN_DEPTH
+        return self._packed_fw[p] is not None and self._dev["fw"][p][1].size(1) >= self.DENSE_MIN_DEPTH
+
+    def _dense_scratch(self, n_groups: int, depth: int, B: int) -> torch.Tensor:
+        return self._packer.scratch(int(_lib.load().pcx_dense_scratch_bytes(n_groups, depth, B)))
+
+    use_dense_kernels = True
 
     def _use_packed(self, params):
         if self._packer is None or _lib.SUM_MODE == 0:
@@ -374,7 +406,12 @@ class SumLayer(Layer, nn.Module):
         B = node_mars.size(1)
         packed = self._use_packed(params)
         for p, (nids, cids, pids, _) in enumerate(self._dev["fw"]):
-            if packed and self._packed_fw[p] is not None:
+            if packed and self._dense_ok(p, B, False):
+                row_group, group_row, n_groups = self._groups_fw[p]
+                scratch = self._dense_scratch(n_groups, cids.size(1), B)
+                _lib.call("pcx_sum_fwd_dense", node_mars, element_mars, self._packed_fw[p], nids, cids, row_group,
+                          group_row, n_groups, scratch, scratch.numel(), nids.numel(), cids.size(1), self.block_size, B)
+            elif packed and self._packed_fw[p] is not None:
                 _lib.call("pcx_sum_fwd_packed", node_mars, element_mars, self._packed_fw[p], nids, cids,
                           nids.numel(), cids.size(1), self.block_size, B)
             else:
@@ -416,14 +453,24 @@ class SumLayer(Layer, nn.Module):
         ls = int(bool(logspace_flows))
         packed = self._use_packed(params)
         for p, ((chids, parids, parpids), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
-            if packed and self._packed_bk[p] is not None:
+            if packed and self._dense_ok(p, B, True):
+                row_group, group_row, n_groups = self._groups_bk[p]
+                scratch = self._dense_scratch(n_groups, parids.size(1) * self.block_size, B)
+                _lib.call("pcx_sum_bwd_ele_dense", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p],
+                          chids, parids, row_group, group_row, n_groups, scratch, scratch.numel(), chids.numel(),
+                          parids.size(1), self.block_size, cbs, B, ls)
+            elif packed and self._packed_bk[p] is not None:
                 _lib.call("pcx_sum_bwd_ele_packed", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p],
                           chids, parids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
             else:
                 _lib.call("pcx_sum_bwd_ele", element_flows, element_mars, node_flows, node_mars, params,
                           chids, parids, parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
         if param_flows is not None:
-            for nids, cids, pids, pfids in self._dev["fw"]:
+            stage = kwargs.get("dense_par_stage")
+            for p, (nids, cids, pids, pfids) in enumerate(self._dev["fw"]):
+                if (stage is not None and packed and self._dense_ok(p, B, False) and self._groups_fw[p][2] == 1
+                        and stage(self, p, node_flows, node_mars, element_mars, ls)):
+                    continue                       # this table's flows come out of one product over all staged layers
                 _lib.call("pcx_sum_bwd_par", param_flows, node_flows, node_mars, element_mars, params,
                           nids, cids, pids, pfids, nids.numel(), cids.size(1), self.block_size, B, ls)
 

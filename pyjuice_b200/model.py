@@ -62,6 +62,7 @@ class TensorCircuit(nn.Module):
         self.use_cuda_graphs = True
         self.use_dataflow_launch = True       # runs of folded depths as one launch (tiles wait on counters)
         self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
+        self.dense_par_max_bytes = 16 << 30   # operand buffers of the dense parameter-flow product (all groups)
         self.default_propagation_alg = "LL"
         self._run_params = {}
         self._cum_flow_host = 0.0
@@ -257,6 +258,7 @@ class TensorCircuit(nn.Module):
         self._graphs = {}
         self._par_job_cache = {}
         self._chain_cache = {}
+        self._dense_par_cache = {}
         self._cum_flow_dev = None
         return self
 
@@ -416,7 +418,8 @@ class TensorCircuit(nn.Module):
 
     def _launch_cfg(self):
         """Everything that changes which kernels a pass launches (part of the key of a captured graph)."""
-        return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile)
+        return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
+                SumLayer.use_dense_kernels, getattr(self._packer, "grown", 0))
 
     def _chain_plan(self, B: int, mode: int):
         """Job table of the dataflow launch (one launch for a run of consecutive depths) for the forward pass
@@ -570,6 +573,49 @@ class TensorCircuit(nn.Module):
         cache[key] = out
         return out
 
+    def _dense_par_plan(self, B: int):
+        """Tables whose parameter flows come from the dense product (include/pcx_b200.h): deep tables whose rows all
+        list the same children, grouped by shared parameters — tied layers are contracted together, their batches
+        concatenated.  Returns {(id(layer), partition): (group, slot)} and the groups, or None when nothing qualifies."""
+        key = (B, self._launch_cfg())
+        cache = self.__dict__.setdefault("_dense_par_cache", {})
+        if key in cache:
+            return cache[key]
+        groups, where = {}, {}
+        cpl = -(-B // 64)
+        for gi in range(len(self.inner_layer_groups) - 1, -1, -1):
+            group = self.inner_layer_groups[gi]
+            if not group.is_sum() or self._fusion_on(gi, True):
+                continue
+            for layer in group:
+                if layer._packer is None:
+                    continue
+                for p, (nids, cids, pids, pfids) in enumerate(layer._dev["fw"]):
+                    if not (layer._dense_ok(p, B, False) and layer._groups_fw[p][2] == 1):
+                        continue
+                    g = groups.setdefault(layer._packed_fw[p].data_ptr(),
+                                          dict(members=[], tables=(cids, pids, pfids), n_blocks=nids.numel(),
+                                               K=cids.size(1), block_size=layer.block_size))
+                    where[(id(layer), p)] = (g, len(g["members"]))
+                    g["members"].append((layer, p))
+        plan = None
+        total = 0
+        for g in groups.values():
+            g["n_chunks"] = len(g["members"]) * cpl
+            row_tiles = g["n_blocks"] * (g["block_size"] // 128)
+            g["x_bytes"] = row_tiles * g["n_chunks"] * 32768
+            g["y_bytes"] = -(-g["K"] // 64) * g["n_chunks"] * 16384
+            total += g["x_bytes"] + g["y_bytes"]
+        if groups and total <= self.dense_par_max_bytes:
+            for g in groups.values():
+                g["x"] = torch.zeros(g["x_bytes"], dtype=torch.uint8, device=self.device)
+                g["y"] = torch.zeros(g["y_bytes"], dtype=torch.uint8, device=self.device)
+            rows = max(g["n_blocks"] * g["block_size"] for g in groups.values())
+            plan = dict(where=where, groups=list(groups.values()),
+                        work=torch.empty((-(-rows // 64) + 1) * B, dtype=torch.float32, device=self.device))
+        cache[key] = plan
+        return plan
+
     def _backward_inner(self, compute_param_flows: bool, logspace_flows: bool):
         """Reverse sweep over the inner layers.  Parameter flows of the depths whose product layer is folded in only
         read node values and node flows, and tiles of different layers are independent: they all run as ONE launch
@@ -577,6 +623,19 @@ class TensorCircuit(nn.Module):
         pf = self.param_flows if compute_param_flows else None
         groups = self.inner_layer_groups
         any_fused = False
+        dense = self._dense_par_plan(self.node_mars.size(1)) if pf is not None else None
+
+        def dense_stage(layer, p, node_flows, node_mars, element_mars, ls):
+            hit = dense["where"].get((id(layer), p))
+            if hit is None:
+                return False
+            g, slot = hit
+            nids, cids, _, _ = layer._dev["fw"][p]
+            _lib.call("pcx_sum_par_dense_stage", g["x"], g["y"], dense["work"], node_flows, node_mars, element_mars,
+                      nids, cids, nids.numel(), cids.size(1), layer.block_size, node_flows.size(1), g["n_chunks"],
+                      slot, ls)
+            return True
+
         plan = self._chain_plan(self.node_mars.size(1), 1)
         for gi in range(len(groups) - 1, -1, -1):
             group = groups[gi]
@@ -599,7 +658,13 @@ class TensorCircuit(nn.Module):
                 groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
                 self._reset_parentless(gi - 1, logspace_flows)
                 group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
-                               self.params.data, param_flows=pf, logspace_flows=logspace_flows)
+                               self.params.data, param_flows=pf, logspace_flows=logspace_flows,
+                               dense_par_stage=dense_stage if dense is not None else None)
+        if dense is not None:
+            for g in dense["groups"]:
+                cids, pids, pfids = g["tables"]
+                _lib.call("pcx_sum_par_dense_gemm", pf, self.params.data, g["x"], g["y"], cids, pids, pfids,
+                          g["n_blocks"], g["K"], g["block_size"], g["n_chunks"])
         if any_fused and pf is not None:
             B = self.node_flows.size(1)
             for fc, jobs, n_jobs, n_items, chunks_per_cta in self._par_jobs(B):

@@ -243,3 +243,40 @@ def test_c_abi_direct_calls():
     ref = torch.stack([nm[4:8] + nm[8:12], nm[12:16], nm[20:24] + nm[36:40]]).reshape(12, B)
     assert torch.allclose(em[4:16], ref, atol=1e-6)
     assert torch.isinf(em[:4]).all()
+
+
+@pytest.mark.parametrize("homogeneous", [True, False])
+@pytest.mark.parametrize("B", [64, 192])
+def test_dense_layers_match_oracle_and_tiled_kernels(B, homogeneous):
+    """Deep tables (here 1024 x 1024 transition blocks) take the two-step dense path: operand pre-pass plus a GEMM
+    over pre-tiled operands, parameter flows of tied layers in one product over their concatenated batches.  Checked
+    against the oracle, against the tile-at-a-time kernels, and over repeated (eager, captured, replayed) steps."""
+    from pyjuice_b200.layers import SumLayer
+    torch.manual_seed(3)
+    ns = pj.structures.HMM(seq_length=5, num_latents=1024, num_emits=16, homogeneous=homogeneous)
+    ns.init_parameters()
+    pc = pj.compile(ns).to(DEV)
+    x = torch.randint(0, 16, (B, 5))
+    assert any(l._dense_ok(0, B, False) for g in pc.inner_layer_groups if g.is_sum() for l in g), "expected dense tables"
+    for rep in range(3):
+        check_against_oracle(pc, x, step=0.05, pseudo=0.1)
+    out = {}
+    try:
+        for dense in (True, False):
+            SumLayer.use_dense_kernels = dense
+            pc.init_param_flows(flows_memory=0.0)
+            lls = pc(x.to(DEV))
+            pc.backward(x.to(DEV))
+            torch.cuda.synchronize()
+            out[dense] = (lls.clone(), pc.node_flows[pc.num_dummy_nodes:].exp().clone(), pc.param_flows.clone())
+    finally:
+        SumLayer.use_dense_kernels = True
+    for a, b in zip(out[True], out[False]):
+        assert torch.allclose(a, b, rtol=2e-4, atol=1e-6), (a - b).abs().max()
+    _lib_status()
+
+
+def _lib_status():
+    from pyjuice_b200 import _lib
+    torch.cuda.synchronize()
+    _lib.check_status()
