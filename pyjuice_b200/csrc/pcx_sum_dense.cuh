@@ -15,9 +15,14 @@
 // the batch, and layers that share their parameters -- tied -- are contracted in one go: the batch dimensions of all
 // of them are concatenated, so the flows of 127 tied layers are ONE 4096 x 4096 x 32512 product).
 //
+// Operand precision: both operands are bf16 hi + lo pairs.  The hi and lo parts of the B operand sit side by side in
+// one 128-row tile, so that A_hi x [B_hi | B_lo] and A_lo x [B_hi | B_lo] are two MMAs of N = 128 per 16-deep step
+// (the cost of an MMA this small is mostly fixed, so two wide ones beat three narrow ones, and lo x lo comes free);
+// the epilogue adds accumulator columns j and j + 64.
+//
 // Accumulation: the tensor core truncates when it adds into its fp32 accumulator, which biases a long sum low.
-// Eight TMEM accumulators (8 x 64 columns = all of TMEM) take the chunks round-robin and are added in registers at
-// the end, which divides the bias by eight.
+// Four TMEM accumulators (4 x 128 columns = all of TMEM) take the chunks round-robin and are added in registers at
+// the end, which divides the bias by four.
 //
 // This file is included by pcx_sum_tc.cu (it uses that file's helpers and status word).
 #pragma once
@@ -31,7 +36,9 @@ constexpr int D_STAGE = D_A_BYTES + D_B_BYTES;      // 48 KB
 constexpr int D_STAGES = 4;
 constexpr int D_SMEM = D_STAGES * D_STAGE + 1024;
 constexpr int D_THREADS = 192;                      // warp 0 copies, warp 1 multiplies, warps 2-5 finish
-constexpr int D_ACCS = 8;
+constexpr int D_ACCS = 4;
+constexpr int D_ACC_COLS = 2 * DN;                  // hi-part columns, then lo-part columns
+constexpr int D_BSLAB = 2 * DN * 16;                // one 8-deep K group of the B tile: 64 hi rows, 64 lo rows
 
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -44,6 +51,20 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_s
 }
 
 enum DenseEpi { D_FWD = 0, D_ELE = 1, D_PAR = 2 };
+
+#ifdef PCX_TRACE
+#define PCX_DT(k)                                                                                          \
+    do {                                                                                                   \
+        const int _slot = blockIdx.x + gridDim.x * blockIdx.y;                                             \
+        if (_slot < kTraceItems) {                                                                         \
+            long long _t;                                                                                  \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                         \
+            g_trace[_slot][(k)] = _t;                                                                      \
+        }                                                                                                  \
+    } while (0)
+#else
+#define PCX_DT(k) do { } while (0)
+#endif
 
 struct DenseArgs {
     const uint8_t* a_tiles;     // A tile of (row tile mt, chunk c) at a_tiles + (mt * n_chunks + c) * 32 KB
@@ -81,6 +102,7 @@ __global__ void __launch_bounds__(D_THREADS, 1) dense_gemm_kernel(const DenseArg
     const int64_t i = mt / tiles_r;
     const int r0 = (int)(mt % tiles_r) * BM;
     const int n_chunks = a.n_chunks;
+    if (tid == 0) PCX_DT(0);
 
     if (tid == 0) {
         for (int s = 0; s < D_STAGES; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
@@ -88,48 +110,66 @@ __global__ void __launch_bounds__(D_THREADS, 1) dense_gemm_kernel(const DenseArg
         fence_mbar_init();
         s_fail = 0;
     }
-    if (warp == 0) tmem_alloc(&s_tmem, D_ACCS * DN);
+    if (warp == 0) tmem_alloc(&s_tmem, D_ACCS * D_ACC_COLS);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = s_tmem;
+    if (tid == 0) PCX_DT(1);
 
     const int64_t b_row = (EPI == D_PAR) ? (int64_t)nt : (int64_t)a.b_group[i] * a.n_ct + nt;
     const uint8_t* a_src = a.a_tiles + (size_t)mt * n_chunks * D_A_BYTES;
     const uint8_t* b_src = a.b_tiles + (size_t)b_row * n_chunks * D_B_BYTES;
 
     if (warp == 0) {
-        // ---- copy thread --------------------------------------------------------------------------------
-        if (lane == 0) {
-            int armed = 0;
-            for (int c = 0; c < n_chunks; ++c) {
-                const int s = c % D_STAGES;
-                if (c >= D_STAGES && !mbar_wait(&s_empty[s], (uint32_t)((c / D_STAGES - 1) & 1))) { s_fail = 1; break; }
-                if (s_fail) break;
-                uint8_t* st = smem + s * D_STAGE;
-                mbar_expect_tx(&s_full[s], D_STAGE);
-                bulk_copy_g2s(st, a_src + (size_t)c * D_A_BYTES, D_A_BYTES, &s_full[s]);
-                bulk_copy_g2s(st + D_A_BYTES, b_src + (size_t)c * D_B_BYTES, D_B_BYTES, &s_full[s]);
-                armed = c + 1;
+        // ---- copy warp: lane 0 waits for the stage and arms its barrier, twelve lanes each move 4 KB of it --------
+        constexpr int PIECE = 4096;
+        static_assert(D_STAGE % PIECE == 0 && D_STAGE / PIECE <= 32 && D_A_BYTES % PIECE == 0, "one piece per lane");
+        int armed = 0;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % D_STAGES;
+            int stop = 0;
+            if (lane == 0) {
+                if (c >= D_STAGES && !mbar_wait(&s_empty[s], (uint32_t)((c / D_STAGES - 1) & 1))) s_fail = 1;
+                stop = s_fail;
+                if (!stop) mbar_expect_tx(&s_full[s], D_STAGE);
             }
-            if (s_fail) {
-                // let the copies that are still in flight land before this CTA's shared memory goes away
-                for (int c = max(0, armed - D_STAGES); c < armed; ++c)
-                    mbar_wait(&s_full[c % D_STAGES], (uint32_t)((c / D_STAGES) & 1), 1u << 16);
+            stop = __shfl_sync(0xffffffffu, stop, 0);
+            if (stop) break;
+            if (lane < D_STAGE / PIECE) {
+                const int off = lane * PIECE;
+                const uint8_t* src = (off < D_A_BYTES) ? a_src + (size_t)c * D_A_BYTES + off
+                                                       : b_src + (size_t)c * D_B_BYTES + (off - D_A_BYTES);
+                bulk_copy_g2s(smem + s * D_STAGE + off, src, PIECE, &s_full[s]);
             }
+            armed = c + 1;
+        }
+        if (lane == 0 && s_fail) {
+            // let the copies that are still in flight land before this CTA's shared memory goes away
+            for (int c = max(0, armed - D_STAGES); c < armed; ++c)
+                mbar_wait(&s_full[c % D_STAGES], (uint32_t)((c / D_STAGES) & 1), 1u << 16);
         }
     } else if (warp == 1) {
         // ---- multiply thread ----------------------------------------------------------------------------
         if (lane == 0) {
-            const uint32_t idesc = idesc_bf16_f32(BM, DN);
+            const uint32_t idesc = idesc_bf16_f32(BM, D_ACC_COLS);
             for (int c = 0; c < n_chunks; ++c) {
                 const int s = c % D_STAGES;
                 if (!mbar_wait(&s_full[s], (uint32_t)((c / D_STAGES) & 1))) { s_fail = 2; break; }
+                if (c == 0) PCX_DT(2);
+                if (c == n_chunks - 1) PCX_DT(3);
                 if (s_fail) break;
                 tc_fence_after_sync();
-                const uint32_t sa = smem_u32(smem + s * D_STAGE);
-                issue_stage<BM * 16, DN * 16>(tmem + (uint32_t)((c % D_ACCS) * DN), sa, sa + D_A_BYTES, idesc,
-                                              c < D_ACCS, a.terms);
+                const uint32_t sa = smem_u32(smem + s * D_STAGE), sb = sa + D_A_BYTES;
+                const uint32_t acc = tmem + (uint32_t)((c % D_ACCS) * D_ACC_COLS);
+#pragma unroll
+                for (int ks = 0; ks < KC / 16; ++ks) {
+                    const uint64_t dAh = smem_desc(sa + ks * 2 * (BM * 16), BM * 16, 128);
+                    const uint64_t dAl = smem_desc(sa + A_TILE + ks * 2 * (BM * 16), BM * 16, 128);
+                    const uint64_t dB = smem_desc(sb + ks * 2 * D_BSLAB, D_BSLAB, 128);
+                    mma_bf16_ss(acc, dAh, dB, idesc, (c >= D_ACCS || ks > 0) ? 1u : 0u);
+                    if (a.terms == 3) mma_bf16_ss(acc, dAl, dB, idesc, 1u);
+                }
                 mma_commit(&s_empty[s]);            // the stage is free once these products have read it
             }
             mma_commit(&s_done);
@@ -140,6 +180,7 @@ __global__ void __launch_bounds__(D_THREADS, 1) dense_gemm_kernel(const DenseArg
         const int row = lq * 32 + lane;
         bool ok = mbar_wait(&s_done, 0u, 1u << 24);
         if (!ok) s_fail = 3;
+        if (tid == 64) PCX_DT(4);
         ok = ok && (s_fail == 0);
         tc_fence_after_sync();
         const int used = n_chunks < D_ACCS ? n_chunks : D_ACCS;
@@ -150,10 +191,11 @@ __global__ void __launch_bounds__(D_THREADS, 1) dense_gemm_kernel(const DenseArg
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = 0.0f;
                 for (int q = 0; q < used; ++q) {
-                    float t[8];
-                    tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(q * DN + 8 * p), t);
+                    float t[8], u[8];
+                    tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(q * D_ACC_COLS + 8 * p), t);
+                    tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(q * D_ACC_COLS + DN + 8 * p), u);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] += t[j];
+                    for (int j = 0; j < 8; ++j) v[j] += t[j] + u[j];
                 }
                 if (EPI == D_PAR) {
 #pragma unroll
@@ -192,10 +234,12 @@ __global__ void __launch_bounds__(D_THREADS, 1) dense_gemm_kernel(const DenseArg
             }
         }
         tc_fence_before_sync();
+        if (tid == 64) PCX_DT(5);
     }
     __syncthreads();
+    if (tid == 0) PCX_DT(6);
     if (tid == 0 && s_fail != 0) atomicCAS(&g_tc_status, 0, 400 + 10 * EPI + s_fail);
-    if (warp == 0) tmem_dealloc(tmem, D_ACCS * DN);
+    if (warp == 0) tmem_dealloc(tmem, D_ACCS * D_ACC_COLS);
 }
 
 // ---- operand pre-passes ------------------------------------------------------------------------------------
@@ -263,7 +307,7 @@ __global__ void dense_shift_kernel(const float* __restrict__ partial, float* __r
 }
 
 // Operand tiles with the contraction over operand rows (FWD, ELE): tile (g, column tile jt, chunk c) is
-// [8 row groups][64 samples][8 rows] bf16, hi tile then lo tile.  Grid (n_chunks, n_ct, n_groups), 256 threads:
+// [8 row groups][64 samples hi, 64 samples lo][8 rows] bf16.  Grid (n_chunks, n_ct, n_groups), 256 threads:
 // thread = (sample of the tile, two of the eight row groups).
 __global__ void dense_rows_tiles_kernel(const PrepArgs a, const float* __restrict__ shift,
                                         uint8_t* __restrict__ tiles, int n_ct, int n_chunks) {
@@ -281,13 +325,14 @@ __global__ void dense_rows_tiles_kernel(const PrepArgs a, const float* __restric
             const float x = prep_value(a, g, c * KC + grp * 8 + j, b);
             v[j] = (x == PCX_NEG_INF) ? 0.0f : __expf(x - mx);
         }
-        uint8_t* dst = tile + grp * (DN * 16) + lc * 16;
-        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + B_TILE), v);
+        uint8_t* dst = tile + grp * D_BSLAB + lc * 16;                 // hi row lc, lo row 64 + lc of the K group
+        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + DN * 16), v);
     }
 }
 
 // Operand tiles with the contraction over the batch (parameter flows).  X: tile (row tile mt, chunk cc) is
-// [8 sample groups][128 rows][8 samples]; Y: tile (edge tile et, chunk cc) is [8 sample groups][64 edges][8 samples].
+// [8 sample groups][128 rows][8 samples], hi tile then lo tile; Y: tile (edge tile et, chunk cc) is
+// [8 sample groups][64 edges hi, 64 edges lo][8 samples].
 // shift[b] = max over the layer's rows of (flow - value), from the two kernels above; x = exp(flow - value - shift),
 // y = exp(element value + shift).
 // Tiles of layer `slot` go to chunk columns slot * cpl + cc of a buffer with `n_chunks` chunk columns per tile row.
@@ -337,8 +382,8 @@ __global__ void dense_par_y_kernel(const float* __restrict__ element_mars, const
             }
             v[t] = y;
         }
-        uint8_t* dst = tile + gq * (DN * 16) + (rb + 32 * j) * 16;
-        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + B_TILE), v);
+        uint8_t* dst = tile + gq * D_BSLAB + (rb + 32 * j) * 16;
+        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + DN * 16), v);
     }
 }
 
