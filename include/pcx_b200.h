@@ -181,6 +181,25 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
                            const int32_t* cids, const int32_t* pids, const int32_t* pfids, int64_t n_blocks, int K,
                            int block_size, int n_chunks_total, void* stream);
 
+/* ---- Small node blocks (32 or 64 nodes) on the tensor cores: sample-major tiles -----------------------------------
+ * A tile is 128 samples x nb nodes (nb = 32 or 64): one node block, or two consecutive 32-node blocks whose table rows
+ * are identical and whose node ids are consecutive ("merged row"; first_row[m] = its first table row).  The batch is
+ * the MMA's M dimension, so blocks need not share children to fill a tile.  Parameters are pre-split per merged row
+ * with pcx_pack_sm_params (mode 0: forward tables nids/cids/pids, block = block size; mode 1: element-flow tables
+ * chids/parids/parpids, block = child block size, par_block = block size of the parents) into a caller-owned buffer
+ * of pcx_sm_packed_bytes(n_merged, depth, nb) bytes (depth = K, or P * par_block).  Same results as pcx_sum_fwd /
+ * pcx_sum_bwd_ele (layer/sum_layer.py:551-929, 1369-1719). */
+int64_t pcx_sm_packed_bytes(int64_t n_merged, int depth, int nb);
+int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_row, const int32_t* kids,
+                       const int32_t* kpar, int64_t n_merged, int nb, int block, int K, int par_block, int mode,
+                       void* stream);
+int pcx_sum_fwd_sm(float* node_mars, const float* element_mars, const void* packed, const int32_t* first_row,
+                   const int32_t* nids, const int32_t* cids, int64_t n_merged, int nb, int K, int B, void* stream);
+int pcx_sum_bwd_ele_sm(float* element_flows, const float* element_mars, const float* node_flows,
+                       const float* node_mars, const void* packed, const int32_t* first_row, const int32_t* chids,
+                       const int32_t* parids, int64_t n_merged, int nb, int P, int block_size, int B, int logspace,
+                       void* stream);
+
 /* Forward (mode 0) or element flows (mode 1) of a RUN of consecutive layers in one launch, product layers folded in
  * (as pcx_sum_fwd_fused / pcx_sum_bwd_ele_fused with direct stores).  Tiles are work items claimed from a device
  * counter in layer order; a tile of level t starts as soon as the tiles of level t - 1 that cover the same batch

@@ -42,6 +42,9 @@ SIGNATURES = {
     "pcx_sum_bwd_ele_dense": [P, P, P, P, P, P, P, P, P, I, P, L, L, I, I, I, I, I],
     "pcx_sum_par_dense_stage": [P, P, P, P, P, P, P, P, L, I, I, I, I, I, I],
     "pcx_sum_par_dense_gemm": [P, P, P, P, P, P, P, L, I, I, I],
+    "pcx_pack_sm_params": [P, P, P, P, P, L, I, I, I, I, I],
+    "pcx_sum_fwd_sm": [P, P, P, P, P, P, L, I, I, I],
+    "pcx_sum_bwd_ele_sm": [P, P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_sum_chain": [I, P, P, P, I, L, I, I, I, I, I, P, L],
     "pcx_sum_bwd_par_batched": [P, P, P, P, P, I, L, I, I, I, I],
     "pcx_sum_fwd_noalloc": [P, P, P, P, P, P, L, I, I, I],
@@ -53,7 +56,8 @@ SIGNATURES = {
 
 # entry points without a stream argument
 PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": [],
-         "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I]}
+         "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I],
+         "pcx_sm_packed_bytes": [L, I, I]}
 SUM_MODE = 1        # mirror of the library's arithmetic mode (see set_sum_mode)
 
 _lib: Optional[ctypes.CDLL] = None
@@ -79,7 +83,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     for name, args in PLAIN.items():
         fn = getattr(lib, name)
-        fn.restype = c_int64 if name in ("pcx_packed_tile_count", "pcx_dense_scratch_bytes") else c_int
+        fn.restype = c_int64 if name in ("pcx_packed_tile_count", "pcx_dense_scratch_bytes", "pcx_sm_packed_bytes") else c_int
         fn.argtypes = list(args)
     for name, args in SIGNATURES.items():
         fn = getattr(lib, name)

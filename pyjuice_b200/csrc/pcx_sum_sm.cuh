@@ -1,0 +1,512 @@
+// Sum layers with small node blocks (16 ... 64 nodes) on the tensor cores: "sample-major" tiles.
+//
+// A tcgen05 tile needs 128 rows.  With 32-node blocks the rows of a layer do not share children, so stacking four
+// blocks into one row tile would waste the contraction.  Instead the BATCH is the M dimension: a tile is 128 samples
+// x NB nodes (NB = 32 or 64: one node block, or the consecutive blocks of a vector that list the same children),
+//     D[b, n] = sum_k exp(child[k, b] - max_b) * theta[n, k],
+// i.e. the transpose of the row-major tile of pcx_sum_tc.cu.  The operand of exponentials (128 samples x K, K-major)
+// is produced by the CTA's threads exactly as there; the parameter operand (NB nodes x K) comes pre-split from
+// global memory.  The accumulator has one sample per TMEM lane and one node per column, so the epilogue writes, for
+// every node, 32 consecutive samples per warp: fully coalesced without a transpose.
+//
+// Forward and element flows share the kernel (element flows: the "children" are the parent nodes' flow / value
+// ratios, the "nodes" are the child elements, and the element's own value is added at the end).
+// Included by pcx_sum_tc.cu.
+#pragma once
+
+namespace {
+
+constexpr int SM_SAMPLES = 128;                       // samples per tile (UMMA M)
+constexpr int SM_E_TILE = KG * SM_SAMPLES * 16;       // 16 KB: one bf16 [128 x 64] tile of exponentials
+constexpr int SM_STAGE = 2 * SM_E_TILE + 2 * B_TILE;  // E hi, E lo, theta hi, theta lo (theta: up to 64 nodes) = 48 KB
+static_assert(SM_STAGE == STAGE_BYTES, "same shared-memory budget as the row-major kernels");
+
+struct SmArgs {
+    float* out;                 // FWD: node_mars            ELE: element_flows
+    const float* src;           // FWD: element_mars         ELE: node_flows
+    const float* src2;          //                           ELE: node_mars
+    const float* emars;         //                           ELE: element_mars
+    const uint4* packed;        // parameter tiles: tile (m, chunk) = [hi | lo] x [8 K groups][NB nodes][8 k] bf16
+    const int32_t* first_row;   // [n_tiles_m] first table row of every merged row
+    const int32_t* rows;        // FWD: nids                 ELE: chids
+    const int32_t* kids;        // FWD: cids [n, K]          ELE: parids [n, P]
+    int64_t n_tiles;            // merged rows x sample tiles
+    int n_st;                   // sample tiles = ceil(B / 128)
+    int K;                      // FWD: table width          ELE: parent blocks per child block
+    int par_block;              // FWD: 1                    ELE: parent block size (multiple of 8)
+    int B;
+    int logspace;
+    int terms;
+};
+
+// One CTA walks tiles m * n_st + st (static round-robin: tiles do not depend on each other).
+template <int NB, bool ELE>
+__global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
+    constexpr int TCOLS = NB < 32 ? 32 : NB;
+    constexpr int TH_TILE = 2 * KG * NB * 16;          // bytes of one parameter tile (hi + lo)
+    constexpr int HC = NB / 2;                         // epilogue: node columns per thread
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t s_bar[STAGES];
+    __shared__ uint32_t s_tmem;
+    __shared__ float s_part[2][SM_SAMPLES];
+    __shared__ float s_max[SM_SAMPLES];
+    __shared__ int s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[s], 1);
+        fence_mbar_init();
+        s_fail = 0;
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    uint32_t ph[STAGES] = {0, 0};                      // completed phases of the two barriers
+
+    const int B = a.B;
+    const int KK = ELE ? a.K * a.par_block : a.K;
+    const int lg_pb = ELE ? (31 - __clz(a.par_block)) : 0;
+    const int n_chunks = (KK + KC - 1) / KC;
+    const int n_groups = (KK + 7) / 8;
+    const int ls = tid & (SM_SAMPLES - 1), h = tid >> 7;       // operand role: sample ls, K groups h, h + 2, ...
+    const uint32_t idesc = idesc_bf16_f32(SM_SAMPLES, NB);
+
+    for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+        const int64_t m = tile / a.n_st;
+        const int b0 = (int)(tile % a.n_st) * SM_SAMPLES;
+        const int i0 = a.first_row[m];
+        const int col = b0 + ls;
+        const bool col_ok = col < B;
+        const int colc = col_ok ? col : 0;
+
+        // log-domain values of one 8-deep K group (unconditional loads, row 0 exists and is masked afterwards)
+        auto load_group = [&](int kb, float* v) {
+            if (!ELE) {
+                int cid[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cid[j] = (col_ok && kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = a.src[(int64_t)cid[j] * B + colc];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = (cid[j] != 0) ? v[j] : PCX_NEG_INF;
+            } else {
+                const int pr = (col_ok && kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
+                const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
+                float nf[8], nm[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { nf[j] = a.src[(row + j) * B + colc]; nm[j] = a.src2[(row + j) * B + colc]; }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float f = nf[j];
+                    if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
+                    v[j] = (pr == 0 || nm[j] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[j];
+                }
+            }
+        };
+        auto copy_theta = [&](int chunk, uint8_t* st) {
+            const uint4* src = a.packed + ((size_t)m * n_chunks + chunk) * (TH_TILE / 16);
+            for (int w = tid; w < TH_TILE / 16; w += NTH) cp_async16(st + 2 * SM_E_TILE + w * 16, src + w);
+        };
+        auto store_group = [&](uint8_t* st, int g, float* v, float mx) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (v[j] == PCX_NEG_INF) ? 0.0f : __expf(v[j] - mx);
+            uint8_t* dst = st + g * (SM_SAMPLES * 16) + ls * 16;
+            store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + SM_E_TILE), v);
+        };
+        auto issue = [&](uint8_t* st, bool first) {
+            const uint32_t sa = smem_u32(st), sb = sa + 2 * SM_E_TILE;
+#pragma unroll
+            for (int ks = 0; ks < KC / 16; ++ks) {
+                const uint64_t dEh = smem_desc(sa + ks * 2 * (SM_SAMPLES * 16), SM_SAMPLES * 16, 128);
+                const uint64_t dEl = smem_desc(sa + SM_E_TILE + ks * 2 * (SM_SAMPLES * 16), SM_SAMPLES * 16, 128);
+                const uint64_t dTh = smem_desc(sb + ks * 2 * (NB * 16), NB * 16, 128);
+                const uint64_t dTl = smem_desc(sb + KG * NB * 16 + ks * 2 * (NB * 16), NB * 16, 128);
+                mma_bf16_ss(tmem, dEh, dTh, idesc, (!first || ks > 0) ? 1u : 0u);
+                if (a.terms == 3) {
+                    mma_bf16_ss(tmem, dEh, dTl, idesc, 1u);
+                    mma_bf16_ss(tmem, dEl, dTh, idesc, 1u);
+                }
+            }
+        };
+
+        // ---- pass 1: per-sample maximum; tables up to 128 deep keep their values in registers -----------------
+        const bool small = n_chunks <= STAGES;
+        float keep[8][8];
+        float mx = PCX_NEG_INF;
+        if (small) {
+            for (int c = 0; c < n_chunks; ++c) copy_theta(c, smem + c * SM_STAGE);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int g = h + 2 * t;
+                if (g < n_groups) load_group(g * 8, keep[t]);
+                else
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) keep[t][j] = PCX_NEG_INF;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[t][j]);
+            }
+        } else {
+            for (int g = h; g < n_groups; g += 2) {
+                float v[8];
+                load_group(g * 8, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[j]);
+            }
+        }
+        s_part[h][ls] = mx;
+        __syncthreads();
+        mx = fmaxf(s_part[0][ls], s_part[1][ls]);
+        if (h == 0) s_max[ls] = mx;
+
+        // ---- pass 2: exponentials -> operand tiles, multiply ------------------------------------------------
+        bool failed = false;
+        if (small) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int g = h + 2 * t;
+                if (g < n_chunks * KG) store_group(smem + (g / KG) * SM_STAGE, g % KG, keep[t], mx);
+            }
+            cp_async_wait_all();
+            fence_async_smem();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after_sync();
+                for (int c = 0; c < n_chunks; ++c) issue(smem + c * SM_STAGE, c == 0);
+                mma_commit(&s_bar[0]);
+            }
+            if (tid == 0 && !mbar_wait(&s_bar[0], ph[0] & 1)) s_fail = 2;      // one thread waits, the rest sleep below
+            ph[0] += 1;
+        } else {
+            for (int c = 0; c < n_chunks; ++c) {
+                const int s = c % STAGES, use = c / STAGES;
+                uint8_t* st = smem + s * SM_STAGE;
+                if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (ph[s] + use - 1) & 1)) { failed = true; s_fail = 1; }
+                copy_theta(c, st);
+                for (int g = h; g < KG; g += 2) {
+                    float v[8];
+                    load_group(c * KC + g * 8, v);
+                    store_group(st, g, v, mx);
+                }
+                cp_async_wait_all();
+                fence_async_smem();
+                __syncthreads();
+                failed = failed || (s_fail != 0);
+                if (tid == 0 && !failed) {
+                    tc_fence_after_sync();
+                    issue(st, c == 0);
+                    mma_commit(&s_bar[s]);
+                }
+            }
+            const int cl = n_chunks - 1;
+            if (tid == 0 && !failed && !mbar_wait(&s_bar[cl % STAGES], (ph[cl % STAGES] + cl / STAGES) & 1)) s_fail = 2;
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) ph[s] += (n_chunks - s + STAGES - 1) / STAGES;
+        }
+        __syncthreads();
+        failed = failed || (s_fail != 0);
+        tc_fence_after_sync();
+
+        // ---- epilogue: lane = sample, column = node; warps w and w + 4 split the nodes ----------------------------
+        if (!failed) {
+            const int lq = warp & 3, c0 = (warp >> 2) * HC;
+            const int es = lq * 32 + lane;                       // sample of this thread within the tile
+            const int b = b0 + es;
+            const float m_s = s_max[es];
+            const int64_t base_row = (int64_t)a.rows[i0];        // merged rows are consecutive in the value buffer
+#pragma unroll
+            for (int p = 0; p < HC / 8; ++p) {
+                float v[8];
+                tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
+                if (b >= B) continue;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int64_t off = (base_row + c0 + 8 * p + j) * B + b;
+                    float o;
+                    if (!ELE) {
+                        o = (m_s == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m_s;
+                    } else {
+                        o = (m_s == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m_s;
+                        const float em = a.emars[off];
+                        o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
+                        if (!a.logspace) o = __expf(o);
+                    }
+                    a.out[off] = o;
+                }
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        if (s_fail != 0) break;
+    }
+    if (tid == 0 && s_fail != 0) atomicCAS(&g_tc_status, 0, 500 + s_fail);
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TCOLS);
+}
+
+// Tables at most 64 deep (the common case for small blocks): one thread per sample, one chunk, no cross-thread
+// reduction, 24 - 48 KB of shared memory -- so that four to six CTAs share an SM and hide each other's latency.
+template <int NB, bool ELE>
+__global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArgs a, const int ng) {
+    constexpr int TCOLS = NB < 32 ? 32 : NB;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t s_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
+        mbar_init(&s_bar, 1);
+        fence_mbar_init();
+        s_fail = 0;
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    uint32_t phase = 0;
+
+    const int B = a.B;
+    const int KK = ELE ? a.K * a.par_block : a.K;
+    const int lg_pb = ELE ? (31 - __clz(a.par_block)) : 0;
+    const uint32_t idesc = idesc_bf16_f32(SM_SAMPLES, NB);
+    // shared memory: E hi [ng][128][16 B], E lo, theta hi [ng][NB][16 B], theta lo
+    uint8_t* e_hi = smem;
+    uint8_t* e_lo = smem + ng * (SM_SAMPLES * 16);
+    uint8_t* t_hi = smem + 2 * ng * (SM_SAMPLES * 16);
+    uint8_t* t_lo = t_hi + ng * (NB * 16);
+
+    for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+        const int64_t m = tile / a.n_st;
+        const int b0 = (int)(tile % a.n_st) * SM_SAMPLES;
+        const int i0 = a.first_row[m];
+        const int col = b0 + tid;
+        const bool col_ok = col < B;
+        const int colc = col_ok ? col : 0;
+
+        // parameter tile: the first ng K groups of the hi half and of the lo half
+        {
+            const uint4* src = a.packed + (size_t)m * (2 * KG * NB);
+            for (int w = tid; w < ng * NB; w += SM_SAMPLES) {
+                cp_async16(t_hi + w * 16, src + w);
+                cp_async16(t_lo + w * 16, src + KG * NB + w);
+            }
+        }
+        float keep[8][8];
+        float mx = PCX_NEG_INF;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (g < ng) {
+                const int kb = g * 8;
+                if (!ELE) {
+                    int cid[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) cid[j] = (col_ok && kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) keep[g][j] = a.src[(int64_t)cid[j] * B + colc];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) keep[g][j] = (cid[j] != 0) ? keep[g][j] : PCX_NEG_INF;
+                } else {
+                    const int pr = (col_ok && kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
+                    const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
+                    float nf[8], nm[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { nf[j] = a.src[(row + j) * B + colc]; nm[j] = a.src2[(row + j) * B + colc]; }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float f = nf[j];
+                        if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
+                        keep[g][j] = (pr == 0 || nm[j] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[j];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[g][j]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (g < ng) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) keep[g][j] = (keep[g][j] == PCX_NEG_INF) ? 0.0f : __expf(keep[g][j] - mx);
+                store_split8(reinterpret_cast<uint4*>(e_hi + g * (SM_SAMPLES * 16) + tid * 16),
+                             reinterpret_cast<uint4*>(e_lo + g * (SM_SAMPLES * 16) + tid * 16), keep[g]);
+            }
+        }
+        cp_async_wait_all();
+        fence_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after_sync();
+            for (int ks = 0; ks < ng / 2; ++ks) {
+                const uint64_t dEh = smem_desc(smem_u32(e_hi) + ks * 2 * (SM_SAMPLES * 16), SM_SAMPLES * 16, 128);
+                const uint64_t dEl = smem_desc(smem_u32(e_lo) + ks * 2 * (SM_SAMPLES * 16), SM_SAMPLES * 16, 128);
+                const uint64_t dTh = smem_desc(smem_u32(t_hi) + ks * 2 * (NB * 16), NB * 16, 128);
+                const uint64_t dTl = smem_desc(smem_u32(t_lo) + ks * 2 * (NB * 16), NB * 16, 128);
+                mma_bf16_ss(tmem, dEh, dTh, idesc, ks > 0 ? 1u : 0u);
+                if (a.terms == 3) {
+                    mma_bf16_ss(tmem, dEh, dTl, idesc, 1u);
+                    mma_bf16_ss(tmem, dEl, dTh, idesc, 1u);
+                }
+            }
+            mma_commit(&s_bar);
+        }
+        // one thread waits for the tensor core, the others sleep in the barrier (128 spinning threads would take
+        // issue slots from the other CTAs of the SM)
+        if (tid == 0 && !mbar_wait(&s_bar, phase & 1)) s_fail = 2;
+        phase += 1;
+        __syncthreads();
+        const bool failed = s_fail != 0;
+        tc_fence_after_sync();
+        if (!failed) {
+            const int64_t base_row = (int64_t)a.rows[i0];
+#pragma unroll
+            for (int p = 0; p < NB / 8; ++p) {
+                float v[8];
+                tmem_ld<8>(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(8 * p), v);    // warp-wide: every lane takes part
+                if (!col_ok) continue;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int64_t off = (base_row + 8 * p + j) * B + col;
+                    float o;
+                    if (!ELE) {
+                        o = (mx == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + mx;
+                    } else {
+                        o = (mx == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + mx;
+                        const float em = a.emars[off];
+                        o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
+                        if (!a.logspace) o = __expf(o);
+                    }
+                    a.out[off] = o;
+                }
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        if (s_fail != 0) break;
+    }
+    if (tid == 0 && s_fail != 0) atomicCAS(&g_tc_status, 0, 510 + s_fail);
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TCOLS);
+}
+
+// Parameter tiles of the sample-major kernels.  One thread per 16-byte (hi) vector: (merged row m, chunk, K group g,
+// node r of the tile).  mode 0: theta[n, k] = params[pids[i, k] + n]; mode 1 (element flows, transposed):
+// theta[c, (p, n)] = params[parpids[j, p] + c * par_block + n]; i / j = first_row[m] + r / block, n / c = r % block.
+__global__ void pack_sm_kernel(uint4* __restrict__ out, const float* __restrict__ params,
+                               const int32_t* __restrict__ first_row, const int32_t* __restrict__ kids,
+                               const int32_t* __restrict__ kpar, int64_t n_vec, int NB, int block, int K,
+                               int par_block, int n_chunks, int mode) {
+    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_vec) return;
+    const int r = (int)(t % NB);
+    const int g = (int)((t / NB) % KG);
+    const int64_t tile = t / ((int64_t)NB * KG);
+    const int chunk = (int)(tile % n_chunks);
+    const int64_t m = tile / n_chunks;
+    const int64_t i = (int64_t)first_row[m] + r / block;
+    const int n = r % block;
+    const int kb = chunk * KC + g * 8;
+    float v[8];
+    if (mode == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = kb + j;
+            v[j] = (k < K) ? params[(int64_t)kpar[i * K + k] + n] : 0.0f;
+        }
+    } else {
+        const int KK = K * par_block;
+        const int p = kb / par_block, np = kb % par_block;
+        const int pr = (kb < KK) ? kids[i * K + p] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] = (pr != 0) ? params[(int64_t)kpar[i * K + p] + (int64_t)n * par_block + np + j] : 0.0f;
+    }
+    uint4* base = out + tile * (2 * KG * NB);
+    store_split8(base + g * NB + r, base + KG * NB + g * NB + r, v);
+}
+
+template <int NB, bool ELE>
+int launch_sm(const SmArgs& a, cudaStream_t st) {
+    static bool done = false;
+    static int sms = 0;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(sum_sm_kernel<NB, ELE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(sum_sm_small_kernel<NB, ELE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    const int depth = ELE ? a.K * a.par_block : a.K;
+    if (depth <= KC) {
+        const int ng = 2 * (int)pcx_cdiv(depth, 16);                    // K groups actually used (pairs: one MMA step)
+        const int bytes = 2 * ng * (SM_SAMPLES * 16) + 2 * ng * (NB * 16) + 1024;
+        const int per_sm = bytes <= 36 * 1024 ? 6 : 4;
+        const int64_t grid = a.n_tiles < per_sm * (int64_t)sms ? a.n_tiles : per_sm * (int64_t)sms;
+        sum_sm_small_kernel<NB, ELE><<<(unsigned)grid, SM_SAMPLES, bytes, st>>>(a, ng);
+        PCX_LAUNCH_CHECK();
+        return 0;
+    }
+    const int64_t grid = a.n_tiles < 2 * (int64_t)sms ? a.n_tiles : 2 * (int64_t)sms;
+    sum_sm_kernel<NB, ELE><<<(unsigned)grid, NTH, SMEM_BYTES, st>>>(a);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t pcx_sm_packed_bytes(int64_t n_merged, int depth, int nb) {
+    return n_merged * pcx_cdiv(depth, KC) * 2 * KG * nb * 16;
+}
+
+int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_row, const int32_t* kids,
+                       const int32_t* kpar, int64_t n_merged, int nb, int block, int K, int par_block, int mode,
+                       void* stream) {
+    if (n_merged <= 0) return 0;
+    if ((nb != 32 && nb != 64) || block <= 0 || nb % block != 0 || (mode != 0 && mode != 1)) return -1;
+    if (mode == 1 && par_block % 8 != 0) return -1;
+    const int depth = mode == 0 ? K : K * par_block;
+    const int n_chunks = (int)pcx_cdiv(depth, KC);
+    const int64_t n_vec = n_merged * n_chunks * KG * nb;
+    pack_sm_kernel<<<(unsigned)pcx_cdiv(n_vec, 256), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<uint4*>(packed), params, first_row, kids, kpar, n_vec, nb, block, K, par_block, n_chunks, mode);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_sum_fwd_sm(float* node_mars, const float* element_mars, const void* packed, const int32_t* first_row,
+                   const int32_t* nids, const int32_t* cids, int64_t n_merged, int nb, int K, int B, void* stream) {
+    if (n_merged <= 0 || B <= 0) return 0;
+    if ((nb != 32 && nb != 64) || K <= 0) return -1;
+    SmArgs a{};
+    a.out = node_mars; a.src = element_mars; a.packed = reinterpret_cast<const uint4*>(packed);
+    a.first_row = first_row; a.rows = nids; a.kids = cids; a.n_st = (int)pcx_cdiv(B, SM_SAMPLES);
+    a.n_tiles = n_merged * a.n_st; a.K = K; a.par_block = 1; a.B = B; a.logspace = 1;
+    a.terms = (g_sum_mode == 2) ? 1 : 3;
+    return nb == 32 ? launch_sm<32, false>(a, (cudaStream_t)stream) : launch_sm<64, false>(a, (cudaStream_t)stream);
+}
+
+int pcx_sum_bwd_ele_sm(float* element_flows, const float* element_mars, const float* node_flows,
+                       const float* node_mars, const void* packed, const int32_t* first_row, const int32_t* chids,
+                       const int32_t* parids, int64_t n_merged, int nb, int P, int block_size, int B, int logspace,
+                       void* stream) {
+    if (n_merged <= 0 || B <= 0) return 0;
+    if ((nb != 32 && nb != 64) || P <= 0 || block_size % 8 != 0 || (block_size & (block_size - 1)) != 0) return -1;
+    SmArgs a{};
+    a.out = element_flows; a.src = node_flows; a.src2 = node_mars; a.emars = element_mars;
+    a.packed = reinterpret_cast<const uint4*>(packed); a.first_row = first_row; a.rows = chids; a.kids = parids;
+    a.n_st = (int)pcx_cdiv(B, SM_SAMPLES); a.n_tiles = n_merged * a.n_st; a.K = P; a.par_block = block_size; a.B = B;
+    a.logspace = logspace; a.terms = (g_sum_mode == 2) ? 1 : 3;
+    return nb == 32 ? launch_sm<32, true>(a, (cudaStream_t)stream) : launch_sm<64, true>(a, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -550,7 +550,8 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
     {
         const int cl = SMALLK ? 0 : n_chunks - 1;       // the last commit covers every MMA issued before it
         const uint32_t par = SMALLK ? ph[0] : ph[cl % STAGES] + cl / STAGES;
-        if (!failed && !mbar_wait(&sh.bar[cl % STAGES], par & 1)) { failed = true; sh.fail = 2; }
+        // one thread waits for the tensor core; the others sleep in the barrier below instead of spinning
+        if (tid == 0 && !failed && !mbar_wait(&sh.bar[cl % STAGES], par & 1)) sh.fail = 2;
         if (SMALLK) ph[0] += 1;
         else
 #pragma unroll
@@ -1439,3 +1440,4 @@ int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, cons
 }  // extern "C"
 
 #include "pcx_sum_dense.cuh"
+#include "pcx_sum_sm.cuh"

@@ -47,6 +47,7 @@ class ParamPacker:
     def __init__(self, device):
         self.device = device
         self.entries = {}
+        self.sm_entries = {}
         self._stamp = None
         self._epoch = 0
 
@@ -80,14 +81,30 @@ class ParamPacker:
         jobs = torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
         return jobs, len(self.entries), vec
 
+    def register_sm(self, key, first_row, kids, kpar, n_merged, nb, block, K, par_block, mode):
+        """Parameter tiles of a sample-major table (small node blocks); identical tables share one buffer."""
+        entry = self.sm_entries.get(key)
+        if entry is None:
+            depth = K if mode == 0 else K * par_block
+            nbytes = int(_lib.load().pcx_sm_packed_bytes(n_merged, depth, nb))
+            entry = dict(buf=torch.empty(nbytes, dtype=torch.uint8, device=self.device),
+                         args=(first_row, kids, kpar, n_merged, nb, block, K, par_block, mode))
+            self.sm_entries[key] = entry
+            self._stamp = None
+        return entry["buf"]
+
     def refresh(self, params: torch.Tensor):
         stamp = (params.data_ptr(), params._version, self._epoch)
-        if stamp == self._stamp or not self.entries:
+        if stamp == self._stamp or not (self.entries or self.sm_entries):
             return
-        if getattr(self, "_jobs", None) is None:
-            self._jobs = self._job_table()
-        jobs, n_jobs, n_vec = self._jobs
-        _lib.call("pcx_pack_sum_params", jobs, n_jobs, n_vec, params)
+        if self.entries:
+            if getattr(self, "_jobs", None) is None:
+                self._jobs = self._job_table()
+            jobs, n_jobs, n_vec = self._jobs
+            _lib.call("pcx_pack_sum_params", jobs, n_jobs, n_vec, params)
+        for e in self.sm_entries.values():
+            first_row, kids, kpar, n_merged, nb, block, K, par_block, mode = e["args"]
+            _lib.call("pcx_pack_sm_params", e["buf"], params, first_row, kids, kpar, n_merged, nb, block, K, par_block, mode)
         self._stamp = stamp
 
     @property
@@ -364,6 +381,57 @@ class SumLayer(Layer, nn.Module):
                         key = ("bk", bs, cbs, tuple(parids.shape), cpu_tables["partitioned_parpids"][p].numpy().tobytes(),
                                (cpu_tables["partitioned_parids"][p] != 0).numpy().tobytes())
                         self._packed_bk[p] = packer.register(key, chids.numel(), parids.size(1), cbs, bs, 1, parids, parpids)
+                # small blocks: sample-major tiles of one block, or of two consecutive blocks that list the same children
+                def merged_rows(table, ids, block):
+                    """[(nb, first_row tensor)]: pairs of consecutive, identical rows (nb = 2 * block <= 64), then singles."""
+                    if block not in (32, 64) or table.size(0) == 0:
+                        return None
+                    n = table.size(0)
+                    pair = torch.zeros(n, dtype=torch.bool)
+                    if block == 32 and n > 1:
+                        same = ((table[1:] == table[:-1]).all(dim=1) & (ids[1:] == ids[:-1] + block)).tolist()
+                        i = 0
+                        while i < n - 1:
+                            if same[i]:
+                                pair[i] = True
+                                i += 2
+                            else:
+                                i += 1
+                    second = torch.zeros(n, dtype=torch.bool)
+                    second[1:] = pair[:-1]
+                    out = []
+                    if bool(pair.any()):
+                        out.append((2 * block, torch.nonzero(pair).reshape(-1)))
+                    single = torch.nonzero(~pair & ~second).reshape(-1)
+                    if single.numel() > 0:
+                        out.append((block, single))
+                    return out
+
+                self._sm_fw = [None] * self.num_fw_partitions
+                self._sm_bk = [None] * self.num_bk_partitions
+                for p, (nids, cids, pids, _) in enumerate(self._dev["fw"]):
+                    groups = merged_rows(cpu_tables["partitioned_cids"][p], cpu_tables["partitioned_nids"][p], bs)
+                    if groups is not None:
+                        self._sm_fw[p] = []
+                        for nb, first in groups:
+                            key = ("smfw", bs, nb, tuple(pids.shape), cpu_tables["partitioned_pids"][p].numpy().tobytes(),
+                                   first.numpy().tobytes())
+                            fr = _dev_i32(first, device)
+                            buf = packer.register_sm(key, fr, cids, pids, first.numel(), nb, bs, cids.size(1), 1, 0)
+                            self._sm_fw[p].append((nb, fr, first.numel(), buf))
+                for p, ((chids, parids, parpids), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
+                    if bs % 8 != 0 or (bs & (bs - 1)) != 0:
+                        continue
+                    groups = merged_rows(cpu_tables["partitioned_parids"][p], cpu_tables["partitioned_chids"][p], cbs)
+                    if groups is not None:
+                        self._sm_bk[p] = []
+                        for nb, first in groups:
+                            # two child blocks can only share a tile if their parameter tiles line up as well
+                            key = ("smbk", bs, cbs, nb, tuple(parids.shape), cpu_tables["partitioned_parpids"][p].numpy().tobytes(),
+                                   (cpu_tables["partitioned_parids"][p] != 0).numpy().tobytes(), first.numpy().tobytes())
+                            fr = _dev_i32(first, device)
+                            buf = packer.register_sm(key, fr, parids, parpids, first.numel(), nb, cbs, parids.size(1), bs, 1)
+                            self._sm_bk[p].append((nb, fr, first.numel(), buf))
             # rows of a table that list the same children (parents) share one tensor-core operand in the dense kernels
             def groups_of(table):
                 uniq, inverse = torch.unique(table, dim=0, return_inverse=True)
@@ -388,6 +456,7 @@ class SumLayer(Layer, nn.Module):
         return self._packer.scratch(int(_lib.load().pcx_dense_scratch_bytes(n_groups, depth, B)))
 
     use_dense_kernels = True
+    use_sample_major = True          # tensor-core tiles of 128 samples x 32/64 nodes for small node blocks
 
     def _use_packed(self, params):
         if self._packer is None or _lib.SUM_MODE == 0:
@@ -414,6 +483,10 @@ class SumLayer(Layer, nn.Module):
             elif packed and self._packed_fw[p] is not None:
                 _lib.call("pcx_sum_fwd_packed", node_mars, element_mars, self._packed_fw[p], nids, cids,
                           nids.numel(), cids.size(1), self.block_size, B)
+            elif packed and self.use_sample_major and self._sm_fw[p] is not None:
+                for nb, first_row, n_merged, buf in self._sm_fw[p]:
+                    _lib.call("pcx_sum_fwd_sm", node_mars, element_mars, buf, first_row, nids, cids, n_merged, nb,
+                              cids.size(1), B)
             else:
                 _lib.call("pcx_sum_fwd", node_mars, element_mars, params, nids, cids, pids,
                           nids.numel(), cids.size(1), self.block_size, B)
@@ -462,6 +535,10 @@ class SumLayer(Layer, nn.Module):
             elif packed and self._packed_bk[p] is not None:
                 _lib.call("pcx_sum_bwd_ele_packed", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p],
                           chids, parids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
+            elif packed and self.use_sample_major and self._sm_bk[p] is not None:
+                for nb, first_row, n_merged, buf in self._sm_bk[p]:
+                    _lib.call("pcx_sum_bwd_ele_sm", element_flows, element_mars, node_flows, node_mars, buf, first_row,
+                              chids, parids, n_merged, nb, parids.size(1), self.block_size, B, ls)
             else:
                 _lib.call("pcx_sum_bwd_ele", element_flows, element_mars, node_flows, node_mars, params,
                           chids, parids, parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)

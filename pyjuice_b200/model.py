@@ -419,7 +419,7 @@ class TensorCircuit(nn.Module):
     def _launch_cfg(self):
         """Everything that changes which kernels a pass launches (part of the key of a captured graph)."""
         return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
-                SumLayer.use_dense_kernels, getattr(self._packer, "grown", 0))
+                SumLayer.use_dense_kernels, SumLayer.use_sample_major, getattr(self._packer, "grown", 0))
 
     def _chain_plan(self, B: int, mode: int):
         """Job table of the dataflow launch (one launch for a run of consecutive depths) for the forward pass
