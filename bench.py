@@ -106,7 +106,9 @@ def family_of(name: str) -> str:
         return "pcx_sum_fwd" if name.endswith("_fwd") else "pcx_sum_bwd_ele"
     if name.startswith("pcx_sum_par_dense"):              # operand staging + one product: the parameter flows
         return "pcx_sum_bwd_par"
-    for suffix in ("_fused", "_packed", "_batched", "_noalloc", "_dense"):
+    if name.startswith("pcx_pack_sm"):
+        return "pcx_pack_sum_params"
+    for suffix in ("_fused", "_packed", "_batched", "_noalloc", "_dense", "_sm"):
         if name.endswith(suffix):
             name = name[:-len(suffix)]
     return name

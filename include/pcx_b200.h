@@ -193,6 +193,24 @@ int64_t pcx_sm_packed_bytes(int64_t n_merged, int depth, int nb);
 int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_row, const int32_t* kids,
                        const int32_t* kpar, int64_t n_merged, int nb, int block, int K, int par_block, int mode,
                        void* stream);
+/* Parameter flows of small blocks on the tensor cores (layer/sum_layer.py:1721-2080): the contraction runs over the
+ * batch, the MMA's M dimension is the edge index (128 per tile), N the nb nodes of the merged row.  B must be a multiple
+ * of 8; element_mars row 0 must hold -inf (the dummy element). */
+int pcx_sum_bwd_par_sm(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                       const float* params, const int32_t* first_row, const int32_t* nids, const int32_t* cids,
+                       const int32_t* pids, const int32_t* pfids, int64_t n_merged, int nb, int block, int K, int B,
+                       int logspace, void* stream);
+/* The same conversion for many tables in one launch: `jobs` is a DEVICE array of n_jobs records, vec_begin the running
+ * sum of n_merged * n_chunks * 8 * nb over the preceding jobs, n_vec the total. */
+typedef struct PcxSmPackJob {
+    void* out;
+    const int32_t* first_row;
+    const int32_t* kids;
+    const int32_t* kpar;
+    int64_t vec_begin;
+    int32_t nb, block, K, par_block, n_chunks, mode;
+} PcxSmPackJob;
+int pcx_pack_sm_jobs(const void* jobs, int n_jobs, int64_t n_vec, const float* params, void* stream);
 int pcx_sum_fwd_sm(float* node_mars, const float* element_mars, const void* packed, const int32_t* first_row,
                    const int32_t* nids, const int32_t* cids, int64_t n_merged, int nb, int K, int B, void* stream);
 int pcx_sum_bwd_ele_sm(float* element_flows, const float* element_mars, const float* node_flows,

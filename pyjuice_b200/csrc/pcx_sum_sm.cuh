@@ -83,17 +83,16 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
         const int colc = col_ok ? col : 0;
 
         // log-domain values of one 8-deep K group (unconditional loads, row 0 exists and is masked afterwards)
+        // (entries without a child / parent read the dummy row 0, see the small-table kernel below)
         auto load_group = [&](int kb, float* v) {
             if (!ELE) {
                 int cid[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) cid[j] = (col_ok && kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
+                for (int j = 0; j < 8; ++j) cid[j] = (kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = a.src[(int64_t)cid[j] * B + colc];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = (cid[j] != 0) ? v[j] : PCX_NEG_INF;
             } else {
-                const int pr = (col_ok && kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
+                const int pr = (kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
                 const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
                 float nf[8], nm[8];
 #pragma unroll
@@ -101,9 +100,49 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     float f = nf[j];
-                    if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
-                    v[j] = (pr == 0 || nm[j] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[j];
+                    if (!a.logspace) f = __logf(f);
+                    v[j] = (pr == 0) ? PCX_NEG_INF : f - fmaxf(nm[j], -3.0e38f);
                 }
+            }
+        };
+        // four groups at once (the thread's share of one chunk): every index, then every value, then the arithmetic,
+        // so that one chunk costs two memory round trips instead of eight
+        auto load_groups4 = [&](int kb0, float (*v)[8]) {
+            if (!ELE) {
+                int cid[4][8];
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = kb0 + 16 * t + j;
+                        cid[t][j] = (k < KK) ? a.kids[(int64_t)i0 * a.K + k] : 0;
+                    }
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[t][j] = a.src[(int64_t)cid[t][j] * B + colc];
+            } else {
+                int pr[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int kb = kb0 + 16 * t;
+                    pr[t] = (kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
+                }
+                float nf[4][8], nm[4][8];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int64_t row = (int64_t)pr[t] + ((kb0 + 16 * t) & (a.par_block - 1));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { nf[t][j] = a.src[(row + j) * B + colc]; nm[t][j] = a.src2[(row + j) * B + colc]; }
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float f = nf[t][j];
+                        if (!a.logspace) f = __logf(f);
+                        v[t][j] = (pr[t] == 0) ? PCX_NEG_INF : f - fmaxf(nm[t][j], -3.0e38f);
+                    }
             }
         };
         auto copy_theta = [&](int chunk, uint8_t* st) {
@@ -111,8 +150,9 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
             for (int w = tid; w < TH_TILE / 16; w += NTH) cp_async16(st + 2 * SM_E_TILE + w * 16, src + w);
         };
         auto store_group = [&](uint8_t* st, int g, float* v, float mx) {
+            const float mxc = (mx == PCX_NEG_INF) ? 0.0f : mx;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = (v[j] == PCX_NEG_INF) ? 0.0f : __expf(v[j] - mx);
+            for (int j = 0; j < 8; ++j) v[j] = __expf(v[j] - mxc);
             uint8_t* dst = st + g * (SM_SAMPLES * 16) + ls * 16;
             store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + SM_E_TILE), v);
         };
@@ -149,11 +189,13 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
                 for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[t][j]);
             }
         } else {
-            for (int g = h; g < n_groups; g += 2) {
-                float v[8];
-                load_group(g * 8, v);
+            for (int c = 0; c < n_chunks; ++c) {                    // groups h, h + 2, h + 4, h + 6 of every chunk
+                float v[4][8];
+                load_groups4(c * KC + h * 8, v);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[j]);
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[t][j]);
             }
         }
         s_part[h][ls] = mx;
@@ -185,10 +227,11 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
                 uint8_t* st = smem + s * SM_STAGE;
                 if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (ph[s] + use - 1) & 1)) { failed = true; s_fail = 1; }
                 copy_theta(c, st);
-                for (int g = h; g < KG; g += 2) {
-                    float v[8];
-                    load_group(c * KC + g * 8, v);
-                    store_group(st, g, v, mx);
+                {
+                    float v[4][8];
+                    load_groups4(c * KC + h * 8, v);
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) store_group(st, h + 2 * t, v[t], mx);
                 }
                 cp_async_wait_all();
                 fence_async_smem();
@@ -225,12 +268,9 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
                 for (int j = 0; j < 8; ++j) {
                     const int64_t off = (base_row + c0 + 8 * p + j) * B + b;
                     float o;
-                    if (!ELE) {
-                        o = (m_s == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m_s;
-                    } else {
-                        o = (m_s == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m_s;
-                        const float em = a.emars[off];
-                        o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
+                    if (!ELE) o = __logf(fmaxf(v[j], 1e-24f)) + m_s;
+                    else {
+                        o = __logf(v[j]) + m_s + a.emars[off];
                         if (!a.logspace) o = __expf(o);
                     }
                     a.out[off] = o;
@@ -296,8 +336,13 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
                 cp_async16(t_lo + w * 16, src + KG * NB + w);
             }
         }
+        // Values of this thread's sample for every table entry.  Entries without a child / parent (id 0) read row 0,
+        // the dummy row, which holds "probability zero" by the buffers' contract (element_mars: -inf); no per-value
+        // masking is needed there.  A sample beyond the batch reads column 0 and is never stored.
         float keep[8][8];
         float mx = PCX_NEG_INF;
+        const float* src_col = a.src + colc;
+        const float* src2_col = ELE ? a.src2 + colc : nullptr;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             if (g < ng) {
@@ -305,33 +350,33 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
                 if (!ELE) {
                     int cid[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) cid[j] = (col_ok && kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
+                    for (int j = 0; j < 8; ++j) cid[j] = (kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) keep[g][j] = a.src[(int64_t)cid[j] * B + colc];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) keep[g][j] = (cid[j] != 0) ? keep[g][j] : PCX_NEG_INF;
+                    for (int j = 0; j < 8; ++j) keep[g][j] = src_col[(int64_t)cid[j] * B];
                 } else {
-                    const int pr = (col_ok && kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
+                    const int pr = (kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
                     const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
                     float nf[8], nm[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) { nf[j] = a.src[(row + j) * B + colc]; nm[j] = a.src2[(row + j) * B + colc]; }
+                    for (int j = 0; j < 8; ++j) { nf[j] = src_col[(row + j) * B]; nm[j] = src2_col[(row + j) * B]; }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         float f = nf[j];
-                        if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
-                        keep[g][j] = (pr == 0 || nm[j] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[j];
+                        if (!a.logspace) f = __logf(f);                              // log(0) = -inf
+                        // flow / value in the log domain; (-inf) - (-inf) must read as -inf, hence the clamp
+                        keep[g][j] = (pr == 0) ? PCX_NEG_INF : f - fmaxf(nm[j], -3.0e38f);
                     }
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[g][j]);
             }
         }
+        const float mxc = (mx == PCX_NEG_INF) ? 0.0f : mx;          // exp(-inf - 0) = 0: no per-value masking either
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             if (g < ng) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) keep[g][j] = (keep[g][j] == PCX_NEG_INF) ? 0.0f : __expf(keep[g][j] - mx);
+                for (int j = 0; j < 8; ++j) keep[g][j] = __expf(keep[g][j] - mxc);
                 store_split8(reinterpret_cast<uint4*>(e_hi + g * (SM_SAMPLES * 16) + tid * 16),
                              reinterpret_cast<uint4*>(e_lo + g * (SM_SAMPLES * 16) + tid * 16), keep[g]);
             }
@@ -362,25 +407,27 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
         const bool failed = s_fail != 0;
         tc_fence_after_sync();
         if (!failed) {
-            const int64_t base_row = (int64_t)a.rows[i0];
+            const int64_t base = (int64_t)a.rows[i0] * B + colc;
+            float* out_col = a.out + base;
+            const float* em_col = ELE ? a.emars + base : nullptr;
 #pragma unroll
             for (int p = 0; p < NB / 8; ++p) {
-                float v[8];
+                float v[8], em[8];
+                if (ELE)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) em[j] = em_col[(int64_t)(8 * p + j) * B];
                 tmem_ld<8>(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(8 * p), v);    // warp-wide: every lane takes part
                 if (!col_ok) continue;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const int64_t off = (base_row + 8 * p + j) * B + col;
+                    // log(0) = -inf and -inf + x = -inf take care of empty sums, zero shifts and zero element values
                     float o;
-                    if (!ELE) {
-                        o = (mx == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + mx;
-                    } else {
-                        o = (mx == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + mx;
-                        const float em = a.emars[off];
-                        o = (o == PCX_NEG_INF || em == PCX_NEG_INF) ? PCX_NEG_INF : o + em;
+                    if (!ELE) o = __logf(fmaxf(v[j], 1e-24f)) + mx;
+                    else {
+                        o = __logf(v[j]) + mx + em[j];
                         if (!a.logspace) o = __expf(o);
                     }
-                    a.out[off] = o;
+                    out_col[(int64_t)(8 * p + j) * B] = o;
                 }
             }
         }
@@ -426,6 +473,245 @@ __global__ void pack_sm_kernel(uint4* __restrict__ out, const float* __restrict_
             v[j] = (pr != 0) ? params[(int64_t)kpar[i * K + p] + (int64_t)n * par_block + np + j] : 0.0f;
     }
     uint4* base = out + tile * (2 * KG * NB);
+    store_split8(base + g * NB + r, base + KG * NB + g * NB + r, v);
+}
+
+// ---- parameter flows of small blocks ------------------------------------------------------------------------------
+// pf[n, k] += theta[n, k] * sum_b exp(flow[n,b] - value[n,b] - shift[b]) * exp(child[k,b] + shift[b]).
+// The contraction runs over the batch; the MMA's M dimension is the EDGE index k (128 per tile, rows beyond the table
+// are zero), N the NB nodes of the merged row.  A CTA (128 threads, four per SM, as sum_par_tc_kernel) walks its share
+// of the batch in 32-sample slices; shift[b] is the maximum over the NB nodes.
+struct SmParArgs {
+    float* param_flows;
+    const float* node_flows;
+    const float* node_mars;
+    const float* element_mars;
+    const float* params;
+    const int32_t* first_row;   // [n_merged]
+    const int32_t* nids;
+    const int32_t* cids;        // [n, K]
+    const int32_t* pids;
+    const int32_t* pfids;
+    int K, block, B, logspace, terms, chunks_per_cta;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(PNTH, 4) sum_sm_par_kernel(const SmParArgs a) {
+    constexpr int NSLAB = NB * 16 + 16;                // padded slab of the node-side tile
+    constexpr int N_TILE = PKG * NSLAB;
+    constexpr int TCOLS = NB < 32 ? 32 : NB;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t s_bar[STAGES];
+    __shared__ uint32_t s_tmem;
+    __shared__ __align__(16) float s_part[PNTH / 32][PKC];
+    __shared__ int s_fail;
+    constexpr int STAGE = 2 * X_TILE + 2 * N_TILE;     // edge-side tile (128 rows, as X_TILE) + node-side tile
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t m = blockIdx.x;
+    const int e0 = blockIdx.y * BM;
+    const int i0 = a.first_row[m];
+    const int B = a.B;
+    const int total_chunks = (B + PKC - 1) / PKC;
+    const int c_begin = blockIdx.z * a.chunks_per_cta;
+    const int c_end = min(total_chunks, c_begin + a.chunks_per_cta);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[s], 1);
+        fence_mbar_init();
+        s_fail = 0;
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+
+    const int g = tid & (PKG - 1), rb = tid / PKG;     // 8-sample group g of the slice, rows rb + 32 j
+    const uint32_t idesc = idesc_bf16_f32(BM, NB);
+    const int64_t nid0 = a.nids[i0];                   // the merged row's nodes are consecutive
+    int cid[4];                                        // this thread's four edge rows
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int e = e0 + rb + 32 * j;
+        cid[j] = (e < a.K) ? a.cids[(int64_t)i0 * a.K + e] : 0;
+    }
+    bool failed = false;
+
+    for (int c = c_begin; c < c_end; ++c) {
+        const int it = c - c_begin, s = it % STAGES, use = it / STAGES;
+        uint8_t* st = smem + s * STAGE;
+        const int bb = c * PKC + g * 8;
+        const bool b_ok = bb < B;                      // B is a multiple of 8 here
+        const int bbc = b_ok ? bb : 0;
+
+        float y[4][8], x[NB / 32][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {                   // edge side: element values (row 0 = dummy = -inf)
+            const float4 q0 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc);
+            const float4 q1 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc + 4);
+            y[j][0] = q0.x; y[j][1] = q0.y; y[j][2] = q0.z; y[j][3] = q0.w;
+            y[j][4] = q1.x; y[j][5] = q1.y; y[j][6] = q1.z; y[j][7] = q1.w;
+        }
+#pragma unroll
+        for (int j = 0; j < NB / 32; ++j) {             // node side: log(flow / value)
+            const int64_t off = (nid0 + rb + 32 * j) * B + bbc;
+            const float4 f0 = *reinterpret_cast<const float4*>(a.node_flows + off);
+            const float4 f1 = *reinterpret_cast<const float4*>(a.node_flows + off + 4);
+            const float4 m0 = *reinterpret_cast<const float4*>(a.node_mars + off);
+            const float4 m1 = *reinterpret_cast<const float4*>(a.node_mars + off + 4);
+            const float nf[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+            const float nm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                float f = nf[t];
+                if (!a.logspace) f = __logf(f);
+                x[j][t] = b_ok ? f - fmaxf(nm[t], -3.0e38f) : PCX_NEG_INF;
+            }
+        }
+        float pm[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            float mm = x[0][t];
+#pragma unroll
+            for (int j = 1; j < NB / 32; ++j) mm = fmaxf(mm, x[j][t]);
+#pragma unroll
+            for (int o = PKG; o < 32; o <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+            pm[t] = mm;
+        }
+        if (lane < PKG) {
+            float4* dst = reinterpret_cast<float4*>(&s_part[warp][lane * 8]);
+            dst[0] = make_float4(pm[0], pm[1], pm[2], pm[3]);
+            dst[1] = make_float4(pm[4], pm[5], pm[6], pm[7]);
+        }
+        if (it >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
+        __syncthreads();
+        float sh[8];
+        {
+            const float4 p0 = *reinterpret_cast<const float4*>(&s_part[0][g * 8]);
+            const float4 p1 = *reinterpret_cast<const float4*>(&s_part[0][g * 8 + 4]);
+            sh[0] = p0.x; sh[1] = p0.y; sh[2] = p0.z; sh[3] = p0.w; sh[4] = p1.x; sh[5] = p1.y; sh[6] = p1.z; sh[7] = p1.w;
+#pragma unroll
+            for (int w = 1; w < PNTH / 32; ++w) {
+                const float4 q0 = *reinterpret_cast<const float4*>(&s_part[w][g * 8]);
+                const float4 q1 = *reinterpret_cast<const float4*>(&s_part[w][g * 8 + 4]);
+                sh[0] = fmaxf(sh[0], q0.x); sh[1] = fmaxf(sh[1], q0.y); sh[2] = fmaxf(sh[2], q0.z); sh[3] = fmaxf(sh[3], q0.w);
+                sh[4] = fmaxf(sh[4], q1.x); sh[5] = fmaxf(sh[5], q1.y); sh[6] = fmaxf(sh[6], q1.z); sh[7] = fmaxf(sh[7], q1.w);
+            }
+        }
+        uint8_t* yhi = st;
+        uint8_t* ylo = st + X_TILE;
+        uint8_t* xhi = st + 2 * X_TILE;
+        uint8_t* xlo = st + 2 * X_TILE + N_TILE;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t)       // a sample without any flow (shift -inf) contributes nothing
+                y[j][t] = (sh[t] == PCX_NEG_INF || !b_ok) ? 0.0f : fminf(__expf(y[j][t] + sh[t]), 3.0e38f);
+            const int o = g * XSLAB + (rb + 32 * j) * 16;
+            store_split8(reinterpret_cast<uint4*>(yhi + o), reinterpret_cast<uint4*>(ylo + o), y[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < NB / 32; ++j) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) x[j][t] = (sh[t] == PCX_NEG_INF) ? 0.0f : __expf(x[j][t] - sh[t]);
+            const int o = g * NSLAB + (rb + 32 * j) * 16;
+            store_split8(reinterpret_cast<uint4*>(xhi + o), reinterpret_cast<uint4*>(xlo + o), x[j]);
+        }
+        fence_async_smem();
+        __syncthreads();
+        failed = failed || (s_fail != 0);
+        if (tid == 0 && !failed) {
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(st);
+            issue_stage<XSLAB, NSLAB, PKC>(tmem, sa, sa + 2 * X_TILE, idesc, it == 0, a.terms);
+            mma_commit(&s_bar[s]);
+        }
+    }
+
+    const int n_it = c_end - c_begin;
+    if (n_it > 0) {
+        const int il = n_it - 1;
+        if (tid == 0 && !failed && !mbar_wait(&s_bar[il % STAGES], (uint32_t)((il / STAGES) & 1))) s_fail = 2;
+    }
+    __syncthreads();
+    failed = failed || (s_fail != 0);
+    tc_fence_after_sync();
+    if (!failed && n_it > 0) {
+        const int e = e0 + warp * 32 + lane;            // this thread's edge (TMEM lane)
+        const bool e_ok = e < a.K && a.cids[(int64_t)i0 * a.K + min(e, a.K - 1)] != 0;
+#pragma unroll 1
+        for (int p = 0; p < NB / 8; ++p) {
+            float v[8];
+            tmem_ld<8>(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(8 * p), v);    // warp-wide
+            if (!e_ok) continue;
+            const int n0 = 8 * p;                       // eight consecutive nodes lie in one block (blocks >= 8 nodes)
+            const int64_t i = (int64_t)i0 + n0 / a.block;
+            const int nn = n0 % a.block;
+            const float* par = a.params + (int64_t)a.pids[i * a.K + e] + nn;
+            float* pf = a.param_flows + (int64_t)a.pfids[i * a.K + e] + nn;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = par[j] * v[j];
+                if (f != 0.0f) atomicAdd(pf + j, f);
+            }
+        }
+    }
+    if (failed && tid == 0) atomicCAS(&g_tc_status, 0, 520 + s_fail);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TCOLS);
+}
+
+// All sample-major tables of a circuit in one launch: a device array of jobs, the job of a vector is found by binary
+// search over vec_begin (the running sum of the jobs' vector counts).
+struct SmPackJob {
+    uint4* out;
+    const int32_t* first_row;
+    const int32_t* kids;
+    const int32_t* kpar;
+    int64_t vec_begin;
+    int32_t nb, block, K, par_block, n_chunks, mode;
+};
+static_assert(sizeof(SmPackJob) == 64, "matches PcxSmPackJob");
+
+__global__ void pack_sm_jobs_kernel(const SmPackJob* __restrict__ jobs, int n_jobs, int64_t n_vec,
+                                    const float* __restrict__ params) {
+    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_vec) return;
+    int lo = 0, hi = n_jobs - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (jobs[mid].vec_begin <= t) lo = mid; else hi = mid - 1;
+    }
+    const SmPackJob a = jobs[lo];
+    t -= a.vec_begin;
+    const int NB = a.nb;
+    const int r = (int)(t % NB);
+    const int g = (int)((t / NB) % KG);
+    const int64_t tile = t / ((int64_t)NB * KG);
+    const int chunk = (int)(tile % a.n_chunks);
+    const int64_t m = tile / a.n_chunks;
+    const int64_t i = (int64_t)a.first_row[m] + r / a.block;
+    const int n = r % a.block;
+    const int kb = chunk * KC + g * 8;
+    float v[8];
+    if (a.mode == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = kb + j;
+            v[j] = (k < a.K) ? params[(int64_t)a.kpar[i * a.K + k] + n] : 0.0f;
+        }
+    } else {
+        const int KK = a.K * a.par_block;
+        const int p = kb / a.par_block, np = kb % a.par_block;
+        const int pr = (kb < KK) ? a.kids[i * a.K + p] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] = (pr != 0) ? params[(int64_t)a.kpar[i * a.K + p] + (int64_t)n * a.par_block + np + j] : 0.0f;
+    }
+    uint4* base = a.out + tile * (2 * KG * NB);
     store_split8(base + g * NB + r, base + KG * NB + g * NB + r, v);
 }
 
@@ -479,6 +765,51 @@ int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_r
     const int64_t n_vec = n_merged * n_chunks * KG * nb;
     pack_sm_kernel<<<(unsigned)pcx_cdiv(n_vec, 256), 256, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<uint4*>(packed), params, first_row, kids, kpar, n_vec, nb, block, K, par_block, n_chunks, mode);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_sum_bwd_par_sm(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                       const float* params, const int32_t* first_row, const int32_t* nids, const int32_t* cids,
+                       const int32_t* pids, const int32_t* pfids, int64_t n_merged, int nb, int block, int K, int B,
+                       int logspace, void* stream) {
+    if (n_merged <= 0 || B <= 0) return 0;
+    if ((nb != 32 && nb != 64) || block < 8 || nb % block != 0 || K <= 0 || B % 8 != 0) return -1;
+    SmParArgs a{param_flows, node_flows, node_mars, element_mars, params, first_row, nids, cids, pids, pfids,
+                K, block, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1};
+    const int64_t base = n_merged * pcx_cdiv(K, BM);
+    const int total_chunks = (int)pcx_cdiv(B, PKC);
+    int64_t splits = pcx_cdiv(8 * 148, base);                  // about two waves of four CTAs per SM
+    if (splits > total_chunks) splits = total_chunks;
+    if (splits < 1) splits = 1;
+    a.chunks_per_cta = (int)pcx_cdiv(total_chunks, splits);
+    dim3 grid((unsigned)n_merged, (unsigned)pcx_cdiv(K, BM), (unsigned)pcx_cdiv(total_chunks, a.chunks_per_cta));
+    const int smem = STAGES * (2 * X_TILE + 2 * PKG * (nb * 16 + 16)) + 1024;
+    static bool done32 = false, done64 = false;
+    cudaError_t e;
+    if (nb == 32) {
+        if (!done32) {
+            e = cudaFuncSetAttribute(sum_sm_par_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return (int)e;
+            done32 = true;
+        }
+        sum_sm_par_kernel<32><<<grid, PNTH, smem, (cudaStream_t)stream>>>(a);
+    } else {
+        if (!done64) {
+            e = cudaFuncSetAttribute(sum_sm_par_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return (int)e;
+            done64 = true;
+        }
+        sum_sm_par_kernel<64><<<grid, PNTH, smem, (cudaStream_t)stream>>>(a);
+    }
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_pack_sm_jobs(const void* jobs, int n_jobs, int64_t n_vec, const float* params, void* stream) {
+    if (n_jobs <= 0 || n_vec <= 0) return 0;
+    pack_sm_jobs_kernel<<<(unsigned)pcx_cdiv(n_vec, 256), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const SmPackJob*>(jobs), n_jobs, n_vec, params);
     PCX_LAUNCH_CHECK();
     return 0;
 }

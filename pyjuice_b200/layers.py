@@ -91,6 +91,7 @@ class ParamPacker:
                          args=(first_row, kids, kpar, n_merged, nb, block, K, par_block, mode))
             self.sm_entries[key] = entry
             self._stamp = None
+            self._sm_jobs = None
         return entry["buf"]
 
     def refresh(self, params: torch.Tensor):
@@ -102,10 +103,28 @@ class ParamPacker:
                 self._jobs = self._job_table()
             jobs, n_jobs, n_vec = self._jobs
             _lib.call("pcx_pack_sum_params", jobs, n_jobs, n_vec, params)
-        for e in self.sm_entries.values():
-            first_row, kids, kpar, n_merged, nb, block, K, par_block, mode = e["args"]
-            _lib.call("pcx_pack_sm_params", e["buf"], params, first_row, kids, kpar, n_merged, nb, block, K, par_block, mode)
+        if self.sm_entries:
+            if getattr(self, "_sm_jobs", None) is None:
+                self._sm_jobs = self._sm_job_table()
+            jobs, n_jobs, n_vec = self._sm_jobs
+            _lib.call("pcx_pack_sm_jobs", jobs, n_jobs, n_vec, params)
         self._stamp = stamp
+
+    def _sm_job_table(self):
+        """Device array of PcxSmPackJob records (include/pcx_b200.h), one per sample-major table."""
+        import numpy as np
+        dt = np.dtype([("out", "<u8"), ("first_row", "<u8"), ("kids", "<u8"), ("kpar", "<u8"), ("vec_begin", "<i8"),
+                       ("nb", "<i4"), ("block", "<i4"), ("K", "<i4"), ("par_block", "<i4"), ("n_chunks", "<i4"), ("mode", "<i4")])
+        rec = np.zeros(len(self.sm_entries), dtype=dt)
+        vec = 0
+        for j, e in enumerate(self.sm_entries.values()):
+            first_row, kids, kpar, n_merged, nb, block, K, par_block, mode = e["args"]
+            n_chunks = ((K if mode == 0 else K * par_block) + 63) // 64
+            rec[j] = (e["buf"].data_ptr(), first_row.data_ptr(), kids.data_ptr(), kpar.data_ptr(), vec, nb, block, K,
+                      par_block, n_chunks, mode)
+            vec += n_merged * n_chunks * 8 * nb
+        jobs = torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
+        return jobs, len(self.sm_entries), vec
 
     @property
     def nbytes(self):
@@ -548,6 +567,12 @@ class SumLayer(Layer, nn.Module):
                 if (stage is not None and packed and self._dense_ok(p, B, False) and self._groups_fw[p][2] == 1
                         and stage(self, p, node_flows, node_mars, element_mars, ls)):
                     continue                       # this table's flows come out of one product over all staged layers
+                if (packed and self.use_sample_major and self._packed_fw[p] is None and self._sm_fw[p] is not None
+                        and B % 8 == 0):
+                    for nb, first_row, n_merged, _ in self._sm_fw[p]:
+                        _lib.call("pcx_sum_bwd_par_sm", param_flows, node_flows, node_mars, element_mars, params,
+                                  first_row, nids, cids, pids, pfids, n_merged, nb, self.block_size, cids.size(1), B, ls)
+                    continue
                 _lib.call("pcx_sum_bwd_par", param_flows, node_flows, node_mars, element_mars, params,
                           nids, cids, pids, pfids, nids.numel(), cids.size(1), self.block_size, B, ls)
 
