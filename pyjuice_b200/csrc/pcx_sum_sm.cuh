@@ -70,7 +70,6 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
     const int KK = ELE ? a.K * a.par_block : a.K;
     const int lg_pb = ELE ? (31 - __clz(a.par_block)) : 0;
     const int n_chunks = (KK + KC - 1) / KC;
-    const int n_groups = (KK + 7) / 8;
     const int ls = tid & (SM_SAMPLES - 1), h = tid >> 7;       // operand role: sample ls, K groups h, h + 2, ...
     const uint32_t idesc = idesc_bf16_f32(SM_SAMPLES, NB);
 
@@ -84,27 +83,6 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
 
         // log-domain values of one 8-deep K group (unconditional loads, row 0 exists and is masked afterwards)
         // (entries without a child / parent read the dummy row 0, see the small-table kernel below)
-        auto load_group = [&](int kb, float* v) {
-            if (!ELE) {
-                int cid[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) cid[j] = (kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = a.src[(int64_t)cid[j] * B + colc];
-            } else {
-                const int pr = (kb < KK) ? a.kids[(int64_t)i0 * a.K + (kb >> lg_pb)] : 0;
-                const int64_t row = (int64_t)pr + (kb & (a.par_block - 1));
-                float nf[8], nm[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { nf[j] = a.src[(row + j) * B + colc]; nm[j] = a.src2[(row + j) * B + colc]; }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float f = nf[j];
-                    if (!a.logspace) f = __logf(f);
-                    v[j] = (pr == 0) ? PCX_NEG_INF : f - fmaxf(nm[j], -3.0e38f);
-                }
-            }
-        };
         // four groups at once (the thread's share of one chunk): every index, then every value, then the arithmetic,
         // so that one chunk costs two memory round trips instead of eight
         auto load_groups4 = [&](int kb0, float (*v)[8]) {
@@ -172,31 +150,15 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
             }
         };
 
-        // ---- pass 1: per-sample maximum; tables up to 128 deep keep their values in registers -----------------
-        const bool small = n_chunks <= STAGES;
-        float keep[8][8];
+        // ---- pass 1: per-sample maximum (tables this deep are read twice; the second read hits L2) -----------------
         float mx = PCX_NEG_INF;
-        if (small) {
-            for (int c = 0; c < n_chunks; ++c) copy_theta(c, smem + c * SM_STAGE);
+        for (int c = 0; c < n_chunks; ++c) {                    // groups h, h + 2, h + 4, h + 6 of every chunk
+            float v[4][8];
+            load_groups4(c * KC + h * 8, v);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const int g = h + 2 * t;
-                if (g < n_groups) load_group(g * 8, keep[t]);
-                else
+            for (int t = 0; t < 4; ++t)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) keep[t][j] = PCX_NEG_INF;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, keep[t][j]);
-            }
-        } else {
-            for (int c = 0; c < n_chunks; ++c) {                    // groups h, h + 2, h + 4, h + 6 of every chunk
-                float v[4][8];
-                load_groups4(c * KC + h * 8, v);
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[t][j]);
-            }
+                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[t][j]);
         }
         s_part[h][ls] = mx;
         __syncthreads();
@@ -205,44 +167,28 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
 
         // ---- pass 2: exponentials -> operand tiles, multiply ------------------------------------------------
         bool failed = false;
-        if (small) {
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % STAGES, use = c / STAGES;
+            uint8_t* st = smem + s * SM_STAGE;
+            if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (ph[s] + use - 1) & 1)) { failed = true; s_fail = 1; }
+            copy_theta(c, st);
+            {
+                float v[4][8];
+                load_groups4(c * KC + h * 8, v);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const int g = h + 2 * t;
-                if (g < n_chunks * KG) store_group(smem + (g / KG) * SM_STAGE, g % KG, keep[t], mx);
+                for (int t = 0; t < 4; ++t) store_group(st, h + 2 * t, v[t], mx);
             }
             cp_async_wait_all();
             fence_async_smem();
             __syncthreads();
-            if (tid == 0) {
+            failed = failed || (s_fail != 0);
+            if (tid == 0 && !failed) {
                 tc_fence_after_sync();
-                for (int c = 0; c < n_chunks; ++c) issue(smem + c * SM_STAGE, c == 0);
-                mma_commit(&s_bar[0]);
+                issue(st, c == 0);
+                mma_commit(&s_bar[s]);
             }
-            if (tid == 0 && !mbar_wait(&s_bar[0], ph[0] & 1)) s_fail = 2;      // one thread waits, the rest sleep below
-            ph[0] += 1;
-        } else {
-            for (int c = 0; c < n_chunks; ++c) {
-                const int s = c % STAGES, use = c / STAGES;
-                uint8_t* st = smem + s * SM_STAGE;
-                if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (ph[s] + use - 1) & 1)) { failed = true; s_fail = 1; }
-                copy_theta(c, st);
-                {
-                    float v[4][8];
-                    load_groups4(c * KC + h * 8, v);
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) store_group(st, h + 2 * t, v[t], mx);
-                }
-                cp_async_wait_all();
-                fence_async_smem();
-                __syncthreads();
-                failed = failed || (s_fail != 0);
-                if (tid == 0 && !failed) {
-                    tc_fence_after_sync();
-                    issue(st, c == 0);
-                    mma_commit(&s_bar[s]);
-                }
-            }
+        }
+        {
             const int cl = n_chunks - 1;
             if (tid == 0 && !failed && !mbar_wait(&s_bar[cl % STAGES], (ph[cl % STAGES] + cl / STAGES) & 1)) s_fail = 2;
 #pragma unroll
