@@ -162,8 +162,9 @@ class TensorCircuit(nn.Module):
         pass, whose tables list every product of the layer (layer/compilation.py:980-1040), would hand the row's
         stale content — the flow of another depth's product with the same element id — down to the children.  The
         reference resets the buffer once per backward pass only (model/tensorcircuit.py:526-528), so it has this
-        defect; here the element range of such a group is reset before the group's element flows are computed, which
-        makes the flows the true gradients (checked against autograd in tests/test_oracle_pins.py)."""
+        defect; here the kernels' copies of the product backward tables skip such products (and `get_node_flows`
+        resets their rows before reading), which makes the flows the true gradients (checked against autograd in
+        tests/test_oracle_pins.py)."""
         out = {}
         groups = self.inner_layer_groups
         for gi in range(0, len(groups) - 1, 2):
@@ -179,14 +180,29 @@ class TensorCircuit(nn.Module):
                 for nids in layer.partitioned_nids:
                     rows = (nids.cpu()[:, None] + torch.arange(layer.block_size)[None, :]).reshape(-1)
                     exists[rows] = True
-            if bool((exists & ~has_parent).any()):
-                out[gi] = (lo, hi)
+            orphan = exists & ~has_parent
+            if bool(orphan.any()):
+                out[gi] = (lo, hi, orphan)
         return out
 
     def _reset_parentless(self, prod_gi: int, logspace_flows: bool):
         rng = self._parentless.get(prod_gi)
         if rng is not None:
             _fill(self.element_flows[rng[0]:rng[1]], NEG_INF if logspace_flows else 0.0)
+
+    def _mask_parentless_in_device_tables(self):
+        """The kernels' copies of the product layers' backward tables skip parentless products (id 0 = padding), so
+        the backward sweep needs no reset of the element-flow buffer; the public tables stay as compiled."""
+        for gi, (lo, hi, orphan) in self._parentless.items():
+            for layer in self.inner_layer_groups[gi]:
+                if layer._dev is None:
+                    continue
+                bk = []
+                for u_cids, parids in layer._dev["bk"]:
+                    p = parids.long().cpu()
+                    dead = orphan[p.clamp(max=hi - 1)] & (p != 0)
+                    bk.append((u_cids, torch.where(dead, torch.zeros_like(p), p).to(torch.int32).to(parids.device)))
+                layer._dev["bk"] = bk
 
     def _compile_em_blocks(self):
         """Per node block of every untied sum vector: first parameter, first flow, real fan-in, block size —
@@ -253,6 +269,8 @@ class TensorCircuit(nn.Module):
                             for start, n, accs in self._tied_sum_groups]
         for name in ("node_mars", "element_mars", "node_flows", "element_flows", "param_flows"):
             setattr(self, name, None)
+        if device.type == "cuda":
+            self._mask_parentless_in_device_tables()
         self._setup_fusion()
         self._side_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self._graphs = {}
@@ -649,14 +667,11 @@ class TensorCircuit(nn.Module):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
             elif self._fusion_on(gi, True):
                 any_fused = True
-                if not self._fused[gi]["direct"]:
-                    self._reset_parentless(gi - 1, logspace_flows)
                 for layer in group:
                     layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
             else:
                 # the shared element buffer holds another depth by now: recompute this depth's products
                 groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
-                self._reset_parentless(gi - 1, logspace_flows)
                 group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
                                self.params.data, param_flows=pf, logspace_flows=logspace_flows,
                                dense_par_stage=dense_stage if dense is not None else None)
