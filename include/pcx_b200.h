@@ -188,7 +188,10 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
  * with pcx_pack_sm_params (mode 0: forward tables nids/cids/pids, block = block size; mode 1: element-flow tables
  * chids/parids/parpids, block = child block size, par_block = block size of the parents) into a caller-owned buffer
  * of pcx_sm_packed_bytes(n_merged, depth, nb) bytes (depth = K, or P * par_block).  Same results as pcx_sum_fwd /
- * pcx_sum_bwd_ele (layer/sum_layer.py:551-929, 1369-1719). */
+ * pcx_sum_bwd_ele (layer/sum_layer.py:551-929, 1369-1719).
+ * Product layer folded in (products of at most two children): pass `fk` instead of reading element_mars -- pairs of
+ * child rows of node_mars, [n, K, 2] per table entry for the forward pass and the parameter flows, [n, child block
+ * size, 2] per output element for the element flows ((0, 0) = no element); fk == NULL reads element_mars. */
 int64_t pcx_sm_packed_bytes(int64_t n_merged, int depth, int nb);
 int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_row, const int32_t* kids,
                        const int32_t* kpar, int64_t n_merged, int nb, int block, int K, int par_block, int mode,
@@ -198,8 +201,8 @@ int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_r
  * of 8; element_mars row 0 must hold -inf (the dummy element). */
 int pcx_sum_bwd_par_sm(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
                        const float* params, const int32_t* first_row, const int32_t* nids, const int32_t* cids,
-                       const int32_t* pids, const int32_t* pfids, int64_t n_merged, int nb, int block, int K, int B,
-                       int logspace, void* stream);
+                       const int32_t* pids, const int32_t* pfids, const int32_t* fk, int64_t n_merged, int nb,
+                       int block, int K, int B, int logspace, void* stream);
 /* The same conversion for many tables in one launch: `jobs` is a DEVICE array of n_jobs records, vec_begin the running
  * sum of n_merged * n_chunks * 8 * nb over the preceding jobs, n_vec the total. */
 typedef struct PcxSmPackJob {
@@ -212,11 +215,12 @@ typedef struct PcxSmPackJob {
 } PcxSmPackJob;
 int pcx_pack_sm_jobs(const void* jobs, int n_jobs, int64_t n_vec, const float* params, void* stream);
 int pcx_sum_fwd_sm(float* node_mars, const float* element_mars, const void* packed, const int32_t* first_row,
-                   const int32_t* nids, const int32_t* cids, int64_t n_merged, int nb, int K, int B, void* stream);
+                   const int32_t* nids, const int32_t* cids, const int32_t* fk, int64_t n_merged, int nb, int K, int B,
+                   void* stream);
 int pcx_sum_bwd_ele_sm(float* element_flows, const float* element_mars, const float* node_flows,
                        const float* node_mars, const void* packed, const int32_t* first_row, const int32_t* chids,
-                       const int32_t* parids, int64_t n_merged, int nb, int P, int block_size, int B, int logspace,
-                       void* stream);
+                       const int32_t* parids, const int32_t* fk, int ch_block_size, int64_t n_merged, int nb, int P,
+                       int block_size, int B, int logspace, void* stream);
 
 /* Forward (mode 0) or element flows (mode 1) of a RUN of consecutive layers in one launch, product layers folded in
  * (as pcx_sum_fwd_fused / pcx_sum_bwd_ele_fused with direct stores).  Tiles are work items claimed from a device

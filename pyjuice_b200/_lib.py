@@ -43,10 +43,10 @@ SIGNATURES = {
     "pcx_sum_par_dense_stage": [P, P, P, P, P, P, P, P, L, I, I, I, I, I, I],
     "pcx_sum_par_dense_gemm": [P, P, P, P, P, P, P, L, I, I, I],
     "pcx_pack_sm_params": [P, P, P, P, P, L, I, I, I, I, I],
-    "pcx_sum_bwd_par_sm": [P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I],
+    "pcx_sum_bwd_par_sm": [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_pack_sm_jobs": [P, I, L, P],
-    "pcx_sum_fwd_sm": [P, P, P, P, P, P, L, I, I, I],
-    "pcx_sum_bwd_ele_sm": [P, P, P, P, P, P, P, P, L, I, I, I, I, I],
+    "pcx_sum_fwd_sm": [P, P, P, P, P, P, P, L, I, I, I],
+    "pcx_sum_bwd_ele_sm": [P, P, P, P, P, P, P, P, P, I, L, I, I, I, I, I],
     "pcx_sum_chain": [I, P, P, P, I, L, I, I, I, I, I, P, L],
     "pcx_sum_bwd_par_batched": [P, P, P, P, P, I, L, I, I, I, I],
     "pcx_sum_fwd_noalloc": [P, P, P, P, P, P, L, I, I, I],

@@ -37,7 +37,19 @@ struct SmArgs {
     int B;
     int logspace;
     int terms;
+    // Product layer folded in (products of at most two children): FWD: fk = [n, K] pairs of child rows of node_mars
+    // per table entry; ELE: fk = [n, child block size] pairs per output element.  nmars = node_mars.  A pair (0, 0)
+    // means "no element"; row 0 of node_mars is the dummy node with value 0, so a single child needs no masking.
+    const int2* fk;
+    const float* nmars;
+    int cbs;                    // ELE: child block size (rows of fk per table row)
 };
+
+// value of a folded product: sum of its two child rows, -inf when it has no child at all
+__device__ __forceinline__ float folded2(const int2 r, const float* nmars_col, int B) {
+    const float v = nmars_col[(int64_t)r.x * B] + nmars_col[(int64_t)r.y * B];
+    return ((r.x | r.y) != 0) ? v : PCX_NEG_INF;
+}
 
 // One CTA walks tiles m * n_st + st (static round-robin: tiles do not depend on each other).
 template <int NB, bool ELE>
@@ -86,7 +98,19 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
         // four groups at once (the thread's share of one chunk): every index, then every value, then the arithmetic,
         // so that one chunk costs two memory round trips instead of eight
         auto load_groups4 = [&](int kb0, float (*v)[8]) {
-            if (!ELE) {
+            if (!ELE && a.fk != nullptr) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    int2 r[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = kb0 + 16 * t + j;
+                        r[j] = (k < KK) ? a.fk[(int64_t)i0 * a.K + k] : make_int2(0, 0);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[t][j] = folded2(r[j], a.nmars + colc, B);
+                }
+            } else if (!ELE) {
                 int cid[4][8];
 #pragma unroll
                 for (int t = 0; t < 4; ++t)
@@ -216,7 +240,9 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
                     float o;
                     if (!ELE) o = __logf(fmaxf(v[j], 1e-24f)) + m_s;
                     else {
-                        o = __logf(v[j]) + m_s + a.emars[off];
+                        const float em = (a.fk != nullptr)
+                            ? folded2(a.fk[(int64_t)i0 * a.cbs + c0 + 8 * p + j], a.nmars + b, B) : a.emars[off];
+                        o = __logf(v[j]) + m_s + em;
                         if (!a.logspace) o = __expf(o);
                     }
                     a.out[off] = o;
@@ -293,7 +319,13 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
         for (int g = 0; g < 8; ++g) {
             if (g < ng) {
                 const int kb = g * 8;
-                if (!ELE) {
+                if (!ELE && a.fk != nullptr) {
+                    int2 r[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) r[j] = (kb + j < KK) ? a.fk[(int64_t)i0 * a.K + kb + j] : make_int2(0, 0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) keep[g][j] = folded2(r[j], a.nmars + colc, B);
+                } else if (!ELE) {
                     int cid[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) cid[j] = (kb + j < KK) ? a.kids[(int64_t)i0 * a.K + kb + j] : 0;
@@ -359,9 +391,15 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
 #pragma unroll
             for (int p = 0; p < NB / 8; ++p) {
                 float v[8], em[8];
-                if (ELE)
+                if (ELE) {
+                    if (a.fk != nullptr) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) em[j] = em_col[(int64_t)(8 * p + j) * B];
+                        for (int j = 0; j < 8; ++j) em[j] = folded2(a.fk[(int64_t)i0 * a.cbs + 8 * p + j], a.nmars + colc, B);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) em[j] = em_col[(int64_t)(8 * p + j) * B];
+                    }
+                }
                 tmem_ld<8>(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(8 * p), v);    // warp-wide: every lane takes part
                 if (!col_ok) continue;
 #pragma unroll
@@ -439,6 +477,7 @@ struct SmParArgs {
     const int32_t* pids;
     const int32_t* pfids;
     int K, block, B, logspace, terms, chunks_per_cta;
+    const int2* fk;             // product layer folded in: [n, K] pairs of child rows of node_mars (see SmArgs)
 };
 
 template <int NB>
@@ -478,10 +517,12 @@ __global__ void __launch_bounds__(PNTH, 4) sum_sm_par_kernel(const SmParArgs a) 
     const uint32_t idesc = idesc_bf16_f32(BM, NB);
     const int64_t nid0 = a.nids[i0];                   // the merged row's nodes are consecutive
     int cid[4];                                        // this thread's four edge rows
+    int2 ch[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int e = e0 + rb + 32 * j;
         cid[j] = (e < a.K) ? a.cids[(int64_t)i0 * a.K + e] : 0;
+        ch[j] = (a.fk != nullptr && cid[j] != 0) ? a.fk[(int64_t)i0 * a.K + e] : make_int2(0, 0);
     }
     bool failed = false;
 
@@ -493,12 +534,27 @@ __global__ void __launch_bounds__(PNTH, 4) sum_sm_par_kernel(const SmParArgs a) 
         const int bbc = b_ok ? bb : 0;
 
         float y[4][8], x[NB / 32][8];
+        if (a.fk != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {                   // edge side: element values (row 0 = dummy = -inf)
-            const float4 q0 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc);
-            const float4 q1 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc + 4);
-            y[j][0] = q0.x; y[j][1] = q0.y; y[j][2] = q0.z; y[j][3] = q0.w;
-            y[j][4] = q1.x; y[j][5] = q1.y; y[j][6] = q1.z; y[j][7] = q1.w;
+            for (int j = 0; j < 4; ++j) {               // edge side, folded: sum of the product's two child rows
+                const float* r0p = a.node_mars + (int64_t)ch[j].x * B + bbc;
+                const float* r1p = a.node_mars + (int64_t)ch[j].y * B + bbc;
+                const float4 p0 = *reinterpret_cast<const float4*>(r0p), p1 = *reinterpret_cast<const float4*>(r0p + 4);
+                const float4 q0 = *reinterpret_cast<const float4*>(r1p), q1 = *reinterpret_cast<const float4*>(r1p + 4);
+                const bool any = (ch[j].x | ch[j].y) != 0;
+                y[j][0] = any ? p0.x + q0.x : PCX_NEG_INF; y[j][1] = any ? p0.y + q0.y : PCX_NEG_INF;
+                y[j][2] = any ? p0.z + q0.z : PCX_NEG_INF; y[j][3] = any ? p0.w + q0.w : PCX_NEG_INF;
+                y[j][4] = any ? p1.x + q1.x : PCX_NEG_INF; y[j][5] = any ? p1.y + q1.y : PCX_NEG_INF;
+                y[j][6] = any ? p1.z + q1.z : PCX_NEG_INF; y[j][7] = any ? p1.w + q1.w : PCX_NEG_INF;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {               // edge side: element values (row 0 = dummy = -inf)
+                const float4 q0 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc);
+                const float4 q1 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc + 4);
+                y[j][0] = q0.x; y[j][1] = q0.y; y[j][2] = q0.z; y[j][3] = q0.w;
+                y[j][4] = q1.x; y[j][5] = q1.y; y[j][6] = q1.z; y[j][7] = q1.w;
+            }
         }
 #pragma unroll
         for (int j = 0; j < NB / 32; ++j) {             // node side: log(flow / value)
@@ -717,12 +773,13 @@ int pcx_pack_sm_params(void* packed, const float* params, const int32_t* first_r
 
 int pcx_sum_bwd_par_sm(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
                        const float* params, const int32_t* first_row, const int32_t* nids, const int32_t* cids,
-                       const int32_t* pids, const int32_t* pfids, int64_t n_merged, int nb, int block, int K, int B,
-                       int logspace, void* stream) {
+                       const int32_t* pids, const int32_t* pfids, const int32_t* fk, int64_t n_merged, int nb,
+                       int block, int K, int B, int logspace, void* stream) {
     if (n_merged <= 0 || B <= 0) return 0;
     if ((nb != 32 && nb != 64) || block < 8 || nb % block != 0 || K <= 0 || B % 8 != 0) return -1;
+    if (fk == nullptr && element_mars == nullptr) return -1;
     SmParArgs a{param_flows, node_flows, node_mars, element_mars, params, first_row, nids, cids, pids, pfids,
-                K, block, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1};
+                K, block, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1, reinterpret_cast<const int2*>(fk)};
     const int64_t base = n_merged * pcx_cdiv(K, BM);
     const int total_chunks = (int)pcx_cdiv(B, PKC);
     int64_t splits = pcx_cdiv(8 * 148, base);                  // about two waves of four CTAs per SM
@@ -761,10 +818,12 @@ int pcx_pack_sm_jobs(const void* jobs, int n_jobs, int64_t n_vec, const float* p
 }
 
 int pcx_sum_fwd_sm(float* node_mars, const float* element_mars, const void* packed, const int32_t* first_row,
-                   const int32_t* nids, const int32_t* cids, int64_t n_merged, int nb, int K, int B, void* stream) {
+                   const int32_t* nids, const int32_t* cids, const int32_t* fk, int64_t n_merged, int nb, int K, int B,
+                   void* stream) {
     if (n_merged <= 0 || B <= 0) return 0;
-    if ((nb != 32 && nb != 64) || K <= 0) return -1;
+    if ((nb != 32 && nb != 64) || K <= 0 || (fk == nullptr && element_mars == nullptr)) return -1;
     SmArgs a{};
+    a.fk = reinterpret_cast<const int2*>(fk); a.nmars = node_mars;
     a.out = node_mars; a.src = element_mars; a.packed = reinterpret_cast<const uint4*>(packed);
     a.first_row = first_row; a.rows = nids; a.kids = cids; a.n_st = (int)pcx_cdiv(B, SM_SAMPLES);
     a.n_tiles = n_merged * a.n_st; a.K = K; a.par_block = 1; a.B = B; a.logspace = 1;
@@ -774,11 +833,13 @@ int pcx_sum_fwd_sm(float* node_mars, const float* element_mars, const void* pack
 
 int pcx_sum_bwd_ele_sm(float* element_flows, const float* element_mars, const float* node_flows,
                        const float* node_mars, const void* packed, const int32_t* first_row, const int32_t* chids,
-                       const int32_t* parids, int64_t n_merged, int nb, int P, int block_size, int B, int logspace,
-                       void* stream) {
+                       const int32_t* parids, const int32_t* fk, int ch_block_size, int64_t n_merged, int nb, int P,
+                       int block_size, int B, int logspace, void* stream) {
     if (n_merged <= 0 || B <= 0) return 0;
     if ((nb != 32 && nb != 64) || P <= 0 || block_size % 8 != 0 || (block_size & (block_size - 1)) != 0) return -1;
+    if (fk == nullptr && element_mars == nullptr) return -1;
     SmArgs a{};
+    a.fk = reinterpret_cast<const int2*>(fk); a.nmars = node_mars; a.cbs = ch_block_size;
     a.out = element_flows; a.src = node_flows; a.src2 = node_mars; a.emars = element_mars;
     a.packed = reinterpret_cast<const uint4*>(packed); a.first_row = first_row; a.rows = chids; a.kids = parids;
     a.n_st = (int)pcx_cdiv(B, SM_SAMPLES); a.n_tiles = n_merged * a.n_st; a.K = P; a.par_block = block_size; a.B = B;

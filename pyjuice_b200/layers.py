@@ -504,7 +504,7 @@ class SumLayer(Layer, nn.Module):
                           nids.numel(), cids.size(1), self.block_size, B)
             elif packed and self.use_sample_major and self._sm_fw[p] is not None:
                 for nb, first_row, n_merged, buf in self._sm_fw[p]:
-                    _lib.call("pcx_sum_fwd_sm", node_mars, element_mars, buf, first_row, nids, cids, n_merged, nb,
+                    _lib.call("pcx_sum_fwd_sm", node_mars, element_mars, buf, first_row, nids, cids, None, n_merged, nb,
                               cids.size(1), B)
             else:
                 _lib.call("pcx_sum_fwd", node_mars, element_mars, params, nids, cids, pids,
@@ -515,12 +515,25 @@ class SumLayer(Layer, nn.Module):
     # ---- product layer folded in (tables prepared by TensorCircuit._setup_fusion) ------------------------------
     def forward_fused(self, node_mars: torch.Tensor):
         B, f = node_mars.size(1), self._fusion
+        if f.get("sm"):                                   # small blocks: sample-major tiles, products of two children
+            for p, (nids, cids, _, _) in enumerate(self._dev["fw"]):
+                for nb, first_row, n_merged, buf in self._sm_fw[p]:
+                    _lib.call("pcx_sum_fwd_sm", node_mars, None, buf, first_row, nids, cids, f["fw"][p], n_merged, nb,
+                              cids.size(1), B)
+            return
         for p, (nids, cids, _, _) in enumerate(self._dev["fw"]):
             _lib.call("pcx_sum_fwd_fused", node_mars, self._packed_fw[p], nids, cids, f["fw"][p], f["fc"],
                       nids.numel(), cids.size(1), self.block_size, B)
 
     def backward_ele_fused(self, node_flows, element_flows, node_mars, logspace_flows: bool):
         B, f = node_flows.size(1), self._fusion
+        if f.get("sm"):
+            for p, ((chids, parids, _), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
+                for nb, first_row, n_merged, buf in self._sm_bk[p]:
+                    _lib.call("pcx_sum_bwd_ele_sm", element_flows, None, node_flows, node_mars, buf, first_row, chids,
+                              parids, f["bk"][p], cbs, n_merged, nb, parids.size(1), self.block_size, B,
+                              int(bool(logspace_flows)))
+            return
         for p, ((chids, parids, _), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
             _lib.call("pcx_sum_bwd_ele_fused", element_flows, node_flows, node_mars, self._packed_bk[p], chids, parids,
                       f["bk"][p], f["fc"], int(f["direct"]), chids.numel(), parids.size(1), self.block_size, cbs, B,
@@ -528,6 +541,13 @@ class SumLayer(Layer, nn.Module):
 
     def backward_par_fused(self, node_flows, node_mars, params, param_flows, logspace_flows: bool):
         B, f = node_flows.size(1), self._fusion
+        if f.get("sm"):
+            for p, (nids, cids, pids, pfids) in enumerate(self._dev["fw"]):
+                for nb, first_row, n_merged, _ in self._sm_fw[p]:
+                    _lib.call("pcx_sum_bwd_par_sm", param_flows, node_flows, node_mars, None, params, first_row, nids,
+                              cids, pids, pfids, f["fw"][p], n_merged, nb, self.block_size, cids.size(1), B,
+                              int(bool(logspace_flows)))
+            return
         for p, (nids, cids, pids, pfids) in enumerate(self._dev["fw"]):
             _lib.call("pcx_sum_bwd_par_fused", param_flows, node_flows, node_mars, params, nids, cids, pids, pfids,
                       f["fw"][p], f["fc"], nids.numel(), cids.size(1), self.block_size, B, int(bool(logspace_flows)))
@@ -557,7 +577,7 @@ class SumLayer(Layer, nn.Module):
             elif packed and self.use_sample_major and self._sm_bk[p] is not None:
                 for nb, first_row, n_merged, buf in self._sm_bk[p]:
                     _lib.call("pcx_sum_bwd_ele_sm", element_flows, element_mars, node_flows, node_mars, buf, first_row,
-                              chids, parids, n_merged, nb, parids.size(1), self.block_size, B, ls)
+                              chids, parids, None, cbs, n_merged, nb, parids.size(1), self.block_size, B, ls)
             else:
                 _lib.call("pcx_sum_bwd_ele", element_flows, element_mars, node_flows, node_mars, params,
                           chids, parids, parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls)
@@ -571,7 +591,7 @@ class SumLayer(Layer, nn.Module):
                         and B % 8 == 0):
                     for nb, first_row, n_merged, _ in self._sm_fw[p]:
                         _lib.call("pcx_sum_bwd_par_sm", param_flows, node_flows, node_mars, element_mars, params,
-                                  first_row, nids, cids, pids, pfids, n_merged, nb, self.block_size, cids.size(1), B, ls)
+                                  first_row, nids, cids, pids, pfids, None, n_merged, nb, self.block_size, cids.size(1), B, ls)
                     continue
                 _lib.call("pcx_sum_bwd_par", param_flows, node_flows, node_mars, element_mars, params,
                           nids, cids, pids, pfids, nids.numel(), cids.size(1), self.block_size, B, ls)

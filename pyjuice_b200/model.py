@@ -304,13 +304,18 @@ class TensorCircuit(nn.Module):
                         parents.index_add_(0, rows, torch.ones_like(rows, dtype=torch.int32))
         for gi in range(1, len(self.inner_layer_groups), 2):
             pgroup, sgroup = self.inner_layer_groups[gi - 1], self.inner_layer_groups[gi]
-            if not all(l.block_size % 128 == 0 and l._packer is not None and all(b is not None for b in l._packed_fw)
-                       and all(b is not None for b in l._packed_bk) for l in sgroup):
+            big = all(l.block_size % 128 == 0 and l._packer is not None and all(b is not None for b in l._packed_fw)
+                      and all(b is not None for b in l._packed_bk) for l in sgroup)
+            # small blocks (sample-major tiles): products of at most two children can be folded in as well
+            small = (not big) and all(l._packer is not None and getattr(l, "_sm_fw", None) is not None
+                                      and all(t is not None for t in l._sm_fw) and all(t is not None for t in l._sm_bk)
+                                      for l in sgroup)
+            if not (big or small):
                 continue
             C = max(int((c != 0).sum(dim=1).max()) for l in pgroup for c in l.partitioned_cids)
-            if C > 8:
+            if C > (8 if big else 2):
                 continue
-            fc = 4 if C <= 4 else 8
+            fc = 2 if small else (4 if C <= 4 else 8)
             n_ele = max(l._layer_nid_range[1] for l in pgroup)
             children = torch.zeros(n_ele, fc, dtype=torch.int32)
             for layer in pgroup:
@@ -323,19 +328,23 @@ class TensorCircuit(nn.Module):
                     ch = (cids[:, None, :fc] + j[None, :, None]) * (cids[:, None, :fc] != 0)
                     children[rows] = ch.reshape(-1, fc).to(torch.int32)
             used = (children != 0).any(dim=1).sum().item()
-            reads = sum(int(l.block_size // 128) * int((c != 0).sum()) for l in sgroup for c in l.partitioned_cids)
+            if big:
+                reads = sum(int(l.block_size // 128) * int((c != 0).sum()) for l in sgroup for c in l.partitioned_cids)
+            else:                                           # every merged row gathers each of its entries once per tile
+                reads = sum(int((c.cpu()[first.long().cpu()] != 0).sum()) for l in sgroup
+                            for c, lists in zip(l.partitioned_cids, l._sm_fw) for _, first, _, _ in lists)
             if used == 0 or reads > 2 * used:
                 continue
             ch_rows = children[children != 0].long()
-            direct = bool((parents[ch_rows] == 1).all())
+            direct = big and bool((parents[ch_rows] == 1).all())
             for layer in sgroup:
                 fw = [children[c.cpu()].contiguous().to(dev) for c in layer.partitioned_cids]
                 bk = []
                 for chids, cbs in zip(layer.partitioned_chids, layer.cs_block_sizes):
                     rows = chids.cpu()[:, None] + torch.arange(cbs)[None, :]
                     bk.append(children[rows].contiguous().to(dev))
-                layer._fusion = dict(fc=fc, fw=fw, bk=bk, direct=direct)
-            self._fused[gi] = dict(fc=fc, direct=direct,
+                layer._fusion = dict(fc=fc, fw=fw, bk=bk, direct=direct, sm=small)
+            self._fused[gi] = dict(fc=fc, direct=direct, sm=small,
                                    child_rows=torch.unique(ch_rows) if not direct else None)
         # rows of node_flows that still need the -inf / 0 reset each pass: children of every depth that is not
         # handled by direct stores (those are accumulated into with logaddexp)
@@ -432,6 +441,8 @@ class TensorCircuit(nn.Module):
         reads eight samples per vector load, so the backward sweep only folds when the batch is a multiple of 8."""
         if not (self.fuse_product_layers and _lib.SUM_MODE != 0 and gi in self._fused):
             return False
+        if self._fused[gi]["sm"] and not SumLayer.use_sample_major:
+            return False
         return (not backward) or self.node_mars.size(1) % 8 == 0
 
     def _launch_cfg(self):
@@ -454,7 +465,8 @@ class TensorCircuit(nn.Module):
         plan = None
         if self.use_dataflow_launch:
             def ok(gi):
-                return self._fusion_on(gi, backward=(mode == 1)) and (mode == 0 or self._fused[gi]["direct"])
+                return (self._fusion_on(gi, backward=(mode == 1)) and not self._fused[gi]["sm"]
+                        and (mode == 0 or self._fused[gi]["direct"]))
             runs, cur = [], []
             for gi in range(1, len(groups), 2):
                 if ok(gi) and (not cur or self._fused[cur[-1]]["fc"] == self._fused[gi]["fc"]):
@@ -565,7 +577,7 @@ class TensorCircuit(nn.Module):
                         ("item_begin", "<i8"), ("K", "<i4"), ("block_size", "<i4"), ("e_tiles", "<i4"), ("splits", "<i4")])
         per_fc = {}
         for gi, group in enumerate(self.inner_layer_groups):
-            if group.is_sum() and self._fusion_on(gi, True):
+            if group.is_sum() and self._fusion_on(gi, True) and not self._fused[gi]["sm"]:
                 for layer in group:
                     f = layer._fusion
                     for p, (nids, cids, pids, pfids) in enumerate(layer._dev["fw"]):
@@ -666,8 +678,10 @@ class TensorCircuit(nn.Module):
                 if not (self._fusion_on(gi + 1, True) and self._fused[gi + 1]["direct"]):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
             elif self._fusion_on(gi, True):
-                any_fused = True
+                any_fused = any_fused or not self._fused[gi]["sm"]
                 for layer in group:
+                    if self._fused[gi]["sm"] and pf is not None:       # (the 128-row kernels do this in one launch below)
+                        layer.backward_par_fused(self.node_flows, self.node_mars, self.params.data, pf, logspace_flows)
                     layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
             else:
                 # the shared element buffer holds another depth by now: recompute this depth's products
