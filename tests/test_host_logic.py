@@ -104,3 +104,19 @@ def test_parameters_are_normalised_after_compile():
         s = pc.params.data[p0:p0 + fan * bs].view(fan, bs).sum(dim=0)
         assert torch.allclose(s, torch.ones_like(s), atol=1e-5)
     assert torch.all(pc.params.data[:pc.num_dummy_params] == 0)
+
+
+def test_patch_pyjuice_rebinds_the_front_door(monkeypatch):
+    """`patch_pyjuice` swaps the compiled path of an installed PyJuice for this engine (a stand-in module here)."""
+    import sys
+    import types
+    import pyjuice_b200 as pj
+    fake = types.ModuleType("pyjuice")
+    fake.model = types.ModuleType("pyjuice.model")
+    fake.optim = types.ModuleType("pyjuice.optim")
+    fake.compile = fake.TensorCircuit = fake.model.compile = fake.model.TensorCircuit = None
+    monkeypatch.setitem(sys.modules, "pyjuice", fake)
+    out = pj.patch_pyjuice()
+    assert out is fake
+    assert fake.compile is pj.compile and fake.model.TensorCircuit is pj.TensorCircuit
+    assert fake.optim.MiniBatchEM is pj.optim.MiniBatchEM and fake.optim.FullBatchEM is pj.optim.FullBatchEM
