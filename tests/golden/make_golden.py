@@ -18,7 +18,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
-REF_SRC = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+if len(sys.argv) < 2:
+    sys.exit("usage: python make_golden.py <path to the PyJuice checkout>/src")
+REF_SRC = sys.argv[1]
 
 
 def load_reference():
