@@ -1,7 +1,7 @@
 """Generates ``tests/golden/<case>.npz``: the index tables the REFERENCE compiler emits for every case of
 ``cases.py``.  Run in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py [/path/to/reference/src]
+    python tests/golden/make_golden.py <path to the PyJuice checkout>/src
 
 The reference imports matplotlib (absent here) and touches CUDA in three places while compiling; both are
 neutralised below, in this script only, so that its table compiler runs on the host
