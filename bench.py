@@ -401,7 +401,7 @@ def main():
     sum_tflops = 6.0 * stats["e_sum"] * B / (sum_ms * 1e-3) / 1e12 if sum_ms > 0 else None
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:            # the CPU baseline is reported by the single-GPU run only
         sample = min(B, args.cpu_sample)
         sec = oracle_step_time(pc, torch.from_numpy(x[:sample]))
         cores = torch.get_num_threads()
