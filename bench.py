@@ -430,9 +430,10 @@ def main():
         "cpu_baseline": cpu,
         "clocks": clocks,
     }
-    print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+    sys.stderr.flush()
+    print(json.dumps(out), flush=True)                 # the one JSON line, last thing on stdout
 
 
 if __name__ == "__main__":
