@@ -260,6 +260,7 @@ def test_dense_layers_match_oracle_and_tiled_kernels(B, homogeneous):
     assert any(l._dense_ok(0, B, False) for g in pc.inner_layer_groups if g.is_sum() for l in g), "expected dense tables"
     for rep in range(3):
         check_against_oracle(pc, x, step=0.05, pseudo=0.1)
+    check_against_oracle(pc, x, step=0.05, pseudo=0.1, logspace_flows=False)
     out = {}
     try:
         for dense in (True, False):
@@ -283,7 +284,7 @@ def _lib_status():
 
 
 @pytest.mark.parametrize("B", [64, 100, 256])
-@pytest.mark.parametrize("case", ["pd", "rat", "hmm64"])
+@pytest.mark.parametrize("case", ["pd", "rat", "hmm64", "hmm32_tied"])
 def test_small_blocks_on_tensor_cores_match_oracle_and_cuda_core_kernels(case, B):
     """Node blocks of 32 / 64 run as sample-major tensor-core tiles (128 samples x 32 / 64 nodes; pairs of blocks that
     list the same children share a tile).  Checked against the oracle, against the fp32 CUDA-core kernels, over
@@ -296,8 +297,10 @@ def test_small_blocks_on_tensor_cores_match_oracle_and_cuda_core_kernels(case, B
         ns = pj.structures.PD((8, 8), num_latents=64, split_points=[[2, 4, 6], [4]], num_cats=6)
     elif case == "rat":
         ns = pj.structures.RAT_SPN(num_vars=24, num_latents=32, depth=3, num_repetitions=4, num_cats=6)
-    else:
+    elif case == "hmm64":
         ns = pj.structures.HMM(seq_length=6, num_latents=64, num_emits=6, homogeneous=False)
+    else:
+        ns = pj.structures.HMM(seq_length=7, num_latents=32, num_emits=6, homogeneous=True)
     ns.init_parameters()
     pc = pj.compile(ns).to(DEV)
     used = [l for g in pc.inner_layer_groups if g.is_sum() for l in g
@@ -306,6 +309,7 @@ def test_small_blocks_on_tensor_cores_match_oracle_and_cuda_core_kernels(case, B
     x = torch.randint(0, 6, (B, pc.num_vars))
     for rep in range(3):
         check_against_oracle(pc, x, step=0.05, pseudo=0.1)
+    check_against_oracle(pc, x, step=0.05, pseudo=0.1, logspace_flows=False)
     out = {}
     try:
         for sm in (True, False):
