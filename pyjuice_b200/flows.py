@@ -69,6 +69,23 @@ class FlowArena:
             dist.all_reduce(part, op=op, group=group)
         return self.buf[:2].clone()                    # decoded lazily with `decode_total` (no host sync here)
 
+    def write_total(self, cum_flow) -> None:
+        """Put the running flow total into the header as (hi, lo), without a host sync for device scalars."""
+        if isinstance(cum_flow, torch.Tensor):
+            t = cum_flow.to(self.buf.device, torch.float64).reshape(())
+            hi = torch.floor(t / _SPLIT)
+            self.buf[:2].copy_(torch.stack((hi, t - hi * _SPLIT)).to(torch.float32))
+        else:
+            hi = float(int(cum_flow // _SPLIT))
+            self.buf[:2].copy_(torch.tensor([hi, float(cum_flow - hi * _SPLIT)], dtype=torch.float32), non_blocking=True)
+
+    def all_reduce_range_async(self, begin: int, end: int, group=None):
+        """Start the fp32 SUM all-reduce of arena[begin:end] and return its work handle: the collective runs on the
+        backend's own stream after the work already enqueued on the current stream, and later kernels on the
+        current stream overlap with it until ``wait()`` is called on the handle."""
+        import torch.distributed as dist
+        return dist.all_reduce(self.buf[begin:end], op=dist.ReduceOp.SUM, group=group, async_op=True)
+
     @staticmethod
     def decode_total(head: torch.Tensor) -> float:
         hi, lo = head.tolist()

@@ -735,6 +735,8 @@ class TensorCircuit(nn.Module):
                 _fill(self.element_flows, NEG_INF if logspace_flows else 0.0)
                 self._eflow_mode = ls
 
+            if compute_param_flows:                          # decay (or clear) the accumulators and the flow total first
+                self.init_param_flows(flows_memory=flows_memory)
             r0, r1 = self._root_node_range
             if ll_weights is None:
                 _lib.call("pcx_set_root_flows", self.node_flows, None, r0, r1 - r0, B, ls)
@@ -750,8 +752,6 @@ class TensorCircuit(nn.Module):
                     s = w.sum(dtype=torch.float64)
                     self._cum_flow_dev = s if self._cum_flow_dev is None else self._cum_flow_dev + s
 
-            if compute_param_flows:
-                self.init_param_flows(flows_memory=flows_memory)
             if _lib.SUM_MODE != 0:
                 self._packer.refresh(self.params.data)
             key = ("bk", B, bool(compute_param_flows), ls, self._launch_cfg(), self.params.data_ptr(),
@@ -759,9 +759,33 @@ class TensorCircuit(nn.Module):
             self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
 
             if compute_param_flows:
+                self._start_early_flow_sync()
                 for layer in self.input_layer_group:
                     layer.backward(data, self.node_flows, self.node_mars, logspace_flows=bool(logspace_flows))
         return None
+
+    # ---- data-parallel flow synchronisation overlapped with the tail of the step ---------------------------------
+    def enable_flow_sync_overlap(self, group=None):
+        """Called by an optimizer that synchronises after EVERY backward pass (``ddp=True``, one mini-batch per
+        update, fp32): the all-reduce is then split in two and overlapped — the sum-layer flows are reduced while
+        the input layer's backward pass runs, the input-layer flows while the sum parameters are updated."""
+        self._overlap_group = (group,)
+
+    def _overlap_ready(self) -> bool:
+        import torch.distributed as dist
+        g = getattr(self, "_overlap_group", None)
+        return (g is not None and self.device.type == "cuda" and dist.is_available() and dist.is_initialized()
+                and dist.get_world_size(g[0]) > 1)
+
+    def _start_early_flow_sync(self):
+        if not self._overlap_ready() or getattr(self, "_early_sync", None) is not None:
+            return
+        arena = self._flow_arena
+        if getattr(self, "_cum_flow_head", None) is not None:
+            _ = self._cum_flow                              # fold a pending total of an earlier sync into the host part
+        total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host
+        arena.write_total(total)
+        self._early_sync = arena.all_reduce_range_async(0, arena.segment_end(0), group=self._overlap_group[0])
 
     @property
     def _cum_flow(self) -> float:
@@ -801,6 +825,15 @@ class TensorCircuit(nn.Module):
         if flows_memory == 0.0:
             for layer in self.input_layer_group:
                 layer._tied_folded = False
+        # The running flow total decays with the flows it normalises.  (The reference only clears it when the
+        # rescaled EM update consumes it, model/tensorcircuit.py:1363-1374, so that under data parallelism, where every
+        # synchronisation replaces it by the sum over ranks, it doubles per step; here it stays the total of the
+        # current accumulation window.)
+        if flows_memory != 1.0:
+            if flows_memory == 0.0:
+                self._cum_flow_host, self._cum_flow_dev, self._cum_flow_head = 0.0, None, None
+            else:
+                self._cum_flow = self._cum_flow * flows_memory
 
     def zero_param_flows(self):
         self.init_param_flows(flows_memory=0.0)
@@ -813,14 +846,18 @@ class TensorCircuit(nn.Module):
         _unsupported(step_size_rescaling=step_size_rescaling)
         self._require_cuda()
         with torch.no_grad():
-            for layer in self.input_layer_group:
-                layer.mini_batch_em(step_size=step_size, pseudocount=pseudocount, keep_zero_params=keep_zero_params)
             for start, n, chs in self._fusing_dev:
                 _lib.call("pcx_tied_accum", self.param_flows, start, n, chs, int(chs.numel()))
             e = self._em_dev
             _lib.call("pcx_em_sum", self.params.data, self.param_flows, e["par"], e["flow"], e["fan"], e["bs"],
                       int(e["par"].numel()), e["max_bs"], float(step_size), float(pseudocount), int(bool(keep_zero_params)))
             self._packer.invalidate()
+            late = getattr(self, "_late_sync", None)
+            if late is not None:                            # input-layer flows of the other ranks (see sync_param_flows)
+                late.wait()
+                self._late_sync = None
+            for layer in self.input_layer_group:
+                layer.mini_batch_em(step_size=step_size, pseudocount=pseudocount, keep_zero_params=keep_zero_params)
 
     def sync_param_flows(self, dtype: Optional[torch.dtype] = None, op=None, group=None, sync_cum_flow: bool = True):
         """Sum the parameter flows (and the running flow total) of all data-parallel ranks with ONE all-reduce over
@@ -842,6 +879,17 @@ class TensorCircuit(nn.Module):
             reduce_len = arena.segment_end(len(layers), last.num_untied_param_flows)
         elif getattr(last, "_tied_folded", False):
             reduce_len = arena.segment_end(len(layers), last.num_untied_param_flows)
+        early = getattr(self, "_early_sync", None)
+        if early is not None:
+            # the header and the sum-layer flows are already being reduced: start the input-layer part, then let the
+            # current stream wait for the first part only (the update of the sum parameters overlaps the second)
+            self._early_sync = None
+            end = arena.total if reduce_len is None else reduce_len
+            self._late_sync = arena.all_reduce_range_async(arena.offsets[1], end, group=group) if len(layers) > 0 else None
+            early.wait()
+            if sync_cum_flow:
+                self._cum_flow_host, self._cum_flow_dev, self._cum_flow_head = 0.0, None, arena.buf[:2].clone()
+            return None
         if getattr(self, "_cum_flow_head", None) is not None:
             _ = self._cum_flow                              # fold a pending total of an earlier sync into the host part
         total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host

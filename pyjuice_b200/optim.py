@@ -53,6 +53,8 @@ class MiniBatchEM(CircuitOptimizer):
         self.step_size = step_size
         self.niters_per_update = niters_per_update
         self._iter = 0
+        if ddp and niters_per_update == 1 and ddp_dtype in (None, torch.float32):
+            pc.enable_flow_sync_overlap(ddp_group)       # every backward pass is followed by a sync: overlap it
 
     def step(self, step_size: Optional[float] = None):
         self._iter += 1
@@ -71,3 +73,4 @@ class FullBatchEM(MiniBatchEM):
     def __init__(self, pc: TensorCircuit, pseudocount: float = 0.0, keep_zero_params: bool = False, **kwargs):
         super().__init__(pc, step_size=1.0, niters_per_update=1, pseudocount=pseudocount,
                          keep_zero_params=keep_zero_params, **kwargs)
+        pc._overlap_group = None      # many backward passes per step: the flows must not be reduced after the first

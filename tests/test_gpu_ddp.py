@@ -43,11 +43,19 @@ def _worker(rank, world, port, out_dir):
         lls.mean().backward()
         pc.sync_param_flows()
         flows = pc.param_flows.clone().cpu()
+        cum = pc._cum_flow                                # flow total of the window, summed over the ranks
         opt.ddp = False                                   # already synchronised above
         opt.step()
         torch.cuda.synchronize()
-        torch.save(dict(flows=flows, params=pc.params.data.cpu(), iparams=pc.input_layer_group[0].params.data.cpu(),
-                        cum=pc._cum_flow), os.path.join(out_dir, f"rank{rank}.pt"))
+        first = dict(flows=flows, params=pc.params.data.cpu(), iparams=pc.input_layer_group[0].params.data.cpu(), cum=cum)
+        # many more steps through the optimizer's own (overlapped, two-part) synchronisation
+        opt.ddp = True
+        for _ in range(60):
+            pc(shard).mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        torch.save(dict(first, params_after=pc.params.data.cpu(), iparams_after=pc.input_layer_group[0].params.data.cpu(),
+                        cum_after=pc._cum_flow), os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -72,3 +80,13 @@ def test_two_rank_step_equals_single_gpu_step(tmp_path):
     assert torch.allclose(r0["flows"], flows, rtol=1e-4, atol=1e-5)
     assert torch.allclose(r0["params"], pc.params.data.cpu(), rtol=1e-4, atol=1e-7)
     assert torch.allclose(r0["iparams"], pc.input_layer_group[0].params.data.cpu(), rtol=1e-4, atol=1e-7)
+
+    # sixty more steps: ranks stay identical and finite, the flow total stays that of one window, and the result is
+    # that of sixty single-GPU steps on the full batch
+    assert torch.equal(r0["params_after"], r1["params_after"]) and torch.equal(r0["iparams_after"], r1["iparams_after"])
+    assert torch.isfinite(r0["params_after"]).all() and r0["cum_after"] == 0.0
+    for _ in range(60):
+        pc(x).mean().backward()
+        opt.step()
+    assert torch.allclose(r0["params_after"], pc.params.data.cpu(), rtol=2e-3, atol=1e-6)
+    assert torch.allclose(r0["iparams_after"], pc.input_layer_group[0].params.data.cpu(), rtol=2e-3, atol=1e-6)
