@@ -925,8 +925,8 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
                     float f = nf[t];
-                    if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
-                    x[j][t] = (nm[t] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[t];
+                    if (!a.logspace) f = __logf(f);                        // log(0) = -inf
+                    x[j][t] = f - fmaxf(nm[t], -3.0e38f);                   // (-inf) - (-inf) reads as -inf
                 }
             } else {
 #pragma unroll
@@ -954,13 +954,10 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
 #pragma unroll
                 for (int t = 0; t < 8; ++t) y[j][t] = 0.0f;
 #pragma unroll
-                for (int c = 0; c < F; ++c) {
-                    const bool on = r[c] != 0;
+                for (int c = 0; c < F; ++c) {                               // row 0 is the dummy node: value 0
                     any |= r[c];
-                    y[j][0] += on ? q[c][0].x : 0.0f; y[j][1] += on ? q[c][0].y : 0.0f;
-                    y[j][2] += on ? q[c][0].z : 0.0f; y[j][3] += on ? q[c][0].w : 0.0f;
-                    y[j][4] += on ? q[c][1].x : 0.0f; y[j][5] += on ? q[c][1].y : 0.0f;
-                    y[j][6] += on ? q[c][1].z : 0.0f; y[j][7] += on ? q[c][1].w : 0.0f;
+                    y[j][0] += q[c][0].x; y[j][1] += q[c][0].y; y[j][2] += q[c][0].z; y[j][3] += q[c][0].w;
+                    y[j][4] += q[c][1].x; y[j][5] += q[c][1].y; y[j][6] += q[c][1].z; y[j][7] += q[c][1].w;
                 }
                 if (!any) {
 #pragma unroll
@@ -1009,19 +1006,20 @@ __device__ __forceinline__ void par_tile_body(const ParArgs& a, const int64_t ro
         uint8_t* xlo = st + X_TILE;
         uint8_t* yhi = st + 2 * X_TILE;
         uint8_t* ylo = st + 2 * X_TILE + Y_TILE;
+        float shc[8];                                   // a sample without any flow: every x is -inf, shift by 0
+#pragma unroll
+        for (int t = 0; t < 8; ++t) shc[t] = (sh[t] == PCX_NEG_INF) ? 0.0f : sh[t];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
-                x[j][t] = (sh[t] == PCX_NEG_INF || x[j][t] == PCX_NEG_INF) ? 0.0f : __expf(x[j][t] - sh[t]);
+            for (int t = 0; t < 8; ++t) x[j][t] = __expf(x[j][t] - shc[t]);   // exp(-inf - s) = 0
             const int o = g * XSLAB + (rb + 32 * j) * 16;
             store_split8(reinterpret_cast<uint4*>(xhi + o), reinterpret_cast<uint4*>(xlo + o), x[j]);
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
-                y[j][t] = (sh[t] == PCX_NEG_INF || y[j][t] == PCX_NEG_INF) ? 0.0f : fminf(__expf(y[j][t] + sh[t]), 3.0e38f);
+            for (int t = 0; t < 8; ++t) y[j][t] = fminf(__expf(y[j][t] + sh[t]), 3.0e38f);   // sh = -inf: exp(-inf) = 0
             const int o = g * YSLAB + (rb + 32 * j) * 16;
             store_split8(reinterpret_cast<uint4*>(yhi + o), reinterpret_cast<uint4*>(ylo + o), y[j]);
         }
