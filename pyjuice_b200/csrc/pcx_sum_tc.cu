@@ -256,7 +256,7 @@ __device__ __forceinline__ float combine_children(const int* r, const float* v) 
     float s = 0.0f;
     int any = 0;
 #pragma unroll
-    for (int c = 0; c < FC; ++c) { s += (r[c] != 0) ? v[c] : 0.0f; any |= r[c]; }
+    for (int c = 0; c < FC; ++c) { s += v[c]; any |= r[c]; }        // row 0 is the dummy node: its value is 0
     return any ? s : PCX_NEG_INF;
 }
 
@@ -342,8 +342,8 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             float f = nf[j];
-            if (!a.logspace) f = (f > 0.0f) ? __logf(f) : PCX_NEG_INF;
-            v[j] = (pr == 0 || nm[j] == PCX_NEG_INF || f == PCX_NEG_INF) ? PCX_NEG_INF : f - nm[j];
+            if (!a.logspace) f = __logf(f);                                  // log(0) = -inf
+            v[j] = (pr == 0) ? PCX_NEG_INF : f - fmaxf(nm[j], -3.0e38f);      // (-inf) - (-inf) reads as -inf
         }
     };
     // raw (log-domain) values of one 8-row group starting at contraction index kb
@@ -373,8 +373,9 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
     };
     // exp(v - mx) of one group -> bf16 hi/lo, written as row `lc` of K group g of the B tile of stage `st`
     auto store_group = [&](uint8_t* st, int g, float* v, float mx) {
+        const float mxc = (mx == PCX_NEG_INF) ? 0.0f : mx;     // a column without any mass: every value is -inf
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (v[j] == PCX_NEG_INF) ? 0.0f : __expf(v[j] - mx);
+        for (int j = 0; j < 8; ++j) v[j] = __expf(v[j] - mxc);          // exp(-inf - s) = 0
         uint8_t* bt = st + 2 * A_TILE + g * BSLAB + lc * 16;
         store_split8(reinterpret_cast<uint4*>(bt), reinterpret_cast<uint4*>(bt + KG * BSLAB), v);
     };
@@ -592,8 +593,9 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float m = sh.smax[c0 + 8 * p + j];
-                    if (MODE == FWD) o[j] = (m == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(v[j], 1e-24f)) + m;
-                    else o[j] = (m == PCX_NEG_INF || v[j] <= 0.0f) ? PCX_NEG_INF : __logf(v[j]) + m;
+                    // log(0) = -inf and -inf + x = -inf cover empty sums and columns without mass
+                    if (MODE == FWD) o[j] = __logf(fmaxf(v[j], 1e-24f)) + m;
+                    else o[j] = __logf(v[j]) + m;
                 }
                 if (MODE == ELE) {
                     float em[8];
@@ -623,7 +625,7 @@ __device__ __forceinline__ bool lse_tile_body(const LseArgs& a, const int64_t ro
                     }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        o[j] = (o[j] == PCX_NEG_INF || em[j] == PCX_NEG_INF) ? PCX_NEG_INF : o[j] + em[j];
+                        o[j] = o[j] + em[j];
                         if (!a.logspace) o[j] = __expf(o[j]);
                     }
                 }
