@@ -898,6 +898,29 @@ class TensorCircuit(nn.Module):
             self._cum_flow_host, self._cum_flow_dev, self._cum_flow_head = 0.0, None, head
         return None
 
+    def average_params(self, dtype: Optional[torch.dtype] = None, group=None):
+        """Replace the sum parameters and every input layer's parameters by their mean over the data-parallel ranks
+        (the exchange step of Local-SGD, PyJuice: optim/optim.py:99-124): the all-reduces are issued together and
+        waited for once; no-op outside an initialised process group of more than one rank."""
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized():
+            return None
+        ws = dist.get_world_size(group)
+        if ws <= 1:
+            return None
+        tensors = [self.params.data] + [l.params.data for l in self.input_layer_group if getattr(l, "params", None) is not None]
+        with torch.no_grad():
+            bufs = [t if dtype is None or t.dtype == dtype else t.to(dtype) for t in tensors]
+            works = [dist.all_reduce(b, op=dist.ReduceOp.SUM, group=group, async_op=True) for b in bufs]
+            for t, b, w in zip(tensors, bufs, works):
+                w.wait()
+                if b is not t:
+                    t.copy_(b)
+                t.mul_(1.0 / ws)
+        if getattr(self, "_packer", None) is not None:
+            self._packer.invalidate()                       # the tensor-core operand tiles are derived from the parameters
+        return None
+
     # ------------------------------------------------------------------------------------------
     # accessors
     # ------------------------------------------------------------------------------------------

@@ -1,5 +1,6 @@
 """World-size-2 data-parallel logic on CPU (gloo): the flow arena's single all-reduce sums every accumulator and the
-running flow total exactly, leaves the excluded tail alone, and is a no-op without a process group."""
+running flow total exactly, leaves the excluded tail alone, and is a no-op without a process group; the Local-SGD
+exchange step averages the parameters of the ranks every `sync_every` updates."""
 import os
 import sys
 
@@ -40,6 +41,46 @@ def _worker(rank, world, port, out_dir):
 def test_flow_arena_allreduce_world2(tmp_path):
     port = 29500 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"rank{r}.txt").read() == "ok"
+
+
+def _avg_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import pyjuice_b200 as pj
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(100 + rank)                              # rank-specific parameters
+        ns = pj.structures.HMM(seq_length=5, num_latents=8, num_emits=11)
+        ns.init_parameters(perturbation=2.0)
+        pc = pj.compile(ns)
+        mine = [pc.params.data.clone()] + [l.params.data.clone() for l in pc.input_layer_group]
+        exp = []
+        for t in mine:
+            e = t.clone()
+            dist.all_reduce(e)
+            exp.append(e / world)
+        opt = pj.optim.MiniBatchEM.__new__(pj.optim.MiniBatchEM)   # the optimizer's exchange step alone (no device)
+        opt.pc, opt.ddp, opt.ddp_dtype, opt.ddp_group, opt.sync_every, opt._update_count = pc, True, None, None, 3, 0
+        opt._post_update_sync(); opt._post_update_sync()           # updates 1 and 2 stay local
+        ok = all(torch.equal(a, b) for a, b in zip(mine, [pc.params.data] + [l.params.data for l in pc.input_layer_group]))
+        opt._post_update_sync()                                    # update 3: parameters are averaged
+        got = [pc.params.data] + [l.params.data for l in pc.input_layer_group]
+        ok = ok and all(torch.allclose(a, b, rtol=1e-6, atol=1e-8) for a, b in zip(got, exp))
+        ok = ok and not torch.equal(got[0], mine[0])
+        eb = pc._em_blocks                                         # a mean of normalised vectors is normalised
+        for i in range(eb["par"].numel()):
+            p0, fan, bs = int(eb["par"][i]), int(eb["fan"][i]), int(eb["bs"][i])
+            sm = pc.params.data[p0:p0 + fan * bs].view(fan, bs).sum(dim=0)
+            ok = ok and torch.allclose(sm, torch.ones_like(sm), atol=1e-5)
+        open(os.path.join(out_dir, f"rank{rank}.txt"), "w").write("ok" if ok else "bad")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_local_sgd_parameter_average_world2(tmp_path):
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_avg_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         assert open(tmp_path / f"rank{r}.txt").read() == "ok"
 

@@ -1,5 +1,6 @@
 """Two data-parallel ranks on two GPUs (NCCL): after `sync_param_flows` every rank holds the flows of the whole
 batch, and the EM update leaves identical parameters on both ranks, equal to a single-GPU step on the full batch.
+Local-SGD (`sync_every > 1`) is checked against two single-GPU circuits averaged on the host.
 Skipped on boxes with fewer than two GPUs."""
 import os
 import sys
@@ -90,3 +91,61 @@ def test_two_rank_step_equals_single_gpu_step(tmp_path):
         opt.step()
     assert torch.allclose(r0["params_after"], pc.params.data.cpu(), rtol=2e-3, atol=1e-6)
     assert torch.allclose(r0["iparams_after"], pc.input_layer_group[0].params.data.cpu(), rtol=2e-3, atol=1e-6)
+
+
+def _local_sgd_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device(dev))
+    try:
+        import pyjuice_b200 as pj
+        pc = _build().to(dev)
+        x = _data(pc, 64)
+        shard = x[rank * 32:(rank + 1) * 32].to(dev)
+        opt = pj.optim.MiniBatchEM(pc, step_size=0.5, pseudocount=0.1, ddp=True, sync_every=2)
+        snaps = []
+        for _ in range(4):                                 # updates 1 and 3 are local, 2 and 4 end with the average
+            pc(shard).mean().backward()
+            opt.step()
+            snaps.append((pc.params.data.cpu().clone(), pc.input_layer_group[0].params.data.cpu().clone()))
+        lls = pc(shard)                                    # the operand tiles must follow the averaged parameters
+        torch.cuda.synchronize()
+        torch.save(dict(snaps=snaps, lls=lls.cpu()), os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_local_sgd_two_ranks(tmp_path):
+    """`sync_every=2`: each rank updates on its own shard's flows, every second update is followed by the average
+    of the parameters; checked against two single-GPU circuits stepped on the shards and averaged on the host."""
+    import torch.multiprocessing as mp
+    import pyjuice_b200 as pj
+    port = 33700 + (os.getpid() % 2000)
+    mp.spawn(_local_sgd_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r = [torch.load(tmp_path / f"rank{k}.pt") for k in range(2)]
+    for step, same in enumerate([False, True, False, True]):
+        for a, b in zip(r[0]["snaps"][step], r[1]["snaps"][step]):
+            assert torch.equal(a, b) == same, f"update {step + 1}: ranks {'differ' if same else 'agree'}"
+
+    pcs = [_build().to("cuda:0") for _ in range(2)]
+    x = _data(pcs[0], 64).to("cuda:0")
+    opts = [pj.optim.MiniBatchEM(pc, step_size=0.5, pseudocount=0.1) for pc in pcs]
+    for step in range(4):
+        for k in range(2):
+            pcs[k](x[k * 32:(k + 1) * 32]).mean().backward()
+            opts[k].step()
+        if step % 2 == 1:
+            for get in (lambda pc: pc.params.data, lambda pc: pc.input_layer_group[0].params.data):
+                mean = (get(pcs[0]) + get(pcs[1])) / 2
+                for pc in pcs:
+                    get(pc).copy_(mean)
+                    pc._packer.invalidate()
+        for k in range(2):
+            assert torch.allclose(r[k]["snaps"][step][0], pcs[k].params.data.cpu(), rtol=1e-4, atol=1e-7)
+            assert torch.allclose(r[k]["snaps"][step][1], pcs[k].input_layer_group[0].params.data.cpu(), rtol=1e-4, atol=1e-7)
+    for k in range(2):
+        assert torch.allclose(r[k]["lls"], pcs[k](x[k * 32:(k + 1) * 32]).cpu(), rtol=1e-5, atol=1e-4)

@@ -90,8 +90,8 @@ def test_unsupported_options_raise():
     pc = pj.compile(ns)
     with pytest.raises(NotImplementedError):
         pc.forward(torch.zeros(2, 4, dtype=torch.long))           # no CPU path
-    with pytest.raises(NotImplementedError):
-        pj.optim.MiniBatchEM(pc, sync_every=4)
+    with pytest.raises(AssertionError):
+        pj.optim.MiniBatchEM(pc, sync_every=0)
 
 
 def test_parameters_are_normalised_after_compile():
