@@ -4,10 +4,11 @@ Front door mirrors PyJuice: ``inputs`` / ``multiply`` / ``summate`` build the no
 into a :class:`TensorCircuit`, ``optim.MiniBatchEM`` drives EM.  Computation happens in hand-written sm_100a
 CUDA kernels behind the C ABI of ``include/pcx_b200.h``; there is no CPU or Triton path.
 """
-from . import nodes, structures, optim
+from . import nodes, structures, optim, io
 from .nodes import inputs, multiply, summate, set_block_size, Categorical, BitSet
 from .nodes import distributions
 from .model import TensorCircuit, compile
+from .io import save, load
 from .layers import InputLayer, ProdLayer, SumLayer, LayerGroup
 
 __version__ = "0.1.0"

@@ -6,7 +6,8 @@
 The reference imports matplotlib (absent here) and touches CUDA in three places while compiling; both are
 neutralised below, in this script only, so that its table compiler runs on the host
 (``disable_gpu_compilation=True``).  Nothing else of the reference is modified, and the fixtures are plain
-NumPy archives of int64 tables.
+NumPy archives of int64 tables.  It also writes one checkpoint with the reference's own ``save``
+(``ref_hmm_blocks.jpc``) for the loader test.
 """
 import contextlib
 import os
@@ -53,6 +54,32 @@ def main():
         tables = dump_tables(pc)
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **tables)
         print(f"{name}: {len(tables)} arrays, num_nodes={pc.num_nodes}, num_edges={pc.num_edges}")
+    checkpoint_fixture(api)
+
+
+def checkpoint_fixture(api):
+    """``ref_hmm_blocks.jpc``: a checkpoint written by the reference's own ``save`` (tied sums, tied leaves, random
+    parameters).  The other direction is checked here, once: the reference's ``load`` reads a file this package
+    wrote and finds the same vectors and parameters."""
+    import tempfile
+    from cases import CASES
+    from pyjuice.io import load, save
+    import pyjuice_b200 as ours
+    torch.manual_seed(7)
+    ns, _ = CASES["hmm_blocks"](api)
+    ns.init_parameters()
+    save(os.path.join(HERE, "ref_hmm_blocks.jpc"), ns)
+    mine = ours.load(os.path.join(HERE, "ref_hmm_blocks.jpc"))
+    with tempfile.TemporaryDirectory() as d:
+        ours.save(os.path.join(d, "ours.jpc"), mine)
+        back = load(os.path.join(d, "ours.jpc"))
+    a, b = list(ns), list(back)
+    assert len(a) == len(b)
+    for x, y in zip(a, b):
+        assert (x.num_node_blocks, x.block_size, x.is_tied()) == (y.num_node_blocks, y.block_size, y.is_tied())
+        if x._params is not None:        # the reference renormalises sum parameters when it loads them
+            assert torch.allclose(x._params, y._params, rtol=1e-6, atol=1e-8)
+    print(f"ref_hmm_blocks.jpc: {len(a)} vectors; the reference loads this package's file")
 
 
 if __name__ == "__main__":

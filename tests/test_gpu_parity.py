@@ -324,3 +324,22 @@ def test_small_blocks_on_tensor_cores_match_oracle_and_cuda_core_kernels(case, B
     for a, b in zip(out[True], out[False]):
         assert torch.allclose(a, b, rtol=2e-4, atol=1e-6), (a - b).abs().max()
     _lib_status()
+
+
+@pytest.mark.parametrize("name", ["hmm_blocks", "hclt_b128"])
+def test_checkpoint_of_a_trained_circuit_reloads_to_the_same_likelihoods(name, tmp_path):
+    """Train a few EM steps on the device, save the compiled circuit, load and compile the file: the new circuit
+    gives the same log-likelihoods (its parameters pass through one more host-side normalisation: 1e-4 nats)."""
+    pc = _build(name).to(DEV)
+    x = _data_for(pc, 64).to(DEV)
+    opt = pj.optim.MiniBatchEM(pc, step_size=0.3, pseudocount=0.05)
+    before = pc(x).clone()
+    for _ in range(3):
+        pc(x).mean().backward()
+        opt.step()
+    after = pc(x).clone()
+    assert (after.mean() > before.mean()).item()
+    pj.save(str(tmp_path / "trained.jpc"), pc)
+    pc2 = pj.compile(pj.load(str(tmp_path / "trained.jpc"))).to(DEV)
+    assert torch.allclose(pc2.params.data, pc.params.data, rtol=1e-5, atol=1e-9)
+    assert torch.allclose(pc2(x), after, rtol=0, atol=1e-4)
