@@ -267,6 +267,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-dataflow", action="store_true", help="per-layer launches instead of one launch per run of layers")
+    ap.add_argument("--no-side-stream", action="store_true", help="every kernel of a step on one stream")
     ap.add_argument("--chain-tile", type=int, default=None, choices=[16, 32, 64], help="tile width of the dataflow launch")
     ap.add_argument("--sum-mode", type=int, default=1, choices=[0, 1, 2],
                     help="0 fp32 CUDA cores, 1 tensor cores with split-bf16 operands, 2 tensor cores single bf16")
@@ -296,6 +297,7 @@ def main():
     pc = pj.compile(ns).to(dev)
     pc.use_cuda_graphs = not args.no_graphs
     pc.use_dataflow_launch = not args.no_dataflow
+    pc.use_side_stream = not args.no_side_stream
     pc.chain_tile = args.chain_tile
     stats = circuit_stats(pc)
     max_cats = max(l.max_cats for l in pc.input_layer_group)
@@ -362,6 +364,7 @@ def main():
     # (every rank takes the steps — they contain the flow all-reduce — but only rank 0 records)
     fam = {}
     pc.use_cuda_graphs = False
+    pc.use_side_stream = False            # one stream: every launch is timed alone
     for rep in range(3):
         _lib.PROFILE = [] if (rep == 2 and rank == 0) else None
         step(resident[0])
@@ -373,6 +376,7 @@ def main():
             d[1] += a.elapsed_time(b)
     _lib.PROFILE = None
     pc.use_cuda_graphs = not args.no_graphs
+    pc.use_side_stream = not args.no_side_stream
 
     if world > 1:
         dist.barrier()

@@ -61,6 +61,7 @@ class TensorCircuit(nn.Module):
         self._graphs = {}
         self.use_cuda_graphs = True
         self.use_dataflow_launch = True       # runs of folded depths as one launch (tiles wait on counters)
+        self.use_side_stream = True           # independent kernels of a step share the device (two streams)
         self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
         self.dense_par_max_bytes = 16 << 30   # operand buffers of the dense parameter-flow product (all groups)
         self.default_propagation_alg = "LL"
@@ -273,6 +274,7 @@ class TensorCircuit(nn.Module):
             self._mask_parentless_in_device_tables()
         self._setup_fusion()
         self._side_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self._bk_par_pending = {}
         self._graphs = {}
         self._par_job_cache = {}
         self._chain_cache = {}
@@ -552,10 +554,20 @@ class TensorCircuit(nn.Module):
             data = self._prepare_inputs(inputs)
             self._ensure_buffers(B)
             self._last_data, self._last_inputs = data, origin_inputs
+            # the operand tiles of the tensor-core kernels are re-packed (when the parameters changed) on a second
+            # stream, beside the input layer: neither reads what the other writes
+            cur = torch.cuda.current_stream(self.device)
+            forked = _lib.SUM_MODE != 0 and self.use_side_stream
+            if forked:
+                self._side_stream.wait_stream(cur)
+                with torch.cuda.stream(self._side_stream):
+                    self._packer.refresh(self.params.data)   # outside any graph capture
+            elif _lib.SUM_MODE != 0:
+                self._packer.refresh(self.params.data)
             for layer in self.input_layer_group:
                 layer.forward(data, self.node_mars)
-            if _lib.SUM_MODE != 0:
-                self._packer.refresh(self.params.data)       # outside any graph capture
+            if forked:
+                cur.wait_stream(self._side_stream)
             self._run_inner(("fw", B, self._launch_cfg(), self.params.data_ptr()), self._forward_inner)
             lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
         if torch.is_grad_enabled():
@@ -649,7 +661,8 @@ class TensorCircuit(nn.Module):
     def _backward_inner(self, compute_param_flows: bool, logspace_flows: bool):
         """Reverse sweep over the inner layers.  Parameter flows of the depths whose product layer is folded in only
         read node values and node flows, and tiles of different layers are independent: they all run as ONE launch
-        once the dependent chain of element-flow kernels has produced every node flow."""
+        once the dependent chain of element-flow kernels has produced every node flow (`_launch_batched_par`, issued
+        by `backward` so that it can share the device with the input layer's backward pass)."""
         pf = self.param_flows if compute_param_flows else None
         groups = self.inner_layer_groups
         any_fused = False
@@ -694,11 +707,13 @@ class TensorCircuit(nn.Module):
                 cids, pids, pfids = g["tables"]
                 _lib.call("pcx_sum_par_dense_gemm", pf, self.params.data, g["x"], g["y"], cids, pids, pfids,
                           g["n_blocks"], g["K"], g["block_size"], g["n_chunks"])
-        if any_fused and pf is not None:
-            B = self.node_flows.size(1)
-            for fc, jobs, n_jobs, n_items, chunks_per_cta in self._par_jobs(B):
-                _lib.call("pcx_sum_bwd_par_batched", pf, self.node_flows, self.node_mars, self.params.data, jobs,
-                          n_jobs, n_items, fc, B, chunks_per_cta, int(bool(logspace_flows)))
+        self._batched_par_pending = any_fused and pf is not None     # launched by `backward`, after this sweep
+
+    def _launch_batched_par(self, logspace_flows: bool):
+        B = self.node_flows.size(1)
+        for fc, jobs, n_jobs, n_items, chunks_per_cta in self._par_jobs(B):
+            _lib.call("pcx_sum_bwd_par_batched", self.param_flows, self.node_flows, self.node_mars, self.params.data,
+                      jobs, n_jobs, n_items, fc, B, chunks_per_cta, int(bool(logspace_flows)))
 
     def backward(self, inputs: Optional[torch.Tensor] = None, ll_weights: Optional[torch.Tensor] = None,
                  compute_param_flows: bool = True, flows_memory: float = 1.0, input_layer_fn=None, cache=None,
@@ -756,19 +771,37 @@ class TensorCircuit(nn.Module):
                 self._packer.refresh(self.params.data)
             key = ("bk", B, bool(compute_param_flows), ls, self._launch_cfg(), self.params.data_ptr(),
                    self.param_flows.data_ptr() if compute_param_flows else 0)
+            self._batched_par_pending = self._bk_par_pending.get(key, False)
             self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
+            self._bk_par_pending[key] = self._batched_par_pending
 
             if compute_param_flows:
-                self._start_early_flow_sync()
-                for layer in self.input_layer_group:
-                    layer.backward(data, self.node_flows, self.node_mars, logspace_flows=bool(logspace_flows))
+                # The parameter flows of the sum layers and of the input layer are independent once every node flow
+                # exists.  One rank: both run together, on two streams.  Data-parallel ranks with the overlapped
+                # all-reduce: the input layer first, then the all-reduce of its flows (the larger part of the
+                # arena) beside the sum layers' parameter-flow kernel.
+                cur = torch.cuda.current_stream(self.device)
+                if self._batched_par_pending and self.use_side_stream and not self._overlap_ready():
+                    self._side_stream.wait_stream(cur)
+                    with torch.cuda.stream(self._side_stream):
+                        for layer in self.input_layer_group:
+                            layer.backward(data, self.node_flows, self.node_mars, logspace_flows=bool(logspace_flows))
+                    self._launch_batched_par(logspace_flows)
+                    cur.wait_stream(self._side_stream)
+                else:
+                    for layer in self.input_layer_group:
+                        layer.backward(data, self.node_flows, self.node_mars, logspace_flows=bool(logspace_flows))
+                    self._start_early_flow_sync()
+                    if self._batched_par_pending:
+                        self._launch_batched_par(logspace_flows)
         return None
 
     # ---- data-parallel flow synchronisation overlapped with the tail of the step ---------------------------------
     def enable_flow_sync_overlap(self, group=None):
         """Called by an optimizer that synchronises after EVERY backward pass (``ddp=True``, one mini-batch per
-        update, fp32): the all-reduce is then split in two and overlapped — the sum-layer flows are reduced while
-        the input layer's backward pass runs, the input-layer flows while the sum parameters are updated."""
+        update, fp32): the all-reduce is then split in two and overlapped — the input-layer flows are reduced while
+        the sum layers' parameter flows are computed, the sum-layer flows (and the flow total in the arena header)
+        while the input-layer parameters are updated."""
         self._overlap_group = (group,)
 
     def _overlap_ready(self) -> bool:
@@ -777,18 +810,42 @@ class TensorCircuit(nn.Module):
         return (g is not None and self.device.type == "cuda" and dist.is_available() and dist.is_initialized()
                 and dist.get_world_size(g[0]) > 1)
 
+    def _input_reduce_end(self) -> int:
+        """Arena offset up to which the input-layer flows take part in the all-reduce: replica accumulators of tied
+        input vectors are folded into their source range first and, when they form the tail of the arena, left out."""
+        arena, layers = self._flow_arena, list(self.input_layer_group)
+        last = layers[-1]
+        if self.device.type == "cuda" and last.tied2source_nids and not getattr(last, "_tied_folded", False):
+            last.fold_tied_flows()
+        if getattr(last, "_tied_folded", False):
+            return arena.segment_end(len(layers), last.num_untied_param_flows)
+        return arena.total
+
     def _start_early_flow_sync(self):
+        """First part of the overlapped all-reduce: the input-layer flows, as soon as the input layer's backward pass
+        is enqueued."""
         if not self._overlap_ready() or getattr(self, "_early_sync", None) is not None:
             return
+        self._finish_late_sync()
         arena = self._flow_arena
-        if getattr(self, "_cum_flow_head", None) is not None:
-            _ = self._cum_flow                              # fold a pending total of an earlier sync into the host part
-        total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host
-        arena.write_total(total)
-        self._early_sync = arena.all_reduce_range_async(0, arena.segment_end(0), group=self._overlap_group[0])
+        self._early_sync = arena.all_reduce_range_async(arena.offsets[1], self._input_reduce_end(),
+                                                        group=self._overlap_group[0])
+
+    def _finish_late_sync(self):
+        """Make the current stream wait for the second part of the overlapped all-reduce (header + sum-layer flows)
+        and pick up the summed flow total."""
+        late = getattr(self, "_late_sync", None)
+        if late is None:
+            return
+        late.wait()
+        self._late_sync = None
+        if self._late_head:
+            self._cum_flow_host, self._cum_flow_dev = 0.0, None
+            self._cum_flow_head = self._flow_arena.buf[:2].clone()
 
     @property
     def _cum_flow(self) -> float:
+        self._finish_late_sync()
         if getattr(self, "_cum_flow_head", None) is not None:          # total left behind by the last flow sync
             self._cum_flow_host += FlowArena.decode_total(self._cum_flow_head)
             self._cum_flow_head = None
@@ -810,6 +867,7 @@ class TensorCircuit(nn.Module):
         assert 0.0 <= flows_memory <= 1.0, "`flows_memory` should be in [0.0, 1.0]"
         _unsupported(batch_size=batch_size is not None)
         self._require_cuda()
+        self._finish_late_sync()
         if self.param_flows is None or self.param_flows.device != self.device:
             # all accumulators are views into one arena: a single all-reduce synchronises data-parallel ranks
             self._flow_arena = FlowArena([self.num_param_flows] + [l.num_param_flows for l in self.input_layer_group],
@@ -846,50 +904,68 @@ class TensorCircuit(nn.Module):
         _unsupported(step_size_rescaling=step_size_rescaling)
         self._require_cuda()
         with torch.no_grad():
-            for start, n, chs in self._fusing_dev:
-                _lib.call("pcx_tied_accum", self.param_flows, start, n, chs, int(chs.numel()))
-            e = self._em_dev
-            _lib.call("pcx_em_sum", self.params.data, self.param_flows, e["par"], e["flow"], e["fan"], e["bs"],
-                      int(e["par"].numel()), e["max_bs"], float(step_size), float(pseudocount), int(bool(keep_zero_params)))
-            self._packer.invalidate()
-            late = getattr(self, "_late_sync", None)
-            if late is not None:                            # input-layer flows of the other ranks (see sync_param_flows)
-                late.wait()
-                self._late_sync = None
-            for layer in self.input_layer_group:
-                layer.mini_batch_em(step_size=step_size, pseudocount=pseudocount, keep_zero_params=keep_zero_params)
+            def sum_update():
+                for start, n, chs in self._fusing_dev:
+                    _lib.call("pcx_tied_accum", self.param_flows, start, n, chs, int(chs.numel()))
+                e = self._em_dev
+                _lib.call("pcx_em_sum", self.params.data, self.param_flows, e["par"], e["flow"], e["fan"], e["bs"],
+                          int(e["par"].numel()), e["max_bs"], float(step_size), float(pseudocount),
+                          int(bool(keep_zero_params)))
+                self._packer.invalidate()
 
-    def sync_param_flows(self, dtype: Optional[torch.dtype] = None, op=None, group=None, sync_cum_flow: bool = True):
+            def input_update():
+                for layer in self.input_layer_group:
+                    layer.mini_batch_em(step_size=step_size, pseudocount=pseudocount, keep_zero_params=keep_zero_params)
+
+            # sum parameters and input-layer parameters are disjoint
+            cur = torch.cuda.current_stream(self.device)
+            if getattr(self, "_late_sync", None) is not None:
+                input_update()                              # beside the all-reduce of the sum-layer flows
+                self._finish_late_sync()
+                sum_update()
+            elif self.use_side_stream:                      # the two updates run on two streams
+                self._side_stream.wait_stream(cur)
+                with torch.cuda.stream(self._side_stream):
+                    sum_update()
+                input_update()
+                cur.wait_stream(self._side_stream)
+            else:
+                sum_update()
+                input_update()
+
+    def sync_param_flows(self, dtype: Optional[torch.dtype] = None, op=None, group=None, sync_cum_flow: bool = True,
+                         _lazy: bool = False):
         """Sum the parameter flows (and the running flow total) of all data-parallel ranks with ONE all-reduce over
         the flow arena; no-op outside an initialised process group of more than one rank.
 
         Replica accumulators of tied input vectors are folded into their source range first and left out of the
         collective when they form the tail of the arena (a homogeneous HMM sends one emission-flow table instead of
-        one per accumulator)."""
+        one per accumulator).  ``_lazy`` (optimizers): with the overlapped all-reduce, return once the input-layer
+        flows are in and let `mini_batch_em` wait for the sum-layer flows."""
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) <= 1:
             return None
         if self.param_flows is None:
             self.init_param_flows()
-        arena, layers = self._flow_arena, list(self.input_layer_group)
-        reduce_len = None
-        last = layers[-1]
-        if self.device.type == "cuda" and last.tied2source_nids and not getattr(last, "_tied_folded", False):
-            last.fold_tied_flows()
-            reduce_len = arena.segment_end(len(layers), last.num_untied_param_flows)
-        elif getattr(last, "_tied_folded", False):
-            reduce_len = arena.segment_end(len(layers), last.num_untied_param_flows)
+        arena = self._flow_arena
         early = getattr(self, "_early_sync", None)
         if early is not None:
-            # the header and the sum-layer flows are already being reduced: start the input-layer part, then let the
-            # current stream wait for the first part only (the update of the sum parameters overlaps the second)
+            # the input-layer flows are already being reduced: start the header + sum-layer part, then let the
+            # current stream wait for the first part only (the input-layer update overlaps the second)
             self._early_sync = None
-            end = arena.total if reduce_len is None else reduce_len
-            self._late_sync = arena.all_reduce_range_async(arena.offsets[1], end, group=group) if len(layers) > 0 else None
+            if getattr(self, "_cum_flow_head", None) is not None:
+                _ = self._cum_flow                          # fold a pending total of an earlier sync into the host part
+            total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host
+            arena.write_total(total)
+            self._late_sync = arena.all_reduce_range_async(0, arena.segment_end(0), group=group)
+            self._late_head = bool(sync_cum_flow)
             early.wait()
-            if sync_cum_flow:
-                self._cum_flow_host, self._cum_flow_dev, self._cum_flow_head = 0.0, None, arena.buf[:2].clone()
+            if not _lazy:
+                self._finish_late_sync()
             return None
+        self._finish_late_sync()
+        end = self._input_reduce_end()
+        reduce_len = None if end == arena.total else end
         if getattr(self, "_cum_flow_head", None) is not None:
             _ = self._cum_flow                              # fold a pending total of an earlier sync into the host part
         total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host

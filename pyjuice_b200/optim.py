@@ -31,7 +31,7 @@ class CircuitOptimizer:
 
     def _sync_flows(self):
         if self.ddp:
-            self.pc.sync_param_flows(dtype=self.ddp_dtype, group=self.ddp_group)
+            self.pc.sync_param_flows(dtype=self.ddp_dtype, group=self.ddp_group, _lazy=True)
 
     def _average_params(self):
         """Local-SGD: every rank's parameters become their mean over the process group (a mean of normalised
