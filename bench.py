@@ -286,7 +286,10 @@ def main():
     dev = torch.device(f"cuda:{local_rank}")
     if world > 1:
         import datetime
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        # NCCL's kernels on a high-priority stream: the all-reduce of the input-layer flows runs beside the
+        # parameter-flow kernel, whose 2000+ CTAs would otherwise keep the collective's few CTAs waiting for an SM
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120), pg_options=opts)
     W, K = max(args.warmup, 3), args.steps
     desc, B = CONFIGS[args.config]
     _lib.set_sum_mode(args.sum_mode)
