@@ -724,8 +724,12 @@ class TensorCircuit(nn.Module):
         ``logspace_flows`` selects whether the flow buffers hold log-flows (default) or linear flows; the
         parameter flows are the same either way."""
         self._require_cuda()
+        # `allow_modify_flows` only permits the reference to overwrite node flows in place (linear flows only,
+        # layer/sum_layer.py:442-455); the kernels here never need to, so it is accepted and changes nothing
+        assert not (allow_modify_flows and logspace_flows), \
+            "`allow_modify_flows` should be set to `False` when using `logspace_flows`."
         _unsupported(input_layer_fn=input_layer_fn is not None, cache=cache is not None, return_cache=return_cache,
-                     allow_modify_flows=allow_modify_flows, propagation_alg=propagation_alg != "LL",
+                     propagation_alg=propagation_alg != "LL",
                      negate_pflows=negate_pflows, pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6,
                      missing_mask=kwargs.get("missing_mask") is not None)
         assert self.node_mars is not None and self.element_mars is not None, "Should run forward path first."

@@ -343,3 +343,17 @@ def test_checkpoint_of_a_trained_circuit_reloads_to_the_same_likelihoods(name, t
     pc2 = pj.compile(pj.load(str(tmp_path / "trained.jpc"))).to(DEV)
     assert torch.allclose(pc2.params.data, pc.params.data, rtol=1e-5, atol=1e-9)
     assert torch.allclose(pc2(x), after, rtol=0, atol=1e-4)
+
+
+def test_allow_modify_flows_is_accepted_and_changes_nothing():
+    """The flag only permits overwriting node flows in place (linear flows); results are those without it, and it
+    is rejected together with log-space flows as in the reference (layer/sum_layer.py:442)."""
+    pc = _build("hclt_cfg0", seed=3).to(DEV)
+    x = _data_for(pc, 32).to(DEV)
+    pc(x)
+    pc.backward(x, logspace_flows=False, flows_memory=0.0)
+    want = pc.param_flows.clone()
+    pc.backward(x, logspace_flows=False, flows_memory=0.0, allow_modify_flows=True)
+    assert torch.equal(pc.param_flows, want)
+    with pytest.raises(AssertionError):
+        pc.backward(x, logspace_flows=True, allow_modify_flows=True)
