@@ -86,7 +86,7 @@ def build_workload(name: str, num_samples: int, seed_offset: int = 0):
     return ns, x
 
 
-def circuit_stats(pc):
+def circuit_stats(pc, B):
     """Algorithmic work per sample and per step (the figures every roofline number is computed from)."""
     e_sum = sum(l.num_edges for g in pc.inner_layer_groups if g.is_sum() for l in g)
     prod_edges = sum(l.num_edges for g in pc.inner_layer_groups if g.is_prod() for l in g)
@@ -95,8 +95,22 @@ def circuit_stats(pc):
     p_in = sum(l.num_parameters for l in pc.input_layer_group)
     f_in = sum(l.num_param_flows for l in pc.input_layer_group)
     sum_rows = sum(l.num_nodes for g in pc.inner_layer_groups if g.is_sum() for l in g)
+    # product layers that still run as kernels of their own (the others are folded into the sum kernels):
+    # (edges + nodes) per forward launch, (edges + 2 nodes) per backward launch, summed over the launches of a step
+    prod_fwd = prod_bwd = 0
+    groups = pc.inner_layer_groups
+    for gi, g in enumerate(groups):
+        if not g.is_prod():
+            continue
+        folded = gi + 1 < len(groups) and pc._fusion_on(gi + 1)
+        folded_bk = folded and B % 8 == 0                  # the backward sweep folds for batches that are multiples of 8
+        e, n = sum(l.num_edges for l in g), sum(l.num_nodes for l in g)
+        prod_fwd += (0 if folded else e + n) + (0 if folded_bk else e + n)      # forward pass + recompute in backward
+        if not (folded_bk and pc._fused[gi + 1]["direct"]):
+            prod_bwd += e + 2 * n
     return dict(e_sum=e_sum, prod_edges=prod_edges, prod_nodes=prod_nodes, n_in=n_in, p_in=p_in, f_in=f_in,
-                p_sum=pc.num_sum_params, f_sum=pc.num_param_flows, sum_rows=sum_rows)
+                p_sum=pc.num_sum_params, f_sum=pc.num_param_flows, sum_rows=sum_rows,
+                prod_fwd_launched=prod_fwd, prod_bwd_launched=prod_bwd)
 
 
 def family_of(name: str) -> str:
@@ -135,9 +149,9 @@ def family_work(stats, B, elsize):
         "pcx_sum_bwd_ele": sum_family(4.0 * B * (2 * s["sum_rows"] + 2 * child_rows) + 4.0 * s["p_sum"]),
         # reads flows and values of the parents and values of the children; parameters read, flows read-modify-write
         "pcx_sum_bwd_par": sum_family(4.0 * B * (2 * s["sum_rows"] + child_rows) + 4.0 * s["p_sum"] + 8.0 * s["f_sum"]),
-        # product layers run twice forward per step (once more inside the backward pass)
-        "pcx_prod_fwd": ("hbm", 2 * 4.0 * (s["prod_edges"] + s["prod_nodes"]) * B, 0.0),
-        "pcx_prod_bwd": ("hbm", 4.0 * (s["prod_edges"] + 2 * s["prod_nodes"]) * B, 0.0),
+        # product layers that are not folded into the sum kernels: forward, once more inside the backward pass
+        "pcx_prod_fwd": ("hbm", 4.0 * s["prod_fwd_launched"] * B, 0.0),
+        "pcx_prod_bwd": ("hbm", 4.0 * s["prod_bwd_launched"] * B, 0.0),
         "pcx_input_cat_fwd": ("hbm", 4.0 * s["n_in"] * B, 0.0),
         "pcx_input_cat_bwd": ("hbm", 4.0 * s["n_in"] * B + 8.0 * s["f_in"], 0.0),
         "pcx_em_input_cat": ("hbm", 12.0 * s["p_in"], 0.0),
@@ -302,7 +316,7 @@ def main():
     pc.use_dataflow_launch = not args.no_dataflow
     pc.use_side_stream = not args.no_side_stream
     pc.chain_tile = args.chain_tile
-    stats = circuit_stats(pc)
+    stats = circuit_stats(pc, B)
     max_cats = max(l.max_cats for l in pc.input_layer_group)
     np_dtype, elsize = (np.uint8, 1) if max_cats <= 256 else (np.int32, 4)
     host = [torch.from_numpy(x[i * B:(i + 1) * B].astype(np_dtype)).pin_memory() for i in range(n_batches)]
