@@ -1,21 +1,27 @@
 """Benchmark of the compiled probabilistic-circuit training step (forward + backward + mini-batch EM).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg1] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg4] [--others cfg1,cfg2,cfg3]
+                    [--impl ours|reference|triton]
 
 One "step" is one mini-batch of the named configuration through ``pc(x)``, ``lls.mean().backward()`` and
-``MiniBatchEM.step()``.  Rank 0 prints ONE JSON line:
+``MiniBatchEM.step()``.  The headline workload is configs[4] (the homogeneous HMM: the largest single-GPU
+configuration and the one whose sum layers are bound by the tensor cores); the other benchmark configurations
+are measured in the same run and reported under ``other_configs``.  Rank 0 prints ONE JSON line:
 
-  value        samples/s over all ranks, inputs already resident in HBM, timed with CUDA events
-  e2e          the same metric with each step's batch copied from pinned host memory inside the timed region
-               and the mean log-likelihood read back to the host
-  roofline     the dominant kernel family, timed per launch with CUDA events in a separate instrumented pass
-  cpu_baseline the CPU oracle (fp32, all host threads) on a bounded sample of the same workload
+  value         samples/s over all ranks, inputs already resident in HBM, timed with CUDA events
+  e2e           the same metric with each step's batch copied from pinned host memory inside the timed region
+                and the mean log-likelihood read back to the host
+  roofline      the dominant kernel family, timed per launch with CUDA events in a separate instrumented pass
+  cpu_baseline  the CPU oracle (fp32, all host threads) on a bounded sample of the same workload
+  other_configs {cfgN: {value, ms_per_step, e2e, roofline, sum_layers}} at the same number of GPUs
 
-``--impl reference`` times that CPU oracle alone (the reference has no runnable CPU implementation of this
-path; the oracle is its restatement) and prints the same line with ``"impl": "reference"``.
+Data parallelism is STRONG scaling: the configuration's stated global batch is split over the ranks (batch / N
+samples each); every rank holds the whole circuit, and parameter flows are all-reduced once per EM step.
 
-Under torchrun every rank holds the full circuit and its own shard of the batch (weak scaling: the per-GPU
-batch is fixed); parameter flows are all-reduced once per EM step.
+``--impl reference`` times the CPU oracle alone (the reference has no runnable CPU implementation of this path;
+the oracle is its restatement) and prints the same line with ``"impl": "reference"``.  ``--impl triton`` times
+the reference's own GPU path (its Triton kernels, through its public API) on one GPU when the reference package
+is installed under ``baseline/_ref``: the number to beat on the same box.
 """
 from __future__ import annotations
 
@@ -37,9 +43,10 @@ import pyjuice_b200 as pj  # noqa: E402
 from pyjuice_b200 import data as pdata  # noqa: E402
 
 STEP_SIZE, PSEUDOCOUNT = 0.1, 0.1
+L2_BYTES = 126e6
 
 CONFIGS = {
-    # name: (description, per-GPU batch)
+    # name: (description, global batch)
     "cfg0": ("HCLT-32 4cats K=8", 256),
     "cfg1": ("HCLT-784 grid28x28 256cats K=128", 512),
     "cfg2": ("PD-28x28 256cats K=64 splits[4,7,14]", 512),
@@ -48,38 +55,87 @@ CONFIGS = {
 }
 
 
-def build_workload(name: str, num_samples: int, seed_offset: int = 0):
-    """Returns (root_ns, data[num_samples, V] as a numpy int64 array).  Circuit structure and parameters depend
-    on the configuration's seed only; ``seed_offset`` (the rank) only changes which samples are drawn."""
+class OurStructures:
+    """Structure builders of this package under one calling convention (see `ReferenceStructures`)."""
+
+    def hclt_from_data(self, x, num_latents, num_cats):
+        return pj.structures.HCLT(torch.from_numpy(x).float(), num_latents=num_latents, num_cats=num_cats)
+
+    def hclt_from_tree(self, tree, root, num_latents, num_cats):
+        return pj.structures.tree_to_hidden_circuit(tree, root, num_latents=num_latents, num_cats=num_cats)
+
+    def pd(self, shape, num_latents, split_points, num_cats):
+        return pj.structures.PD(shape, num_latents=num_latents, split_points=split_points, num_cats=num_cats)
+
+    def rat_spn(self, num_vars, num_latents, depth, num_repetitions, num_cats):
+        return pj.structures.RAT_SPN(num_vars=num_vars, num_latents=num_latents, depth=depth,
+                                     num_repetitions=num_repetitions, num_cats=num_cats)
+
+    def hmm(self, seq_length, num_latents, num_emits):
+        return pj.structures.HMM(seq_length=seq_length, num_latents=num_latents, num_emits=num_emits, homogeneous=True)
+
+
+class ReferenceStructures:
+    """The same five builders over the reference package (``--impl triton`` only)."""
+
+    def __init__(self, juice):
+        self.juice = juice
+        import pyjuice.nodes.distributions as dists
+        self.dists = dists
+
+    def hclt_from_data(self, x, num_latents, num_cats):
+        return self.juice.structures.HCLT(torch.from_numpy(x).float(), num_latents,
+                                          input_node_params={"num_cats": num_cats})
+
+    def hclt_from_tree(self, tree, root, num_latents, num_cats):
+        import networkx as nx
+        from pyjuice.structures.compilation import BayesianTreeToHiddenRegionGraph
+        g = nx.Graph()
+        g.add_nodes_from(range(tree.n))
+        g.add_edges_from(tree.edges)
+        return BayesianTreeToHiddenRegionGraph(g, root, num_latents, self.dists.Categorical, {"num_cats": num_cats})
+
+    def pd(self, shape, num_latents, split_points, num_cats):
+        return self.juice.structures.PD(shape, num_latents, split_points=split_points,
+                                        input_node_params={"num_cats": num_cats})
+
+    def rat_spn(self, num_vars, num_latents, depth, num_repetitions, num_cats):
+        return self.juice.structures.RAT_SPN(num_vars=num_vars, num_latents=num_latents, depth=depth,
+                                             num_repetitions=num_repetitions, input_node_params={"num_cats": num_cats})
+
+    def hmm(self, seq_length, num_latents, num_emits):
+        return self.juice.structures.HMM(seq_length=seq_length, num_latents=num_latents, num_emits=num_emits,
+                                         homogeneous=True)
+
+
+def build_workload(name: str, num_samples: int, lib=None):
+    """Returns (root_ns, data[num_samples, V] as a numpy int64 array); both depend on the configuration's seed only."""
+    import random
+    lib = lib or OurStructures()
     if name == "cfg0":
         torch.manual_seed(0)
         x = pdata.tree_bn_samples(4096, 32, 4, seed=0)
-        ns = pj.structures.HCLT(torch.from_numpy(x).float(), num_latents=8, num_cats=4)
-        x = x[(np.arange(num_samples) + seed_offset * num_samples) % 4096]
+        ns = lib.hclt_from_data(x, 8, 4)
+        x = x[np.arange(num_samples) % 4096]
     elif name == "cfg1":
         torch.manual_seed(1)
-        _, tree, root = pdata.grid_gaussian_bn_samples(16, 28, 28, seed=1)
-        ns = pj.structures.tree_to_hidden_circuit(tree, root, num_latents=128, num_cats=256)
-        x, _, _ = pdata.grid_gaussian_bn_samples(num_samples * (seed_offset + 1), 28, 28, seed=1)
-        x = x[-num_samples:]
+        x, tree, root = pdata.grid_gaussian_bn_samples(num_samples, 28, 28, seed=1)
+        ns = lib.hclt_from_tree(tree, root, 128, 256)
     elif name == "cfg2":
-        import random
         torch.manual_seed(2)
         random.seed(2)
         pts = sorted(set(range(4, 28, 4)) | set(range(7, 28, 7)) | set(range(14, 28, 14)))
-        ns = pj.structures.PD((28, 28), num_latents=64, split_points=[pts, pts], num_cats=256)
-        x, _, _ = pdata.grid_gaussian_bn_samples(num_samples * (seed_offset + 1), 28, 28, seed=2)
-        x = x[-num_samples:]
+        ns = lib.pd((28, 28), 64, [pts, pts], 256)
+        x, _, _ = pdata.grid_gaussian_bn_samples(num_samples, 28, 28, seed=2)
     elif name == "cfg3":
-        import random
         torch.manual_seed(3)
         random.seed(3)
-        ns = pj.structures.RAT_SPN(num_vars=784, num_latents=32, depth=5, num_repetitions=16, num_cats=256)
-        x = pdata.mixture_samples(num_samples * (seed_offset + 1), 784, 256, seed=3)[-num_samples:]
+        ns = lib.rat_spn(784, 32, 5, 16, 256)
+        x = pdata.mixture_samples(num_samples, 784, 256, seed=3)
     elif name == "cfg4":
         torch.manual_seed(4)
-        ns = pj.structures.HMM(seq_length=128, num_latents=4096, num_emits=32768, homogeneous=True)
-        x = pdata.hmm_samples(num_samples * (seed_offset + 1), 128, 32768, seed=4)[-num_samples:]
+        ns = lib.hmm(128, 4096, 32768)
+        x = pdata.hmm_samples(num_samples, 128, 32768, seed=4)
     else:
         raise ValueError(name)
     ns.init_parameters()
@@ -87,16 +143,18 @@ def build_workload(name: str, num_samples: int, seed_offset: int = 0):
 
 
 def circuit_stats(pc, B):
-    """Algorithmic work per sample and per step (the figures every roofline number is computed from)."""
+    """Algorithmic work per sample and per step (the figures every roofline number is computed from).
+
+    Product layers: a forward launch must read every DISTINCT child row once and write every product row once; a
+    backward launch reads every product row's flow once and reads and writes every distinct child row's flow."""
     e_sum = sum(l.num_edges for g in pc.inner_layer_groups if g.is_sum() for l in g)
     prod_edges = sum(l.num_edges for g in pc.inner_layer_groups if g.is_prod() for l in g)
     prod_nodes = sum(l.num_nodes for g in pc.inner_layer_groups if g.is_prod() for l in g)
     n_in = sum(l.num_nodes for l in pc.input_layer_group)
     p_in = sum(l.num_parameters for l in pc.input_layer_group)
     f_in = sum(l.num_param_flows for l in pc.input_layer_group)
+    f_in_untied = sum(l.num_untied_param_flows for l in pc.input_layer_group)
     sum_rows = sum(l.num_nodes for g in pc.inner_layer_groups if g.is_sum() for l in g)
-    # product layers that still run as kernels of their own (the others are folded into the sum kernels):
-    # (edges + nodes) per forward launch, (edges + 2 nodes) per backward launch, summed over the launches of a step
     prod_fwd = prod_bwd = 0
     groups = pc.inner_layer_groups
     for gi, g in enumerate(groups):
@@ -104,12 +162,13 @@ def circuit_stats(pc, B):
             continue
         folded = gi + 1 < len(groups) and pc._fusion_on(gi + 1)
         folded_bk = folded and B % 8 == 0                  # the backward sweep folds for batches that are multiples of 8
-        e, n = sum(l.num_edges for l in g), sum(l.num_nodes for l in g)
-        prod_fwd += (0 if folded else e + n) + (0 if folded_bk else e + n)      # forward pass + recompute in backward
+        n = sum(l.num_nodes for l in g)
+        u = sum(int(t.numel()) * l.block_size for l in g for t in l.partitioned_u_cids)      # distinct child rows
+        prod_fwd += (0 if folded else u + n) + (0 if folded_bk else u + n)      # forward pass + recompute in backward
         if not (folded_bk and pc._fused[gi + 1]["direct"]):
-            prod_bwd += e + 2 * n
+            prod_bwd += n + 2 * u
     return dict(e_sum=e_sum, prod_edges=prod_edges, prod_nodes=prod_nodes, n_in=n_in, p_in=p_in, f_in=f_in,
-                p_sum=pc.num_sum_params, f_sum=pc.num_param_flows, sum_rows=sum_rows,
+                f_in_untied=f_in_untied, p_sum=pc.num_sum_params, f_sum=pc.num_param_flows, sum_rows=sum_rows,
                 prod_fwd_launched=prod_fwd, prod_bwd_launched=prod_bwd)
 
 
@@ -122,6 +181,10 @@ def family_of(name: str) -> str:
         return "pcx_sum_bwd_par"
     if name.startswith("pcx_pack_sm"):
         return "pcx_pack_sum_params"
+    if name.startswith("pcx_input_cat_fwd"):
+        return "pcx_input_cat_fwd"
+    if name.startswith("pcx_input_cat_bwd"):
+        return "pcx_input_cat_bwd"
     for suffix in ("_fused", "_packed", "_batched", "_noalloc", "_dense", "_sm"):
         if name.endswith(suffix):
             name = name[:-len(suffix)]
@@ -153,7 +216,8 @@ def family_work(stats, B, elsize):
         "pcx_prod_fwd": ("hbm", 4.0 * s["prod_fwd_launched"] * B, 0.0),
         "pcx_prod_bwd": ("hbm", 4.0 * s["prod_bwd_launched"] * B, 0.0),
         "pcx_input_cat_fwd": ("hbm", 4.0 * s["n_in"] * B, 0.0),
-        "pcx_input_cat_bwd": ("hbm", 4.0 * s["n_in"] * B + 8.0 * s["f_in"], 0.0),
+        # flows of every (node, sample) read; one flow cell per (node, sample) read and written
+        "pcx_input_cat_bwd": ("hbm", 4.0 * s["n_in"] * B + 8.0 * min(s["f_in"], s["n_in"] * B), 0.0),
         "pcx_em_input_cat": ("hbm", 12.0 * s["p_in"], 0.0),
         "pcx_em_sum": ("hbm", 12.0 * s["p_sum"], 0.0),
         "pcx_fill_f32": ("hbm", 4.0 * (s["f_sum"] + s["f_in"]), 0.0),
@@ -161,10 +225,11 @@ def family_work(stats, B, elsize):
     }
 
 
-# DRAM bytes per step (read + write) of a launch family, from ncu captures of the same kernels; None = not captured
-TRAFFIC_PER_STEP = {
+# DRAM bytes (read + write) of ONE launch of the named family's dominant kernel, from ncu captures of the same
+# kernels on one B200 (summaries under profiles/); None = not captured.  (config, family) -> bytes per launch
+TRAFFIC_PER_LAUNCH = {
     # configs[1], B = 512: one dataflow launch each for the forward pass and the element flows, one batched launch
-    # for the parameter flows (profiles/ncu_full_cfg1_chain_par.md)
+    # for the parameter flows
     ("cfg1", "pcx_sum_fwd"): 389.0e6,
     ("cfg1", "pcx_sum_bwd_ele"): 801.4e6,
     ("cfg1", "pcx_sum_bwd_par"): 636.3e6,
@@ -220,6 +285,17 @@ def measured_peaks():
     return {"hbm": 6650.0, "tensor": 1590.0, "source": "fallback"}
 
 
+def host_threads() -> int:
+    """Host cores this process may use.  Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU arm sets the
+    thread count itself so that it is the same however the script was started."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def oracle_step_time(pc, x_cpu: torch.Tensor, repeats: int = 1):
     """Seconds per forward + backward + EM step of the fp32 CPU oracle on ``x_cpu``."""
     from oracle import pc_oracle as orc
@@ -236,16 +312,21 @@ def oracle_step_time(pc, x_cpu: torch.Tensor, repeats: int = 1):
     return best
 
 
+def cpu_sample_size(config: str, B: int, requested: int) -> int:
+    """Samples per CPU step: the oracle does configs[4]'s 12.8 GFLOP per sample at a few hundred GFLOP/s."""
+    return min(B, requested, 16 if config == "cfg4" else requested)
+
+
 def run_reference(args, rank):
     """CPU arm: the oracle restatement of the reference algorithm on the host cores, one bounded sample per step."""
     if rank != 0:
         return
+    cores = host_threads()
     desc, B = CONFIGS[args.config]
-    sample = min(B, args.cpu_sample)
+    sample = cpu_sample_size(args.config, B, args.cpu_sample)
     ns, x = build_workload(args.config, sample)
     pc = pj.compile(ns)
     xc = torch.from_numpy(x)
-    cores = torch.get_num_threads()
     # one step at the full sample size tells how long K of them would take; the sample shrinks until the whole
     # run fits in about two minutes (throughput of this CPU path is close to linear in the number of samples)
     t_one = oracle_step_time(pc, xc)
@@ -254,72 +335,106 @@ def run_reference(args, rank):
         sample = max(8, int(sample * budget / (t_one * args.steps)) // 8 * 8)
         xc = xc[:sample]
         oracle_step_time(pc, xc)
+    steps = max(1, min(args.steps, int(budget / max(t_one * sample / max(xc.size(0), 1), 1e-3))))
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         oracle_step_time(pc, xc)
-    dt = (time.perf_counter() - t0) / args.steps
+    dt = (time.perf_counter() - t0) / steps
     value = sample / dt
-    what = f"{sample} samples per step (of the {B}-sample batch), fwd+bwd+EM, fp32 torch CPU, {cores} threads"
+    what = (f"{sample} samples per step (of the {B}-sample batch), fwd+bwd+EM, fp32 torch CPU, {cores} threads, "
+            f"{steps} timed steps")
     print(json.dumps({
         "impl": "reference", "metric": "samples/sec fwd+bwd+EM", "value": value, "unit": "samples/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.config}: {desc}", "batch_per_gpu": B},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.config, max(args.gpus, 1)),
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port", "sample": what},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--config", default="cfg1", choices=sorted(CONFIGS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--no-dataflow", action="store_true", help="per-layer launches instead of one launch per run of layers")
-    ap.add_argument("--no-side-stream", action="store_true", help="every kernel of a step on one stream")
-    ap.add_argument("--chain-tile", type=int, default=None, choices=[16, 32, 64], help="tile width of the dataflow launch")
-    ap.add_argument("--sum-mode", type=int, default=1, choices=[0, 1, 2],
-                    help="0 fp32 CUDA cores, 1 tensor cores with split-bf16 operands, 2 tensor cores single bf16")
-    args = ap.parse_args()
+def workload_config(config: str, world: int) -> dict:
+    desc, B = CONFIGS[config]
+    return {"workload": f"{config}: {desc}", "global_batch": B, "batch_per_gpu": B // world, "parallelism": f"dp{world}",
+            "em": {"step_size": STEP_SIZE, "pseudocount": PSEUDOCOUNT}}
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
-        return run_reference(args, rank)
 
+def run_triton(args, rank):
+    """The reference's own GPU path (Triton kernels, public API, stock code) on one GPU: the number to beat."""
+    if rank != 0:
+        return
+    import types
+    pkg = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(pkg, "pyjuice")):
+        print(json.dumps({"impl": "triton", "unavailable": "the reference package is not installed under baseline/_ref"}))
+        return
+    os.environ.setdefault("PYJUICE_DISABLE_CUDA_KERNELS", "1")      # its CuTe kernels wait on barriers without a bound
+    os.environ.setdefault("PYJUICE_DISABLE_DIST_CUDA_KERNELS", "1")
+    os.environ.setdefault("PYJUICE_AUTOTUNE", "0")
+    for name in ("matplotlib", "matplotlib.pyplot", "matplotlib.patches"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.path.insert(0, pkg)
+    import pyjuice as juice
+    dev = torch.device("cuda:0")
+    desc, B = CONFIGS[args.config]
+    n_batches = 4
+    ns, x = build_workload(args.config, B * n_batches, lib=ReferenceStructures(juice))
+    pc = juice.compile(ns, verbose=False)
+    pc.to(dev)
+    xs = [torch.from_numpy(x[i * B:(i + 1) * B]).to(dev) for i in range(n_batches)]
+    opt = juice.optim.MiniBatchEM(pc, step_size=STEP_SIZE, pseudocount=PSEUDOCOUNT)
+    results = {}
+    for mode, kw in (("eager", {}), ("cudagraph", {"record_cudagraph": True}),
+                     ("fp32", {"force_use_fp32": True})):
+        def step(xb):
+            lls = pc(xb, **kw)
+            lls.mean().backward()
+            opt.step()
+            return lls
+        try:
+            for i in range(max(args.warmup, 3)):
+                step(xs[i % n_batches])
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for i in range(args.steps):
+                step(xs[i % n_batches])
+            ev1.record()
+            torch.cuda.synchronize()
+            results[mode] = ev0.elapsed_time(ev1) / args.steps
+        except Exception as e:                               # one variant must not lose the others
+            results[mode] = f"{type(e).__name__}: {e}"[:200]
+    ok = {k: v for k, v in results.items() if isinstance(v, float) and k != "fp32"}
+    best = min(ok.values()) if ok else None
+    print(json.dumps({
+        "impl": "triton", "metric": "samples/sec fwd+bwd+EM", "value": B / (best * 1e-3) if best else None,
+        "unit": "samples/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": best,
+        "higher_is_better": True, "dtype": "reference default (bf16 forward, tf32 backward tensor cores)",
+        "data": "synthetic", "config": workload_config(args.config, 1),
+        "ms_per_step_by_variant": results,
+        "note": "reference 2.6.3, Triton kernels only (CuTe kernels and autotuning switched off by its own env flags)",
+    }), flush=True)
+
+
+def measure_ours(config: str, args, rank: int, world: int, dev, K: int, W: int, sampler, with_cpu: bool):
+    """Build one configuration on this rank, time it, and return the fields of its result (rank 0) or None."""
     import torch.distributed as dist
     from pyjuice_b200 import _lib
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device(f"cuda:{local_rank}")
-    if world > 1:
-        import datetime
-        # NCCL's kernels on a high-priority stream: the all-reduce of the input-layer flows runs beside the
-        # parameter-flow kernel, whose 2000+ CTAs would otherwise keep the collective's few CTAs waiting for an SM
-        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120), pg_options=opts)
-    W, K = max(args.warmup, 3), args.steps
-    desc, B = CONFIGS[args.config]
-    _lib.set_sum_mode(args.sum_mode)
-
-    sampler = ClockSampler(local_rank) if rank == 0 else None      # started early: see the class comment
+    desc, B = CONFIGS[config]
+    assert B % world == 0, f"the global batch {B} does not split over {world} ranks"
+    Bl = B // world
     n_batches = 4
-    ns, x = build_workload(args.config, B * n_batches, seed_offset=rank)
+    ns, x = build_workload(config, B * n_batches)
     pc = pj.compile(ns).to(dev)
     pc.use_cuda_graphs = not args.no_graphs
     pc.use_dataflow_launch = not args.no_dataflow
     pc.use_side_stream = not args.no_side_stream
     pc.chain_tile = args.chain_tile
-    stats = circuit_stats(pc, B)
+    stats = circuit_stats(pc, Bl)
     max_cats = max(l.max_cats for l in pc.input_layer_group)
     np_dtype, elsize = (np.uint8, 1) if max_cats <= 256 else (np.int32, 4)
-    host = [torch.from_numpy(x[i * B:(i + 1) * B].astype(np_dtype)).pin_memory() for i in range(n_batches)]
+    shard = lambda i: x[i * B + rank * Bl:i * B + (rank + 1) * Bl]
+    host = [torch.from_numpy(shard(i).astype(np_dtype)).pin_memory() for i in range(n_batches)]
     resident = [h.to(dev) for h in host]
     opt = pj.optim.MiniBatchEM(pc, step_size=STEP_SIZE, pseudocount=PSEUDOCOUNT, ddp=world > 1)
 
@@ -370,7 +485,7 @@ def main():
     ms_e2e = ev0.elapsed_time(ev1)
     if sampler:
         sampler.window(t0, time.time())
-    clocks = sampler.stop() if sampler else None
+    _lib.check_status(dev)                 # a bounded device wait that ran out would have produced wrong numbers
 
     t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
     if world > 1:
@@ -392,67 +507,138 @@ def main():
             d[0] += 1
             d[1] += a.elapsed_time(b)
     _lib.PROFILE = None
-    pc.use_cuda_graphs = not args.no_graphs
-    pc.use_side_stream = not args.no_side_stream
-
+    _lib.check_status(dev)
     if world > 1:
         dist.barrier()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     peaks = measured_peaks()
-    work = family_work(stats, B, elsize)
+    work = family_work(stats, Bl, elsize)
     fam_ms = {k: round(v[1], 4) for k, v in sorted(fam.items(), key=lambda kv: -kv[1][1])}
     top = max(fam, key=lambda k: fam[k][1])
     bound, amount, fam_flops = work.get(top, ("hbm", 0.0, 0.0))
     n_launch, tot_ms = fam[top]
     achieved = amount / (tot_ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+
+    def frac_of(k, v):
+        """Fraction of the binding roofline, or None when one launch moves less than the L2 holds (then the bytes
+        need not come from HBM and the HBM roofline does not apply)."""
+        b, amt, _ = work[k]
+        if b == "hbm" and amt / max(v[0], 1) < L2_BYTES:
+            return None
+        return round(amt / (v[1] * 1e-3) / (1e12 if b == "tensor" else 1e9) / peaks[b], 4)
+
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peaks[bound],
                 "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": achieved / peaks[bound],
-                "traffic": TRAFFIC_PER_STEP.get((args.config, top)), "peak_source": peaks["source"],
+                "traffic": TRAFFIC_PER_LAUNCH.get((config, top)), "peak_source": peaks["source"],
                 "launches_per_step": n_launch, "ms_per_step_in_kernel": tot_ms,
                 "algorithmic_bytes_or_flops_per_step": amount,
                 "tensor_tflops": fam_flops / (tot_ms * 1e-3) / 1e12 if fam_flops else None,
                 "family_ms_per_step": fam_ms,
-                "family_frac": {k: round(work[k][1] / (v[1] * 1e-3) / (1e12 if work[k][0] == "tensor" else 1e9)
-                                         / peaks[work[k][0]], 4) for k, v in fam.items() if k in work and v[1] > 0}}
+                "family_frac": {k: frac_of(k, v) for k, v in fam.items() if k in work and v[1] > 0}}
     sum_ms = sum(fam[k][1] for k in ("pcx_sum_fwd", "pcx_sum_bwd_ele", "pcx_sum_bwd_par") if k in fam)
-    sum_tflops = 6.0 * stats["e_sum"] * B / (sum_ms * 1e-3) / 1e12 if sum_ms > 0 else None
+    sum_tflops = 6.0 * stats["e_sum"] * Bl / (sum_ms * 1e-3) / 1e12 if sum_ms > 0 else None
 
     cpu = None
-    if not args.no_cpu_baseline and world == 1:            # the CPU baseline is reported by the single-GPU run only
-        sample = min(B, args.cpu_sample)
+    if with_cpu:
+        cores = host_threads()
+        sample = cpu_sample_size(config, B, args.cpu_sample)
         sec = oracle_step_time(pc, torch.from_numpy(x[:sample]))
-        cores = torch.get_num_threads()
         cpu = {"value": sample / sec, "unit": "samples/s", "cores": cores, "kind": "port",
                "sample": f"one fwd+bwd+EM step on {sample} samples, fp32 torch CPU oracle, {cores} threads, {sec:.2f} s"}
 
-    total = B * world * K
+    total = B * K
+    cfg = workload_config(config, world)
+    cfg.update({"input_dtype": np.dtype(np_dtype).name, "cuda_graphs": not args.no_graphs,
+                "l2": "value buffers (%.2f GB per GPU) exceed the 126 MB L2; no explicit flush" %
+                      (4.0 * Bl * 2 * (pc.num_nodes + pc.num_elements) / 1e9),
+                "circuit": {k: int(v) for k, v in stats.items()}})
     out = {
-        "metric": "samples/sec fwd+bwd+EM", "value": total / (ms_dev * 1e-3), "unit": "samples/s",
-        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev / K, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.config}: {desc}", "batch_per_gpu": B, "global_batch": B * world,
-                   "parallelism": f"dp{world}", "em": {"step_size": STEP_SIZE, "pseudocount": PSEUDOCOUNT},
-                   "input_dtype": np.dtype(np_dtype).name, "cuda_graphs": not args.no_graphs,
-                   "l2": "value buffers (%.2f GB) exceed the 126 MB L2; no explicit flush" %
-                         (4.0 * B * 2 * (pc.num_nodes + pc.num_elements) / 1e9),
-                   "circuit": {k: int(v) for k, v in stats.items()}},
+        "value": total / (ms_dev * 1e-3), "ms_per_step": ms_dev / K, "steps": K, "warmup": W, "config": cfg,
         "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e / K,
-                "h2d_bytes_per_step": int(B * pc.num_vars * elsize), "d2h_bytes_per_step": 4, "last_mean_ll": last},
+                "h2d_bytes_per_step": int(B * pc.num_vars * elsize), "d2h_bytes_per_step": 4 * world,
+                "last_mean_ll": last},
         "gpu_launches": launches_per_step * K,
         "roofline": roofline,
-        "sum_layers": {"tflops": sum_tflops, "ms_per_step": sum_ms, "frac_of_bf16_peak": (sum_tflops or 0) / peaks["tensor"],
+        "sum_layers": {"tflops": sum_tflops, "ms_per_step": sum_ms,
+                       "frac_of_bf16_peak": (sum_tflops or 0) / peaks["tensor"],
                        "arith": ["fp32 FMA (CUDA cores)",
                                  "tcgen05 bf16 hi/lo split x3, fp32 accumulate (fwd, element flows, parameter flows)",
                                  "tcgen05 single bf16, fp32 accumulate (fwd, element flows, parameter flows)"][args.sum_mode]},
         "cpu_baseline": cpu,
-        "clocks": clocks,
     }
+    del pc, opt, resident, host
+    torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS))
+    ap.add_argument("--others", default=None,
+                    help="comma-separated configurations measured in the same run (default: cfg1,cfg2,cfg3 beside cfg4)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
+    ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-dataflow", action="store_true", help="per-layer launches instead of one launch per run of layers")
+    ap.add_argument("--no-side-stream", action="store_true", help="every kernel of a step on one stream")
+    ap.add_argument("--chain-tile", type=int, default=None, choices=[16, 32, 64], help="tile width of the dataflow launch")
+    ap.add_argument("--sum-mode", type=int, default=1, choices=[0, 1, 2],
+                    help="0 fp32 CUDA cores, 1 tensor cores with split-bf16 operands, 2 tensor cores single bf16")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+    if args.impl == "triton":
+        return run_triton(args, rank)
+
+    import torch.distributed as dist
+    from pyjuice_b200 import _lib
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
     if world > 1:
+        import datetime
+        # NCCL's kernels on a high-priority stream: the all-reduce of the input-layer flows runs beside the
+        # parameter-flow kernel, whose 2000+ CTAs would otherwise keep the collective's few CTAs waiting for an SM
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120), pg_options=opts)
+    W, K = max(args.warmup, 3), args.steps
+    _lib.set_sum_mode(args.sum_mode)
+    others = args.others if args.others is not None else ("cfg1,cfg2,cfg3" if args.config == "cfg4" else "")
+    others = [c for c in others.split(",") if c and c != args.config]
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None      # started early: see the class comment
+    head = measure_ours(args.config, args, rank, world, dev, K, W, sampler,
+                        with_cpu=not args.no_cpu_baseline and world == 1 and rank == 0)
+    other_out = {}
+    for c in others:
+        r = measure_ours(c, args, rank, world, dev, min(K, 30), 3, sampler, with_cpu=False)
+        if r is not None:
+            other_out[c] = {"value": r["value"], "unit": "samples/s", "ms_per_step": r["ms_per_step"], "steps": r["steps"],
+                            "global_batch": r["config"]["global_batch"], "e2e": r["e2e"], "gpu_launches": r["gpu_launches"],
+                            "roofline": {k: r["roofline"][k] for k in ("kernel", "bound", "achieved", "peak", "unit", "frac",
+                                                                        "traffic", "family_ms_per_step", "family_frac")},
+                            "sum_layers": r["sum_layers"]}
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if rank != 0:
+        return
+    out = {"metric": "samples/sec fwd+bwd+EM", "value": head["value"], "unit": "samples/s", "n_gpus": world,
+           "steps": K, "warmup": W, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+           "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": head["config"], "e2e": head["e2e"],
+           "gpu_launches": head["gpu_launches"], "roofline": head["roofline"], "sum_layers": head["sum_layers"],
+           "cpu_baseline": head["cpu_baseline"], "other_configs": other_out, "clocks": clocks}
     sys.stderr.flush()
     print(json.dumps(out), flush=True)                 # the one JSON line, last thing on stdout
 

@@ -35,6 +35,13 @@ int pcx_build_arch(void);
 int pcx_set_sum_mode(int mode);
 /* 0, or the code of the first tensor-core kernel whose bounded barrier wait ran out (synchronises the device). */
 int pcx_get_status(void);
+/* Reset that status word to 0 (after the caller has dealt with the failure). */
+int pcx_clear_status(void);
+/* Self-test of the failure path: one warp waits, for at most `max_polls` (<= 65536) polls, on a counter that
+ * nothing advances (which = 0) or on an mbarrier nothing arrives on (which = 1), gives up, records status
+ * 900 + which and returns; the context stays usable.  The reference's kernels have no such path: their barrier
+ * waits are unbounded loops (layer/kernels/c/tlmm_forward_sum.cu:55-61). */
+int pcx_probe_bounded_wait(int which, int max_polls, void* stream);
 
 /* p[i] = v  /  p[i] *= v  for i < n.
  * Replaces the buffer resets of model/tensorcircuit.py:357-359, 528-529, 1761-1773 and the
@@ -317,8 +324,8 @@ int pcx_sum_bwd_par(float* param_flows, const float* node_flows, const float* no
                     const int32_t* nids, const int32_t* cids, const int32_t* pids, const int32_t* pfids,
                     int64_t n_blocks, int K, int block_size, int B, int logspace, void* stream);
 
-/* target[start + j] = sum_c flows[ch_starts[c] + j], j < n  (in place on `flows`; the source's own range is
- * one of the ch_starts).  Replaces InputLayer._pflow_accum_kernel (layer/input_layer.py:755-783, 1391-1411)
+/* flows[start + j] = sum_c flows[ch_starts[c] + j], j < n, and every other accumulator is cleared (in place on
+ * `flows`; the source's own range is one of the ch_starts), so a second call changes nothing.  Replaces InputLayer._pflow_accum_kernel (layer/input_layer.py:755-783, 1391-1411)
  * and cum_par_flows_kernel (model/backend/parflow_fusing.py:80-112). */
 int pcx_tied_accum(float* flows, int64_t start, int64_t n, const int64_t* ch_starts, int n_chs, void* stream);
 

@@ -16,11 +16,17 @@ of PyJuice's algorithm, driven purely by the compiled index tables:
   * tied accumulate  source range := sum of accumulators              model/backend/parflow_fusing.py:80-99, layer/input_layer.py:1391-1411
   * EM update        (1-eta) theta + eta (F + alpha/nch)/(sum F + alpha)   model/backend/par_update.py:173-256, categorical.py:191-228
 
-Pinning: the reference cannot execute this path without a GPU (its leaf and product layers are
-Triton-only), so the oracle is pinned (tests/test_oracle_pins.py) against the closed-form dense
-restatements and known-answer values that the reference's own tests assert
-(tests/model/simple_model_test.py:191-528, tests/structures/hmm_correctness_test.py), evaluated on
-tables that are themselves checked bit-for-bit against the reference compiler's output.
+Pinning.  Tables: the compiled tables the oracle is driven by are checked bit-for-bit against the reference
+compiler's output (tests/golden/*.npz, tests/test_tables_golden.py).  Values: tests/golden/values_<case>.npz hold
+what the reference ITSELF computes on a B200 (its Triton path through its public API: log-likelihoods, node values,
+node flows, parameter flows, post-EM parameters; written by tests/golden/make_values.py), and
+tests/test_reference_values.py checks every function below against them.  tests/test_oracle_pins.py adds the
+closed-form dense restatements that the reference's own tests assert (tests/model/simple_model_test.py:191-528,
+tests/structures/hmm_correctness_test.py) and an autograd evaluator that shares no code with this file.
+
+Two behaviours of the reference's kernels that change results beyond rounding are reproduced only when
+``reference_compat=True`` is passed (product nodes without a sum parent; padding slots of the tied-flow fusing
+kernel); by default flows are the exact gradients of the log-likelihood.
 """
 from __future__ import annotations
 
@@ -193,9 +199,12 @@ def forward(pc, x: torch.Tensor, params: torch.Tensor, input_params, dtype=torch
 
 def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: OracleState,
              ll_weights: Optional[torch.Tensor] = None, compute_param_flows: bool = True,
-             param_flows: Optional[torch.Tensor] = None, input_param_flows=None):
+             param_flows: Optional[torch.Tensor] = None, input_param_flows=None, reference_compat: bool = False):
     """Log-space node/element flows and (accumulated) parameter flows.  ``st`` comes from
-    :func:`forward` on the same inputs.  Existing ``param_flows`` are added to, as the reference does."""
+    :func:`forward` on the same inputs.  Existing ``param_flows`` are added to, as the reference does.
+
+    ``reference_compat`` reproduces the reference's handling of product nodes without a sum parent (see the
+    comment in the loop below) instead of giving them zero flow."""
     t = st.tables
     dtype = st.node_mars.dtype
     B = x.size(0)
@@ -219,7 +228,8 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
             # written below, so clear the buffer per depth (the reference clears it once per pass only,
             # model/tensorcircuit.py:526-528, and lets such a row keep another depth's flow; that defect is
             # deliberately not reproduced: the flows here are the true gradients, see tests/test_oracle_pins.py).
-            st.element_flows.fill_(NEG_INF)
+            if not reference_compat:
+                st.element_flows.fill_(NEG_INF)
             for layer in layers:
                 _sum_backward(layer, st, params, compute_param_flows)
     st.input_param_flows = []
@@ -235,8 +245,11 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
     return st
 
 
-def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size: float, pseudocount: float = 0.0):
-    """Returns ``(new_params, [new_input_params])``; flows are taken from ``st``."""
+def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size: float, pseudocount: float = 0.0,
+              reference_compat: bool = False):
+    """Returns ``(new_params, [new_input_params])``; flows are taken from ``st``.
+
+    ``reference_compat`` reproduces the reference's tied-flow fusing kernel on padding slots (see below)."""
     dtype = st.param_flows.dtype
     new_inputs = []
     for lt, ip, pf in zip(st.tables["inputs"], input_params, st.input_param_flows):
@@ -256,6 +269,7 @@ def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size
 
     params = params.detach().cpu().to(dtype).clone()
     pf = st.param_flows.clone()
+    head = pf.clone()          # what the reference's kernel reads through a padding slot: param_flows[0 : n]
     for tgt, sizes, chs, G, M in pc.parflow_fusing_kwargs:
         for i in range(tgt.numel()):
             n = int(sizes[i])
@@ -264,7 +278,10 @@ def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size
             # param_flows[0:n] as well; that is a defect for non-power-of-two accumulator counts and is
             # deliberately not reproduced.)
             real = [int(c) for k, c in enumerate(chs[i].tolist()) if k == 0 or c != 0]
-            pf[int(tgt[i]):int(tgt[i]) + n] = sum(pf[c:c + n] for c in real)
+            total = sum(pf[c:c + n] for c in real)
+            if reference_compat:
+                total = total + (chs[i].numel() - len(real)) * head[:n]
+            pf[int(tgt[i]):int(tgt[i]) + n] = total
     par_start, pflow_start, blk_sizes, blk_int, gnids, nchs = [a.cpu() for a in pc.par_update_kwargs[:6]]
     tot = int(gnids.max().item()) + 1
     j = torch.arange(int(blk_sizes.max().item()))

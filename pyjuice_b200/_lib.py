@@ -54,10 +54,11 @@ SIGNATURES = {
     "pcx_tied_accum": [P, L, L, P, I],
     "pcx_em_sum": [P, P, P, P, P, P, L, I, F, F, I],
     "pcx_em_input_cat": [P, P, P, P, P, P, L, I, F, F, I],
+    "pcx_probe_bounded_wait": [I, I],
 }
 
 # entry points without a stream argument
-PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": [],
+PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": [], "pcx_clear_status": [],
          "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I],
          "pcx_sm_packed_bytes": [L, I, I]}
 SUM_MODE = 1        # mirror of the library's arithmetic mode (see set_sum_mode)
@@ -95,18 +96,18 @@ def load() -> ctypes.CDLL:
     return lib
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
-
-
 def call(name: str, *args) -> None:
-    """Invoke one entry point on the current CUDA stream; tensors are passed as device pointers."""
+    """Invoke one entry point; tensors are passed as device pointers.  The launch goes to the device of the first
+    tensor argument, on torch's current stream OF THAT DEVICE (which need not be the current device)."""
     lib = load()
     conv = []
+    dev = None
     for a in args:
         if isinstance(a, torch.Tensor):
             if not a.is_cuda:
                 raise PcxError(f"{name}: tensor argument is not on a CUDA device (no CPU path exists)")
+            if dev is None:
+                dev = a.device
             conv.append(a.data_ptr())
         elif a is None:
             conv.append(None)
@@ -114,20 +115,29 @@ def call(name: str, *args) -> None:
             conv.append(a)
     global COUNT
     COUNT += 1
-    if PROFILE is not None:
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        rc = getattr(lib, name)(*conv, _stream())
-        b.record()
-        # the dataflow launch serves two operators: tell them apart by its first argument (0 forward, 1 element flows)
-        PROFILE.append((name + ("_fwd", "_ele")[args[0]] if name == "pcx_sum_chain" else name, a, b))
+    if dev is not None and dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):             # the C side reads per-device state (SM count, built-in scratch)
+            rc = _invoke(lib, name, conv, args, dev)
     else:
-        rc = getattr(lib, name)(*conv, _stream())
-    if rc == -2:
+        rc = _invoke(lib, name, conv, args, dev)
+    if rc == -2 and name == "pcx_sum_fwd_noalloc":
         raise PcxError(f"{name}: the table needs more pre-split parameter tiles than the library's built-in scratch "
                        "holds (256 tiles of 32 KB); use the packed entry points with a caller-owned buffer instead")
     if rc != 0:
         raise PcxError(f"{name} failed with status {rc}")
+
+
+def _invoke(lib, name, conv, args, dev) -> int:
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    if PROFILE is None:
+        return getattr(lib, name)(*conv, stream)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    rc = getattr(lib, name)(*conv, stream)
+    b.record()
+    # the dataflow launch serves two operators: tell them apart by its first argument (0 forward, 1 element flows)
+    PROFILE.append((name + ("_fwd", "_ele")[args[0]] if name == "pcx_sum_chain" else name, a, b))
+    return rc
 
 
 def set_sum_mode(mode: int) -> None:
@@ -138,8 +148,27 @@ def set_sum_mode(mode: int) -> None:
     SUM_MODE = int(mode)
 
 
-def check_status() -> None:
-    """Raise if a tensor-core kernel reported that one of its bounded barrier waits ran out."""
-    code = load().pcx_get_status()
+def get_status(device=None) -> int:
+    """Status word of ``device`` (default: the current device): 0, or the code of the first bounded wait of a
+    tensor-core kernel that ran out since the word was last cleared.  Synchronises that device."""
+    with torch.cuda.device(device):
+        return int(load().pcx_get_status())
+
+
+def clear_status(device=None) -> None:
+    with torch.cuda.device(device):
+        rc = load().pcx_clear_status()
+    if rc != 0:
+        raise PcxError(f"pcx_clear_status failed with status {rc}")
+
+
+def check_status(device=None) -> None:
+    """Raise if a tensor-core kernel on ``device`` reported that one of its bounded barrier waits ran out (its tile
+    was skipped, so results computed since are wrong); the word is cleared so that later checks start afresh.
+
+    The library calls this where the host synchronises anyway (`TensorCircuit.update_parameters`, `io.save`, reading
+    `_cum_flow`); a training loop that never does any of these should call it itself now and then."""
+    code = get_status(device)
     if code != 0:
+        clear_status(device)
         raise PcxError(f"a tensor-core kernel gave up waiting on a barrier (status {code})")

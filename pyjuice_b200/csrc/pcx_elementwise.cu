@@ -45,30 +45,37 @@ __global__ void root_flows_kernel(float* __restrict__ node_flows, const float* _
 }
 
 // Categorical leaves, general form: one CTA per node, threads walk the batch.  Used when the batch is not a multiple
-// of four or a node has too many categories to stage its table in shared memory.
+// of four or a node has too many categories to stage its table in shared memory.  A category id outside the node's
+// table (invalid data) must not address outside it: the forward kernel clamps it, the backward kernel adds no flow.
 __global__ void input_cat_fwd_kernel(float* __restrict__ node_mars, const float* __restrict__ params,
                                      const void* __restrict__ data, int elsize,
                                      const int32_t* __restrict__ vids, const int32_t* __restrict__ s_pids,
+                                     const int32_t* __restrict__ node_cats, int max_cats,
                                      int64_t n_nodes, int64_t node_off, int B) {
     const int64_t n = blockIdx.x;
     const int64_t drow = (int64_t)vids[n] * B;
     const float* prow = params + (int64_t)s_pids[n];
+    const int cap = (node_cats ? node_cats[n] : max_cats) - 1;
     float* out = node_mars + (node_off + n) * B;
-    for (int b = threadIdx.x; b < B; b += blockDim.x) out[b] = logf(prow[pcx_load_cat(data, elsize, drow + b)]);
+    for (int b = threadIdx.x; b < B; b += blockDim.x)
+        out[b] = logf(prow[min(max(pcx_load_cat(data, elsize, drow + b), 0), cap)]);
 }
 
 __global__ void input_cat_bwd_kernel(float* __restrict__ param_flows, const float* __restrict__ node_flows,
                                      const void* __restrict__ data, int elsize,
                                      const int32_t* __restrict__ vids, const int32_t* __restrict__ s_pfids,
+                                     const int32_t* __restrict__ node_cats, int max_cats,
                                      int64_t n_nodes, int64_t node_off, int B, int logspace) {
     const int64_t n = blockIdx.x;
     const int64_t drow = (int64_t)vids[n] * B;
     float* frow = param_flows + (int64_t)s_pfids[n];
+    const int nc = node_cats ? node_cats[n] : max_cats;
     const float* in = node_flows + (node_off + n) * B;
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
         float f = in[b];
         f = logspace ? expf(f) : f;
-        if (f != 0.0f) atomicAdd(frow + pcx_load_cat(data, elsize, drow + b), f);
+        const int c = pcx_load_cat(data, elsize, drow + b);
+        if (f != 0.0f && c >= 0 && c < nc) atomicAdd(frow + c, f);
     }
 }
 
@@ -295,6 +302,7 @@ int pcx_input_cat_fwd(float* node_mars, const float* params, const void* data, i
                       int64_t n_nodes, int64_t node_off, int B, void* stream) {
     if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
     if (n_nodes <= 0 || B <= 0) return 0;
+    if (max_cats <= 0) return -1;
     const int G = node_cats ? stage_group(max_cats) : 0;
     if (G >= 1 && B % 4 == 0 && (reinterpret_cast<uintptr_t>(node_mars) & 15) == 0) {
         dim3 grid((unsigned)pcx_cdiv(n_nodes, G), (unsigned)pcx_cdiv(B, kStageThreads * 4));
@@ -302,7 +310,7 @@ int pcx_input_cat_fwd(float* node_mars, const float* params, const void* data, i
             node_mars, params, data, data_elsize, vids, s_pids, node_cats, max_cats, G, n_nodes, node_off, B);
     } else {
         input_cat_fwd_kernel<<<(unsigned)n_nodes, B >= 256 ? 256 : 128, 0, (cudaStream_t)stream>>>(
-            node_mars, params, data, data_elsize, vids, s_pids, n_nodes, node_off, B);
+            node_mars, params, data, data_elsize, vids, s_pids, node_cats, max_cats, n_nodes, node_off, B);
     }
     PCX_LAUNCH_CHECK();
     return 0;
@@ -313,6 +321,7 @@ int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* d
                       int64_t n_nodes, int64_t node_off, int B, int logspace, void* stream) {
     if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
     if (n_nodes <= 0 || B <= 0) return 0;
+    if (max_cats <= 0) return -1;
     const int G = node_cats ? stage_group(max_cats) : 0;
     if (G >= 1 && B % 4 == 0 && (reinterpret_cast<uintptr_t>(node_flows) & 15) == 0) {
         input_cat_bwd_staged<<<(unsigned)pcx_cdiv(n_nodes, G), kStageThreads, (size_t)G * max_cats * sizeof(float),
@@ -320,7 +329,7 @@ int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* d
             param_flows, node_flows, data, data_elsize, vids, s_pfids, node_cats, max_cats, G, n_nodes, node_off, B, logspace);
     } else {
         input_cat_bwd_kernel<<<(unsigned)n_nodes, B >= 256 ? 256 : 128, 0, (cudaStream_t)stream>>>(
-            param_flows, node_flows, data, data_elsize, vids, s_pfids, n_nodes, node_off, B, logspace);
+            param_flows, node_flows, data, data_elsize, vids, s_pfids, node_cats, max_cats, n_nodes, node_off, B, logspace);
     }
     PCX_LAUNCH_CHECK();
     return 0;

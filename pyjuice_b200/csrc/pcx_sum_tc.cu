@@ -94,9 +94,9 @@ __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
-// Bounded wait until *ctr >= target (acquire): about a second at most.
-__device__ __forceinline__ bool poll_counter(const int* ctr, int target) {
-    for (uint32_t n = 0; n < (1u << 21); ++n) {
+// Bounded wait until *ctr >= target (acquire): about a second at most with the default limit.
+__device__ __forceinline__ bool poll_counter(const int* ctr, int target, uint32_t max_polls = (1u << 21)) {
+    for (uint32_t n = 0; n < max_polls; ++n) {
         int v;
         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
         if (v >= target) return true;
@@ -1105,11 +1105,32 @@ sum_par_tc_batched(const ParJob* __restrict__ jobs, int n_jobs, ParArgs a) {
     par_tile_body<FC>(a, t / j.e_tiles, et, z);
 }
 
+// One warp exercises the give-up branch of the two bounded waits the tensor-core kernels use: it waits, with a small
+// explicit limit, on a counter that nothing advances (which = 0) or on an mbarrier that no copy or MMA ever arrives
+// on (which = 1), records the status code 900 + which and returns normally.
+__device__ int g_probe_counter = 0;
+__global__ void bounded_wait_probe_kernel(int which, uint32_t max_polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x != 0) return;
+    bool ok;
+    if (which == 0) {
+        ok = poll_counter(&g_probe_counter, 1, max_polls);
+    } else {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        ok = mbar_wait(&bar, 0u, max_polls);
+        mbar_inval(&bar);
+    }
+    if (!ok) atomicCAS(&g_tc_status, 0, 900 + which);
+}
+
 // Built-in scratch of the allocation-free forward entry point: room for PCX_NOALLOC_MAX_TILES pre-split parameter
 // tiles.  Every GPU that loads the library reserves it until the process exits.
 __device__ __align__(256) unsigned char g_noalloc_tiles[(size_t)PCX_NOALLOC_MAX_TILES * 2 * A_TILE];
 constexpr int kMaxDevices = 64;
-unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};      // device address of the scratch, per device ordinal
+// Device address of the scratch, per device ordinal.  Written without a lock: two host threads that make the first
+// call on one device at the same time both resolve the same address and store the same value.
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
 
 int g_sum_mode = 1;      // 0: fp32 CUDA cores only, 1: tensor cores with bf16 hi/lo split, 2: tensor cores, single bf16
 
@@ -1252,6 +1273,19 @@ int pcx_get_status(void) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
     return e == cudaSuccess ? v : -(int)e;
+}
+
+int pcx_clear_status(void) {
+    const int v = 0;
+    cudaError_t e = cudaMemcpyToSymbol(g_tc_status, &v, sizeof(int));
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int pcx_probe_bounded_wait(int which, int max_polls, void* stream) {
+    if ((which != 0 && which != 1) || max_polls < 1 || max_polls > (1 << 16)) return -1;
+    bounded_wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(which, (uint32_t)max_polls);
+    PCX_LAUNCH_CHECK();
+    return 0;
 }
 
 int64_t pcx_packed_tile_count(int64_t n_rows, int K, int row_block, int par_block, int mode) {

@@ -226,8 +226,7 @@ class InputLayer(Layer, nn.Module):
             _fill(self.param_flows, 0.0)
         elif flows_memory < 1.0:
             _scale(self.param_flows, flows_memory)
-        if flows_memory == 0.0:
-            self._tied_folded = False
+        self._tied_folded = False
 
     def _require_cuda(self):
         if self.device.type != "cuda":
@@ -252,6 +251,7 @@ class InputLayer(Layer, nn.Module):
             self.init_param_flows()
         data = data.contiguous()
         B = node_flows.size(1)
+        self._tied_folded = False                         # replica accumulators receive new flows
         _lib.call("pcx_input_cat_bwd", self.param_flows, node_flows, data, data.element_size(),
                   self._dev["vids"], self._dev["s_pfids"], self._dev["node_cats"], self.max_cats,
                   self.num_nodes, self._output_ind_range[0], B, int(bool(logspace_flows)))
@@ -262,8 +262,11 @@ class InputLayer(Layer, nn.Module):
         return int(sum(ns.num_nodes * ns.dist.num_param_flows() for ns in self.nodes if not ns.is_tied()))
 
     def fold_tied_flows(self):
-        """Source range := sum of all accumulators of every tied group (layer/input_layer.py:755-783, 1391-1411).
-        Done at most once per update window; `init_param_flows(0)` re-arms it."""
+        """Move the flows of every tied group's replica accumulators into its source range: source += replicas,
+        replicas = 0 (layer/input_layer.py:755-783, 1391-1411 computes the same sum).  Because the replicas are cleared
+        the fold can run any number of times; the flag only saves the pass when no backward pass has run since.
+        (The reference leaves the replicas in place, so that with `flows_memory` in (0, 1) their decayed content is
+        added to the source again at the next update; that double count is not reproduced.)"""
         if getattr(self, "_tied_folded", False):
             return
         for start, n, ch_pfids in self.tied2source_nids:
@@ -333,7 +336,8 @@ class ProdLayer(Layer, nn.Module):
         if self._dev is None:
             raise NotImplementedError("product layers run on CUDA only (no CPU path)")
         B = node_flows.size(1)
-        for u_cids, parids in self._dev["bk"]:
+        raw = getattr(self, "_raw_backward_tables", False) and "bk_raw" in self._dev
+        for u_cids, parids in self._dev["bk_raw" if raw else "bk"]:
             _lib.call("pcx_prod_bwd", node_flows, element_flows, u_cids, parids, u_cids.numel(), parids.size(1),
                       self.block_size, B, int(bool(logspace_flows)))
 

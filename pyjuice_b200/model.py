@@ -69,6 +69,30 @@ class TensorCircuit(nn.Module):
         self._cum_flow_host = 0.0
         self._cum_flow_dev = None
         self._eflow_mode = 1
+        self._reference_compat = False
+
+    @property
+    def reference_compat(self) -> bool:
+        """False (default): flows are the exact gradients.  True: reproduce two behaviours of the reference's kernels
+        that change results beyond rounding.  (1) A product node without a sum parent at its depth (block-sparse sum
+        vectors, e.g. Poon-Domingos circuits) hands down whatever its row of the shared element-flow buffer holds —
+        the flow of a product with the same element id at a depth processed earlier in the pass, or nothing — because
+        the reference clears that buffer once per backward pass only (model/tensorcircuit.py:526-528) while its
+        backward tables skip child blocks without parents (layer/sum_layer.py:273-275).  (2) The tied-flow fusing
+        kernel adds ``param_flows[0:n]`` once per padding slot when a tied sum vector owns a number of flow
+        accumulators that is not a power of two (model/backend/parflow_fusing.py:50, 86-87).  In this mode the backward
+        sweep keeps product layers as kernels of their own (element flows go through the shared buffer)."""
+        return self._reference_compat
+
+    @reference_compat.setter
+    def reference_compat(self, on: bool):
+        self._reference_compat = bool(on)
+        self._graphs = {}
+        self._chain_cache, self._par_job_cache, self._dense_par_cache = {}, {}, {}
+        for group in self.inner_layer_groups:
+            if group.is_prod():
+                for layer in group:
+                    layer._raw_backward_tables = bool(on)
 
     # ------------------------------------------------------------------------------------------
     # construction
@@ -199,6 +223,7 @@ class TensorCircuit(nn.Module):
                 if layer._dev is None:
                     continue
                 bk = []
+                layer._dev["bk_raw"] = list(layer._dev["bk"])          # as compiled (`reference_compat`)
                 for u_cids, parids in layer._dev["bk"]:
                     p = parids.long().cpu()
                     dead = orphan[p.clamp(max=hi - 1)] & (p != 0)
@@ -445,12 +470,15 @@ class TensorCircuit(nn.Module):
             return False
         if self._fused[gi]["sm"] and not SumLayer.use_sample_major:
             return False
+        if backward and self._reference_compat:
+            return False
         return (not backward) or self.node_mars.size(1) % 8 == 0
 
     def _launch_cfg(self):
         """Everything that changes which kernels a pass launches (part of the key of a captured graph)."""
         return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
-                SumLayer.use_dense_kernels, SumLayer.use_sample_major, getattr(self._packer, "grown", 0))
+                SumLayer.use_dense_kernels, SumLayer.use_sample_major, getattr(self._packer, "grown", 0),
+                self._reference_compat)
 
     def _chain_plan(self, B: int, mode: int):
         """Job table of the dataflow launch (one launch for a run of consecutive depths) for the forward pass
@@ -744,13 +772,16 @@ class TensorCircuit(nn.Module):
             self._ensure_buffers(B, backward=True)
             ls = int(bool(logspace_flows))
             reset = NEG_INF if logspace_flows else 0.0
-            ranges = self._flow_reset_ranges if (self.fuse_product_layers and _lib.SUM_MODE != 0 and B % 8 == 0) else None
+            ranges = self._flow_reset_ranges if (self.fuse_product_layers and _lib.SUM_MODE != 0 and B % 8 == 0
+                                                 and not self._reference_compat) else None
             if ranges is None:
                 _fill(self.node_flows, reset)
             else:                                            # every other row is rewritten by a direct store
                 for a0, a1 in ranges:
                     _fill(self.node_flows[a0:a1], reset)
-            if self._eflow_mode != ls:           # dummy / parentless element rows: -inf in log space, 0 linearly
+            if self._eflow_mode != ls or self._reference_compat:
+                # dummy / parentless element rows: -inf in log space, 0 linearly (`reference_compat`: the buffer is
+                # cleared once per pass, as the reference does, and rows without a writer keep an earlier depth's flow)
                 _fill(self.element_flows, NEG_INF if logspace_flows else 0.0)
                 self._eflow_mode = ls
 
@@ -828,8 +859,14 @@ class TensorCircuit(nn.Module):
     def _start_early_flow_sync(self):
         """First part of the overlapped all-reduce: the input-layer flows, as soon as the input layer's backward pass
         is enqueued."""
-        if not self._overlap_ready() or getattr(self, "_early_sync", None) is not None:
+        if not self._overlap_ready():
             return
+        if getattr(self, "_early_sync", None) is not None:
+            # the input-layer flows of the previous pass are already summed over the ranks; this pass has just added
+            # local flows on top of them, and no later collective can separate the two
+            raise RuntimeError("two backward passes that compute parameter flows ran without an optimizer step in "
+                               "between while the overlapped flow synchronisation is on (MiniBatchEM(ddp=True), one "
+                               "mini-batch per update); use `niters_per_update` to accumulate over several batches")
         self._finish_late_sync()
         arena = self._flow_arena
         self._early_sync = arena.all_reduce_range_async(arena.offsets[1], self._input_reduce_end(),
@@ -856,6 +893,7 @@ class TensorCircuit(nn.Module):
         if self._cum_flow_dev is not None:
             self._cum_flow_host += float(self._cum_flow_dev.item())
             self._cum_flow_dev = None
+            _lib.check_status(self.device)                  # the host has just synchronised: a cheap place to look
         return self._cum_flow_host
 
     @_cum_flow.setter
@@ -884,9 +922,6 @@ class TensorCircuit(nn.Module):
             _fill(self._flow_arena.buf, 0.0)
         elif flows_memory != 1.0:
             _scale(self._flow_arena.buf, flows_memory)
-        if flows_memory == 0.0:
-            for layer in self.input_layer_group:
-                layer._tied_folded = False
         # The running flow total decays with the flows it normalises.  (The reference only clears it when the
         # rescaled EM update consumes it, model/tensorcircuit.py:1363-1374, so that under data parallelism, where every
         # synchronisation replaces it by the sum over ranks, it doubles per step; here it stays the total of the
@@ -909,8 +944,15 @@ class TensorCircuit(nn.Module):
         self._require_cuda()
         with torch.no_grad():
             def sum_update():
+                head = self.param_flows[:2048].clone() if (self._reference_compat and self._fusing_dev) else None
                 for start, n, chs in self._fusing_dev:
                     _lib.call("pcx_tied_accum", self.param_flows, start, n, chs, int(chs.numel()))
+                if head is not None:
+                    for tgt, sizes, ch, G, M in self.parflow_fusing_kwargs:
+                        pads = ((ch == 0).sum(dim=1) - (ch[:, 0] == 0).long()).tolist()
+                        for t, n, pad in zip(tgt.tolist(), sizes.tolist(), pads):
+                            if pad > 0:
+                                self.param_flows[t:t + n].add_(head[:n], alpha=float(pad))
                 e = self._em_dev
                 _lib.call("pcx_em_sum", self.params.data, self.param_flows, e["par"], e["flow"], e["fan"], e["bs"],
                           int(e["par"].numel()), e["max_bs"], float(step_size), float(pseudocount),
@@ -1005,6 +1047,8 @@ class TensorCircuit(nn.Module):
     # accessors
     # ------------------------------------------------------------------------------------------
     def update_parameters(self, clone: bool = True):
+        if self.device.type == "cuda":
+            _lib.check_status(self.device)                  # parameters computed after a timed-out wait are wrong
         params = self.params.detach().cpu()
         for ns in self.root_ns:
             if ns.is_sum() and not ns.is_tied():

@@ -217,6 +217,13 @@ def pd_small(api):
     return api.pd((8, 8), 32, 16, split_points=[pts, pts], block_size=8), dict()
 
 
+def pd_parentless(api):
+    """Poon-Domingos over an 8x8 grid, 2 node blocks of 8 per region: block-sparse sum vectors leave some product
+    blocks without any sum parent (the case in which the reference's backward pass hands stale element flows down)."""
+    _seed(0)
+    return api.pd((8, 8), 16, 4, split_points=[[2, 4, 6], [2, 4, 6]], block_size=8), dict()
+
+
 def rat_small(api):
     _seed(3)
     return api.rat_spn(8, num_vars=24, num_latents=16, depth=3, num_repetitions=4, block_size=8), dict()
@@ -237,8 +244,20 @@ CASES = {
     "hclt_b128": hclt_b128,
     "hmm_b128": hmm_b128,
     "pd_small": pd_small,
+    "pd_parentless": pd_parentless,
     "rat_small": rat_small,
 }
+
+
+def data_for(pc, B, seed=0):
+    """Seeded categorical inputs ``[B, num_vars]`` (int64) within every variable's category count; works on a circuit
+    compiled by this package or by the reference (both expose ``vids``, ``metadata`` and ``s_mids``)."""
+    g = torch.Generator().manual_seed(seed)
+    cats = torch.zeros(pc.num_vars, dtype=torch.long)
+    for layer in pc.input_layer_group:
+        node_cats = layer.metadata.cpu()[layer.s_mids.cpu()].long()
+        cats[layer.vids[:, 0].cpu()] = node_cats
+    return (torch.rand(B, pc.num_vars, generator=g) * cats[None, :].clamp(min=1)).long()
 
 
 def dump_tables(pc) -> dict:

@@ -58,3 +58,61 @@ def check_against_oracle(pc, x, step=0.1, pseudo=0.1, logspace_flows=True, rtol=
         assert ok, f"post-EM input parameters rel err {out['input_params']}"
     torch.cuda.synchronize()
     return out
+
+
+def fold_tied_flows_(pc, param_flows, input_param_flows):
+    """In place on oracle-side accumulators: every tied group's source range += its replica accumulators, replicas = 0
+    (what `pcx_tied_accum` does on the device before an EM update)."""
+    for start, n, accs in pc._tied_sum_groups:
+        tot = sum(param_flows[a:a + n].clone() for a in accs)
+        for a in accs:
+            param_flows[a:a + n] = 0.0
+        param_flows[start:start + n] = tot
+    for layer, pf in zip(pc.input_layer_group, input_param_flows):
+        for start, n, ch in layer.tied2source_nids:
+            start, n = int(start), int(n)
+            tot = sum(pf[int(c):int(c) + n].clone() for c in ch)
+            for c in ch:
+                pf[int(c):int(c) + n] = 0.0
+            pf[start:start + n] = tot
+
+
+class OracleTrainer:
+    """CPU-side mirror of a training loop: parameters and accumulated flows carried from step to step."""
+
+    def __init__(self, pc):
+        self.pc = pc
+        self.params = pc.params.data.detach().cpu().double().clone()
+        self.iparams = [l.params.data.detach().cpu().double().clone() for l in pc.input_layer_group]
+        self.pf = torch.zeros(pc.num_param_flows, dtype=torch.float64)
+        self.ipf = [torch.zeros(l.num_param_flows, dtype=torch.float64) for l in pc.input_layer_group]
+
+    def accumulate(self, x, flows_memory=1.0):
+        """One forward + backward pass: flows *= flows_memory, then += the flows of ``x``.  Returns the LLs."""
+        self.pf *= flows_memory
+        for f in self.ipf:
+            f *= flows_memory
+        lls, st = orc.forward(self.pc, x.cpu(), self.params, self.iparams)
+        orc.backward(self.pc, x.cpu(), self.params, self.iparams, st, param_flows=self.pf, input_param_flows=self.ipf)
+        self.pf, self.ipf = st.param_flows, st.input_param_flows
+        self._st = st
+        return lls
+
+    def update(self, step_size, pseudocount, zero_flows=True):
+        fold_tied_flows_(self.pc, self.pf, self.ipf)
+        self._st.param_flows, self._st.input_param_flows = self.pf, self.ipf
+        self.params, self.iparams = orc.em_update(self.pc, self.params, self.iparams, self._st, step_size, pseudocount)
+        if zero_flows:
+            self.pf.zero_()
+            for f in self.ipf:
+                f.zero_()
+
+    def check_params(self, pc, rtol=REL_TOL):
+        ok, err = rel_close(pc.params.data[pc.num_dummy_params:], self.params[pc.num_dummy_params:], rtol)
+        assert ok, f"sum parameters rel err {err}"
+        worst = err
+        for layer, ref in zip(pc.input_layer_group, self.iparams):
+            ok, err = rel_close(layer.params.data, ref, rtol)
+            assert ok, f"input parameters rel err {err}"
+            worst = max(worst, err)
+        return worst
