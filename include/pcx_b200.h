@@ -188,6 +188,40 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
                            const int32_t* cids, const int32_t* pids, const int32_t* pfids, int64_t n_blocks, int K,
                            int block_size, int n_chunks_total, void* stream);
 
+/* ---- Dense layers, wide tiles ----------------------------------------------------------------------------------
+ * Same contractions as the four entry points above with output tiles of 128 rows x up to 256 samples (a parameter
+ * tile is fetched once per layer and pass) and the contraction split over several CTAs per tile; preferred whenever
+ * B is a multiple of 8 and the operand has at most 6144 rows.  The product layer can be folded in: with `fkids`
+ * ([table rows * K][fc] for the forward pass, [child rows][fc] for the element flows; fc = 2, 4 or 8 child rows of
+ * every product, 0 = none) a product's value is gathered from node_mars and element_mars / element_flows are not
+ * used; with `direct` (every child row has exactly one parent product) an element's flow is stored straight into its
+ * children's rows of node_flows.  `scratch`: pcx_dense2_scratch_bytes(n_groups, depth, B, row tiles) bytes, 256-byte
+ * aligned; `counters`: one int32 per (row tile, column tile), zero before the first call (the kernels leave them zero).
+ * Replace, like the entry points above: SumLayer._forward_block_sparse / _backward_block_sparse_ele_flows /
+ * _backward_block_sparse_par_flows (layer/sum_layer.py:551-929, 1369-1719, 1721-2080), with ProdLayer.forward /
+ * backward folded in (layer/prod_layer.py:161-238). */
+int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B, int64_t n_row_tiles);
+int pcx_sum_fwd_dense2(float* node_mars, const float* element_mars, const void* packed, const int32_t* nids,
+                       const int32_t* cids, const int32_t* fkids, int fc, const int32_t* row_group,
+                       const int32_t* group_row, int n_groups, void* scratch, int64_t scratch_bytes, int32_t* counters,
+                       int64_t n_blocks, int K, int block_size, int B, void* stream);
+int pcx_sum_bwd_ele_dense2(float* element_flows, const float* element_mars, float* node_flows, const float* node_mars,
+                           const void* packed, const int32_t* chids, const int32_t* parids, const int32_t* fkids,
+                           int fc, int direct, const int32_t* row_group, const int32_t* group_row, int n_groups,
+                           void* scratch, int64_t scratch_bytes, int32_t* counters, int64_t n_blocks, int P,
+                           int block_size, int ch_block_size, int B, int logspace, void* stream);
+/* Parameter flows: step 1 writes the operands of one layer at sample positions [slot * B, (slot + 1) * B) of the
+ * concatenated batch (x_tiles: [row tiles][n_chunks_total] tiles of 32 KB; y_tiles: [ceil(K / 256)][n_chunks_total]
+ * tiles of 64 KB; both zero-filled once by the caller; n_chunks_total = ceil(layers * B / 64)); `cids_row` / `fkids_row`
+ * are the children of table row 0 (every row lists the same).  Step 2 is one product per group of tied layers. */
+int pcx_sum_par_dense2_stage(void* x_tiles, void* y_tiles, const float* node_flows, const float* node_mars,
+                             const float* element_mars, const int32_t* nids, const int32_t* cids_row,
+                             const int32_t* fkids_row, int fc, int64_t n_blocks, int K, int block_size, int B,
+                             int n_chunks_total, int slot, int logspace, void* stream);
+int pcx_sum_par_dense2_gemm(float* param_flows, const float* params, const void* x_tiles, const void* y_tiles,
+                            const int32_t* cids, const int32_t* pids, const int32_t* pfids, int64_t n_blocks, int K,
+                            int block_size, int n_chunks_total, void* stream);
+
 /* ---- Small node blocks (32 or 64 nodes) on the tensor cores: sample-major tiles -----------------------------------
  * A tile is 128 samples x nb nodes (nb = 32 or 64): one node block, or two consecutive 32-node blocks whose table rows
  * are identical and whose node ids are consecutive ("merged row"; first_row[m] = its first table row).  The batch is

@@ -1,0 +1,724 @@
+// Dense sum layers, wide tiles: the second generation of the two-step dense path (pcx_sum_dense.cuh).
+//
+// What changed and why.  The first version multiplied 128 x 64 tiles: every 32 KB parameter tile was fetched once
+// per 64 samples, so a 4096 x 4096 layer at 256 samples moved 400 MB from L2 to the SMs per pass and ran at the
+// per-SM copy rate, not at the tensor-core rate.  Here an output tile is 128 rows x up to 256 samples (all samples
+// of a rank for the usual batch sizes), so a parameter tile is fetched ONCE per layer and pass; the machine is
+// filled by splitting the contraction over several CTAs per tile instead (split-K), whose partial tiles meet in
+// an fp32 scratch buffer: the CTA that arrives last (a counter per tile, no waiting) adds them in a fixed order and
+// runs the epilogue, so results do not depend on the arrival order.
+//
+//   operand pre-pass   ONE kernel per layer and pass: a CTA owns 8 samples and ALL operand rows; it gathers the
+//                      log-domain values (the product layer is folded in: a product's value is the sum of its
+//                      children's rows), keeps them in shared memory, reduces the per-sample maximum, and writes
+//                      exp(value - max) as bf16 hi / lo operand tiles.  No element_mars, no separate maximum pass.
+//   GEMM               warp 0 streams 32-deep operand slices with bulk copies into a ring of 4-8 stages, one thread
+//                      of warp 1 issues three tcgen05.mma per 16-deep step (hi x hi, hi x lo, lo x hi; N = 64, 128
+//                      or 256) into a TMEM accumulator, warps 2-5 finish: log + shift (forward), + element value and
+//                      a direct store into the children's flow rows (element flows, product backward folded in),
+//                      or parameter * sum -> atomic add (parameter flows).
+//   parameter flows    as before ONE product per group of layers that share parameters, contraction over the
+//                      concatenated batches; its operands (X = exp(flow - value - shift) and Y = exp(child value
+//                      + shift)) are staged per layer by one kernel; samples of consecutive layers are packed
+//                      back to back, so small per-rank batches (data parallelism) do not pad the contraction.
+//
+// B operand tile of (group g, column tile jt, chunk c): [8 K-groups][DN samples][8 x bf16] hi, then the same for lo
+// (2 * DN * 128 bytes).  A tiles are the pre-split parameter tiles of pcx_pack_sum_params (unchanged).
+//
+// This file is included by pcx_sum_tc.cu after pcx_sum_dense.cuh and uses their helpers and the status word.
+#pragma once
+
+namespace {
+
+constexpr int W_STEP = 32;                          // contraction depth per pipeline stage
+constexpr int W_A_HALF = (W_STEP / 8) * BM * 16;    // 8 KB: hi (or lo) part of the A operand of one stage
+constexpr int W_THREADS = 192;                      // warp 0 copies, warp 1 multiplies, warps 2-5 finish
+constexpr int W_PREP_THREADS = 512;
+constexpr int W_PREP_SAMPLES = 8;                   // samples per pre-pass CTA (one 32-byte sector per row)
+constexpr int W_MAX_DEPTH = 6144;                   // operand rows the pre-pass can hold in shared memory
+
+template <int DN>
+struct WideCfg {
+    static constexpr int B_HALF = (W_STEP / 8) * DN * 16;               // hi (or lo) part of the B operand of one stage
+    static constexpr int STAGE = 2 * W_A_HALF + 2 * B_HALF;            // DN = 256: 48 KB, 128: 32 KB, 64: 24 KB
+    static constexpr int STAGES = (DN == 256) ? 4 : ((DN == 128) ? 6 : 8);
+    static constexpr int SMEM = STAGES * STAGE + 1024;
+    static constexpr int B_TILE = 2 * 8 * DN * 16;                     // one 64-deep operand tile, hi then lo
+};
+
+enum WideEpi { W_FWD = 0, W_ELE = 1, W_PAR = 2 };
+
+struct WideArgs {
+    const uint8_t* a_tiles;     // A tile of (row tile mt, chunk c) at a_tiles + (mt * n_chunks + c) * 32 KB
+    const uint8_t* b_tiles;     // B tile of (operand row r, chunk c) at b_tiles + (r * n_chunks + c) * B_TILE
+    const int32_t* b_group;     // FWD / ELE: group of every table row (rows of a group share their operand)
+    int n_chunks;               // 64-deep chunks of the whole contraction
+    int splits;                 // CTAs per output tile along the contraction (divides n_chunks)
+    int n_ct;                   // FWD / ELE: column tiles per group
+    int row_block;              // rows per table row (multiple of 128)
+    int B;
+    int logspace;
+    int terms;
+    const int32_t* rows;        // FWD: nids   ELE: chids
+    float* out;                 // FWD: node_mars   ELE: element_flows (unless direct)   PAR: param_flows
+    const float* shift;         // FWD / ELE: [n_groups, B] per-sample shifts
+    const float* emars;         // ELE, products not folded: element_mars
+    const float* nmars;         // ELE, products folded: node_mars (an element's value = sum of its children's rows)
+    float* nflows;              // ELE, direct: node_flows (an element's flow is stored into its children's rows)
+    const int32_t* fkids;       // ELE, folded: [n_rows * row_block][fc] child rows of every element (0 = none)
+    int fc;
+    int direct;
+    float* partial;             // split-K: [tile][split][128][DN] fp32
+    int* counters;              // split-K: one per tile, zero between launches
+    const float* params;        // PAR
+    const int32_t* cids;        // PAR: [n_rows, K]
+    const int32_t* pids;        // PAR
+    const int32_t* pfids;       // PAR
+    int K;                      // PAR: table width
+};
+
+__device__ __forceinline__ void bar_sync_epilogue() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Epilogue of one row and 32 consecutive columns.
+template <int EPI, int DN>
+__device__ __forceinline__ void wide_finish(const WideArgs& a, int64_t i, int r0, int row, int nt, int cb, const float* v) {
+    if (EPI == W_PAR) {
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) {
+            const int e = nt * DN + cb + j;
+            if (e >= a.K) break;
+            if (a.cids[i * a.K + e] == 0) continue;
+            const float pf = a.params[(int64_t)a.pids[i * a.K + e] + r0 + row] * v[j];
+            if (pf != 0.0f) atomicAdd(a.out + (int64_t)a.pfids[i * a.K + e] + r0 + row, pf);
+        }
+        return;
+    }
+    const int b0 = nt * DN + cb;
+    if (b0 >= a.B) return;
+    const float* sh = a.shift + (int64_t)a.b_group[i] * a.B + b0;
+    const int64_t erow = i * a.row_block + r0 + row;                 // index of this output row in its table
+    const int64_t orow = ((int64_t)a.rows[i] + r0 + row) * a.B + b0;
+    int fk[8];
+    if (EPI == W_ELE && a.fkids != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) fk[q] = (q < a.fc) ? a.fkids[erow * a.fc + q] : 0;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        if (b0 + j >= a.B) break;                                    // B is a multiple of 4
+        const float4 m4 = *reinterpret_cast<const float4*>(sh + j);
+        const float m[4] = {m4.x, m4.y, m4.z, m4.w};
+        float o[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float x = v[j + t];
+            if (EPI == W_FWD) o[t] = (m[t] == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(x, 1e-24f)) + m[t];
+            else o[t] = (m[t] == PCX_NEG_INF || x <= 0.0f) ? PCX_NEG_INF : __logf(x) + m[t];
+        }
+        if (EPI == W_FWD) {
+            *reinterpret_cast<float4*>(a.out + orow + j) = make_float4(o[0], o[1], o[2], o[3]);
+            continue;
+        }
+        float em[4];
+        if (a.fkids != nullptr) {                                    // element value = sum of the children's rows
+            bool any = false;
+            em[0] = em[1] = em[2] = em[3] = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (q < a.fc && fk[q] != 0) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(a.nmars + (int64_t)fk[q] * a.B + b0 + j);
+                    em[0] += c4.x; em[1] += c4.y; em[2] += c4.z; em[3] += c4.w;
+                    any = true;
+                }
+            }
+            if (!any) em[0] = em[1] = em[2] = em[3] = PCX_NEG_INF;
+        } else {
+            const float4 e4 = *reinterpret_cast<const float4*>(a.emars + orow + j);
+            em[0] = e4.x; em[1] = e4.y; em[2] = e4.z; em[3] = e4.w;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            o[t] = (o[t] == PCX_NEG_INF || em[t] == PCX_NEG_INF) ? PCX_NEG_INF : o[t] + em[t];
+            if (!a.logspace) o[t] = __expf(o[t]);
+        }
+        const float4 o4 = make_float4(o[0], o[1], o[2], o[3]);
+        if (a.fkids != nullptr && a.direct) {                         // every child has this one parent: plain stores
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < a.fc && fk[q] != 0) *reinterpret_cast<float4*>(a.nflows + (int64_t)fk[q] * a.B + b0 + j) = o4;
+        } else {
+            *reinterpret_cast<float4*>(a.out + orow + j) = o4;
+        }
+    }
+}
+
+template <int EPI, int DN>
+__global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs a) {
+    using C = WideCfg<DN>;
+    constexpr int ACCS = (EPI == W_PAR) ? 2 : 1;         // the long contraction of the parameter flows alternates two
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t s_full[C::STAGES], s_empty[C::STAGES], s_done;
+    __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_fail;
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t mt = blockIdx.x;                  // 128-row tile
+    const int nt = blockIdx.y;                      // FWD / ELE: sample tile      PAR: edge tile
+    const int split = blockIdx.z;
+    const int tiles_r = a.row_block / BM;
+    const int64_t i = mt / tiles_r;
+    const int r0 = (int)(mt % tiles_r) * BM;
+    const int chunks_here = a.n_chunks / a.splits;
+    const int c_begin = split * chunks_here;
+    const int n_steps = chunks_here * (KC / W_STEP);
+
+    if (tid == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+        mbar_init(&s_done, 1);
+        fence_mbar_init();
+        s_fail = 0;
+        s_last = 0;
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, (ACCS * DN < 32) ? 32 : ACCS * DN);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+
+    const int64_t b_row = (EPI == W_PAR) ? (int64_t)nt : (int64_t)a.b_group[i] * a.n_ct + nt;
+    const uint8_t* a_src = a.a_tiles + ((size_t)mt * a.n_chunks + c_begin) * (2 * A_TILE);
+    const uint8_t* b_src = a.b_tiles + ((size_t)b_row * a.n_chunks + c_begin) * C::B_TILE;
+
+    if (warp == 0) {
+        // ---- copy warp: lane 0 waits for the stage and arms its barrier, four lanes move one piece each -------------
+        int armed = 0;
+        for (int t = 0; t < n_steps; ++t) {
+            const int s = t % C::STAGES;
+            int stop = 0;
+            if (lane == 0) {
+                if (t >= C::STAGES && !mbar_wait(&s_empty[s], (uint32_t)((t / C::STAGES - 1) & 1))) s_fail = 1;
+                stop = s_fail;
+                if (!stop) mbar_expect_tx(&s_full[s], C::STAGE);
+            }
+            stop = __shfl_sync(0xffffffffu, stop, 0);
+            if (stop) break;
+            const int c = t / (KC / W_STEP), h = t % (KC / W_STEP);
+            uint8_t* dst = smem + s * C::STAGE;
+            if (lane == 0) bulk_copy_g2s(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s]);
+            if (lane == 1) bulk_copy_g2s(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s]);
+            if (lane == 2) bulk_copy_g2s(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s]);
+            if (lane == 3) bulk_copy_g2s(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s]);
+            armed = t + 1;
+        }
+        if (lane == 0 && s_fail) {
+            // let the copies that are still in flight land before this CTA's shared memory goes away
+            for (int t = max(0, armed - C::STAGES); t < armed; ++t)
+                mbar_wait(&s_full[t % C::STAGES], (uint32_t)((t / C::STAGES) & 1), 1u << 16);
+        }
+    } else if (warp == 1) {
+        // ---- multiply thread ----------------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = idesc_bf16_f32(BM, DN);
+            for (int t = 0; t < n_steps; ++t) {
+                const int s = t % C::STAGES;
+                if (!mbar_wait(&s_full[s], (uint32_t)((t / C::STAGES) & 1))) { s_fail = 2; break; }
+                if (s_fail) break;
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(smem + s * C::STAGE), sb = sa + 2 * W_A_HALF;
+                const uint32_t acc = tmem + (uint32_t)((t % ACCS) * DN);
+#pragma unroll
+                for (int ks = 0; ks < W_STEP / 16; ++ks) {
+                    const uint64_t dAh = smem_desc(sa + ks * 2 * (BM * 16), BM * 16, 128);
+                    const uint64_t dAl = smem_desc(sa + W_A_HALF + ks * 2 * (BM * 16), BM * 16, 128);
+                    const uint64_t dBh = smem_desc(sb + ks * 2 * (DN * 16), DN * 16, 128);
+                    const uint64_t dBl = smem_desc(sb + C::B_HALF + ks * 2 * (DN * 16), DN * 16, 128);
+                    mma_bf16_ss(acc, dAh, dBh, idesc, (t >= ACCS || ks > 0) ? 1u : 0u);
+                    if (a.terms == 3) {
+                        mma_bf16_ss(acc, dAh, dBl, idesc, 1u);
+                        mma_bf16_ss(acc, dAl, dBh, idesc, 1u);
+                    }
+                }
+                mma_commit(&s_empty[s]);            // the stage is free once these products have read it
+            }
+            mma_commit(&s_done);
+        }
+    } else {
+        // ---- epilogue warps: TMEM lane quarter warp % 4, one output row per thread --------------------------
+        const int lq = warp & 3;
+        const int row = lq * 32 + lane;
+        bool ok = mbar_wait(&s_done, 0u, 1u << 24);
+        if (!ok) s_fail = 3;
+        ok = ok && (s_fail == 0);
+        tc_fence_after_sync();
+        const uint32_t tbase = tmem + ((uint32_t)(lq * 32) << 16);
+        const int used = n_steps < ACCS ? n_steps : ACCS;
+        if (a.splits == 1) {
+            if (ok) {
+#pragma unroll 1
+                for (int cb = 0; cb < DN; cb += 32) {
+                    float v[32];
+                    tmem_ld<32>(tbase + (uint32_t)cb, v);
+                    if (ACCS == 2 && used == 2) {
+                        float u[32];
+                        tmem_ld<32>(tbase + (uint32_t)(DN + cb), u);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] += u[j];
+                    }
+                    wide_finish<EPI, DN>(a, i, r0, row, nt, cb, v);
+                }
+            }
+        } else {
+            // split contraction: park this CTA's partial tile, count, and let the last arrival add them up
+            const int64_t tile = (int64_t)blockIdx.x * gridDim.y + blockIdx.y;
+            float* mine = a.partial + ((tile * a.splits + split) * BM + row) * DN;
+#pragma unroll 1
+            for (int cb = 0; cb < DN; cb += 32) {
+                float v[32];
+                if (ok) tmem_ld<32>(tbase + (uint32_t)cb, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    __stcg(reinterpret_cast<float4*>(mine + cb + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            }
+            __threadfence();
+            bar_sync_epilogue();
+            if (tid == 64) {
+                const int before = atomicAdd(a.counters + tile, 1);
+                s_last = (before == a.splits - 1) ? 1 : 0;
+                if (s_last) a.counters[tile] = 0;            // ready for the next launch
+            }
+            bar_sync_epilogue();
+            if (s_last) {
+                __threadfence();
+                const float* base = a.partial + (tile * a.splits * BM + row) * DN;
+#pragma unroll 1
+                for (int cb = 0; cb < DN; cb += 32) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                    for (int q = 0; q < a.splits; ++q) {          // fixed order: the sum does not depend on who is last
+                        const float* src = base + (size_t)q * BM * DN + cb;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 p = __ldcg(reinterpret_cast<const float4*>(src + j));
+                            v[j] += p.x; v[j + 1] += p.y; v[j + 2] += p.z; v[j + 3] += p.w;
+                        }
+                    }
+                    wide_finish<EPI, DN>(a, i, r0, row, nt, cb, v);
+                }
+            }
+        }
+        tc_fence_before_sync();
+    }
+    __syncthreads();
+    if (tid == 0 && s_fail != 0) atomicCAS(&g_tc_status, 0, 600 + 10 * EPI + s_fail);
+    if (warp == 0) tmem_dealloc(tmem, (ACCS * DN < 32) ? 32 : ACCS * DN);
+}
+
+// ---- operand pre-passes --------------------------------------------------------------------------------------
+struct WidePrepArgs {
+    const float* src;           // FWD: element_mars, or node_mars when products are folded     ELE / PAR: node_flows
+    const float* src2;          // ELE / PAR: node_mars
+    const int32_t* kids;        // FWD: cids [n, K]   ELE: parids [n, P]   PAR: nids [n]
+    const int32_t* fkids;       // FWD folded: [n * K][fc] child rows of every listed element
+    const int32_t* group_row;   // [n_groups] a table row that stands for the group (PAR: unused)
+    int fc;
+    int K;                      // table width (FWD: children, ELE: parent blocks, PAR: 1)
+    int par_block;              // ELE: parent block size   PAR: block size   FWD: 1
+    int depth;                  // operand rows per group
+    int depth_pad;              // rounded up to whole 64-deep chunks
+    int B;
+    int logspace;
+    int mode;                   // 0 FWD, 1 ELE, 2 PAR
+    int DN, n_ct, n_chunks;     // FWD / ELE tile geometry
+    uint8_t* tiles;             // FWD / ELE: operand tiles     PAR: X tiles
+    float* shift;               // FWD / ELE: [n_groups, B]
+    // PAR only
+    uint8_t* y_tiles;
+    const float* emars;         // products not folded
+    const int32_t* cids_row;    // [Kfw] children of the layer's rows (every row lists the same)
+    const int32_t* fk_row;      // folded: [Kfw][fc]
+    int Kfw;
+    int n_chunks_total, slot;
+};
+
+// Eight consecutive samples of operand row k, in the log domain.
+template <int FC>
+__device__ __forceinline__ void wide_prep_value(const WidePrepArgs& a, int g, int k, int b0, float* v) {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) v[s] = PCX_NEG_INF;
+    if (k >= a.depth) return;
+    if (a.mode == 0) {
+        const int64_t at = (int64_t)a.group_row[g] * a.K + k;
+        if (FC == 0) {
+            const int cid = a.kids[at];
+            if (cid == 0) return;
+            const float4 p = *reinterpret_cast<const float4*>(a.src + (int64_t)cid * a.B + b0);
+            const float4 q = *reinterpret_cast<const float4*>(a.src + (int64_t)cid * a.B + b0 + 4);
+            v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
+            return;
+        }
+        int fk[FC > 0 ? FC : 1];
+        bool any = false;
+#pragma unroll
+        for (int j = 0; j < FC; ++j) { fk[j] = a.fkids[at * FC + j]; any = any || fk[j] != 0; }
+        if (!any) return;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < FC; ++j) {                               // row 0 exists and holds zeros: load it regardless
+            const float4 p = *reinterpret_cast<const float4*>(a.src + (int64_t)fk[j] * a.B + b0);
+            const float4 q = *reinterpret_cast<const float4*>(a.src + (int64_t)fk[j] * a.B + b0 + 4);
+            const float w = fk[j] != 0 ? 1.0f : 0.0f;
+            acc[0] += w * p.x; acc[1] += w * p.y; acc[2] += w * p.z; acc[3] += w * p.w;
+            acc[4] += w * q.x; acc[5] += w * q.y; acc[6] += w * q.z; acc[7] += w * q.w;
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) v[s] = acc[s];
+        return;
+    }
+    int64_t r;
+    if (a.mode == 1) {
+        const int pr = a.kids[(int64_t)a.group_row[g] * a.K + k / a.par_block];
+        if (pr == 0) return;
+        r = (int64_t)pr + k % a.par_block;
+    } else {
+        r = (int64_t)a.kids[k / a.par_block] + k % a.par_block;
+    }
+    const float4 f0 = *reinterpret_cast<const float4*>(a.src + r * a.B + b0);
+    const float4 f1 = *reinterpret_cast<const float4*>(a.src + r * a.B + b0 + 4);
+    const float4 m0 = *reinterpret_cast<const float4*>(a.src2 + r * a.B + b0);
+    const float4 m1 = *reinterpret_cast<const float4*>(a.src2 + r * a.B + b0 + 4);
+    const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+    const float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        float x = f[s];
+        if (!a.logspace) x = (x > 0.0f) ? __logf(x) : PCX_NEG_INF;
+        v[s] = (m[s] == PCX_NEG_INF || x == PCX_NEG_INF) ? PCX_NEG_INF : x - m[s];
+    }
+}
+
+// Shared-memory staging of the log-domain values of all operand rows for the CTA's eight samples, and the per-sample
+// maximum: returns it in sh[0..8) to every thread.  s_val is [8][ld] floats, ld = depth_pad + 4.
+template <int FC>
+__device__ __forceinline__ void wide_prep_stage(const WidePrepArgs& a, int g, int b0, float* s_val, int ld, float* s_red, float* sh) {
+    const int tid = threadIdx.x;
+    float mx[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) mx[s] = PCX_NEG_INF;
+#pragma unroll 2
+    for (int k = tid; k < a.depth_pad; k += W_PREP_THREADS) {
+        float v[8];
+        wide_prep_value<FC>(a, g, k, b0, v);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) { s_val[s * ld + k] = v[s]; mx[s] = fmaxf(mx[s], v[s]); }
+    }
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx[s] = fmaxf(mx[s], __shfl_xor_sync(0xffffffffu, mx[s], o));
+    if ((tid & 31) == 0) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) s_red[(tid >> 5) * 8 + s] = mx[s];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        float m = PCX_NEG_INF;
+#pragma unroll
+        for (int w = 0; w < W_PREP_THREADS / 32; ++w) m = fmaxf(m, s_red[w * 8 + s]);
+        sh[s] = m;
+    }
+}
+
+// FWD / ELE operand tiles (contraction over operand rows).  Grid (ceil(B / 8), n_groups), 512 threads.
+template <int FC>
+__global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_rows_kernel(const WidePrepArgs a) {
+    extern __shared__ float s_dyn[];
+    __shared__ float s_red[(W_PREP_THREADS / 32) * 8];
+    const int tid = threadIdx.x, g = blockIdx.y;
+    const int b0 = blockIdx.x * W_PREP_SAMPLES;                      // B is a multiple of 8
+    const int ld = a.depth_pad + 4;
+    float sh[8];
+    wide_prep_stage<FC>(a, g, b0, s_dyn, ld, s_red, sh);
+    if (tid < 8) a.shift[(int64_t)g * a.B + b0 + tid] = sh[tid];
+
+    const int tile_bytes = 2 * 8 * a.DN * 16;
+    const int items = a.depth_pad;                                   // (depth_pad / 8) K-groups x 8 samples
+    for (int it = tid; it < items; it += W_PREP_THREADS) {
+        const int s = it & 7, kg = it >> 3;
+        const float4 p = *reinterpret_cast<const float4*>(s_dyn + s * ld + kg * 8);
+        const float4 q = *reinterpret_cast<const float4*>(s_dyn + s * ld + kg * 8 + 4);
+        const float x[8] = {p.x, p.y, p.z, p.w, q.x, q.y, q.z, q.w};
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (x[j] == PCX_NEG_INF || sh[s] == PCX_NEG_INF) ? 0.0f : __expf(x[j] - sh[s]);
+        const int b = b0 + s;
+        const int jt = b / a.DN, bl = b % a.DN;
+        uint8_t* tile = a.tiles + (((size_t)g * a.n_ct + jt) * a.n_chunks + (kg >> 3)) * tile_bytes;
+        uint8_t* dst = tile + (size_t)(kg & 7) * (a.DN * 16) + bl * 16;
+        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + tile_bytes / 2), v);
+    }
+}
+
+// Parameter-flow operands of one layer (contraction over the batch), into the columns of slot `slot`:
+// X tile (row tile mt, chunk cc): [8 sample groups][128 rows][8 samples] hi, lo; Y tile (edge tile et of 256, chunk cc):
+// [8 sample groups][256 edges][8 samples] hi, lo.  The concatenated sample index of (slot, b) is slot * B + b.
+// Grid (ceil(B / 8)), 512 threads.
+template <int FC>
+__global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const WidePrepArgs a) {
+    extern __shared__ float s_dyn[];
+    __shared__ float s_red[(W_PREP_THREADS / 32) * 8];
+    const int tid = threadIdx.x;
+    const int b0 = blockIdx.x * W_PREP_SAMPLES;
+    const int ld = a.depth_pad + 4;
+    float sh[8];
+    wide_prep_stage<0>(a, 0, b0, s_dyn, ld, s_red, sh);              // mode 2: rows of the layer, flow - value
+
+    const int64_t q0 = (int64_t)a.slot * a.B + b0;
+    const int64_t cc = q0 / KC;
+    const int sg = (int)(q0 % KC) / 8;
+    for (int r = tid; r < a.depth; r += W_PREP_THREADS) {
+        float v[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const float x = s_dyn[s * ld + r];
+            v[s] = (x == PCX_NEG_INF || sh[s] == PCX_NEG_INF) ? 0.0f : __expf(x - sh[s]);
+        }
+        uint8_t* tile = a.tiles + ((size_t)(r / BM) * a.n_chunks_total + cc) * (2 * A_TILE);
+        uint8_t* dst = tile + sg * (BM * 16) + (r % BM) * 16;
+        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + A_TILE), v);
+    }
+    constexpr int EN = 256;
+    for (int e = tid; e < a.Kfw; e += W_PREP_THREADS) {
+        float em[8];
+        bool live;
+        if (FC == 0) {
+            const int cid = a.cids_row[e];
+            live = cid != 0;
+            const float4 p = *reinterpret_cast<const float4*>(a.emars + (int64_t)cid * a.B + b0);
+            const float4 q = *reinterpret_cast<const float4*>(a.emars + (int64_t)cid * a.B + b0 + 4);
+            em[0] = p.x; em[1] = p.y; em[2] = p.z; em[3] = p.w; em[4] = q.x; em[5] = q.y; em[6] = q.z; em[7] = q.w;
+        } else {
+            live = false;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) em[s] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < (FC > 0 ? FC : 1); ++j) {
+                const int fk = a.fk_row[(int64_t)e * FC + j];
+                const float4 p = *reinterpret_cast<const float4*>(a.src2 + (int64_t)fk * a.B + b0);
+                const float4 q = *reinterpret_cast<const float4*>(a.src2 + (int64_t)fk * a.B + b0 + 4);
+                const float w = fk != 0 ? 1.0f : 0.0f;
+                live = live || fk != 0;
+                em[0] += w * p.x; em[1] += w * p.y; em[2] += w * p.z; em[3] += w * p.w;
+                em[4] += w * q.x; em[5] += w * q.y; em[6] += w * q.z; em[7] += w * q.w;
+            }
+        }
+        float v[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            v[s] = (!live || em[s] == PCX_NEG_INF || sh[s] == PCX_NEG_INF) ? 0.0f : fminf(__expf(em[s] + sh[s]), 3.0e38f);
+        uint8_t* tile = a.y_tiles + ((size_t)(e / EN) * a.n_chunks_total + cc) * (2 * 8 * EN * 16);
+        uint8_t* dst = tile + sg * (EN * 16) + (e % EN) * 16;
+        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + 8 * EN * 16), v);
+    }
+}
+
+inline int wide_dn(int B) { return B > 128 ? 256 : (B > 64 ? 128 : 64); }
+
+// CTAs per output tile along the contraction: enough to fill the machine, a power of two that divides the chunks.
+inline int wide_splits(int64_t tiles, int n_chunks) {
+    int s = 1;
+    while (s < 8 && tiles * (s * 2) <= 160 && n_chunks % (s * 2) == 0 && n_chunks / (s * 2) >= 2) s *= 2;
+    return s;
+}
+
+template <typename Kern>
+int wide_set_smem(Kern kern, int bytes, bool* done) {
+    if (!*done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return (int)e;
+        *done = true;
+    }
+    return 0;
+}
+
+template <int EPI, int DN>
+int launch_wide_gemm(const WideArgs& a, dim3 grid, cudaStream_t st) {
+    static bool done = false;
+    int rc = wide_set_smem(wide_gemm_kernel<EPI, DN>, WideCfg<DN>::SMEM, &done);
+    if (rc != 0) return rc;
+    wide_gemm_kernel<EPI, DN><<<grid, W_THREADS, WideCfg<DN>::SMEM, st>>>(a);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int EPI>
+int launch_wide_gemm_dn(const WideArgs& a, int DN, dim3 grid, cudaStream_t st) {
+    if (DN == 256) return launch_wide_gemm<EPI, 256>(a, grid, st);
+    if (DN == 128) return launch_wide_gemm<EPI, 128>(a, grid, st);
+    return launch_wide_gemm<EPI, 64>(a, grid, st);
+}
+
+template <int FC>
+int launch_wide_prep_rows(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStream_t st) {
+    static bool done = false;
+    int rc = wide_set_smem(wide_prep_rows_kernel<FC>, (W_MAX_DEPTH + 4) * 8 * (int)sizeof(float), &done);
+    if (rc != 0) return rc;
+    wide_prep_rows_kernel<FC><<<grid, W_PREP_THREADS, smem, st>>>(p);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int FC>
+int launch_wide_prep_par(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStream_t st) {
+    static bool done = false;
+    int rc = wide_set_smem(wide_prep_par_kernel<FC>, (W_MAX_DEPTH + 4) * 8 * (int)sizeof(float), &done);
+    if (rc != 0) return rc;
+    wide_prep_par_kernel<FC><<<grid, W_PREP_THREADS, smem, st>>>(p);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+struct WideScratch {
+    uint8_t* tiles;
+    float* shift;
+    float* partial;
+    int64_t total;
+};
+
+inline WideScratch wide_scratch(void* base, int n_groups, int depth, int B, int64_t row_tiles) {
+    const int DN = wide_dn(B);
+    const int64_t n_chunks = pcx_cdiv(depth, KC), n_ct = pcx_cdiv(B, DN);
+    const int splits = wide_splits(row_tiles * n_ct, (int)n_chunks);
+    const size_t t = align256((size_t)n_groups * n_ct * n_chunks * (2 * 8 * DN * 16));
+    const size_t s = align256((size_t)n_groups * B * sizeof(float));
+    const size_t p = splits > 1 ? align256((size_t)row_tiles * n_ct * splits * BM * DN * sizeof(float)) : 0;
+    WideScratch w;
+    uint8_t* b = reinterpret_cast<uint8_t*>(base);
+    w.tiles = b;
+    w.shift = reinterpret_cast<float*>(b + t);
+    w.partial = reinterpret_cast<float*>(b + t + s);
+    w.total = (int64_t)(t + s + p);
+    return w;
+}
+
+// Shared host part of the forward pass and the element flows.
+static int wide_rows_op(int mode, float* out, const float* src, const float* src2, const float* emars, float* nflows,
+                        const void* packed, const int32_t* rows, const int32_t* kids, const int32_t* fkids_prep,
+                        const int32_t* fkids_epi, int fc, int direct, const int32_t* row_group, const int32_t* group_row,
+                        int n_groups, void* scratch, int64_t scratch_bytes, int* counters, int64_t n_rows, int K,
+                        int row_block, int par_block, int B, int logspace, cudaStream_t st) {
+    if (n_rows <= 0 || B <= 0) return 0;
+    const int depth = (mode == 0) ? K : K * par_block;
+    if (row_block % BM != 0 || B % 8 != 0 || n_groups <= 0 || depth <= 0 || depth > W_MAX_DEPTH) return -1;
+    if (fc != 0 && fc != 2 && fc != 4 && fc != 8) return -1;
+    const int64_t row_tiles = n_rows * (row_block / BM);
+    const WideScratch w = wide_scratch(scratch, n_groups, depth, B, row_tiles);
+    if (scratch == nullptr || (reinterpret_cast<uintptr_t>(scratch) & 255) != 0 || scratch_bytes < w.total) return -1;
+    const int DN = wide_dn(B);
+    const int n_chunks = (int)pcx_cdiv(depth, KC), n_ct = (int)pcx_cdiv(B, DN);
+    const int splits = wide_splits(row_tiles * n_ct, n_chunks);
+    if (splits > 1 && counters == nullptr) return -1;
+
+    WidePrepArgs p{};
+    p.src = src; p.src2 = src2; p.kids = kids; p.fkids = fkids_prep; p.group_row = group_row; p.fc = fc; p.K = K;
+    p.par_block = (mode == 0) ? 1 : par_block; p.depth = depth; p.depth_pad = n_chunks * KC; p.B = B;
+    p.logspace = logspace; p.mode = mode; p.DN = DN; p.n_ct = n_ct; p.n_chunks = n_chunks; p.tiles = w.tiles;
+    p.shift = w.shift;
+    const dim3 pgrid((unsigned)(B / W_PREP_SAMPLES), (unsigned)n_groups);
+    const size_t psmem = (size_t)(p.depth_pad + 4) * 8 * sizeof(float);
+    int rc;
+    const int pfc = (mode == 0 && fkids_prep != nullptr) ? fc : 0;
+    if (pfc == 0) rc = launch_wide_prep_rows<0>(p, pgrid, psmem, st);
+    else if (pfc == 2) rc = launch_wide_prep_rows<2>(p, pgrid, psmem, st);
+    else if (pfc == 4) rc = launch_wide_prep_rows<4>(p, pgrid, psmem, st);
+    else rc = launch_wide_prep_rows<8>(p, pgrid, psmem, st);
+    if (rc != 0) return rc;
+
+    WideArgs a{};
+    a.a_tiles = reinterpret_cast<const uint8_t*>(packed); a.b_tiles = w.tiles; a.b_group = row_group;
+    a.n_chunks = n_chunks; a.splits = splits; a.n_ct = n_ct; a.row_block = row_block; a.B = B; a.logspace = logspace;
+    a.terms = (g_sum_mode == 2) ? 1 : 3; a.rows = rows; a.out = out; a.shift = w.shift; a.emars = emars;
+    a.nmars = src2; a.nflows = nflows; a.fkids = fkids_epi; a.fc = fc; a.direct = direct;
+    a.partial = w.partial; a.counters = counters;
+    const dim3 grid((unsigned)row_tiles, (unsigned)n_ct, (unsigned)splits);
+    return mode == 0 ? launch_wide_gemm_dn<W_FWD>(a, DN, grid, st) : launch_wide_gemm_dn<W_ELE>(a, DN, grid, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B, int64_t n_row_tiles) {
+    return wide_scratch(nullptr, n_groups, depth, B, n_row_tiles).total;
+}
+
+int pcx_sum_fwd_dense2(float* node_mars, const float* element_mars, const void* packed, const int32_t* nids,
+                       const int32_t* cids, const int32_t* fkids, int fc, const int32_t* row_group,
+                       const int32_t* group_row, int n_groups, void* scratch, int64_t scratch_bytes, int32_t* counters,
+                       int64_t n_blocks, int K, int block_size, int B, void* stream) {
+    if (fkids == nullptr && element_mars == nullptr) return -1;
+    const float* src = fkids != nullptr ? node_mars : element_mars;
+    return wide_rows_op(0, node_mars, src, nullptr, nullptr, nullptr, packed, nids, cids, fkids, nullptr,
+                        fkids != nullptr ? fc : 0, 0, row_group, group_row, n_groups, scratch, scratch_bytes, counters,
+                        n_blocks, K, block_size, 1, B, 1, (cudaStream_t)stream);
+}
+
+int pcx_sum_bwd_ele_dense2(float* element_flows, const float* element_mars, float* node_flows, const float* node_mars,
+                           const void* packed, const int32_t* chids, const int32_t* parids, const int32_t* fkids,
+                           int fc, int direct, const int32_t* row_group, const int32_t* group_row, int n_groups,
+                           void* scratch, int64_t scratch_bytes, int32_t* counters, int64_t n_blocks, int P,
+                           int block_size, int ch_block_size, int B, int logspace, void* stream) {
+    if (block_size % 8 != 0) return -1;
+    if (fkids == nullptr && (element_mars == nullptr || element_flows == nullptr)) return -1;
+    if (fkids != nullptr && !direct && element_flows == nullptr) return -1;
+    return wide_rows_op(1, element_flows, node_flows, node_mars, element_mars, node_flows, packed, chids, parids, nullptr,
+                        fkids, fkids != nullptr ? fc : 0, direct, row_group, group_row, n_groups, scratch, scratch_bytes,
+                        counters, n_blocks, P, ch_block_size, block_size, B, logspace, (cudaStream_t)stream);
+}
+
+int pcx_sum_par_dense2_stage(void* x_tiles, void* y_tiles, const float* node_flows, const float* node_mars,
+                             const float* element_mars, const int32_t* nids, const int32_t* cids_row,
+                             const int32_t* fkids_row, int fc, int64_t n_blocks, int K, int block_size, int B,
+                             int n_chunks_total, int slot, int logspace, void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    const int64_t rows = n_blocks * block_size;
+    if (block_size % BM != 0 || K <= 0 || slot < 0 || B % 8 != 0 || rows > W_MAX_DEPTH) return -1;
+    if (((int64_t)slot + 1) * B > (int64_t)n_chunks_total * KC) return -1;
+    if (fkids_row == nullptr && element_mars == nullptr) return -1;
+    if (fkids_row != nullptr && fc != 2 && fc != 4 && fc != 8) return -1;
+    WidePrepArgs p{};
+    p.src = node_flows; p.src2 = node_mars; p.kids = nids; p.K = 1; p.par_block = block_size; p.depth = (int)rows;
+    p.depth_pad = (int)pcx_cdiv(rows, KC) * KC; p.B = B; p.logspace = logspace; p.mode = 2;
+    p.tiles = reinterpret_cast<uint8_t*>(x_tiles); p.y_tiles = reinterpret_cast<uint8_t*>(y_tiles);
+    p.emars = element_mars; p.cids_row = cids_row; p.fk_row = fkids_row; p.fc = fc; p.Kfw = K;
+    p.n_chunks_total = n_chunks_total; p.slot = slot;
+    const dim3 grid((unsigned)(B / W_PREP_SAMPLES));
+    const size_t smem = (size_t)(p.depth_pad + 4) * 8 * sizeof(float);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (fkids_row == nullptr) return launch_wide_prep_par<0>(p, grid, smem, st);
+    if (fc == 2) return launch_wide_prep_par<2>(p, grid, smem, st);
+    if (fc == 4) return launch_wide_prep_par<4>(p, grid, smem, st);
+    return launch_wide_prep_par<8>(p, grid, smem, st);
+}
+
+int pcx_sum_par_dense2_gemm(float* param_flows, const float* params, const void* x_tiles, const void* y_tiles,
+                            const int32_t* cids, const int32_t* pids, const int32_t* pfids, int64_t n_blocks, int K,
+                            int block_size, int n_chunks_total, void* stream) {
+    if (n_blocks <= 0 || n_chunks_total <= 0) return 0;
+    if (block_size % BM != 0 || K <= 0) return -1;
+    WideArgs a{};
+    a.a_tiles = reinterpret_cast<const uint8_t*>(x_tiles); a.b_tiles = reinterpret_cast<const uint8_t*>(y_tiles);
+    a.n_chunks = n_chunks_total; a.splits = 1; a.row_block = block_size; a.terms = (g_sum_mode == 2) ? 1 : 3;
+    a.out = param_flows; a.params = params; a.cids = cids; a.pids = pids; a.pfids = pfids; a.K = K;
+    const dim3 grid((unsigned)(n_blocks * (block_size / BM)), (unsigned)pcx_cdiv(K, 256), 1);
+    return launch_wide_gemm<W_PAR, 256>(a, grid, (cudaStream_t)stream);
+}
+
+}  // extern "C"

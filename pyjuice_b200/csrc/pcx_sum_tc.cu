@@ -1474,4 +1474,5 @@ int pcx_sum_bwd_ele_packed(float* element_flows, const float* element_mars, cons
 }  // extern "C"
 
 #include "pcx_sum_dense.cuh"
+#include "pcx_sum_dense2.cuh"
 #include "pcx_sum_sm.cuh"

@@ -478,6 +478,52 @@ class SumLayer(Layer, nn.Module):
     def _dense_scratch(self, n_groups: int, depth: int, B: int) -> torch.Tensor:
         return self._packer.scratch(int(_lib.load().pcx_dense_scratch_bytes(n_groups, depth, B)))
 
+    # The wide-tile dense kernels (128 rows x up to 256 samples, contraction split over CTAs) hold all operand rows of
+    # eight samples in shared memory during their pre-pass: at most this many rows.
+    DENSE_WIDE_MAX_DEPTH = 6144
+    use_wide_dense = True
+
+    def _wide_ok(self, p: int, B: int, backward: bool) -> bool:
+        if not (self.use_dense_kernels and self.use_wide_dense) or B % 8 != 0 or _lib.SUM_MODE == 0 or self._packer is None:
+            return False
+        if backward:
+            depth = self._dev["bk"][p][1].size(1) * self.block_size
+            return self._packed_bk[p] is not None and self.DENSE_MIN_DEPTH <= depth <= self.DENSE_WIDE_MAX_DEPTH
+        depth = self._dev["fw"][p][1].size(1)
+        return self._packed_fw[p] is not None and self.DENSE_MIN_DEPTH <= depth <= self.DENSE_WIDE_MAX_DEPTH
+
+    def _wide_buffers(self, kind: str, p: int, n_groups: int, depth: int, B: int, row_tiles: int):
+        """(scratch, bytes, counters) of one wide-tile launch: the scratch is shared by all layers (they run one after
+        the other), the split-contraction counters belong to this table and stay zero between launches."""
+        nbytes = int(_lib.load().pcx_dense2_scratch_bytes(n_groups, depth, B, row_tiles))
+        scratch = self._packer.scratch(nbytes)
+        cache = self.__dict__.setdefault("_wide_counters", {})
+        key = (kind, p, B)
+        if key not in cache:
+            cache[key] = torch.zeros(row_tiles * max(1, -(-B // 64)), dtype=torch.int32, device=self.device)
+        return scratch, scratch.numel(), cache[key]
+
+    def _forward_wide(self, p: int, node_mars, element_mars, fkids, fc: int):
+        nids, cids, _, _ = self._dev["fw"][p]
+        B = node_mars.size(1)
+        row_group, group_row, n_groups = self._groups_fw[p]
+        scratch, nbytes, counters = self._wide_buffers("fw", p, n_groups, cids.size(1), B,
+                                                       nids.numel() * (self.block_size // 128))
+        _lib.call("pcx_sum_fwd_dense2", node_mars, element_mars, self._packed_fw[p], nids, cids, fkids, fc, row_group,
+                  group_row, n_groups, scratch, nbytes, counters, nids.numel(), cids.size(1), self.block_size, B)
+
+    def _backward_ele_wide(self, p: int, node_flows, element_flows, node_mars, element_mars, fkids, fc: int, direct: bool,
+                           logspace_flows: bool):
+        chids, parids, _ = self._dev["bk"][p]
+        cbs = self.cs_block_sizes[p]
+        B = node_flows.size(1)
+        row_group, group_row, n_groups = self._groups_bk[p]
+        scratch, nbytes, counters = self._wide_buffers("bk", p, n_groups, parids.size(1) * self.block_size, B,
+                                                       chids.numel() * (cbs // 128))
+        _lib.call("pcx_sum_bwd_ele_dense2", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p], chids,
+                  parids, fkids, fc, int(bool(direct)), row_group, group_row, n_groups, scratch, nbytes, counters,
+                  chids.numel(), parids.size(1), self.block_size, cbs, B, int(bool(logspace_flows)))
+
     use_dense_kernels = True
     use_sample_major = True          # tensor-core tiles of 128 samples x 32/64 nodes for small node blocks
 
@@ -498,7 +544,9 @@ class SumLayer(Layer, nn.Module):
         B = node_mars.size(1)
         packed = self._use_packed(params)
         for p, (nids, cids, pids, _) in enumerate(self._dev["fw"]):
-            if packed and self._dense_ok(p, B, False):
+            if packed and self._wide_ok(p, B, False):
+                self._forward_wide(p, node_mars, element_mars, None, 0)
+            elif packed and self._dense_ok(p, B, False):
                 row_group, group_row, n_groups = self._groups_fw[p]
                 scratch = self._dense_scratch(n_groups, cids.size(1), B)
                 _lib.call("pcx_sum_fwd_dense", node_mars, element_mars, self._packed_fw[p], nids, cids, row_group,
@@ -525,6 +573,10 @@ class SumLayer(Layer, nn.Module):
                     _lib.call("pcx_sum_fwd_sm", node_mars, None, buf, first_row, nids, cids, f["fw"][p], n_merged, nb,
                               cids.size(1), B)
             return
+        if f.get("dense"):                                # deep tables: the wide-tile dense kernels gather the products
+            for p in range(self.num_fw_partitions):
+                self._forward_wide(p, node_mars, None, f["fw"][p], f["fc"])
+            return
         for p, (nids, cids, _, _) in enumerate(self._dev["fw"]):
             _lib.call("pcx_sum_fwd_fused", node_mars, self._packed_fw[p], nids, cids, f["fw"][p], f["fc"],
                       nids.numel(), cids.size(1), self.block_size, B)
@@ -537,6 +589,11 @@ class SumLayer(Layer, nn.Module):
                     _lib.call("pcx_sum_bwd_ele_sm", element_flows, None, node_flows, node_mars, buf, first_row, chids,
                               parids, f["bk"][p], cbs, n_merged, nb, parids.size(1), self.block_size, B,
                               int(bool(logspace_flows)))
+            return
+        if f.get("dense"):
+            for p in range(self.num_bk_partitions):
+                self._backward_ele_wide(p, node_flows, None if f["direct"] else element_flows, node_mars, None,
+                                        f["bk"][p], f["fc"], f["direct"], logspace_flows)
             return
         for p, ((chids, parids, _), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
             _lib.call("pcx_sum_bwd_ele_fused", element_flows, node_flows, node_mars, self._packed_bk[p], chids, parids,
@@ -569,7 +626,9 @@ class SumLayer(Layer, nn.Module):
         ls = int(bool(logspace_flows))
         packed = self._use_packed(params)
         for p, ((chids, parids, parpids), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
-            if packed and self._dense_ok(p, B, True):
+            if packed and self._wide_ok(p, B, True):
+                self._backward_ele_wide(p, node_flows, element_flows, node_mars, element_mars, None, 0, False, ls)
+            elif packed and self._dense_ok(p, B, True):
                 row_group, group_row, n_groups = self._groups_bk[p]
                 scratch = self._dense_scratch(n_groups, parids.size(1) * self.block_size, B)
                 _lib.call("pcx_sum_bwd_ele_dense", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p],
@@ -588,8 +647,8 @@ class SumLayer(Layer, nn.Module):
         if param_flows is not None:
             stage = kwargs.get("dense_par_stage")
             for p, (nids, cids, pids, pfids) in enumerate(self._dev["fw"]):
-                if (stage is not None and packed and self._dense_ok(p, B, False) and self._groups_fw[p][2] == 1
-                        and stage(self, p, node_flows, node_mars, element_mars, ls)):
+                if (stage is not None and packed and (self._dense_ok(p, B, False) or self._wide_ok(p, B, False))
+                        and self._groups_fw[p][2] == 1 and stage(self, p, node_flows, node_mars, element_mars, ls)):
                     continue                       # this table's flows come out of one product over all staged layers
                 if (packed and self.use_sample_major and self._packed_fw[p] is None and self._sm_fw[p] is not None
                         and B % 8 == 0):

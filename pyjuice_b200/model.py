@@ -360,8 +360,14 @@ class TensorCircuit(nn.Module):
             else:                                           # every merged row gathers each of its entries once per tile
                 reads = sum(int((c.cpu()[first.long().cpu()] != 0).sum()) for l in sgroup
                             for c, lists in zip(l.partitioned_cids, l._sm_fw) for _, first, _, _ in lists)
-            if used == 0 or reads > 2 * used:
+            # deep tables run on the wide-tile dense kernels, whose operand pre-pass computes every product once per
+            # group of rows: folding costs them nothing, whatever the duplication
+            lo_d, hi_d = SumLayer.DENSE_MIN_DEPTH, SumLayer.DENSE_WIDE_MAX_DEPTH
+            dense = big and all(lo_d <= c.size(1) <= hi_d for l in sgroup for c in l.partitioned_cids) and \
+                all(lo_d <= pr.size(1) * l.block_size <= hi_d for l in sgroup for pr in l.partitioned_parids)
+            if used == 0 or (reads > 2 * used and not dense):
                 continue
+            dense = dense and reads > 2 * used              # tables the tile-at-a-time kernels handle well stay there
             ch_rows = children[children != 0].long()
             direct = big and bool((parents[ch_rows] == 1).all())
             for layer in sgroup:
@@ -370,8 +376,8 @@ class TensorCircuit(nn.Module):
                 for chids, cbs in zip(layer.partitioned_chids, layer.cs_block_sizes):
                     rows = chids.cpu()[:, None] + torch.arange(cbs)[None, :]
                     bk.append(children[rows].contiguous().to(dev))
-                layer._fusion = dict(fc=fc, fw=fw, bk=bk, direct=direct, sm=small)
-            self._fused[gi] = dict(fc=fc, direct=direct, sm=small,
+                layer._fusion = dict(fc=fc, fw=fw, bk=bk, direct=direct, sm=small, dense=dense)
+            self._fused[gi] = dict(fc=fc, direct=direct, sm=small, dense=dense,
                                    child_rows=torch.unique(ch_rows) if not direct else None)
         # rows of node_flows that still need the -inf / 0 reset each pass: children of every depth that is not
         # handled by direct stores (those are accumulated into with logaddexp)
@@ -472,12 +478,16 @@ class TensorCircuit(nn.Module):
             return False
         if backward and self._reference_compat:
             return False
+        if self._fused[gi].get("dense") and not (SumLayer.use_dense_kernels and SumLayer.use_wide_dense
+                                                 and self.node_mars is not None and self.node_mars.size(1) % 8 == 0):
+            return False
         return (not backward) or self.node_mars.size(1) % 8 == 0
 
     def _launch_cfg(self):
         """Everything that changes which kernels a pass launches (part of the key of a captured graph)."""
         return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
-                SumLayer.use_dense_kernels, SumLayer.use_sample_major, getattr(self._packer, "grown", 0),
+                SumLayer.use_dense_kernels, SumLayer.use_wide_dense, SumLayer.use_sample_major,
+                getattr(self._packer, "grown", 0),
                 self._reference_compat)
 
     def _chain_plan(self, B: int, mode: int):
@@ -496,7 +506,7 @@ class TensorCircuit(nn.Module):
         if self.use_dataflow_launch:
             def ok(gi):
                 return (self._fusion_on(gi, backward=(mode == 1)) and not self._fused[gi]["sm"]
-                        and (mode == 0 or self._fused[gi]["direct"]))
+                        and not self._fused[gi].get("dense") and (mode == 0 or self._fused[gi]["direct"]))
             runs, cur = [], []
             for gi in range(1, len(groups), 2):
                 if ok(gi) and (not cur or self._fused[cur[-1]]["fc"] == self._fused[gi]["fc"]):
@@ -617,7 +627,8 @@ class TensorCircuit(nn.Module):
                         ("item_begin", "<i8"), ("K", "<i4"), ("block_size", "<i4"), ("e_tiles", "<i4"), ("splits", "<i4")])
         per_fc = {}
         for gi, group in enumerate(self.inner_layer_groups):
-            if group.is_sum() and self._fusion_on(gi, True) and not self._fused[gi]["sm"]:
+            if (group.is_sum() and self._fusion_on(gi, True) and not self._fused[gi]["sm"]
+                    and not self._fused[gi].get("dense")):
                 for layer in group:
                     f = layer._fusion
                     for p, (nids, cids, pids, pfids) in enumerate(layer._dev["fw"]):
@@ -655,26 +666,35 @@ class TensorCircuit(nn.Module):
         cpl = -(-B // 64)
         for gi in range(len(self.inner_layer_groups) - 1, -1, -1):
             group = self.inner_layer_groups[gi]
-            if not group.is_sum() or self._fusion_on(gi, True):
+            if not group.is_sum():
+                continue
+            folded = self._fusion_on(gi, True)
+            if folded and not self._fused[gi].get("dense"):
                 continue
             for layer in group:
                 if layer._packer is None:
                     continue
                 for p, (nids, cids, pids, pfids) in enumerate(layer._dev["fw"]):
-                    if not (layer._dense_ok(p, B, False) and layer._groups_fw[p][2] == 1):
+                    wide = layer._wide_ok(p, B, False) and nids.numel() * layer.block_size <= SumLayer.DENSE_WIDE_MAX_DEPTH
+                    if not ((wide or layer._dense_ok(p, B, False)) and layer._groups_fw[p][2] == 1):
+                        assert not folded, "a dense-folded table must qualify for the dense parameter-flow product"
                         continue
-                    g = groups.setdefault(layer._packed_fw[p].data_ptr(),
+                    g = groups.setdefault((layer._packed_fw[p].data_ptr(), wide),
                                           dict(members=[], tables=(cids, pids, pfids), n_blocks=nids.numel(),
-                                               K=cids.size(1), block_size=layer.block_size))
+                                               K=cids.size(1), block_size=layer.block_size, wide=wide))
                     where[(id(layer), p)] = (g, len(g["members"]))
                     g["members"].append((layer, p))
         plan = None
         total = 0
         for g in groups.values():
-            g["n_chunks"] = len(g["members"]) * cpl
             row_tiles = g["n_blocks"] * (g["block_size"] // 128)
+            if g["wide"]:                                   # samples of consecutive layers packed back to back
+                g["n_chunks"] = -(-len(g["members"]) * B // 64)
+                g["y_bytes"] = -(-g["K"] // 256) * g["n_chunks"] * 65536
+            else:
+                g["n_chunks"] = len(g["members"]) * cpl
+                g["y_bytes"] = -(-g["K"] // 64) * g["n_chunks"] * 16384
             g["x_bytes"] = row_tiles * g["n_chunks"] * 32768
-            g["y_bytes"] = -(-g["K"] // 64) * g["n_chunks"] * 16384
             total += g["x_bytes"] + g["y_bytes"]
         if groups and total <= self.dense_par_max_bytes:
             for g in groups.values():
@@ -683,6 +703,9 @@ class TensorCircuit(nn.Module):
             rows = max(g["n_blocks"] * g["block_size"] for g in groups.values())
             plan = dict(where=where, groups=list(groups.values()),
                         work=torch.empty((-(-rows // 64) + 1) * B, dtype=torch.float32, device=self.device))
+        elif groups:
+            assert not any(self._fused.get(gi, {}).get("dense") for gi in self._fused), \
+                "`dense_par_max_bytes` is too small for the operands of the dense parameter-flow product"
         cache[key] = plan
         return plan
 
@@ -702,9 +725,16 @@ class TensorCircuit(nn.Module):
                 return False
             g, slot = hit
             nids, cids, _, _ = layer._dev["fw"][p]
-            _lib.call("pcx_sum_par_dense_stage", g["x"], g["y"], dense["work"], node_flows, node_mars, element_mars,
-                      nids, cids, nids.numel(), cids.size(1), layer.block_size, node_flows.size(1), g["n_chunks"],
-                      slot, ls)
+            if g["wide"]:
+                f = getattr(layer, "_fusion", None)
+                fk = f["fw"][p] if (f is not None and f.get("dense") and element_mars is None) else None
+                _lib.call("pcx_sum_par_dense2_stage", g["x"], g["y"], node_flows, node_mars, element_mars, nids, cids,
+                          fk, f["fc"] if fk is not None else 0, nids.numel(), cids.size(1), layer.block_size,
+                          node_flows.size(1), g["n_chunks"], slot, ls)
+            else:
+                _lib.call("pcx_sum_par_dense_stage", g["x"], g["y"], dense["work"], node_flows, node_mars, element_mars,
+                          nids, cids, nids.numel(), cids.size(1), layer.block_size, node_flows.size(1), g["n_chunks"],
+                          slot, ls)
             return True
 
         plan = self._chain_plan(self.node_mars.size(1), 1)
@@ -718,6 +748,16 @@ class TensorCircuit(nn.Module):
             if group.is_prod():
                 if not (self._fusion_on(gi + 1, True) and self._fused[gi + 1]["direct"]):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
+            elif self._fusion_on(gi, True) and self._fused[gi].get("dense"):
+                for layer in group:                         # operands of the tied parameter-flow product, then the flows
+                    if pf is not None:
+                        for p in range(layer.num_fw_partitions):
+                            ok = dense is not None and dense_stage(layer, p, self.node_flows, self.node_mars, None,
+                                                                   int(bool(logspace_flows)))
+                            assert ok, "a dense-folded table must have a slot in the dense parameter-flow product"
+                    layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
+                if not self._fused[gi]["direct"]:
+                    pass                                    # the product layer below picks the flows up from element_flows
             elif self._fusion_on(gi, True):
                 any_fused = any_fused or not self._fused[gi]["sm"]
                 for layer in group:
@@ -733,8 +773,8 @@ class TensorCircuit(nn.Module):
         if dense is not None:
             for g in dense["groups"]:
                 cids, pids, pfids = g["tables"]
-                _lib.call("pcx_sum_par_dense_gemm", pf, self.params.data, g["x"], g["y"], cids, pids, pfids,
-                          g["n_blocks"], g["K"], g["block_size"], g["n_chunks"])
+                _lib.call("pcx_sum_par_dense2_gemm" if g["wide"] else "pcx_sum_par_dense_gemm", pf, self.params.data,
+                          g["x"], g["y"], cids, pids, pfids, g["n_blocks"], g["K"], g["block_size"], g["n_chunks"])
         self._batched_par_pending = any_fused and pf is not None     # launched by `backward`, after this sweep
 
     def _launch_batched_par(self, logspace_flows: bool):
