@@ -195,20 +195,21 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
  * ([table rows * K][fc] for the forward pass, [child rows][fc] for the element flows; fc = 2, 4 or 8 child rows of
  * every product, 0 = none) a product's value is gathered from node_mars and element_mars / element_flows are not
  * used; with `direct` (every child row has exactly one parent product) an element's flow is stored straight into its
- * children's rows of node_flows.  `scratch`: pcx_dense2_scratch_bytes(n_groups, depth, B, row tiles) bytes, 256-byte
- * aligned; `counters`: one int32 per (row tile, column tile), zero before the first call (the kernels leave them zero).
+ * children's rows of node_flows.  `scratch`: pcx_dense2_scratch_bytes(n_groups, depth, B) bytes, 256-byte aligned.
+ * The CTAs that split one tile's contraction form a thread-block cluster and exchange partial sums through
+ * distributed shared memory.
  * Replace, like the entry points above: SumLayer._forward_block_sparse / _backward_block_sparse_ele_flows /
  * _backward_block_sparse_par_flows (layer/sum_layer.py:551-929, 1369-1719, 1721-2080), with ProdLayer.forward /
  * backward folded in (layer/prod_layer.py:161-238). */
-int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B, int64_t n_row_tiles);
+int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B);
 int pcx_sum_fwd_dense2(float* node_mars, const float* element_mars, const void* packed, const int32_t* nids,
                        const int32_t* cids, const int32_t* fkids, int fc, const int32_t* row_group,
-                       const int32_t* group_row, int n_groups, void* scratch, int64_t scratch_bytes, int32_t* counters,
+                       const int32_t* group_row, int n_groups, void* scratch, int64_t scratch_bytes,
                        int64_t n_blocks, int K, int block_size, int B, void* stream);
 int pcx_sum_bwd_ele_dense2(float* element_flows, const float* element_mars, float* node_flows, const float* node_mars,
                            const void* packed, const int32_t* chids, const int32_t* parids, const int32_t* fkids,
                            int fc, int direct, const int32_t* row_group, const int32_t* group_row, int n_groups,
-                           void* scratch, int64_t scratch_bytes, int32_t* counters, int64_t n_blocks, int P,
+                           void* scratch, int64_t scratch_bytes, int64_t n_blocks, int P,
                            int block_size, int ch_block_size, int B, int logspace, void* stream);
 /* Parameter flows: step 1 writes the operands of one layer at sample positions [slot * B, (slot + 1) * B) of the
  * concatenated batch (x_tiles: [row tiles][n_chunks_total] tiles of 32 KB; y_tiles: [ceil(K / 256)][n_chunks_total]

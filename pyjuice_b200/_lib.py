@@ -55,8 +55,8 @@ SIGNATURES = {
     "pcx_em_sum": [P, P, P, P, P, P, L, I, F, F, I],
     "pcx_em_input_cat": [P, P, P, P, P, P, L, I, F, F, I],
     "pcx_probe_bounded_wait": [I, I],
-    "pcx_sum_fwd_dense2": [P, P, P, P, P, P, I, P, P, I, P, L, P, L, I, I, I],
-    "pcx_sum_bwd_ele_dense2": [P, P, P, P, P, P, P, P, I, I, P, P, I, P, L, P, L, I, I, I, I, I],
+    "pcx_sum_fwd_dense2": [P, P, P, P, P, P, I, P, P, I, P, L, L, I, I, I],
+    "pcx_sum_bwd_ele_dense2": [P, P, P, P, P, P, P, P, I, I, P, P, I, P, L, L, I, I, I, I, I],
     "pcx_sum_par_dense2_stage": [P, P, P, P, P, P, P, P, I, L, I, I, I, I, I, I],
     "pcx_sum_par_dense2_gemm": [P, P, P, P, P, P, P, L, I, I, I],
 }
@@ -64,7 +64,7 @@ SIGNATURES = {
 # entry points without a stream argument
 PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": [], "pcx_clear_status": [],
          "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I],
-         "pcx_sm_packed_bytes": [L, I, I], "pcx_dense2_scratch_bytes": [I, I, I, L]}
+         "pcx_sm_packed_bytes": [L, I, I], "pcx_dense2_scratch_bytes": [I, I, I]}
 SUM_MODE = 1        # mirror of the library's arithmetic mode (see set_sum_mode)
 
 _lib: Optional[ctypes.CDLL] = None

@@ -14,11 +14,9 @@ __global__ void tied_accum_kernel(float* __restrict__ flows, int64_t start, int6
     int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
     float s = 0.0f;
-    for (int c = 0; c < n_chs; ++c) {
-        const int64_t at = ch_starts[c] + j;
-        s += flows[at];
-        if (ch_starts[c] != start) flows[at] = 0.0f;      // moved into the source: running the fold again adds nothing
-    }
+    for (int c = 0; c < n_chs; ++c) s += __ldcs(flows + ch_starts[c] + j);        // all loads first: they overlap
+    for (int c = 0; c < n_chs; ++c)                       // moved into the source: running the fold again adds nothing
+        if (ch_starts[c] != start) __stcs(flows + ch_starts[c] + j, 0.0f);
     flows[start + j] = s;     // `start` is one of ch_starts: each thread reads its own slot before writing it
 }
 

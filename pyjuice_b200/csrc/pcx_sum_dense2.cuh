@@ -4,9 +4,11 @@
 // per 64 samples, so a 4096 x 4096 layer at 256 samples moved 400 MB from L2 to the SMs per pass and ran at the
 // per-SM copy rate, not at the tensor-core rate.  Here an output tile is 128 rows x up to 256 samples (all samples
 // of a rank for the usual batch sizes), so a parameter tile is fetched ONCE per layer and pass; the machine is
-// filled by splitting the contraction over several CTAs per tile instead (split-K), whose partial tiles meet in
-// an fp32 scratch buffer: the CTA that arrives last (a counter per tile, no waiting) adds them in a fixed order and
-// runs the epilogue, so results do not depend on the arrival order.
+// filled by splitting the contraction over the 2, 4 or 8 CTAs of a thread-block cluster instead (split-K): after the
+// main loop every CTA sends, through distributed shared memory, the columns of its partial accumulator that a peer
+// owns, and each CTA finishes its own share of the columns, adding the partial tiles in rank order (so results are
+// reproducible bit for bit) -- no global scratch, no counters, and the epilogue runs on every SM.  The only waits
+// between CTAs are the hardware's cluster barriers (the CTAs of a cluster are resident together by construction).
 //
 //   operand pre-pass   ONE kernel per layer and pass: a CTA owns 8 samples and ALL operand rows; it gathers the
 //                      log-domain values (the product layer is folded in: a product's value is the sum of its
@@ -68,8 +70,6 @@ struct WideArgs {
     const int32_t* fkids;       // ELE, folded: [n_rows * row_block][fc] child rows of every element (0 = none)
     int fc;
     int direct;
-    float* partial;             // split-K: [tile][split][128][DN] fp32
-    int* counters;              // split-K: one per tile, zero between launches
     const float* params;        // PAR
     const int32_t* cids;        // PAR: [n_rows, K]
     const int32_t* pids;        // PAR
@@ -77,7 +77,27 @@ struct WideArgs {
     int K;                      // PAR: table width
 };
 
-__device__ __forceinline__ void bar_sync_epilogue() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// ---- thread-block cluster helpers (the CTAs that share one output tile) -----------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Barrier over all threads of all CTAs of the cluster (release / acquire); every warp must arrive converged.
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
+// Address of `smem_addr` (an address in this CTA's shared memory) in the shared memory of the CTA with rank `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 
 // Epilogue of one row and 32 consecutive columns.
 template <int EPI, int DN>
@@ -161,7 +181,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
     __shared__ uint64_t s_full[C::STAGES], s_empty[C::STAGES], s_done;
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_fail;
-    __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t mt = blockIdx.x;                  // 128-row tile
@@ -179,7 +198,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
         mbar_init(&s_done, 1);
         fence_mbar_init();
         s_fail = 0;
-        s_last = 0;
     }
     if (warp == 0) tmem_alloc(&s_tmem, (ACCS * DN < 32) ? 32 : ACCS * DN);
     tc_fence_before_sync();
@@ -244,7 +262,12 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
             }
             mma_commit(&s_done);
         }
-    } else {
+    }
+    if (warp < 2 && a.splits > 1) {         // the cluster barriers of the epilogue count every thread of the cluster
+        cluster_sync_all();
+        cluster_sync_all();
+    }
+    if (warp >= 2) {
         // ---- epilogue warps: TMEM lane quarter warp % 4, one output row per thread --------------------------
         const int lq = warp & 3;
         const int row = lq * 32 + lane;
@@ -270,46 +293,48 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
                 }
             }
         } else {
-            // split contraction: park this CTA's partial tile, count, and let the last arrival add them up
-            const int64_t tile = (int64_t)blockIdx.x * gridDim.y + blockIdx.y;
-            float* mine = a.partial + ((tile * a.splits + split) * BM + row) * DN;
+            // split contraction: this CTA finishes columns [rank * QW, (rank + 1) * QW) of the tile.  Peers' stage
+            // buffers are free once every CTA's products are complete (first cluster barrier); the partial columns a
+            // peer owns go into its shared memory as recv[sender][column][row]; after the second barrier the partials
+            // are added in rank order.
+            const int QW = DN / a.splits;
+            const uint32_t me = cluster_cta_rank();
+            cluster_sync_all();
+            const uint32_t recv = smem_u32(smem);
+            for (int r = 0; r < a.splits; ++r) {
+                if ((uint32_t)r == me) continue;
+                const uint32_t dst = cluster_map(recv + (uint32_t)(((int)me * QW) * BM + row) * 4u, (uint32_t)r);
 #pragma unroll 1
-            for (int cb = 0; cb < DN; cb += 32) {
-                float v[32];
-                if (ok) tmem_ld<32>(tbase + (uint32_t)cb, v);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-                }
-#pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    __stcg(reinterpret_cast<float4*>(mine + cb + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
-            }
-            __threadfence();
-            bar_sync_epilogue();
-            if (tid == 64) {
-                const int before = atomicAdd(a.counters + tile, 1);
-                s_last = (before == a.splits - 1) ? 1 : 0;
-                if (s_last) a.counters[tile] = 0;            // ready for the next launch
-            }
-            bar_sync_epilogue();
-            if (s_last) {
-                __threadfence();
-                const float* base = a.partial + (tile * a.splits * BM + row) * DN;
-#pragma unroll 1
-                for (int cb = 0; cb < DN; cb += 32) {
+                for (int cb = 0; cb < QW; cb += 32) {
                     float v[32];
+                    if (ok) tmem_ld<32>(tbase + (uint32_t)(r * QW + cb), v);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) cluster_store(dst + (uint32_t)((cb + j) * BM) * 4u, v[j]);
+                }
+            }
+            cluster_sync_all();
+            const float* mine = reinterpret_cast<const float*>(smem);
+            if (ok) {
+#pragma unroll 1
+                for (int cb = 0; cb < QW; cb += 32) {
+                    float own[32], v[32];
+                    tmem_ld<32>(tbase + (uint32_t)((int)me * QW + cb), own);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-                    for (int q = 0; q < a.splits; ++q) {          // fixed order: the sum does not depend on who is last
-                        const float* src = base + (size_t)q * BM * DN + cb;
+                    for (int q = 0; q < a.splits; ++q) {          // rank order: the sum is reproducible
+                        if ((uint32_t)q == me) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            const float4 p = __ldcg(reinterpret_cast<const float4*>(src + j));
-                            v[j] += p.x; v[j + 1] += p.y; v[j + 2] += p.z; v[j + 3] += p.w;
+                            for (int j = 0; j < 32; ++j) v[j] += own[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] += mine[((q * QW) + cb + j) * BM + row];
                         }
                     }
-                    wide_finish<EPI, DN>(a, i, r0, row, nt, cb, v);
+                    wide_finish<EPI, DN>(a, i, r0, row, nt, (int)me * QW + cb, v);
                 }
             }
         }
@@ -411,7 +436,7 @@ __device__ __forceinline__ void wide_prep_stage(const WidePrepArgs& a, int g, in
     float mx[8];
 #pragma unroll
     for (int s = 0; s < 8; ++s) mx[s] = PCX_NEG_INF;
-#pragma unroll 2
+#pragma unroll 4
     for (int k = tid; k < a.depth_pad; k += W_PREP_THREADS) {
         float v[8];
         wide_prep_value<FC>(a, g, k, b0, v);
@@ -531,10 +556,11 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
 
 inline int wide_dn(int B) { return B > 128 ? 256 : (B > 64 ? 128 : 64); }
 
-// CTAs per output tile along the contraction: enough to fill the machine, a power of two that divides the chunks.
-inline int wide_splits(int64_t tiles, int n_chunks) {
+// CTAs per output tile along the contraction (= cluster size): enough to fill the machine, a power of two that divides
+// the chunks and leaves every CTA at least 32 columns of the tile to finish.
+inline int wide_splits(int64_t tiles, int n_chunks, int DN) {
     int s = 1;
-    while (s < 8 && tiles * (s * 2) <= 160 && n_chunks % (s * 2) == 0 && n_chunks / (s * 2) >= 2) s *= 2;
+    while (s < 8 && s * 2 <= DN / 32 && tiles * (s * 2) <= 160 && n_chunks % (s * 2) == 0 && n_chunks / (s * 2) >= 2) s *= 2;
     return s;
 }
 
@@ -553,7 +579,20 @@ int launch_wide_gemm(const WideArgs& a, dim3 grid, cudaStream_t st) {
     static bool done = false;
     int rc = wide_set_smem(wide_gemm_kernel<EPI, DN>, WideCfg<DN>::SMEM, &done);
     if (rc != 0) return rc;
-    wide_gemm_kernel<EPI, DN><<<grid, W_THREADS, WideCfg<DN>::SMEM, st>>>(a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(W_THREADS);
+    cfg.dynamicSmemBytes = WideCfg<DN>::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;       // the CTAs that split one tile's contraction
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = grid.z > 1 ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, wide_gemm_kernel<EPI, DN>, a);
+    if (e != cudaSuccess) return (int)e;
     PCX_LAUNCH_CHECK();
     return 0;
 }
@@ -588,23 +627,19 @@ int launch_wide_prep_par(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStre
 struct WideScratch {
     uint8_t* tiles;
     float* shift;
-    float* partial;
     int64_t total;
 };
 
-inline WideScratch wide_scratch(void* base, int n_groups, int depth, int B, int64_t row_tiles) {
+inline WideScratch wide_scratch(void* base, int n_groups, int depth, int B) {
     const int DN = wide_dn(B);
     const int64_t n_chunks = pcx_cdiv(depth, KC), n_ct = pcx_cdiv(B, DN);
-    const int splits = wide_splits(row_tiles * n_ct, (int)n_chunks);
     const size_t t = align256((size_t)n_groups * n_ct * n_chunks * (2 * 8 * DN * 16));
     const size_t s = align256((size_t)n_groups * B * sizeof(float));
-    const size_t p = splits > 1 ? align256((size_t)row_tiles * n_ct * splits * BM * DN * sizeof(float)) : 0;
     WideScratch w;
     uint8_t* b = reinterpret_cast<uint8_t*>(base);
     w.tiles = b;
     w.shift = reinterpret_cast<float*>(b + t);
-    w.partial = reinterpret_cast<float*>(b + t + s);
-    w.total = (int64_t)(t + s + p);
+    w.total = (int64_t)(t + s);
     return w;
 }
 
@@ -612,19 +647,18 @@ inline WideScratch wide_scratch(void* base, int n_groups, int depth, int B, int6
 static int wide_rows_op(int mode, float* out, const float* src, const float* src2, const float* emars, float* nflows,
                         const void* packed, const int32_t* rows, const int32_t* kids, const int32_t* fkids_prep,
                         const int32_t* fkids_epi, int fc, int direct, const int32_t* row_group, const int32_t* group_row,
-                        int n_groups, void* scratch, int64_t scratch_bytes, int* counters, int64_t n_rows, int K,
+                        int n_groups, void* scratch, int64_t scratch_bytes, int64_t n_rows, int K,
                         int row_block, int par_block, int B, int logspace, cudaStream_t st) {
     if (n_rows <= 0 || B <= 0) return 0;
     const int depth = (mode == 0) ? K : K * par_block;
     if (row_block % BM != 0 || B % 8 != 0 || n_groups <= 0 || depth <= 0 || depth > W_MAX_DEPTH) return -1;
     if (fc != 0 && fc != 2 && fc != 4 && fc != 8) return -1;
     const int64_t row_tiles = n_rows * (row_block / BM);
-    const WideScratch w = wide_scratch(scratch, n_groups, depth, B, row_tiles);
+    const WideScratch w = wide_scratch(scratch, n_groups, depth, B);
     if (scratch == nullptr || (reinterpret_cast<uintptr_t>(scratch) & 255) != 0 || scratch_bytes < w.total) return -1;
     const int DN = wide_dn(B);
     const int n_chunks = (int)pcx_cdiv(depth, KC), n_ct = (int)pcx_cdiv(B, DN);
-    const int splits = wide_splits(row_tiles * n_ct, n_chunks);
-    if (splits > 1 && counters == nullptr) return -1;
+    const int splits = wide_splits(row_tiles * n_ct, n_chunks, DN);
 
     WidePrepArgs p{};
     p.src = src; p.src2 = src2; p.kids = kids; p.fkids = fkids_prep; p.group_row = group_row; p.fc = fc; p.K = K;
@@ -646,7 +680,6 @@ static int wide_rows_op(int mode, float* out, const float* src, const float* src
     a.n_chunks = n_chunks; a.splits = splits; a.n_ct = n_ct; a.row_block = row_block; a.B = B; a.logspace = logspace;
     a.terms = (g_sum_mode == 2) ? 1 : 3; a.rows = rows; a.out = out; a.shift = w.shift; a.emars = emars;
     a.nmars = src2; a.nflows = nflows; a.fkids = fkids_epi; a.fc = fc; a.direct = direct;
-    a.partial = w.partial; a.counters = counters;
     const dim3 grid((unsigned)row_tiles, (unsigned)n_ct, (unsigned)splits);
     return mode == 0 ? launch_wide_gemm_dn<W_FWD>(a, DN, grid, st) : launch_wide_gemm_dn<W_ELE>(a, DN, grid, st);
 }
@@ -655,32 +688,32 @@ static int wide_rows_op(int mode, float* out, const float* src, const float* src
 
 extern "C" {
 
-int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B, int64_t n_row_tiles) {
-    return wide_scratch(nullptr, n_groups, depth, B, n_row_tiles).total;
+int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B) {
+    return wide_scratch(nullptr, n_groups, depth, B).total;
 }
 
 int pcx_sum_fwd_dense2(float* node_mars, const float* element_mars, const void* packed, const int32_t* nids,
                        const int32_t* cids, const int32_t* fkids, int fc, const int32_t* row_group,
-                       const int32_t* group_row, int n_groups, void* scratch, int64_t scratch_bytes, int32_t* counters,
+                       const int32_t* group_row, int n_groups, void* scratch, int64_t scratch_bytes,
                        int64_t n_blocks, int K, int block_size, int B, void* stream) {
     if (fkids == nullptr && element_mars == nullptr) return -1;
     const float* src = fkids != nullptr ? node_mars : element_mars;
     return wide_rows_op(0, node_mars, src, nullptr, nullptr, nullptr, packed, nids, cids, fkids, nullptr,
-                        fkids != nullptr ? fc : 0, 0, row_group, group_row, n_groups, scratch, scratch_bytes, counters,
+                        fkids != nullptr ? fc : 0, 0, row_group, group_row, n_groups, scratch, scratch_bytes,
                         n_blocks, K, block_size, 1, B, 1, (cudaStream_t)stream);
 }
 
 int pcx_sum_bwd_ele_dense2(float* element_flows, const float* element_mars, float* node_flows, const float* node_mars,
                            const void* packed, const int32_t* chids, const int32_t* parids, const int32_t* fkids,
                            int fc, int direct, const int32_t* row_group, const int32_t* group_row, int n_groups,
-                           void* scratch, int64_t scratch_bytes, int32_t* counters, int64_t n_blocks, int P,
+                           void* scratch, int64_t scratch_bytes, int64_t n_blocks, int P,
                            int block_size, int ch_block_size, int B, int logspace, void* stream) {
     if (block_size % 8 != 0) return -1;
     if (fkids == nullptr && (element_mars == nullptr || element_flows == nullptr)) return -1;
     if (fkids != nullptr && !direct && element_flows == nullptr) return -1;
     return wide_rows_op(1, element_flows, node_flows, node_mars, element_mars, node_flows, packed, chids, parids, nullptr,
                         fkids, fkids != nullptr ? fc : 0, direct, row_group, group_row, n_groups, scratch, scratch_bytes,
-                        counters, n_blocks, P, ch_block_size, block_size, B, logspace, (cudaStream_t)stream);
+                        n_blocks, P, ch_block_size, block_size, B, logspace, (cudaStream_t)stream);
 }
 
 int pcx_sum_par_dense2_stage(void* x_tiles, void* y_tiles, const float* node_flows, const float* node_mars,

@@ -492,25 +492,18 @@ class SumLayer(Layer, nn.Module):
         depth = self._dev["fw"][p][1].size(1)
         return self._packed_fw[p] is not None and self.DENSE_MIN_DEPTH <= depth <= self.DENSE_WIDE_MAX_DEPTH
 
-    def _wide_buffers(self, kind: str, p: int, n_groups: int, depth: int, B: int, row_tiles: int):
-        """(scratch, bytes, counters) of one wide-tile launch: the scratch is shared by all layers (they run one after
-        the other), the split-contraction counters belong to this table and stay zero between launches."""
-        nbytes = int(_lib.load().pcx_dense2_scratch_bytes(n_groups, depth, B, row_tiles))
-        scratch = self._packer.scratch(nbytes)
-        cache = self.__dict__.setdefault("_wide_counters", {})
-        key = (kind, p, B)
-        if key not in cache:
-            cache[key] = torch.zeros(row_tiles * max(1, -(-B // 64)), dtype=torch.int32, device=self.device)
-        return scratch, scratch.numel(), cache[key]
+    def _wide_scratch(self, n_groups: int, depth: int, B: int):
+        """Operand scratch of one wide-tile launch, shared by all layers (they run one after the other)."""
+        scratch = self._packer.scratch(int(_lib.load().pcx_dense2_scratch_bytes(n_groups, depth, B)))
+        return scratch, scratch.numel()
 
     def _forward_wide(self, p: int, node_mars, element_mars, fkids, fc: int):
         nids, cids, _, _ = self._dev["fw"][p]
         B = node_mars.size(1)
         row_group, group_row, n_groups = self._groups_fw[p]
-        scratch, nbytes, counters = self._wide_buffers("fw", p, n_groups, cids.size(1), B,
-                                                       nids.numel() * (self.block_size // 128))
+        scratch, nbytes = self._wide_scratch(n_groups, cids.size(1), B)
         _lib.call("pcx_sum_fwd_dense2", node_mars, element_mars, self._packed_fw[p], nids, cids, fkids, fc, row_group,
-                  group_row, n_groups, scratch, nbytes, counters, nids.numel(), cids.size(1), self.block_size, B)
+                  group_row, n_groups, scratch, nbytes, nids.numel(), cids.size(1), self.block_size, B)
 
     def _backward_ele_wide(self, p: int, node_flows, element_flows, node_mars, element_mars, fkids, fc: int, direct: bool,
                            logspace_flows: bool):
@@ -518,10 +511,9 @@ class SumLayer(Layer, nn.Module):
         cbs = self.cs_block_sizes[p]
         B = node_flows.size(1)
         row_group, group_row, n_groups = self._groups_bk[p]
-        scratch, nbytes, counters = self._wide_buffers("bk", p, n_groups, parids.size(1) * self.block_size, B,
-                                                       chids.numel() * (cbs // 128))
+        scratch, nbytes = self._wide_scratch(n_groups, parids.size(1) * self.block_size, B)
         _lib.call("pcx_sum_bwd_ele_dense2", element_flows, element_mars, node_flows, node_mars, self._packed_bk[p], chids,
-                  parids, fkids, fc, int(bool(direct)), row_group, group_row, n_groups, scratch, nbytes, counters,
+                  parids, fkids, fc, int(bool(direct)), row_group, group_row, n_groups, scratch, nbytes,
                   chids.numel(), parids.size(1), self.block_size, cbs, B, int(bool(logspace_flows)))
 
     use_dense_kernels = True

@@ -812,8 +812,9 @@ class TensorCircuit(nn.Module):
             self._ensure_buffers(B, backward=True)
             ls = int(bool(logspace_flows))
             reset = NEG_INF if logspace_flows else 0.0
-            ranges = self._flow_reset_ranges if (self.fuse_product_layers and _lib.SUM_MODE != 0 and B % 8 == 0
-                                                 and not self._reference_compat) else None
+            # the partial reset is only valid while every depth that was counted as "stores flows directly" does so
+            ranges = self._flow_reset_ranges if (B % 8 == 0 and not self._reference_compat
+                                                 and all(self._fusion_on(gi, True) for gi in self._fused)) else None
             if ranges is None:
                 _fill(self.node_flows, reset)
             else:                                            # every other row is rewritten by a direct store

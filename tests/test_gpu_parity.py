@@ -246,34 +246,63 @@ def test_c_abi_direct_calls():
 
 
 @pytest.mark.parametrize("homogeneous", [True, False])
-@pytest.mark.parametrize("B", [64, 192])
+@pytest.mark.parametrize("B", [32, 64, 192, 256, 320])
 def test_dense_layers_match_oracle_and_tiled_kernels(B, homogeneous):
     """Deep tables (here 1024 x 1024 transition blocks) take the two-step dense path: operand pre-pass plus a GEMM
-    over pre-tiled operands, parameter flows of tied layers in one product over their concatenated batches.  Checked
-    against the oracle, against the tile-at-a-time kernels, and over repeated (eager, captured, replayed) steps."""
+    over pre-tiled operands, parameter flows of tied layers in one product over their concatenated batches.  The
+    wide-tile kernels (128 rows x up to 256 samples, split contraction, product layer folded in, flows stored directly
+    into the children's rows) are checked against the oracle, against the first-generation dense kernels (batches
+    that are multiples of 64) and against the tile-at-a-time kernels, over repeated (eager, captured, replayed) steps."""
     from pyjuice_b200.layers import SumLayer
     torch.manual_seed(3)
     ns = pj.structures.HMM(seq_length=5, num_latents=1024, num_emits=16, homogeneous=homogeneous)
     ns.init_parameters()
     pc = pj.compile(ns).to(DEV)
     x = torch.randint(0, 16, (B, 5))
-    assert any(l._dense_ok(0, B, False) for g in pc.inner_layer_groups if g.is_sum() for l in g), "expected dense tables"
+    assert any(l._wide_ok(0, B, False) for g in pc.inner_layer_groups if g.is_sum() for l in g), "expected dense tables"
+    assert any(f.get("dense") for f in pc._fused.values()), "expected depths with the product layer folded into the dense kernels"
     for rep in range(3):
         check_against_oracle(pc, x, step=0.05, pseudo=0.1)
     check_against_oracle(pc, x, step=0.05, pseudo=0.1, logspace_flows=False)
     out = {}
     try:
-        for dense in (True, False):
-            SumLayer.use_dense_kernels = dense
+        for mode, (dense, wide) in {"wide": (True, True), "dense": (True, False), "tiled": (False, False)}.items():
+            SumLayer.use_dense_kernels, SumLayer.use_wide_dense = dense, wide
             pc.init_param_flows(flows_memory=0.0)
             lls = pc(x.to(DEV))
             pc.backward(x.to(DEV))
             torch.cuda.synchronize()
-            out[dense] = (lls.clone(), pc.node_flows[pc.num_dummy_nodes:].exp().clone(), pc.param_flows.clone())
+            out[mode] = (lls.clone(), pc.node_flows[pc.num_dummy_nodes:].exp().clone(), pc.param_flows.clone())
     finally:
-        SumLayer.use_dense_kernels = True
-    for a, b in zip(out[True], out[False]):
-        assert torch.allclose(a, b, rtol=2e-4, atol=1e-6), (a - b).abs().max()
+        SumLayer.use_dense_kernels, SumLayer.use_wide_dense = True, True
+    for other in ("dense", "tiled"):
+        for a, b in zip(out["wide"], out[other]):
+            assert torch.allclose(a, b, rtol=2e-4, atol=1e-6), (other, (a - b).abs().max())
+    # two runs of the split contraction give bit-equal results: partial tiles are added in a fixed order
+    pc.init_param_flows(flows_memory=0.0)
+    lls2 = pc(x.to(DEV))
+    assert torch.equal(lls2, out["wide"][0])
+    _lib_status()
+
+
+def test_wide_dense_kernels_without_folding_and_with_weights():
+    """The wide-tile kernels behind the per-layer interface (element_mars / element_flows in use, no folding), and a
+    weighted backward pass."""
+    torch.manual_seed(4)
+    ns = pj.structures.HMM(seq_length=4, num_latents=1024, num_emits=12, homogeneous=True)
+    ns.init_parameters()
+    pc = pj.compile(ns).to(DEV)
+    pc.fuse_product_layers = False
+    x = torch.randint(0, 12, (72, 4))
+    check_against_oracle(pc, x, step=0.1, pseudo=0.1)
+    pc.fuse_product_layers = True
+    w = torch.rand(72) + 0.5
+    ref_lls, st, _ = oracle_step(pc, x, ll_weights=w)
+    pc.init_param_flows(flows_memory=0.0)
+    pc(x.to(DEV))
+    pc.backward(x.to(DEV), ll_weights=w.to(DEV))
+    ok, err = rel_close(pc.param_flows, st.param_flows)
+    assert ok, err
     _lib_status()
 
 
