@@ -52,6 +52,9 @@ CONFIGS = {
     "cfg2": ("PD-28x28 256cats K=64 splits[4,7,14]", 512),
     "cfg3": ("RAT-SPN-784 256cats depth5 rep16 K=32", 1024),
     "cfg4": ("HMM 4096 states vocab32768 T=128 tied", 256),
+    # profiling case: the layer shape of cfg4 (4096 x 4096 tied transitions, 256 samples) in a circuit small enough
+    # for multi-pass profiler captures (8 tokens, 2048-word vocabulary: well under 1 GB on the device)
+    "cfg4-short": ("HMM 4096 states vocab2048 T=8 tied (profiling case)", 256),
 }
 
 
@@ -136,6 +139,10 @@ def build_workload(name: str, num_samples: int, lib=None):
         torch.manual_seed(4)
         ns = lib.hmm(128, 4096, 32768)
         x = pdata.hmm_samples(num_samples, 128, 32768, seed=4)
+    elif name == "cfg4-short":
+        torch.manual_seed(4)
+        ns = lib.hmm(8, 4096, 2048)
+        x = pdata.hmm_samples(num_samples, 8, 2048, seed=4)
     else:
         raise ValueError(name)
     ns.init_parameters()

@@ -78,6 +78,24 @@ int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* d
                       const int32_t* vids, const int32_t* s_pfids, const int32_t* node_cats, int max_cats,
                       int64_t n_nodes, int64_t node_off, int B, int logspace, void* stream);
 
+/* Categorical leaves with very large tables (too many categories to stage a node's table in shared memory): the same
+ * two operators on a transposed shadow of the parameter table.  logp_t[c * n_rows + r] = log params[r * num_cats + c]
+ * (pcx_input_cat_shadow, once per parameter update); prow[n] = row of node n (= s_pids[n] / num_cats); flows are
+ * accumulated into flows_t[c * n_rows + r] (zero-initialised by the caller) and moved into the reference's layout by
+ * pcx_input_cat_flush_t: param_flows[row_pfid[r] + c] += flows_t[c, r], flows_t = 0.  Flows of tied replicas all land
+ * in their source row.  B must be a multiple of 4.  Replace, like the two entry points above, Categorical.fw_mar_fn /
+ * bk_flow_fn (nodes/distributions/categorical.py:82-120) and layer/kernels/c/input_layers/cat_backward.cu:24-52,
+ * whose histogram does not cover tied or large tables (layer/input_layer.py:304-316). */
+int pcx_input_cat_shadow(float* logp_t, const float* params, int64_t n_rows, int num_cats, void* stream);
+int pcx_input_cat_fwd_t(float* node_mars, const float* logp_t, const void* data, int data_elsize, const int32_t* vids,
+                        const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
+                        void* stream);
+int pcx_input_cat_bwd_t(float* flows_t, const float* node_flows, const void* data, int data_elsize, const int32_t* vids,
+                        const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
+                        int logspace, void* stream);
+int pcx_input_cat_flush_t(float* param_flows, float* flows_t, const int64_t* row_pfid, int64_t n_rows, int num_cats,
+                          void* stream);
+
 /* Product layer forward:  element_mars[nids[i]+j, b] = sum_c node_mars[cids[i,c]+j, b]   (cids == 0 skipped).
  * Replaces ProdLayer.forward -> _forward_backward_kernel_2d
  * (layer/prod_layer.py:161-205, 263-369; layer/kernels/prod.py:156-226 with accum=False). */

@@ -158,6 +158,130 @@ input_cat_bwd_staged(float* __restrict__ param_flows, const float* __restrict__ 
     }
 }
 
+// ---- Categorical leaves with tables too large to stage (tens of thousands of categories) ---------------------------
+// The parameter table is [row, category] (a row = the distribution of one source node).  Nodes of one variable are
+// consecutive rows, so a lookup of category c for 128 consecutive nodes touches 128 different rows: one 32-byte
+// sector per useful float.  These kernels work on a TRANSPOSED shadow instead: logp_T[category, row] (the logarithm is
+// taken once per update) and flows_T[category, row], in which the same lookup is 512 contiguous bytes.
+//   forward   tile of 128 nodes x 64 samples: per sample a coalesced read of the shadow, staged in shared memory,
+//             written out as whole 256-byte pieces of the nodes' rows
+//   backward  the same tile read coalesced, then per sample one coalesced reduction into flows_T
+//   flush     param_flows[row_pfid[row] + c] += flows_T[c, row]; flows_T = 0   (tiled transpose)
+// Flows of tied replicas all land in the source node's row of flows_T, so nothing is left to fold afterwards.
+constexpr int kTN = 128, kTS = 64;
+
+__global__ void __launch_bounds__(256)
+input_cat_shadow_kernel(float* __restrict__ logp_t, const float* __restrict__ params, int64_t R, int C) {
+    __shared__ float tile[32][33];
+    const int64_t r0 = (int64_t)blockIdx.x * 32;
+    const int c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int k = ty; k < 32; k += 8) {
+        const int64_t r = r0 + k;
+        const int c = c0 + tx;
+        tile[k][tx] = (r < R && c < C) ? logf(params[r * C + c]) : 0.0f;
+    }
+    __syncthreads();
+    for (int k = ty; k < 32; k += 8) {
+        const int c = c0 + k;
+        const int64_t r = r0 + tx;
+        if (c < C && r < R) logp_t[(int64_t)c * R + r] = tile[tx][k];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+input_cat_fwd_t_kernel(float* __restrict__ node_mars, const float* __restrict__ logp_t,
+                       const void* __restrict__ data, int elsize, const int32_t* __restrict__ vids,
+                       const int32_t* __restrict__ prow, int64_t R, int C, int64_t n_nodes, int64_t node_off, int B) {
+    __shared__ float tile[kTN][kTS + 1];
+    const int64_t n0 = (int64_t)blockIdx.x * kTN;
+    const int b0 = blockIdx.y * kTS;
+    const int nl = threadIdx.x & (kTN - 1), h = threadIdx.x >> 7;
+    const int64_t n = n0 + nl;
+    if (n < n_nodes) {
+        const int64_t drow = (int64_t)vids[n] * B;
+        const int64_t pr = prow[n];
+#pragma unroll 8
+        for (int s = h * (kTS / 2); s < (h + 1) * (kTS / 2); ++s) {
+            const int b = b0 + s;
+            float x = 0.0f;
+            if (b < B) {
+                const int c = min(max(pcx_load_cat(data, elsize, drow + b), 0), C - 1);
+                x = logp_t[(int64_t)c * R + pr];
+            }
+            tile[nl][s] = x;
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < kTN * (kTS / 4); idx += 256) {       // B is a multiple of 4
+        const int row = idx / (kTS / 4), f = (idx % (kTS / 4)) * 4;
+        if (n0 + row < n_nodes && b0 + f < B)
+            *reinterpret_cast<float4*>(node_mars + (node_off + n0 + row) * B + b0 + f) =
+                make_float4(tile[row][f], tile[row][f + 1], tile[row][f + 2], tile[row][f + 3]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+input_cat_bwd_t_kernel(float* __restrict__ flows_t, const float* __restrict__ node_flows,
+                       const void* __restrict__ data, int elsize, const int32_t* __restrict__ vids,
+                       const int32_t* __restrict__ prow, int64_t R, int C, int64_t n_nodes, int64_t node_off, int B,
+                       int logspace) {
+    __shared__ float tile[kTN][kTS + 1];
+    const int64_t n0 = (int64_t)blockIdx.x * kTN;
+    const int b0 = blockIdx.y * kTS;
+    for (int idx = threadIdx.x; idx < kTN * (kTS / 4); idx += 256) {
+        const int row = idx / (kTS / 4), f = (idx % (kTS / 4)) * 4;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (n0 + row < n_nodes && b0 + f < B) {
+            q = *reinterpret_cast<const float4*>(node_flows + (node_off + n0 + row) * B + b0 + f);
+            if (logspace) q = make_float4(__expf(q.x), __expf(q.y), __expf(q.z), __expf(q.w));
+        }
+        tile[row][f] = q.x; tile[row][f + 1] = q.y; tile[row][f + 2] = q.z; tile[row][f + 3] = q.w;
+    }
+    __syncthreads();
+    const int nl = threadIdx.x & (kTN - 1), h = threadIdx.x >> 7;
+    const int64_t n = n0 + nl;
+    if (n >= n_nodes) return;
+    const int64_t drow = (int64_t)vids[n] * B;
+    const int64_t pr = prow[n];
+#pragma unroll 4
+    for (int s = h * (kTS / 2); s < (h + 1) * (kTS / 2); ++s) {
+        const int b = b0 + s;
+        if (b >= B) break;
+        const float x = tile[nl][s];
+        const int c = pcx_load_cat(data, elsize, drow + b);
+        if (x != 0.0f && c >= 0 && c < C) atomicAdd(flows_t + (int64_t)c * R + pr, x);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+input_cat_flush_t_kernel(float* __restrict__ param_flows, float* __restrict__ flows_t,
+                         const int64_t* __restrict__ row_pfid, int64_t R, int C) {
+    __shared__ float tile[32][33];
+    const int64_t r0 = (int64_t)blockIdx.x * 32;
+    const int c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int k = ty; k < 32; k += 8) {
+        const int c = c0 + k;
+        const int64_t r = r0 + tx;
+        float x = 0.0f;
+        if (c < C && r < R) {
+            x = flows_t[(int64_t)c * R + r];
+            if (x != 0.0f) flows_t[(int64_t)c * R + r] = 0.0f;
+        }
+        tile[k][tx] = x;
+    }
+    __syncthreads();
+    for (int k = ty; k < 32; k += 8) {
+        const int64_t r = r0 + k;
+        const int c = c0 + tx;
+        if (r < R && c < C) {
+            const float x = tile[tx][k];
+            if (x != 0.0f) param_flows[row_pfid[r] + c] += x;
+        }
+    }
+}
+
 // Nodes per CTA of the staged kernels: up to 16, limited by 32 KB of shared memory; 0 = table too large to stage.
 inline int stage_group(int max_cats) {
     if (max_cats <= 0) return 0;
@@ -331,6 +455,49 @@ int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* d
         input_cat_bwd_kernel<<<(unsigned)n_nodes, B >= 256 ? 256 : 128, 0, (cudaStream_t)stream>>>(
             param_flows, node_flows, data, data_elsize, vids, s_pfids, node_cats, max_cats, n_nodes, node_off, B, logspace);
     }
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_input_cat_shadow(float* logp_t, const float* params, int64_t n_rows, int num_cats, void* stream) {
+    if (n_rows <= 0 || num_cats <= 0) return 0;
+    dim3 grid((unsigned)pcx_cdiv(n_rows, 32), (unsigned)pcx_cdiv(num_cats, 32));
+    input_cat_shadow_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(logp_t, params, n_rows, num_cats);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_input_cat_fwd_t(float* node_mars, const float* logp_t, const void* data, int data_elsize, const int32_t* vids,
+                        const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
+                        void* stream) {
+    if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
+    if (n_nodes <= 0 || B <= 0) return 0;
+    if (B % 4 != 0 || num_cats <= 0 || (reinterpret_cast<uintptr_t>(node_mars) & 15) != 0) return -1;
+    dim3 grid((unsigned)pcx_cdiv(n_nodes, kTN), (unsigned)pcx_cdiv(B, kTS));
+    input_cat_fwd_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(node_mars, logp_t, data, data_elsize, vids, prow,
+                                                                   n_rows, num_cats, n_nodes, node_off, B);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_input_cat_bwd_t(float* flows_t, const float* node_flows, const void* data, int data_elsize, const int32_t* vids,
+                        const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
+                        int logspace, void* stream) {
+    if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
+    if (n_nodes <= 0 || B <= 0) return 0;
+    if (B % 4 != 0 || num_cats <= 0 || (reinterpret_cast<uintptr_t>(node_flows) & 15) != 0) return -1;
+    dim3 grid((unsigned)pcx_cdiv(n_nodes, kTN), (unsigned)pcx_cdiv(B, kTS));
+    input_cat_bwd_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(flows_t, node_flows, data, data_elsize, vids, prow,
+                                                                   n_rows, num_cats, n_nodes, node_off, B, logspace);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_input_cat_flush_t(float* param_flows, float* flows_t, const int64_t* row_pfid, int64_t n_rows, int num_cats,
+                          void* stream) {
+    if (n_rows <= 0 || num_cats <= 0) return 0;
+    dim3 grid((unsigned)pcx_cdiv(n_rows, 32), (unsigned)pcx_cdiv(num_cats, 32));
+    input_cat_flush_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(param_flows, flows_t, row_pfid, n_rows, num_cats);
     PCX_LAUNCH_CHECK();
     return 0;
 }

@@ -118,57 +118,79 @@ __device__ __forceinline__ void wide_finish(const WideArgs& a, int64_t i, int r0
     const float* sh = a.shift + (int64_t)a.b_group[i] * a.B + b0;
     const int64_t erow = i * a.row_block + r0 + row;                 // index of this output row in its table
     const int64_t orow = ((int64_t)a.rows[i] + r0 + row) * a.B + b0;
-    int fk[8];
-    if (EPI == W_ELE && a.fkids != nullptr) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) fk[q] = (q < a.fc) ? a.fkids[erow * a.fc + q] : 0;
-    }
+    const int nv = min(32, a.B - b0);                                // valid columns: B is a multiple of 4
+    float o[32];
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
-        if (b0 + j >= a.B) break;                                    // B is a multiple of 4
-        const float4 m4 = *reinterpret_cast<const float4*>(sh + j);
-        const float m[4] = {m4.x, m4.y, m4.z, m4.w};
-        float o[4];
+        if (j < nv) {
+            const float4 m4 = *reinterpret_cast<const float4*>(sh + j);
+            const float m[4] = {m4.x, m4.y, m4.z, m4.w};
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const float x = v[j + t];
-            if (EPI == W_FWD) o[t] = (m[t] == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(x, 1e-24f)) + m[t];
-            else o[t] = (m[t] == PCX_NEG_INF || x <= 0.0f) ? PCX_NEG_INF : __logf(x) + m[t];
+            for (int t = 0; t < 4; ++t) {
+                const float x = v[j + t];
+                if (EPI == W_FWD) o[j + t] = (m[t] == PCX_NEG_INF) ? PCX_NEG_INF : __logf(fmaxf(x, 1e-24f)) + m[t];
+                else o[j + t] = (m[t] == PCX_NEG_INF || x <= 0.0f) ? PCX_NEG_INF : __logf(x) + m[t];
+            }
         }
-        if (EPI == W_FWD) {
-            *reinterpret_cast<float4*>(a.out + orow + j) = make_float4(o[0], o[1], o[2], o[3]);
-            continue;
-        }
-        float em[4];
-        if (a.fkids != nullptr) {                                    // element value = sum of the children's rows
-            bool any = false;
-            em[0] = em[1] = em[2] = em[3] = 0.0f;
+    }
+    if (EPI == W_FWD) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                if (q < a.fc && fk[q] != 0) {
-                    const float4 c4 = *reinterpret_cast<const float4*>(a.nmars + (int64_t)fk[q] * a.B + b0 + j);
-                    em[0] += c4.x; em[1] += c4.y; em[2] += c4.z; em[3] += c4.w;
-                    any = true;
+        for (int j = 0; j < 32; j += 4)
+            if (j < nv) *reinterpret_cast<float4*>(a.out + orow + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        return;
+    }
+    // element flows: all loads of the element's value first (they overlap), then the stores
+    float em[32];
+    int fk[8];
+    if (a.fkids != nullptr) {                                        // element value = sum of the children's rows
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { fk[q] = (q < a.fc) ? a.fkids[erow * a.fc + q] : 0; any = any || fk[q] != 0; }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) em[j] = any ? 0.0f : PCX_NEG_INF;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (fk[q] != 0) {
+                const float* src = a.nmars + (int64_t)fk[q] * a.B + b0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    if (j < nv) {
+                        const float4 c4 = *reinterpret_cast<const float4*>(src + j);
+                        em[j] += c4.x; em[j + 1] += c4.y; em[j + 2] += c4.z; em[j + 3] += c4.w;
+                    }
                 }
             }
-            if (!any) em[0] = em[1] = em[2] = em[3] = PCX_NEG_INF;
-        } else {
-            const float4 e4 = *reinterpret_cast<const float4*>(a.emars + orow + j);
-            em[0] = e4.x; em[1] = e4.y; em[2] = e4.z; em[3] = e4.w;
         }
+    } else {
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            o[t] = (o[t] == PCX_NEG_INF || em[t] == PCX_NEG_INF) ? PCX_NEG_INF : o[t] + em[t];
-            if (!a.logspace) o[t] = __expf(o[t]);
+        for (int j = 0; j < 32; j += 4) {
+            if (j < nv) {
+                const float4 e4 = *reinterpret_cast<const float4*>(a.emars + orow + j);
+                em[j] = e4.x; em[j + 1] = e4.y; em[j + 2] = e4.z; em[j + 3] = e4.w;
+            }
         }
-        const float4 o4 = make_float4(o[0], o[1], o[2], o[3]);
-        if (a.fkids != nullptr && a.direct) {                         // every child has this one parent: plain stores
+    }
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (q < a.fc && fk[q] != 0) *reinterpret_cast<float4*>(a.nflows + (int64_t)fk[q] * a.B + b0 + j) = o4;
-        } else {
-            *reinterpret_cast<float4*>(a.out + orow + j) = o4;
+    for (int j = 0; j < 32; ++j) {
+        if (j < nv) {
+            o[j] = (o[j] == PCX_NEG_INF || em[j] == PCX_NEG_INF) ? PCX_NEG_INF : o[j] + em[j];
+            if (!a.logspace) o[j] = __expf(o[j]);
         }
+    }
+    if (a.fkids != nullptr && a.direct) {                             // every child has this one parent: plain stores
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (fk[q] != 0) {
+                float* dst = a.nflows + (int64_t)fk[q] * a.B + b0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    if (j < nv) *reinterpret_cast<float4*>(dst + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            if (j < nv) *reinterpret_cast<float4*>(a.out + orow + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
     }
 }
 
@@ -370,50 +392,53 @@ struct WidePrepArgs {
     const int32_t* fk_row;      // folded: [Kfw][fc]
     int Kfw;
     int n_chunks_total, slot;
+    int cs;                     // CTAs (one cluster) that share the operand rows of a group
 };
 
-// Eight consecutive samples of operand row k, in the log domain.
+// Eight consecutive samples of operand row k, in the log domain.  Every load is unconditional (row 0 of each value
+// buffer exists; what it holds is replaced by a select), so that the loads of several rows are in flight together.
 template <int FC>
 __device__ __forceinline__ void wide_prep_value(const WidePrepArgs& a, int g, int k, int b0, float* v) {
-#pragma unroll
-    for (int s = 0; s < 8; ++s) v[s] = PCX_NEG_INF;
-    if (k >= a.depth) return;
+    const bool in = k < a.depth;
     if (a.mode == 0) {
-        const int64_t at = (int64_t)a.group_row[g] * a.K + k;
+        const int64_t at = (int64_t)a.group_row[g] * a.K + (in ? k : 0);
         if (FC == 0) {
-            const int cid = a.kids[at];
-            if (cid == 0) return;
+            const int cid = in ? a.kids[at] : 0;
             const float4 p = *reinterpret_cast<const float4*>(a.src + (int64_t)cid * a.B + b0);
             const float4 q = *reinterpret_cast<const float4*>(a.src + (int64_t)cid * a.B + b0 + 4);
-            v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
+            const float x[8] = {p.x, p.y, p.z, p.w, q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int s = 0; s < 8; ++s) v[s] = cid != 0 ? x[s] : PCX_NEG_INF;
             return;
         }
         int fk[FC > 0 ? FC : 1];
         bool any = false;
 #pragma unroll
-        for (int j = 0; j < FC; ++j) { fk[j] = a.fkids[at * FC + j]; any = any || fk[j] != 0; }
-        if (!any) return;
+        for (int j = 0; j < FC; ++j) { fk[j] = in ? a.fkids[at * FC + j] : 0; any = any || fk[j] != 0; }
+        float4 p[FC > 0 ? FC : 1], q[FC > 0 ? FC : 1];
+#pragma unroll
+        for (int j = 0; j < FC; ++j) {
+            p[j] = *reinterpret_cast<const float4*>(a.src + (int64_t)fk[j] * a.B + b0);
+            q[j] = *reinterpret_cast<const float4*>(a.src + (int64_t)fk[j] * a.B + b0 + 4);
+        }
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < FC; ++j) {                               // row 0 exists and holds zeros: load it regardless
-            const float4 p = *reinterpret_cast<const float4*>(a.src + (int64_t)fk[j] * a.B + b0);
-            const float4 q = *reinterpret_cast<const float4*>(a.src + (int64_t)fk[j] * a.B + b0 + 4);
-            const float w = fk[j] != 0 ? 1.0f : 0.0f;
-            acc[0] += w * p.x; acc[1] += w * p.y; acc[2] += w * p.z; acc[3] += w * p.w;
-            acc[4] += w * q.x; acc[5] += w * q.y; acc[6] += w * q.z; acc[7] += w * q.w;
+        for (int j = 0; j < FC; ++j) {
+            if (fk[j] != 0) {
+                acc[0] += p[j].x; acc[1] += p[j].y; acc[2] += p[j].z; acc[3] += p[j].w;
+                acc[4] += q[j].x; acc[5] += q[j].y; acc[6] += q[j].z; acc[7] += q[j].w;
+            }
         }
 #pragma unroll
-        for (int s = 0; s < 8; ++s) v[s] = acc[s];
+        for (int s = 0; s < 8; ++s) v[s] = any ? acc[s] : PCX_NEG_INF;
         return;
     }
-    int64_t r;
-    if (a.mode == 1) {
-        const int pr = a.kids[(int64_t)a.group_row[g] * a.K + k / a.par_block];
-        if (pr == 0) return;
-        r = (int64_t)pr + k % a.par_block;
-    } else {
-        r = (int64_t)a.kids[k / a.par_block] + k % a.par_block;
-    }
+    const int kk = in ? k : 0;
+    int pr;
+    if (a.mode == 1) pr = a.kids[(int64_t)a.group_row[g] * a.K + kk / a.par_block];
+    else pr = a.kids[kk / a.par_block];
+    const bool live = in && pr != 0;
+    const int64_t r = live ? (int64_t)pr + kk % a.par_block : 0;
     const float4 f0 = *reinterpret_cast<const float4*>(a.src + r * a.B + b0);
     const float4 f1 = *reinterpret_cast<const float4*>(a.src + r * a.B + b0 + 4);
     const float4 m0 = *reinterpret_cast<const float4*>(a.src2 + r * a.B + b0);
@@ -424,24 +449,31 @@ __device__ __forceinline__ void wide_prep_value(const WidePrepArgs& a, int g, in
     for (int s = 0; s < 8; ++s) {
         float x = f[s];
         if (!a.logspace) x = (x > 0.0f) ? __logf(x) : PCX_NEG_INF;
-        v[s] = (m[s] == PCX_NEG_INF || x == PCX_NEG_INF) ? PCX_NEG_INF : x - m[s];
+        v[s] = (!live || m[s] == PCX_NEG_INF || x == PCX_NEG_INF) ? PCX_NEG_INF : x - m[s];
     }
 }
 
-// Shared-memory staging of the log-domain values of all operand rows for the CTA's eight samples, and the per-sample
-// maximum: returns it in sh[0..8) to every thread.  s_val is [8][ld] floats, ld = depth_pad + 4.
+// The operand rows of a group are split over the `cs` CTAs of a cluster (whole 64-row chunks each); every CTA stages
+// the log-domain values of ITS rows for the eight samples in shared memory ([8][ld] floats) and the per-sample maximum
+// over ALL rows is formed by exchanging the CTAs' maxima through distributed shared memory.  Returns it in sh[0..8).
 template <int FC>
-__device__ __forceinline__ void wide_prep_stage(const WidePrepArgs& a, int g, int b0, float* s_val, int ld, float* s_red, float* sh) {
+__device__ __forceinline__ void wide_prep_stage(const WidePrepArgs& a, int g, int b0, int k_begin, int rows_here,
+                                                float* s_val, int ld, float* s_red, float* s_peer, float* sh) {
     const int tid = threadIdx.x;
     float mx[8];
 #pragma unroll
     for (int s = 0; s < 8; ++s) mx[s] = PCX_NEG_INF;
-#pragma unroll 4
-    for (int k = tid; k < a.depth_pad; k += W_PREP_THREADS) {
-        float v[8];
-        wide_prep_value<FC>(a, g, k, b0, v);
+    for (int k = tid; k < rows_here; k += 2 * W_PREP_THREADS) {      // two rows per round: their loads overlap
+        const int k2 = k + W_PREP_THREADS;
+        float v[8], w[8];
+        wide_prep_value<FC>(a, g, k_begin + k, b0, v);
+        wide_prep_value<FC>(a, g, k2 < rows_here ? k_begin + k2 : a.depth, b0, w);
 #pragma unroll
         for (int s = 0; s < 8; ++s) { s_val[s * ld + k] = v[s]; mx[s] = fmaxf(mx[s], v[s]); }
+        if (k2 < rows_here) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) { s_val[s * ld + k2] = w[s]; mx[s] = fmaxf(mx[s], w[s]); }
+        }
     }
 #pragma unroll
     for (int s = 0; s < 8; ++s)
@@ -452,37 +484,59 @@ __device__ __forceinline__ void wide_prep_stage(const WidePrepArgs& a, int g, in
         for (int s = 0; s < 8; ++s) s_red[(tid >> 5) * 8 + s] = mx[s];
     }
     __syncthreads();
+    if (a.cs > 1) {
+        const uint32_t me = cluster_cta_rank();
+        if (tid < 8) {
+            float m = PCX_NEG_INF;
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-        float m = PCX_NEG_INF;
+            for (int w = 0; w < W_PREP_THREADS / 32; ++w) m = fmaxf(m, s_red[w * 8 + tid]);
+            for (int r = 0; r < a.cs; ++r)
+                cluster_store(cluster_map(smem_u32(s_peer + me * 8 + tid), (uint32_t)r), m);
+        }
+        cluster_sync_all();
 #pragma unroll
-        for (int w = 0; w < W_PREP_THREADS / 32; ++w) m = fmaxf(m, s_red[w * 8 + s]);
-        sh[s] = m;
+        for (int s = 0; s < 8; ++s) {
+            float m = PCX_NEG_INF;
+            for (int r = 0; r < a.cs; ++r) m = fmaxf(m, s_peer[r * 8 + s]);
+            sh[s] = m;
+        }
+    } else {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            float m = PCX_NEG_INF;
+#pragma unroll
+            for (int w = 0; w < W_PREP_THREADS / 32; ++w) m = fmaxf(m, s_red[w * 8 + s]);
+            sh[s] = m;
+        }
     }
 }
 
-// FWD / ELE operand tiles (contraction over operand rows).  Grid (ceil(B / 8), n_groups), 512 threads.
+// FWD / ELE operand tiles (contraction over operand rows).  Grid (ceil(B / 8), n_groups, cs), clusters of cs along z,
+// 512 threads.
 template <int FC>
 __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_rows_kernel(const WidePrepArgs a) {
     extern __shared__ float s_dyn[];
     __shared__ float s_red[(W_PREP_THREADS / 32) * 8];
+    __shared__ float s_peer[8 * 8];
     const int tid = threadIdx.x, g = blockIdx.y;
     const int b0 = blockIdx.x * W_PREP_SAMPLES;                      // B is a multiple of 8
-    const int ld = a.depth_pad + 4;
+    const int rows_here = a.depth_pad / a.cs;
+    const int k_begin = blockIdx.z * rows_here;
+    const int ld = rows_here + 4;
     float sh[8];
-    wide_prep_stage<FC>(a, g, b0, s_dyn, ld, s_red, sh);
-    if (tid < 8) a.shift[(int64_t)g * a.B + b0 + tid] = sh[tid];
+    wide_prep_stage<FC>(a, g, b0, k_begin, rows_here, s_dyn, ld, s_red, s_peer, sh);
+    if (blockIdx.z == 0 && tid < 8) a.shift[(int64_t)g * a.B + b0 + tid] = sh[tid];
 
     const int tile_bytes = 2 * 8 * a.DN * 16;
-    const int items = a.depth_pad;                                   // (depth_pad / 8) K-groups x 8 samples
-    for (int it = tid; it < items; it += W_PREP_THREADS) {
-        const int s = it & 7, kg = it >> 3;
-        const float4 p = *reinterpret_cast<const float4*>(s_dyn + s * ld + kg * 8);
-        const float4 q = *reinterpret_cast<const float4*>(s_dyn + s * ld + kg * 8 + 4);
+    for (int it = tid; it < rows_here; it += W_PREP_THREADS) {       // (rows / 8) K-groups x 8 samples
+        const int s = it & 7, kl = it >> 3;
+        const float4 p = *reinterpret_cast<const float4*>(s_dyn + s * ld + kl * 8);
+        const float4 q = *reinterpret_cast<const float4*>(s_dyn + s * ld + kl * 8 + 4);
         const float x[8] = {p.x, p.y, p.z, p.w, q.x, q.y, q.z, q.w};
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = (x[j] == PCX_NEG_INF || sh[s] == PCX_NEG_INF) ? 0.0f : __expf(x[j] - sh[s]);
+        const int kg = k_begin / 8 + kl;
         const int b = b0 + s;
         const int jt = b / a.DN, bl = b % a.DN;
         uint8_t* tile = a.tiles + (((size_t)g * a.n_ct + jt) * a.n_chunks + (kg >> 3)) * tile_bytes;
@@ -494,25 +548,30 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_rows_kernel(const Wi
 // Parameter-flow operands of one layer (contraction over the batch), into the columns of slot `slot`:
 // X tile (row tile mt, chunk cc): [8 sample groups][128 rows][8 samples] hi, lo; Y tile (edge tile et of 256, chunk cc):
 // [8 sample groups][256 edges][8 samples] hi, lo.  The concatenated sample index of (slot, b) is slot * B + b.
-// Grid (ceil(B / 8)), 512 threads.
+// Grid (ceil(B / 8), 1, cs), clusters of cs along z (rows and edges are split over the cluster), 512 threads.
 template <int FC>
 __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const WidePrepArgs a) {
     extern __shared__ float s_dyn[];
     __shared__ float s_red[(W_PREP_THREADS / 32) * 8];
+    __shared__ float s_peer[8 * 8];
     const int tid = threadIdx.x;
     const int b0 = blockIdx.x * W_PREP_SAMPLES;
-    const int ld = a.depth_pad + 4;
+    const int rows_here = a.depth_pad / a.cs;
+    const int k_begin = blockIdx.z * rows_here;
+    const int ld = rows_here + 4;
     float sh[8];
-    wide_prep_stage<0>(a, 0, b0, s_dyn, ld, s_red, sh);              // mode 2: rows of the layer, flow - value
+    wide_prep_stage<0>(a, 0, b0, k_begin, rows_here, s_dyn, ld, s_red, s_peer, sh);   // mode 2: flow - value of the layer's rows
 
     const int64_t q0 = (int64_t)a.slot * a.B + b0;
     const int64_t cc = q0 / KC;
     const int sg = (int)(q0 % KC) / 8;
-    for (int r = tid; r < a.depth; r += W_PREP_THREADS) {
+    for (int rl = tid; rl < rows_here; rl += W_PREP_THREADS) {
+        const int r = k_begin + rl;
+        if (r >= a.depth) break;
         float v[8];
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const float x = s_dyn[s * ld + r];
+            const float x = s_dyn[s * ld + rl];
             v[s] = (x == PCX_NEG_INF || sh[s] == PCX_NEG_INF) ? 0.0f : __expf(x - sh[s]);
         }
         uint8_t* tile = a.tiles + ((size_t)(r / BM) * a.n_chunks_total + cc) * (2 * A_TILE);
@@ -520,7 +579,9 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
         store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + A_TILE), v);
     }
     constexpr int EN = 256;
-    for (int e = tid; e < a.Kfw; e += W_PREP_THREADS) {
+    const int e_per = (a.Kfw + a.cs - 1) / a.cs;
+    const int e_end = min(a.Kfw, (int)(blockIdx.z + 1) * e_per);
+    for (int e = blockIdx.z * e_per + tid; e < e_end; e += W_PREP_THREADS) {
         float em[8];
         bool live;
         if (FC == 0) {
@@ -533,15 +594,22 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
             live = false;
 #pragma unroll
             for (int s = 0; s < 8; ++s) em[s] = 0.0f;
+            int fk[FC > 0 ? FC : 1];
+            float4 p[FC > 0 ? FC : 1], q[FC > 0 ? FC : 1];
 #pragma unroll
-            for (int j = 0; j < (FC > 0 ? FC : 1); ++j) {
-                const int fk = a.fk_row[(int64_t)e * FC + j];
-                const float4 p = *reinterpret_cast<const float4*>(a.src2 + (int64_t)fk * a.B + b0);
-                const float4 q = *reinterpret_cast<const float4*>(a.src2 + (int64_t)fk * a.B + b0 + 4);
-                const float w = fk != 0 ? 1.0f : 0.0f;
-                live = live || fk != 0;
-                em[0] += w * p.x; em[1] += w * p.y; em[2] += w * p.z; em[3] += w * p.w;
-                em[4] += w * q.x; em[5] += w * q.y; em[6] += w * q.z; em[7] += w * q.w;
+            for (int j = 0; j < FC; ++j) fk[j] = a.fk_row[(int64_t)e * FC + j];
+#pragma unroll
+            for (int j = 0; j < FC; ++j) {
+                p[j] = *reinterpret_cast<const float4*>(a.src2 + (int64_t)fk[j] * a.B + b0);
+                q[j] = *reinterpret_cast<const float4*>(a.src2 + (int64_t)fk[j] * a.B + b0 + 4);
+            }
+#pragma unroll
+            for (int j = 0; j < FC; ++j) {
+                if (fk[j] != 0) {
+                    live = true;
+                    em[0] += p[j].x; em[1] += p[j].y; em[2] += p[j].z; em[3] += p[j].w;
+                    em[4] += q[j].x; em[5] += q[j].y; em[6] += q[j].z; em[7] += q[j].w;
+                }
             }
         }
         float v[8];
@@ -552,6 +620,33 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
         uint8_t* dst = tile + sg * (EN * 16) + (e % EN) * 16;
         store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + 8 * EN * 16), v);
     }
+}
+
+// CTAs per group that share the operand rows of a pre-pass (= its cluster size): whole 64-row chunks each.
+inline int wide_prep_cluster(int n_chunks) {
+    int cs = 1;
+    while (cs < 8 && n_chunks % (cs * 2) == 0 && n_chunks / (cs * 2) >= 4) cs *= 2;
+    return cs;
+}
+
+template <typename Kern>
+int wide_launch_prep(Kern kern, const WidePrepArgs& p, dim3 grid, size_t smem, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(W_PREP_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = grid.z > 1 ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return (int)e;
+    PCX_LAUNCH_CHECK();
+    return 0;
 }
 
 inline int wide_dn(int B) { return B > 128 ? 256 : (B > 64 ? 128 : 64); }
@@ -609,9 +704,7 @@ int launch_wide_prep_rows(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStr
     static bool done = false;
     int rc = wide_set_smem(wide_prep_rows_kernel<FC>, (W_MAX_DEPTH + 4) * 8 * (int)sizeof(float), &done);
     if (rc != 0) return rc;
-    wide_prep_rows_kernel<FC><<<grid, W_PREP_THREADS, smem, st>>>(p);
-    PCX_LAUNCH_CHECK();
-    return 0;
+    return wide_launch_prep(wide_prep_rows_kernel<FC>, p, grid, smem, st);
 }
 
 template <int FC>
@@ -619,9 +712,7 @@ int launch_wide_prep_par(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStre
     static bool done = false;
     int rc = wide_set_smem(wide_prep_par_kernel<FC>, (W_MAX_DEPTH + 4) * 8 * (int)sizeof(float), &done);
     if (rc != 0) return rc;
-    wide_prep_par_kernel<FC><<<grid, W_PREP_THREADS, smem, st>>>(p);
-    PCX_LAUNCH_CHECK();
-    return 0;
+    return wide_launch_prep(wide_prep_par_kernel<FC>, p, grid, smem, st);
 }
 
 struct WideScratch {
@@ -665,8 +756,9 @@ static int wide_rows_op(int mode, float* out, const float* src, const float* src
     p.par_block = (mode == 0) ? 1 : par_block; p.depth = depth; p.depth_pad = n_chunks * KC; p.B = B;
     p.logspace = logspace; p.mode = mode; p.DN = DN; p.n_ct = n_ct; p.n_chunks = n_chunks; p.tiles = w.tiles;
     p.shift = w.shift;
-    const dim3 pgrid((unsigned)(B / W_PREP_SAMPLES), (unsigned)n_groups);
-    const size_t psmem = (size_t)(p.depth_pad + 4) * 8 * sizeof(float);
+    p.cs = wide_prep_cluster(n_chunks);
+    const dim3 pgrid((unsigned)(B / W_PREP_SAMPLES), (unsigned)n_groups, (unsigned)p.cs);
+    const size_t psmem = (size_t)(p.depth_pad / p.cs + 4) * 8 * sizeof(float);
     int rc;
     const int pfc = (mode == 0 && fkids_prep != nullptr) ? fc : 0;
     if (pfc == 0) rc = launch_wide_prep_rows<0>(p, pgrid, psmem, st);
@@ -732,8 +824,9 @@ int pcx_sum_par_dense2_stage(void* x_tiles, void* y_tiles, const float* node_flo
     p.tiles = reinterpret_cast<uint8_t*>(x_tiles); p.y_tiles = reinterpret_cast<uint8_t*>(y_tiles);
     p.emars = element_mars; p.cids_row = cids_row; p.fk_row = fkids_row; p.fc = fc; p.Kfw = K;
     p.n_chunks_total = n_chunks_total; p.slot = slot;
-    const dim3 grid((unsigned)(B / W_PREP_SAMPLES));
-    const size_t smem = (size_t)(p.depth_pad + 4) * 8 * sizeof(float);
+    p.cs = wide_prep_cluster(p.depth_pad / KC);
+    const dim3 grid((unsigned)(B / W_PREP_SAMPLES), 1, (unsigned)p.cs);
+    const size_t smem = (size_t)(p.depth_pad / p.cs + 4) * 8 * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
     if (fkids_row == nullptr) return launch_wide_prep_par<0>(p, grid, smem, st);
     if (fc == 2) return launch_wide_prep_par<2>(p, grid, smem, st);

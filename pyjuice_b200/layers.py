@@ -183,11 +183,61 @@ class InputLayer(Layer, nn.Module):
         self.node_cats = self.metadata[self.s_mids].to(torch.int64)       # categories of every node
         self.max_cats = int(self.node_cats.max().item())
         self.params = nn.Parameter(torch.empty([max(self.num_parameters, 1)], dtype=torch.float32), requires_grad=False)
+        self._shadow = None
+        self._param_epoch = 0
         self.param_flows = None
         self._dev = {}
 
     def is_input(self):
         return True
+
+    # Tables with more categories than the staged kernels can hold in shared memory are looked up through a transposed
+    # shadow ([category, row] instead of [row, category]); flows are accumulated in the same layout and moved into
+    # `param_flows` (the reference's layout) whenever that tensor is read.
+    SHADOW_MIN_CATS = 8193
+
+    @property
+    def param_flows(self):
+        self._flush_shadow()
+        return self._param_flows
+
+    @param_flows.setter
+    def param_flows(self, value):
+        self._param_flows = value
+
+    def _setup_shadow(self, device):
+        self._shadow = None
+        C = self.max_cats
+        if device.type != "cuda" or C < self.SHADOW_MIN_CATS or int(self.node_cats.min()) != C:
+            return
+        s_pids = self.s_pids.cpu()
+        if self.num_parameters % C != 0 or bool((s_pids % C != 0).any()):
+            return
+        R = self.num_parameters // C
+        src = self.source_nids.cpu()
+        row_pfid = torch.full((R,), -1, dtype=torch.int64)
+        row_pfid[s_pids[src] // C] = self.s_pfids.cpu()[src]
+        if bool((row_pfid < 0).any()):
+            return
+        self._shadow = dict(R=R, C=C, prow=_dev_i32(s_pids // C, device), row_pfid=row_pfid.to(device), logp=None,
+                            flows=None, stamp=None, dirty=False)
+
+    def _shadow_ok(self, B: int) -> bool:
+        return self._shadow is not None and B % 4 == 0
+
+    def _flush_shadow(self):
+        """Move the flows accumulated in the transposed shadow into `param_flows` (source rows) and clear the shadow."""
+        sh = self._shadow
+        if sh is None or not sh["dirty"] or self._param_flows is None:
+            return
+        _lib.call("pcx_input_cat_flush_t", self._param_flows, sh["flows"], sh["row_pfid"], sh["R"], sh["C"])
+        sh["dirty"] = False
+
+    def _zero_shadow(self):
+        sh = self._shadow
+        if sh is not None and sh["dirty"]:
+            _fill(sh["flows"], 0.0)
+            sh["dirty"] = False
 
     def to(self, device):
         device = torch.device(f"cuda:{device}") if isinstance(device, int) else torch.device(device)
@@ -202,6 +252,7 @@ class InputLayer(Layer, nn.Module):
             self._dev = dict(vids=_dev_i32(self.vids[:, 0], device), s_pids=_dev_i32(self.s_pids, device),
                              s_pfids=_dev_i32(self.s_pfids, device), source_nids=_dev_i32(self.source_nids, device),
                              node_cats=_dev_i32(self.node_cats, device))
+        self._setup_shadow(device)
         return self
 
     def _init_parameters(self, perturbation: float):
@@ -220,12 +271,14 @@ class InputLayer(Layer, nn.Module):
 
     def init_param_flows(self, flows_memory: float = 1.0):
         """Stand-alone use only: inside a `TensorCircuit` the flows are a view into the circuit's flow arena."""
-        if self.param_flows is None or self.param_flows.device != self.device:
+        if self._param_flows is None or self._param_flows.device != self.device:
             self.param_flows = torch.zeros([self.num_param_flows], dtype=torch.float32, device=self.device)
+            self._zero_shadow()
         elif flows_memory == 0.0:
-            _fill(self.param_flows, 0.0)
+            self._zero_shadow()
+            _fill(self._param_flows, 0.0)
         elif flows_memory < 1.0:
-            _scale(self.param_flows, flows_memory)
+            _scale(self.param_flows, flows_memory)            # (reading the property moves shadow flows in first)
         self._tied_folded = False
 
     def _require_cuda(self):
@@ -238,6 +291,17 @@ class InputLayer(Layer, nn.Module):
         self._require_cuda()
         data = data.contiguous()
         B = node_mars.size(1)
+        if self._shadow_ok(B):
+            sh = self._shadow
+            stamp = (self.params.data_ptr(), self.params._version, self._param_epoch)
+            if sh["logp"] is None:
+                sh["logp"] = torch.empty(sh["R"] * sh["C"], dtype=torch.float32, device=self.device)
+            if sh["stamp"] != stamp:                        # parameters changed: transpose and take logarithms once
+                _lib.call("pcx_input_cat_shadow", sh["logp"], self.params.data, sh["R"], sh["C"])
+                sh["stamp"] = stamp
+            _lib.call("pcx_input_cat_fwd_t", node_mars, sh["logp"], data, data.element_size(), self._dev["vids"],
+                      sh["prow"], sh["R"], sh["C"], self.num_nodes, self._output_ind_range[0], B)
+            return
         _lib.call("pcx_input_cat_fwd", node_mars, self.params.data, data, data.element_size(),
                   self._dev["vids"], self._dev["s_pids"], self._dev["node_cats"], self.max_cats,
                   self.num_nodes, self._output_ind_range[0], B)
@@ -247,12 +311,21 @@ class InputLayer(Layer, nn.Module):
         """Adds the (linear) flow of every (node, sample) to the flow of the observed category."""
         _unsupported(params=params is not None, missing_mask=missing_mask is not None)
         self._require_cuda()
-        if self.param_flows is None:
+        if self._param_flows is None:
             self.init_param_flows()
         data = data.contiguous()
         B = node_flows.size(1)
+        if self._shadow_ok(B):
+            sh = self._shadow
+            if sh["flows"] is None:
+                sh["flows"] = torch.zeros(sh["R"] * sh["C"], dtype=torch.float32, device=self.device)
+            _lib.call("pcx_input_cat_bwd_t", sh["flows"], node_flows, data, data.element_size(), self._dev["vids"],
+                      sh["prow"], sh["R"], sh["C"], self.num_nodes, self._output_ind_range[0], B,
+                      int(bool(logspace_flows)))
+            sh["dirty"] = True                            # every flow lands in its source row: replicas stay as they are
+            return
         self._tied_folded = False                         # replica accumulators receive new flows
-        _lib.call("pcx_input_cat_bwd", self.param_flows, node_flows, data, data.element_size(),
+        _lib.call("pcx_input_cat_bwd", self._param_flows, node_flows, data, data.element_size(),
                   self._dev["vids"], self._dev["s_pfids"], self._dev["node_cats"], self.max_cats,
                   self.num_nodes, self._output_ind_range[0], B, int(bool(logspace_flows)))
 
@@ -267,16 +340,18 @@ class InputLayer(Layer, nn.Module):
         the fold can run any number of times; the flag only saves the pass when no backward pass has run since.
         (The reference leaves the replicas in place, so that with `flows_memory` in (0, 1) their decayed content is
         added to the source again at the next update; that double count is not reproduced.)"""
+        self._flush_shadow()
         if getattr(self, "_tied_folded", False):
             return
         for start, n, ch_pfids in self.tied2source_nids:
-            _lib.call("pcx_tied_accum", self.param_flows, int(start), int(n), ch_pfids, int(ch_pfids.numel()))
+            _lib.call("pcx_tied_accum", self._param_flows, int(start), int(n), ch_pfids, int(ch_pfids.numel()))
         self._tied_folded = True
 
     def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False):
         self._require_cuda()
         self.fold_tied_flows()
-        _lib.call("pcx_em_input_cat", self.params.data, self.param_flows, self._dev["source_nids"],
+        self._param_epoch += 1                            # the kernel below writes the parameters behind torch's back
+        _lib.call("pcx_em_input_cat", self.params.data, self._param_flows, self._dev["source_nids"],
                   self._dev["s_pids"], self._dev["s_pfids"], self._dev["node_cats"], int(self.source_nids.numel()), self.max_cats,
                   float(step_size), float(pseudocount), int(bool(keep_zero_params)))
 

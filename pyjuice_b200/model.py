@@ -891,9 +891,12 @@ class TensorCircuit(nn.Module):
         input vectors are folded into their source range first and, when they form the tail of the arena, left out."""
         arena, layers = self._flow_arena, list(self.input_layer_group)
         last = layers[-1]
-        if self.device.type == "cuda" and last.tied2source_nids and not getattr(last, "_tied_folded", False):
-            last.fold_tied_flows()
-        if getattr(last, "_tied_folded", False):
+        if self.device.type == "cuda":
+            for layer in layers:
+                layer._flush_shadow()                       # flows still held in a transposed shadow table
+            if last.tied2source_nids:
+                last.fold_tied_flows()
+        if last.tied2source_nids and getattr(last, "_tied_folded", False):
             return arena.segment_end(len(layers), last.num_untied_param_flows)
         return arena.total
 
@@ -960,8 +963,12 @@ class TensorCircuit(nn.Module):
                 layer.param_flows = view
             self._graphs = {k: g for k, g in self._graphs.items() if k[0] != "bk"}
         elif flows_memory == 0.0:
+            for layer in self.input_layer_group:
+                layer._zero_shadow()
             _fill(self._flow_arena.buf, 0.0)
         elif flows_memory != 1.0:
+            for layer in self.input_layer_group:
+                layer._flush_shadow()
             _scale(self._flow_arena.buf, flows_memory)
         # The running flow total decays with the flows it normalises.  (The reference only clears it when the
         # rescaled EM update consumes it, model/tensorcircuit.py:1363-1374, so that under data parallelism, where every

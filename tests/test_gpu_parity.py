@@ -306,6 +306,39 @@ def test_wide_dense_kernels_without_folding_and_with_weights():
     _lib_status()
 
 
+@pytest.mark.parametrize("B", [64, 100, 30])
+@pytest.mark.parametrize("homogeneous", [True, False])
+def test_large_vocabulary_leaves_use_the_transposed_shadow(B, homogeneous):
+    """Categorical leaves with more categories than the staged kernels hold (here 9000) are looked up through a
+    transposed copy of the parameter table and accumulate their flows in the same layout; flows of tied replicas are
+    reported in the source range.  Batches that are not multiples of 4 take the general kernels instead."""
+    torch.manual_seed(8)
+    ns = pj.structures.HMM(seq_length=6, num_latents=32, num_emits=9000, homogeneous=homogeneous, block_size=8)
+    ns.init_parameters()
+    pc = pj.compile(ns, max_tied_ns_per_parflow_block=2).to(DEV)
+    layer = pc.input_layer_group[0]
+    assert layer._shadow is not None
+    assert layer._shadow_ok(B) == (B % 4 == 0)
+    x = torch.randint(0, 9000, (B, 6))
+    x[:, 0] = torch.arange(B) % 7                       # repeated tokens: several samples add to one row of flows
+    for rep in range(3):
+        errs = check_against_oracle(pc, x, step=0.2, pseudo=0.1, fold_input_flows=True)
+    print(B, homogeneous, errs)
+    # decaying flows over several steps, shadow flows included
+    from helpers import OracleTrainer
+    ref = OracleTrainer(pc)
+    pc.init_param_flows(flows_memory=0.0)
+    for i in range(3):
+        xi = torch.randint(0, 9000, (B, 6))
+        pc(xi.to(DEV))
+        pc.backward(xi.to(DEV), flows_memory=0.5)
+        pc.mini_batch_em(step_size=0.3, pseudocount=0.1)
+        ref.accumulate(xi, flows_memory=0.5)
+        ref.update(0.3, 0.1, zero_flows=False)
+        ref.check_params(pc)
+    _lib_status()
+
+
 def _lib_status():
     from pyjuice_b200 import _lib
     torch.cuda.synchronize()

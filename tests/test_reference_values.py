@@ -21,7 +21,7 @@ import pytest
 import torch
 
 from cases import CASES, OursApi
-from helpers import rel_close
+from helpers import folded_input_flows as _folded, rel_close
 from oracle import pc_oracle as orc
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -41,17 +41,6 @@ def _load(name):
     t = lambda k: torch.from_numpy(v[k])
     tensor_cores = bool(np.abs(v["lls"] - v["lls_default"]).max() > 0)
     return pc, v, t, n_in, ((1e-2, 5e-3) if tensor_cores else (1e-3, 1e-3))
-
-
-def _folded(layer, flows):
-    f = flows.detach().double().cpu().clone()
-    for start, n, ch in layer.tied2source_nids:
-        start, n = int(start), int(n)
-        tot = sum(f[int(c):int(c) + n].clone() for c in ch)
-        for c in ch:
-            f[int(c):int(c) + n] = 0.0
-        f[start:start + n] = tot
-    return f
 
 
 def _compare(name, pc, t, n_in, tol, lls, node_flows, param_flows, input_flows, params, input_params):
