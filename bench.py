@@ -186,13 +186,15 @@ def family_of(name: str) -> str:
         return "pcx_sum_fwd" if name.endswith("_fwd") else "pcx_sum_bwd_ele"
     if name.startswith("pcx_sum_par_dense"):              # operand staging + one product: the parameter flows
         return "pcx_sum_bwd_par"
+    if name in ("pcx_input_cat_shadow", "pcx_input_cat_flush_t"):     # upkeep of the transposed leaf tables
+        return "pcx_input_cat_upkeep"
     if name.startswith("pcx_pack_sm"):
         return "pcx_pack_sum_params"
     if name.startswith("pcx_input_cat_fwd"):
         return "pcx_input_cat_fwd"
     if name.startswith("pcx_input_cat_bwd"):
         return "pcx_input_cat_bwd"
-    for suffix in ("_fused", "_packed", "_batched", "_noalloc", "_dense", "_sm"):
+    for suffix in ("_fused", "_packed", "_batched", "_noalloc", "_dense2", "_dense", "_sm", "_t"):
         if name.endswith(suffix):
             name = name[:-len(suffix)]
     return name
@@ -320,8 +322,8 @@ def oracle_step_time(pc, x_cpu: torch.Tensor, repeats: int = 1):
 
 
 def cpu_sample_size(config: str, B: int, requested: int) -> int:
-    """Samples per CPU step: the oracle does configs[4]'s 12.8 GFLOP per sample at a few hundred GFLOP/s."""
-    return min(B, requested, 16 if config == "cfg4" else requested)
+    """Samples per CPU step (configs[4] is 12.8 GFLOP per sample plus half a minute of per-step table work on the host)."""
+    return min(B, requested, 128 if config.startswith("cfg4") else requested)
 
 
 def run_reference(args, rank):
@@ -334,15 +336,15 @@ def run_reference(args, rank):
     ns, x = build_workload(args.config, sample)
     pc = pj.compile(ns)
     xc = torch.from_numpy(x)
-    # one step at the full sample size tells how long K of them would take; the sample shrinks until the whole
-    # run fits in about two minutes (throughput of this CPU path is close to linear in the number of samples)
+    # one step at the full sample size (also the warm-up) tells how many fit into about two minutes; a step that is
+    # itself longer shrinks the sample (for most circuits this CPU path is close to linear in the number of samples)
     t_one = oracle_step_time(pc, xc)
     budget = 120.0
-    if t_one * args.steps > budget and sample > 8:
-        sample = max(8, int(sample * budget / (t_one * args.steps)) // 8 * 8)
+    if t_one > budget and sample > 8:
+        sample = max(8, int(sample * budget / t_one) // 8 * 8)
         xc = xc[:sample]
-        oracle_step_time(pc, xc)
-    steps = max(1, min(args.steps, int(budget / max(t_one * sample / max(xc.size(0), 1), 1e-3))))
+        t_one = oracle_step_time(pc, xc)
+    steps = max(1, min(args.steps, int(budget // max(t_one, 1e-3))))
     t0 = time.perf_counter()
     for _ in range(steps):
         oracle_step_time(pc, xc)
@@ -437,7 +439,6 @@ def measure_ours(config: str, args, rank: int, world: int, dev, K: int, W: int, 
     pc.use_dataflow_launch = not args.no_dataflow
     pc.use_side_stream = not args.no_side_stream
     pc.chain_tile = args.chain_tile
-    stats = circuit_stats(pc, Bl)
     max_cats = max(l.max_cats for l in pc.input_layer_group)
     np_dtype, elsize = (np.uint8, 1) if max_cats <= 256 else (np.int32, 4)
     shard = lambda i: x[i * B + rank * Bl:i * B + (rank + 1) * Bl]
@@ -459,6 +460,7 @@ def measure_ours(config: str, args, rank: int, world: int, dev, K: int, W: int, 
     for i in range(W):
         step(resident[i % n_batches])
     barrier()
+    stats = circuit_stats(pc, Bl)          # after the first steps: which depths fold their product layer depends on the batch
 
     # launches per step, counted on an eager step (graph replays launch the same kernels)
     pc.use_cuda_graphs = False

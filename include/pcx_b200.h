@@ -82,19 +82,20 @@ int pcx_input_cat_bwd(float* param_flows, const float* node_flows, const void* d
  * two operators on a transposed shadow of the parameter table.  logp_t[c * n_rows + r] = log params[r * num_cats + c]
  * (pcx_input_cat_shadow, once per parameter update); prow[n] = row of node n (= s_pids[n] / num_cats); flows are
  * accumulated into flows_t[c * n_rows + r] (zero-initialised by the caller) and moved into the reference's layout by
- * pcx_input_cat_flush_t: param_flows[row_pfid[r] + c] += flows_t[c, r], flows_t = 0.  Flows of tied replicas all land
- * in their source row.  B must be a multiple of 4.  Replace, like the two entry points above, Categorical.fw_mar_fn /
+ * pcx_input_cat_flush_t: param_flows[row_pfid[r] + c] += flows_t[c, r], flows_t = 0; `touched` ([num_cats] int32, zero
+ * at first) marks the categories that received flow, so that the flush skips the others.  Flows of tied replicas all
+ * land in their source row.  B must be a multiple of 4.  Replace, like the two entry points above, Categorical.fw_mar_fn /
  * bk_flow_fn (nodes/distributions/categorical.py:82-120) and layer/kernels/c/input_layers/cat_backward.cu:24-52,
  * whose histogram does not cover tied or large tables (layer/input_layer.py:304-316). */
 int pcx_input_cat_shadow(float* logp_t, const float* params, int64_t n_rows, int num_cats, void* stream);
 int pcx_input_cat_fwd_t(float* node_mars, const float* logp_t, const void* data, int data_elsize, const int32_t* vids,
                         const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
                         void* stream);
-int pcx_input_cat_bwd_t(float* flows_t, const float* node_flows, const void* data, int data_elsize, const int32_t* vids,
-                        const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
-                        int logspace, void* stream);
-int pcx_input_cat_flush_t(float* param_flows, float* flows_t, const int64_t* row_pfid, int64_t n_rows, int num_cats,
-                          void* stream);
+int pcx_input_cat_bwd_t(float* flows_t, int32_t* touched, const float* node_flows, const void* data, int data_elsize,
+                        const int32_t* vids, const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes,
+                        int64_t node_off, int B, int logspace, void* stream);
+int pcx_input_cat_flush_t(float* param_flows, float* flows_t, int32_t* touched, const int64_t* row_pfid, int64_t n_rows,
+                          int num_cats, void* stream);
 
 /* Product layer forward:  element_mars[nids[i]+j, b] = sum_c node_mars[cids[i,c]+j, b]   (cids == 0 skipped).
  * Replaces ProdLayer.forward -> _forward_backward_kernel_2d
@@ -343,8 +344,9 @@ int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const f
  *
  *   - needs block_size % 128 == 0; n_blocks * (block_size / 128) * ceil(K / 64) tiles must fit, otherwise
  *     PCX_ERR_SCRATCH_TOO_SMALL is returned and nothing is launched;
- *   - the first call on each device looks up the array's device address (with that device current); make that
- *     first call before starting any stream capture;
+ *   - the first call on each device looks up the array's device address (with that device current) and caches it per
+ *     device ordinal without a lock — two host threads making that first call together store the same value; make
+ *     that first call before starting any stream capture;
  *   - all calls share the one array: calls that may overlap on the GPU (different streams, no ordering) race on
  *     it and must be serialised by the caller.  Each call rewrites every tile it uses, padding included, so a call
  *     never depends on what an earlier one left behind. */

@@ -44,6 +44,7 @@ class OracleState:
         self.node_mars = self.element_mars = self.node_flows = self.element_flows = None
         self.param_flows = None
         self.input_param_flows = []
+        self.cache = {}                 # parameter blocks gathered per distinct index table (see `_gathered`)
 
 
 def _tables(pc):
@@ -98,14 +99,30 @@ def _neg_inf_like(x):
     return torch.full_like(x, NEG_INF)
 
 
-def _sum_forward(layer, node_mars, element_mars, params):
+def _table_key(*tables):
+    """Identity of index tables by content: layers with tied parameters carry equal tables."""
+    return tuple((tuple(t.shape), hash(t.numpy().tobytes())) for t in tables)
+
+
+def _gathered(cache, key, make):
+    """Parameter blocks gathered through an index table, computed once per distinct table (tied layers share them)."""
+    if cache is None:
+        return make()
+    if key not in cache:
+        cache[key] = make()
+    return cache[key]
+
+
+def _sum_forward(layer, node_mars, element_mars, params, cache=None):
     m = torch.arange(layer["bs"])
     B = node_mars.size(1)
     for nids, cids, pids in zip(layer["nids"], layer["cids"], layer["pids"]):
         K = cids.size(1)
+        pkey = _table_key(pids) if cache is not None else None
         for r0, r1 in _row_chunks(nids.numel(), K * (B + layer["bs"])):
             em = element_mars[cids[r0:r1]]                           # [n, K, B]
-            th = params[pids[r0:r1, :, None] + m[None, None, :]]     # [n, K, bs]
+            th = _gathered(cache, ("fw", pkey, r0, r1),
+                           lambda: params[pids[r0:r1, :, None] + m[None, None, :]])     # [n, K, bs]
             mx = em.max(dim=1).values                                # [n, B]
             dead = torch.isinf(mx) & (mx < 0)
             mx0 = torch.where(dead, torch.zeros_like(mx), mx)
@@ -115,7 +132,7 @@ def _sum_forward(layer, node_mars, element_mars, params):
             node_mars[(nids[r0:r1, None] + m[None, :]).reshape(-1)] = out.reshape(-1, B)
 
 
-def _sum_backward(layer, st, params, compute_param_flows):
+def _sum_backward(layer, st, params, compute_param_flows, cache=None, pending=None):
     bs = layer["bs"]
     n = torch.arange(bs)
     B = st.node_mars.size(1)
@@ -123,6 +140,7 @@ def _sum_backward(layer, st, params, compute_param_flows):
     for chids, parids, parpids, cbs in zip(layer["chids"], layer["parids"], layer["parpids"], layer["cs_block_sizes"]):
         c = torch.arange(cbs)
         P = parids.size(1)
+        bkey = _table_key(parpids) if cache is not None else None
         for r0, r1 in _row_chunks(chids.numel(), P * bs * (2 * B + cbs)):
             pr, pp = parids[r0:r1], parpids[r0:r1]                   # [r, P]
             rows = (pr[:, :, None] + n[None, None, :]).reshape(pr.size(0), -1)          # [r, P*bs]
@@ -130,8 +148,9 @@ def _sum_backward(layer, st, params, compute_param_flows):
             lnf = torch.where(torch.isinf(nm) & (nm < 0), _neg_inf_like(nf), nf - nm)
             pad = (pr == 0)[:, :, None].expand(-1, -1, bs).reshape(pr.size(0), -1)
             lnf = torch.where(pad[:, :, None], _neg_inf_like(lnf), lnf)
-            th = params[pp[:, :, None, None] + c[None, None, :, None] * bs + n[None, None, None, :]]   # [r, P, cbs, bs]
-            th = th.permute(0, 2, 1, 3).reshape(pr.size(0), cbs, -1)                    # [r, cbs, P*bs]
+            th = _gathered(cache, ("bk", bkey, cbs, r0, r1), lambda: params[
+                pp[:, :, None, None] + c[None, None, :, None] * bs + n[None, None, None, :]]     # [r, P, cbs, bs]
+                .permute(0, 2, 1, 3).reshape(pr.size(0), cbs, -1))                                # [r, cbs, P*bs]
             mx = lnf.max(dim=1).values
             dead = torch.isinf(mx) & (mx < 0)
             mx0 = torch.where(dead, torch.zeros_like(mx), mx)
@@ -146,6 +165,7 @@ def _sum_backward(layer, st, params, compute_param_flows):
     # parameter flows
     for nids, cids, pids, pfids in zip(layer["nids"], layer["cids"], layer["pids"], layer["pfids"]):
         K = cids.size(1)
+        fkey = _table_key(pids, pfids) if pending is not None else None
         for r0, r1 in _row_chunks(nids.numel(), (K + 2 * bs) * B + 2 * K * bs):
             rows = (nids[r0:r1, None] + n[None, :])                  # [r, bs]
             nf, nm = st.node_flows[rows], st.node_mars[rows]         # [r, bs, B]
@@ -154,9 +174,22 @@ def _sum_backward(layer, st, params, compute_param_flows):
             shift = lnf.max(dim=1).values
             shift = torch.where(torch.isinf(shift), torch.zeros_like(shift), shift)
             acc = torch.bmm((lnf - shift[:, None, :]).exp(), (em + shift[:, None, :]).exp().transpose(1, 2))   # [r, bs, K]
+            if pending is not None:
+                # layers with the same parameter and flow tables (tied): sum their contractions, scatter once at the end
+                slot = pending.setdefault((fkey, r0, r1), dict(pids=pids[r0:r1], pfids=pfids[r0:r1], bs=bs, acc=None))
+                slot["acc"] = acc if slot["acc"] is None else slot["acc"] + acc
+                continue
             th = params[pids[r0:r1, None, :] + n[None, :, None]]     # [r, bs, K]
             idx = (pfids[r0:r1, None, :] + n[None, :, None]).reshape(-1)
             st.param_flows.index_add_(0, idx, (th * acc).reshape(-1))
+
+
+def _flush_pending_param_flows(pending, st, params):
+    for slot in pending.values():
+        n = torch.arange(slot["bs"])
+        th = params[slot["pids"][:, None, :] + n[None, :, None]]
+        idx = (slot["pfids"][:, None, :] + n[None, :, None]).reshape(-1)
+        st.param_flows.index_add_(0, idx, (th * slot["acc"]).reshape(-1))
 
 
 def _prod_backward(layer, st):
@@ -192,7 +225,7 @@ def forward(pc, x: torch.Tensor, params: torch.Tensor, input_params, dtype=torch
             if kind == "prod":
                 _prod_forward(layer, st.node_mars, st.element_mars)
             else:
-                _sum_forward(layer, st.node_mars, st.element_mars, params)
+                _sum_forward(layer, st.node_mars, st.element_mars, params, cache=st.cache)
     st.tables = t
     return st.node_mars[t["root"][0]:t["root"][1]].t().clone(), st
 
@@ -216,6 +249,7 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
     st.node_flows[r0:r1] = 0.0 if ll_weights is None else ll_weights.to(dtype).reshape(-1, B).log()
     st.param_flows = torch.zeros(t["num_param_flows"], dtype=dtype) if param_flows is None else param_flows.detach().cpu().to(dtype).clone()
     inner = t["inner"]
+    pending = {}
     for gi in range(len(inner) - 1, -1, -1):
         kind, layers = inner[gi]
         if kind == "prod":
@@ -231,7 +265,8 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
             if not reference_compat:
                 st.element_flows.fill_(NEG_INF)
             for layer in layers:
-                _sum_backward(layer, st, params, compute_param_flows)
+                _sum_backward(layer, st, params, compute_param_flows, cache=st.cache, pending=pending)
+    _flush_pending_param_flows(pending, st, params)
     st.input_param_flows = []
     for li, lt in enumerate(t["inputs"]):
         pf = torch.zeros(lt["num_param_flows"], dtype=dtype)

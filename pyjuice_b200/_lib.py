@@ -57,8 +57,8 @@ SIGNATURES = {
     "pcx_probe_bounded_wait": [I, I],
     "pcx_input_cat_shadow": [P, P, L, I],
     "pcx_input_cat_fwd_t": [P, P, P, I, P, P, L, I, L, L, I],
-    "pcx_input_cat_bwd_t": [P, P, P, I, P, P, L, I, L, L, I, I],
-    "pcx_input_cat_flush_t": [P, P, P, L, I],
+    "pcx_input_cat_bwd_t": [P, P, P, P, I, P, P, L, I, L, L, I, I],
+    "pcx_input_cat_flush_t": [P, P, P, P, L, I],
     "pcx_sum_fwd_dense2": [P, P, P, P, P, P, I, P, P, I, P, L, L, I, I, I],
     "pcx_sum_bwd_ele_dense2": [P, P, P, P, P, P, P, P, I, I, P, P, I, P, L, L, I, I, I, I, I],
     "pcx_sum_par_dense2_stage": [P, P, P, P, P, P, P, P, I, L, I, I, I, I, I, I],

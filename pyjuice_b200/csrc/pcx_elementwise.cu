@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(256)
 input_cat_bwd_t_kernel(float* __restrict__ flows_t, const float* __restrict__ node_flows,
                        const void* __restrict__ data, int elsize, const int32_t* __restrict__ vids,
                        const int32_t* __restrict__ prow, int64_t R, int C, int64_t n_nodes, int64_t node_off, int B,
-                       int logspace) {
+                       int logspace, int32_t* __restrict__ touched) {
     __shared__ float tile[kTN][kTS + 1];
     const int64_t n0 = (int64_t)blockIdx.x * kTN;
     const int b0 = blockIdx.y * kTS;
@@ -250,17 +250,26 @@ input_cat_bwd_t_kernel(float* __restrict__ flows_t, const float* __restrict__ no
         if (b >= B) break;
         const float x = tile[nl][s];
         const int c = pcx_load_cat(data, elsize, drow + b);
-        if (x != 0.0f && c >= 0 && c < C) atomicAdd(flows_t + (int64_t)c * R + pr, x);
+        if (x != 0.0f && c >= 0 && c < C) {
+            atomicAdd(flows_t + (int64_t)c * R + pr, x);
+            if (touched[c] == 0) touched[c] = 1;                 // categories whose row of flows_t is not all zero
+        }
     }
 }
 
 __global__ void __launch_bounds__(256)
 input_cat_flush_t_kernel(float* __restrict__ param_flows, float* __restrict__ flows_t,
-                         const int64_t* __restrict__ row_pfid, int64_t R, int C) {
+                         const int64_t* __restrict__ row_pfid, int64_t R, int C, const int32_t* __restrict__ touched) {
     __shared__ float tile[32][33];
+    __shared__ int s_any;
     const int64_t r0 = (int64_t)blockIdx.x * 32;
     const int c0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    if (threadIdx.x == 0) s_any = 0;
+    __syncthreads();
+    if (threadIdx.x < 32 && c0 + threadIdx.x < C && touched[c0 + threadIdx.x] != 0) s_any = 1;
+    __syncthreads();
+    if (s_any == 0) return;                                  // no sample of the window carried these categories
     for (int k = ty; k < 32; k += 8) {
         const int c = c0 + k;
         const int64_t r = r0 + tx;
@@ -480,26 +489,27 @@ int pcx_input_cat_fwd_t(float* node_mars, const float* logp_t, const void* data,
     return 0;
 }
 
-int pcx_input_cat_bwd_t(float* flows_t, const float* node_flows, const void* data, int data_elsize, const int32_t* vids,
-                        const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes, int64_t node_off, int B,
-                        int logspace, void* stream) {
+int pcx_input_cat_bwd_t(float* flows_t, int32_t* touched, const float* node_flows, const void* data, int data_elsize,
+                        const int32_t* vids, const int32_t* prow, int64_t n_rows, int num_cats, int64_t n_nodes,
+                        int64_t node_off, int B, int logspace, void* stream) {
     if (data_elsize != 1 && data_elsize != 2 && data_elsize != 4 && data_elsize != 8) return -1;
     if (n_nodes <= 0 || B <= 0) return 0;
     if (B % 4 != 0 || num_cats <= 0 || (reinterpret_cast<uintptr_t>(node_flows) & 15) != 0) return -1;
     dim3 grid((unsigned)pcx_cdiv(n_nodes, kTN), (unsigned)pcx_cdiv(B, kTS));
     input_cat_bwd_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(flows_t, node_flows, data, data_elsize, vids, prow,
-                                                                   n_rows, num_cats, n_nodes, node_off, B, logspace);
+                                                                   n_rows, num_cats, n_nodes, node_off, B, logspace, touched);
     PCX_LAUNCH_CHECK();
     return 0;
 }
 
-int pcx_input_cat_flush_t(float* param_flows, float* flows_t, const int64_t* row_pfid, int64_t n_rows, int num_cats,
-                          void* stream) {
+int pcx_input_cat_flush_t(float* param_flows, float* flows_t, int32_t* touched, const int64_t* row_pfid, int64_t n_rows,
+                          int num_cats, void* stream) {
     if (n_rows <= 0 || num_cats <= 0) return 0;
     dim3 grid((unsigned)pcx_cdiv(n_rows, 32), (unsigned)pcx_cdiv(num_cats, 32));
-    input_cat_flush_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(param_flows, flows_t, row_pfid, n_rows, num_cats);
+    input_cat_flush_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(param_flows, flows_t, row_pfid, n_rows, num_cats, touched);
     PCX_LAUNCH_CHECK();
-    return 0;
+    cudaError_t e = cudaMemsetAsync(touched, 0, (size_t)num_cats * sizeof(int32_t), (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 int pcx_prod_fwd(float* element_mars, const float* node_mars, const int32_t* nids, const int32_t* cids,

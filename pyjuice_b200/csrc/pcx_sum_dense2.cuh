@@ -77,6 +77,21 @@ struct WideArgs {
     int K;                      // PAR: table width
 };
 
+// ---- L2 residency -----------------------------------------------------------------------------------------------------
+// The parameter tiles of a layer are read once per pass and, for tied layers, again by the next layer a few tens of
+// microseconds later: they are fetched with an evict-last policy so that the operand tiles and value rows streaming
+// through L2 in between do not push them out.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
+                                                   uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
+
 // ---- thread-block cluster helpers (the CTAs that share one output tile) -----------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
     uint32_t r;
@@ -234,6 +249,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
     if (warp == 0) {
         // ---- copy warp: lane 0 waits for the stage and arms its barrier, four lanes move one piece each -------------
         int armed = 0;
+        const uint64_t keep = l2_policy_evict_last();
         for (int t = 0; t < n_steps; ++t) {
             const int s = t % C::STAGES;
             int stop = 0;
@@ -246,8 +262,13 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
             if (stop) break;
             const int c = t / (KC / W_STEP), h = t % (KC / W_STEP);
             uint8_t* dst = smem + s * C::STAGE;
-            if (lane == 0) bulk_copy_g2s(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s]);
-            if (lane == 1) bulk_copy_g2s(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s]);
+            if (EPI == W_PAR) {                      // staged operands, read once: no residency wanted
+                if (lane == 0) bulk_copy_g2s(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s]);
+                if (lane == 1) bulk_copy_g2s(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s]);
+            } else {
+                if (lane == 0) bulk_copy_g2s_hint(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
+                if (lane == 1) bulk_copy_g2s_hint(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
+            }
             if (lane == 2) bulk_copy_g2s(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s]);
             if (lane == 3) bulk_copy_g2s(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s]);
             armed = t + 1;
@@ -625,7 +646,7 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
 // CTAs per group that share the operand rows of a pre-pass (= its cluster size): whole 64-row chunks each.
 inline int wide_prep_cluster(int n_chunks) {
     int cs = 1;
-    while (cs < 8 && n_chunks % (cs * 2) == 0 && n_chunks / (cs * 2) >= 4) cs *= 2;
+    while (cs < 4 && n_chunks % (cs * 2) == 0 && n_chunks / (cs * 2) >= 4) cs *= 2;
     return cs;
 }
 

@@ -230,13 +230,14 @@ class InputLayer(Layer, nn.Module):
         sh = self._shadow
         if sh is None or not sh["dirty"] or self._param_flows is None:
             return
-        _lib.call("pcx_input_cat_flush_t", self._param_flows, sh["flows"], sh["row_pfid"], sh["R"], sh["C"])
+        _lib.call("pcx_input_cat_flush_t", self._param_flows, sh["flows"], sh["touched"], sh["row_pfid"], sh["R"], sh["C"])
         sh["dirty"] = False
 
     def _zero_shadow(self):
         sh = self._shadow
         if sh is not None and sh["dirty"]:
             _fill(sh["flows"], 0.0)
+            sh["touched"].zero_()
             sh["dirty"] = False
 
     def to(self, device):
@@ -319,7 +320,8 @@ class InputLayer(Layer, nn.Module):
             sh = self._shadow
             if sh["flows"] is None:
                 sh["flows"] = torch.zeros(sh["R"] * sh["C"], dtype=torch.float32, device=self.device)
-            _lib.call("pcx_input_cat_bwd_t", sh["flows"], node_flows, data, data.element_size(), self._dev["vids"],
+                sh["touched"] = torch.zeros(sh["C"], dtype=torch.int32, device=self.device)
+            _lib.call("pcx_input_cat_bwd_t", sh["flows"], sh["touched"], node_flows, data, data.element_size(), self._dev["vids"],
                       sh["prow"], sh["R"], sh["C"], self.num_nodes, self._output_ind_range[0], B,
                       int(bool(logspace_flows)))
             sh["dirty"] = True                            # every flow lands in its source row: replicas stay as they are

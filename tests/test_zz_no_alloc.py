@@ -13,26 +13,41 @@ import pytest
 import torch
 
 from cases import CASES, OursApi
+from oracle import pc_oracle as orc
 from pyjuice_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _circuit():
+def _circuit(dev=DEV):
     api = OursApi()
     torch.manual_seed(11)
     ns, kw = CASES["hclt_b128"](api)
     ns.init_parameters()
-    return api.compile(ns, **kw).to(DEV)
+    return api.compile(ns, **kw).to(dev)
 
 
 def test_noalloc_forward_matches_packed_entry_point_twice():
-    pc = _circuit()
+    _check_twice(DEV)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_noalloc_forward_on_a_second_device():
+    """The scratch array exists once per GPU and its address is looked up per device: the same check on cuda:1 while
+    cuda:0 stays the current device."""
+    assert torch.cuda.current_device() == 0
+    _check_twice("cuda:1")
+    _check_twice(DEV)                                          # and the first device's address is still its own
+
+
+def _check_twice(DEV):
+    pc = _circuit(DEV)
     B = 96
     g = torch.Generator().manual_seed(3)
     x = (torch.rand(B, pc.num_vars, generator=g) * 12).long()
     pc(x.to(DEV))                                              # fills node_mars / element_mars, packs the tiles
+    _, oracle = orc.forward(pc, x, pc.params.data.double().cpu(), [l.params.data.double().cpu() for l in pc.input_layer_group])
     sum_groups = [(gi, grp) for gi, grp in enumerate(pc.inner_layer_groups) if grp.is_sum() and grp[0].block_size % 128 == 0]
     assert len(sum_groups) >= 2
     checked = 0
@@ -45,15 +60,17 @@ def test_noalloc_forward_matches_packed_entry_point_twice():
         _lib.call("pcx_sum_fwd_packed", ref, pc.element_mars, layer._packed_fw[0], nids, cids, *args)
         out = torch.full_like(pc.node_mars, float("nan"))
         _lib.call("pcx_sum_fwd_noalloc", out, pc.element_mars, pc.params.data, nids, cids, pids, *args)
-        torch.cuda.synchronize()
+        torch.cuda.synchronize(DEV)
         s, e = layer._layer_nid_range
         assert torch.isfinite(out[s:e]).all()
         # same kernel, same tiles: the tolerance of the parity tests (1e-3 nats) is met with room to spare
         assert (out[s:e] - ref[s:e]).abs().max().item() <= 1e-3
         assert torch.equal(out[s:e], ref[s:e])
+        # and against the CPU oracle's values of the same rows
+        assert (out[s:e].double().cpu() - oracle.node_mars[s:e]).abs().max().item() <= 1e-3
         checked += 1
     assert checked == 2
-    _lib.check_status()
+    _lib.check_status(DEV)
 
 
 def test_noalloc_rejects_tables_beyond_the_builtin_scratch():
