@@ -596,6 +596,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-dataflow", action="store_true", help="per-layer launches instead of one launch per run of layers")
     ap.add_argument("--no-side-stream", action="store_true", help="every kernel of a step on one stream")
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="plain stream order between the dense kernels (no programmatic dependent launch)")
     ap.add_argument("--chain-tile", type=int, default=None, choices=[16, 32, 64], help="tile width of the dataflow launch")
     ap.add_argument("--sum-mode", type=int, default=1, choices=[0, 1, 2],
                     help="0 fp32 CUDA cores, 1 tensor cores with split-bf16 operands, 2 tensor cores single bf16")
@@ -622,6 +624,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120), pg_options=opts)
     W, K = max(args.warmup, 3), args.steps
     _lib.set_sum_mode(args.sum_mode)
+    _lib.load().pcx_set_dependent_launch(0 if args.no_dependent_launch else 1)
     others = args.others if args.others is not None else ("cfg1,cfg2,cfg3" if args.config == "cfg4" else "")
     others = [c for c in others.split(",") if c and c != args.config]
 

@@ -220,6 +220,9 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
  * Replace, like the entry points above: SumLayer._forward_block_sparse / _backward_block_sparse_ele_flows /
  * _backward_block_sparse_par_flows (layer/sum_layer.py:551-929, 1369-1719, 1721-2080), with ProdLayer.forward /
  * backward folded in (layer/prod_layer.py:161-238). */
+/* The wide-tile kernels are launched with programmatic stream serialization (a kernel sets itself up while its
+ * predecessor drains, then waits for it); 0 switches that off, e.g. to compare timings. */
+int pcx_set_dependent_launch(int on);
 int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B);
 int pcx_sum_fwd_dense2(float* node_mars, const float* element_mars, const void* packed, const int32_t* nids,
                        const int32_t* cids, const int32_t* fkids, int fc, const int32_t* row_group,

@@ -66,7 +66,7 @@ SIGNATURES = {
 }
 
 # entry points without a stream argument
-PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_get_status": [], "pcx_clear_status": [],
+PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_set_dependent_launch": [I], "pcx_get_status": [], "pcx_clear_status": [],
          "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I],
          "pcx_sm_packed_bytes": [L, I, I], "pcx_dense2_scratch_bytes": [I, I, I]}
 SUM_MODE = 1        # mirror of the library's arithmetic mode (see set_sum_mode)

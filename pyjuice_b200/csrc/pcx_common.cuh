@@ -14,6 +14,21 @@
 
 static inline int64_t pcx_cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// A "done once" flag PER DEVICE for set-up that CUDA keeps per device (kernel attributes such as the dynamic
+// shared-memory limit): reads and writes refer to the flag of the current device, so a process that drives several
+// GPUs configures every kernel on each of them.  Used as `static PcxOnce done; if (!done) { ...; done = true; }`.
+struct PcxOnce {
+    bool flags[64] = {};
+    bool& here() {
+        int d = 0;
+        if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) d = 0;
+        return flags[d];
+    }
+    operator bool() { return here(); }
+    PcxOnce& operator=(bool v) { here() = v; return *this; }
+    bool* operator&() { return &here(); }
+};
+
 // log(exp(a) + exp(b)) with -inf handled (no NaN from inf - inf).
 __device__ __forceinline__ float pcx_logaddexp(float a, float b) {
     float hi = fmaxf(a, b), lo = fminf(a, b);

@@ -389,7 +389,7 @@ __global__ void dense_par_y_kernel(const float* __restrict__ element_mars, const
 
 template <int EPI>
 int launch_dense_gemm(const DenseArgs& a, dim3 grid, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(dense_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM);
         if (e != cudaSuccess) return (int)e;

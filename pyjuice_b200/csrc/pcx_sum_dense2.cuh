@@ -77,6 +77,16 @@ struct WideArgs {
     int K;                      // PAR: table width
 };
 
+// ---- programmatic dependent launch --------------------------------------------------------------------------------
+// A pass over a deep circuit is a chain of short kernels (pre-pass, GEMM, pre-pass, GEMM, ...), each of which needs
+// all of its predecessor's output.  Launched with the programmatic-serialization attribute, a kernel may become
+// resident while its predecessor is still running and set itself up (barriers, tensor memory, index arithmetic); it
+// then waits here until the predecessor has completed and its writes are visible.  `launch_dependents` lets the
+// successor start that early.  Off (plain stream order) when pcx_set_dependent_launch(0) was called.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+int g_wide_pdl = 1;
+
 // ---- L2 residency -----------------------------------------------------------------------------------------------------
 // The parameter tiles of a layer are read once per pass and, for tied layers, again by the next layer a few tens of
 // microseconds later: they are fetched with an evict-last policy so that the operand tiles and value rows streaming
@@ -241,6 +251,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = s_tmem;
+    griddep_wait();                                 // everything above overlapped the previous kernel's tail
+    griddep_launch_dependents();
 
     const int64_t b_row = (EPI == W_PAR) ? (int64_t)nt : (int64_t)a.b_group[i] * a.n_ct + nt;
     const uint8_t* a_src = a.a_tiles + ((size_t)mt * a.n_chunks + c_begin) * (2 * A_TILE);
@@ -545,6 +557,8 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_rows_kernel(const Wi
     const int k_begin = blockIdx.z * rows_here;
     const int ld = rows_here + 4;
     float sh[8];
+    griddep_wait();
+    griddep_launch_dependents();
     wide_prep_stage<FC>(a, g, b0, k_begin, rows_here, s_dyn, ld, s_red, s_peer, sh);
     if (blockIdx.z == 0 && tid < 8) a.shift[(int64_t)g * a.B + b0 + tid] = sh[tid];
 
@@ -581,6 +595,8 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
     const int k_begin = blockIdx.z * rows_here;
     const int ld = rows_here + 4;
     float sh[8];
+    griddep_wait();
+    griddep_launch_dependents();
     wide_prep_stage<0>(a, 0, b0, k_begin, rows_here, s_dyn, ld, s_red, s_peer, sh);   // mode 2: flow - value of the layer's rows
 
     const int64_t q0 = (int64_t)a.slot * a.B + b0;
@@ -657,13 +673,22 @@ int wide_launch_prep(Kern kern, const WidePrepArgs& p, dim3 grid, size_t smem, c
     cfg.blockDim = dim3(W_PREP_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = grid.z;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (grid.z > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = grid.z;
+        ++n_attr;
+    }
+    if (g_wide_pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = grid.z > 1 ? 1 : 0;
+    cfg.numAttrs = n_attr;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) return (int)e;
     PCX_LAUNCH_CHECK();
@@ -692,7 +717,7 @@ int wide_set_smem(Kern kern, int bytes, bool* done) {
 
 template <int EPI, int DN>
 int launch_wide_gemm(const WideArgs& a, dim3 grid, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     int rc = wide_set_smem(wide_gemm_kernel<EPI, DN>, WideCfg<DN>::SMEM, &done);
     if (rc != 0) return rc;
     cudaLaunchConfig_t cfg = {};
@@ -700,13 +725,22 @@ int launch_wide_gemm(const WideArgs& a, dim3 grid, cudaStream_t st) {
     cfg.blockDim = dim3(W_THREADS);
     cfg.dynamicSmemBytes = WideCfg<DN>::SMEM;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;       // the CTAs that split one tile's contraction
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = grid.z;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (grid.z > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;       // the CTAs that split one tile's contraction
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = grid.z;
+        ++n_attr;
+    }
+    if (g_wide_pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = grid.z > 1 ? 1 : 0;
+    cfg.numAttrs = n_attr;
     cudaError_t e = cudaLaunchKernelEx(&cfg, wide_gemm_kernel<EPI, DN>, a);
     if (e != cudaSuccess) return (int)e;
     PCX_LAUNCH_CHECK();
@@ -722,7 +756,7 @@ int launch_wide_gemm_dn(const WideArgs& a, int DN, dim3 grid, cudaStream_t st) {
 
 template <int FC>
 int launch_wide_prep_rows(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     int rc = wide_set_smem(wide_prep_rows_kernel<FC>, (W_MAX_DEPTH + 4) * 8 * (int)sizeof(float), &done);
     if (rc != 0) return rc;
     return wide_launch_prep(wide_prep_rows_kernel<FC>, p, grid, smem, st);
@@ -730,7 +764,7 @@ int launch_wide_prep_rows(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStr
 
 template <int FC>
 int launch_wide_prep_par(const WidePrepArgs& p, dim3 grid, size_t smem, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     int rc = wide_set_smem(wide_prep_par_kernel<FC>, (W_MAX_DEPTH + 4) * 8 * (int)sizeof(float), &done);
     if (rc != 0) return rc;
     return wide_launch_prep(wide_prep_par_kernel<FC>, p, grid, smem, st);
@@ -800,6 +834,11 @@ static int wide_rows_op(int mode, float* out, const float* src, const float* src
 }  // namespace
 
 extern "C" {
+
+int pcx_set_dependent_launch(int on) {
+    g_wide_pdl = on ? 1 : 0;
+    return 0;
+}
 
 int64_t pcx_dense2_scratch_bytes(int n_groups, int depth, int B) {
     return wide_scratch(nullptr, n_groups, depth, B).total;

@@ -719,7 +719,7 @@ __global__ void pack_sm_jobs_kernel(const SmPackJob* __restrict__ jobs, int n_jo
 
 template <int NB, bool ELE>
 int launch_sm(const SmArgs& a, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     static int sms = 0;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(sum_sm_kernel<NB, ELE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -788,7 +788,7 @@ int pcx_sum_bwd_par_sm(float* param_flows, const float* node_flows, const float*
     a.chunks_per_cta = (int)pcx_cdiv(total_chunks, splits);
     dim3 grid((unsigned)n_merged, (unsigned)pcx_cdiv(K, BM), (unsigned)pcx_cdiv(total_chunks, a.chunks_per_cta));
     const int smem = STAGES * (2 * X_TILE + 2 * PKG * (nb * 16 + 16)) + 1024;
-    static bool done32 = false, done64 = false;
+    static PcxOnce done32, done64;
     cudaError_t e;
     if (nb == 32) {
         if (!done32) {

@@ -1146,7 +1146,7 @@ int configure_once(Kern kern, bool* done) {
 
 template <int MODE, int FC, int TN>
 int launch_lse_tn(const LseArgs& a, int64_t n_rows, cudaStream_t st) {
-    static bool done_small = false, done_big = false;
+    static PcxOnce done_small, done_big;
     const int KK = (MODE == FWD) ? a.K : a.K * a.par_block;
     dim3 grid((unsigned)(n_rows * (a.row_block / BM)), (unsigned)pcx_cdiv(a.B, TN));
     if (KK <= 2 * KC) {
@@ -1192,7 +1192,7 @@ int launch_lse(const LseArgs& a_in, int64_t n_rows, int fc, cudaStream_t st) {
 template <int MODE, int FC, int TN>
 int launch_chain_tn(const LseArgs& a, const ChainJob* jobs, int n_jobs, int64_t n_items, int n_ct, int* ctrl,
                     int n_ctas, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     int rc = configure_once(sum_chain_kernel<MODE, FC, TN>, &done);
     if (rc) return rc;
     sum_chain_kernel<MODE, FC, TN><<<n_ctas, NTH, SMEM_BYTES, st>>>(a, jobs, n_jobs, n_items, n_ct, ctrl);
@@ -1218,7 +1218,7 @@ int pcx_tc_sum_mode() { return g_sum_mode; }
 
 template <int FC>
 static int launch_par_fc(const ParArgs& a, dim3 grid, cudaStream_t st) {
-    static bool done = false;
+    static PcxOnce done;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(sum_par_tc_kernel<FC>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
@@ -1434,7 +1434,7 @@ int pcx_sum_bwd_par_batched(float* param_flows, const float* node_flows, const f
     ParArgs a{};
     a.param_flows = param_flows; a.node_flows = node_flows; a.node_mars = node_mars; a.params = params;
     a.B = B; a.logspace = logspace; a.terms = (g_sum_mode == 2) ? 1 : 3; a.chunks_per_cta = chunks_per_cta;
-    static bool done4 = false, done8 = false;
+    static PcxOnce done4, done8;
     cudaError_t e;
     if (fc == 4) {
         if (!done4) {

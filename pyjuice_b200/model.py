@@ -738,6 +738,9 @@ class TensorCircuit(nn.Module):
             return True
 
         plan = self._chain_plan(self.node_mars.size(1), 1)
+        cur = torch.cuda.current_stream(self.device)
+        side = self._side_stream if self.use_side_stream else None
+        forked = False
         for gi in range(len(groups) - 1, -1, -1):
             group = groups[gi]
             if plan is not None and plan["lo"] - 1 <= gi <= plan["hi"]:
@@ -749,15 +752,22 @@ class TensorCircuit(nn.Module):
                 if not (self._fusion_on(gi + 1, True) and self._fused[gi + 1]["direct"]):
                     group.backward(self.node_flows, self.element_flows, logspace_flows=logspace_flows)
             elif self._fusion_on(gi, True) and self._fused[gi].get("dense"):
-                for layer in group:                         # operands of the tied parameter-flow product, then the flows
-                    if pf is not None:
-                        for p in range(layer.num_fw_partitions):
-                            ok = dense is not None and dense_stage(layer, p, self.node_flows, self.node_mars, None,
-                                                                   int(bool(logspace_flows)))
-                            assert ok, "a dense-folded table must have a slot in the dense parameter-flow product"
+                # The operands of the (tied) parameter-flow product only read this depth's node flows and values, which
+                # are final by now; the element flows below read the same rows and write the children's.  The two are
+                # independent, so the operand staging goes to the second stream and shares the device with the chain
+                # of element-flow kernels (which are short and leave SMs idle between them).
+                if pf is not None:
+                    if side is not None:
+                        side.wait_stream(cur)
+                    with torch.cuda.stream(side if side is not None else cur):
+                        for layer in group:
+                            for p in range(layer.num_fw_partitions):
+                                ok = dense is not None and dense_stage(layer, p, self.node_flows, self.node_mars, None,
+                                                                       int(bool(logspace_flows)))
+                                assert ok, "a dense-folded table must have a slot in the dense parameter-flow product"
+                    forked = forked or side is not None
+                for layer in group:
                     layer.backward_ele_fused(self.node_flows, self.element_flows, self.node_mars, logspace_flows)
-                if not self._fused[gi]["direct"]:
-                    pass                                    # the product layer below picks the flows up from element_flows
             elif self._fusion_on(gi, True):
                 any_fused = any_fused or not self._fused[gi]["sm"]
                 for layer in group:
@@ -771,10 +781,15 @@ class TensorCircuit(nn.Module):
                                self.params.data, param_flows=pf, logspace_flows=logspace_flows,
                                dense_par_stage=dense_stage if dense is not None else None)
         if dense is not None:
-            for g in dense["groups"]:
-                cids, pids, pfids = g["tables"]
-                _lib.call("pcx_sum_par_dense2_gemm" if g["wide"] else "pcx_sum_par_dense_gemm", pf, self.params.data,
-                          g["x"], g["y"], cids, pids, pfids, g["n_blocks"], g["K"], g["block_size"], g["n_chunks"])
+            if forked:
+                side.wait_stream(cur)                        # operands staged on the main stream are complete too
+            with torch.cuda.stream(side if forked else cur):
+                for g in dense["groups"]:
+                    cids, pids, pfids = g["tables"]
+                    _lib.call("pcx_sum_par_dense2_gemm" if g["wide"] else "pcx_sum_par_dense_gemm", pf, self.params.data,
+                              g["x"], g["y"], cids, pids, pfids, g["n_blocks"], g["K"], g["block_size"], g["n_chunks"])
+        if forked:
+            cur.wait_stream(side)
         self._batched_par_pending = any_fused and pf is not None     # launched by `backward`, after this sweep
 
     def _launch_batched_par(self, logspace_flows: bool):
