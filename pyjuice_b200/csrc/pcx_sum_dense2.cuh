@@ -96,6 +96,25 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// Streaming (evict-first) variant of store_split8 for operands that are written once and read much later.
+__device__ __forceinline__ void store_split8_streaming(uint4* hi, uint4* lo, const float* x) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 hp = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+        h[j] = *reinterpret_cast<const uint32_t*>(&hp);
+        const float h0 = __uint_as_float(h[j] << 16), h1 = __uint_as_float(h[j] & 0xffff0000u);
+        const __nv_bfloat162 lp = __floats2bfloat162_rn(x[2 * j] - h0, x[2 * j + 1] - h1);
+        l[j] = *reinterpret_cast<const uint32_t*>(&lp);
+    }
+    __stcs(hi, make_uint4(h[0], h[1], h[2], h[3]));
+    __stcs(lo, make_uint4(l[0], l[1], l[2], l[3]));
+}
 __device__ __forceinline__ void bulk_copy_g2s_hint(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
                                                    uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
@@ -124,9 +143,47 @@ __device__ __forceinline__ void cluster_store(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+// Element flows: value of the element in row (i, r0 + row) for the 32 columns from b0 on, and its child rows.
+__device__ __forceinline__ void wide_gather_em(const WideArgs& a, int64_t i, int r0, int row, int b0, float* em, int* fk) {
+    const int nv = min(32, a.B - b0);
+    if (a.fkids != nullptr) {                                        // element value = sum of the children's rows
+        const int64_t erow = i * a.row_block + r0 + row;
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { fk[q] = (q < a.fc) ? a.fkids[erow * a.fc + q] : 0; any = any || fk[q] != 0; }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) em[j] = any ? 0.0f : PCX_NEG_INF;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (fk[q] != 0) {
+                const float* src = a.nmars + (int64_t)fk[q] * a.B + b0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    if (j < nv) {
+                        const float4 c4 = *reinterpret_cast<const float4*>(src + j);
+                        em[j] += c4.x; em[j + 1] += c4.y; em[j + 2] += c4.z; em[j + 3] += c4.w;
+                    }
+                }
+            }
+        }
+    } else {
+        const int64_t orow = ((int64_t)a.rows[i] + r0 + row) * a.B + b0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) fk[q] = 0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            if (j < nv) {
+                const float4 e4 = *reinterpret_cast<const float4*>(a.emars + orow + j);
+                em[j] = e4.x; em[j + 1] = e4.y; em[j + 2] = e4.z; em[j + 3] = e4.w;
+            }
+        }
+    }
+}
+
 // Epilogue of one row and 32 consecutive columns.
 template <int EPI, int DN>
-__device__ __forceinline__ void wide_finish(const WideArgs& a, int64_t i, int r0, int row, int nt, int cb, const float* v) {
+__device__ __forceinline__ void wide_finish(const WideArgs& a, int64_t i, int r0, int row, int nt, int cb, const float* v,
+                                            const float* pre_em = nullptr, const int* pre_fk = nullptr) {
     if (EPI == W_PAR) {
 #pragma unroll 4
         for (int j = 0; j < 32; ++j) {
@@ -164,36 +221,16 @@ __device__ __forceinline__ void wide_finish(const WideArgs& a, int64_t i, int r0
             if (j < nv) *reinterpret_cast<float4*>(a.out + orow + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
         return;
     }
-    // element flows: all loads of the element's value first (they overlap), then the stores
+    // element flows: the element's value (gathered here, or already gathered while the main loop ran), then the stores
     float em[32];
     int fk[8];
-    if (a.fkids != nullptr) {                                        // element value = sum of the children's rows
-        bool any = false;
+    if (pre_em != nullptr) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) { fk[q] = (q < a.fc) ? a.fkids[erow * a.fc + q] : 0; any = any || fk[q] != 0; }
+        for (int j = 0; j < 32; ++j) em[j] = pre_em[j];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) em[j] = any ? 0.0f : PCX_NEG_INF;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            if (fk[q] != 0) {
-                const float* src = a.nmars + (int64_t)fk[q] * a.B + b0;
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    if (j < nv) {
-                        const float4 c4 = *reinterpret_cast<const float4*>(src + j);
-                        em[j] += c4.x; em[j + 1] += c4.y; em[j + 2] += c4.z; em[j + 3] += c4.w;
-                    }
-                }
-            }
-        }
+        for (int q = 0; q < 8; ++q) fk[q] = pre_fk[q];
     } else {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            if (j < nv) {
-                const float4 e4 = *reinterpret_cast<const float4*>(a.emars + orow + j);
-                em[j] = e4.x; em[j + 1] = e4.y; em[j + 2] = e4.z; em[j + 3] = e4.w;
-            }
-        }
+        wide_gather_em(a, i, r0, row, b0, em, fk);
     }
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -261,7 +298,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
     if (warp == 0) {
         // ---- copy warp: lane 0 waits for the stage and arms its barrier, four lanes move one piece each -------------
         int armed = 0;
-        const uint64_t keep = l2_policy_evict_last();
+        // parameter tiles: keep; staged operands of the parameter-flow product (a gigabyte, read once): do not
+        const uint64_t keep = (EPI == W_PAR) ? l2_policy_evict_first() : l2_policy_evict_last();
         for (int t = 0; t < n_steps; ++t) {
             const int s = t % C::STAGES;
             int stop = 0;
@@ -274,15 +312,15 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
             if (stop) break;
             const int c = t / (KC / W_STEP), h = t % (KC / W_STEP);
             uint8_t* dst = smem + s * C::STAGE;
-            if (EPI == W_PAR) {                      // staged operands, read once: no residency wanted
-                if (lane == 0) bulk_copy_g2s(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s]);
-                if (lane == 1) bulk_copy_g2s(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s]);
+            if (lane == 0) bulk_copy_g2s_hint(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
+            if (lane == 1) bulk_copy_g2s_hint(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
+            if (EPI == W_PAR) {
+                if (lane == 2) bulk_copy_g2s_hint(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s], keep);
+                if (lane == 3) bulk_copy_g2s_hint(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s], keep);
             } else {
-                if (lane == 0) bulk_copy_g2s_hint(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
-                if (lane == 1) bulk_copy_g2s_hint(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
+                if (lane == 2) bulk_copy_g2s(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s]);
+                if (lane == 3) bulk_copy_g2s(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s]);
             }
-            if (lane == 2) bulk_copy_g2s(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s]);
-            if (lane == 3) bulk_copy_g2s(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s]);
             armed = t + 1;
         }
         if (lane == 0 && s_fail) {
@@ -326,6 +364,18 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
         // ---- epilogue warps: TMEM lane quarter warp % 4, one output row per thread --------------------------
         const int lq = warp & 3;
         const int row = lq * 32 + lane;
+        // Element flows, tile split over 4 or 8 CTAs: this CTA finishes at most 64 columns, and what the epilogue needs
+        // beside the accumulator -- the elements' values, gathered from their child rows -- does not depend on the
+        // products.  Fetch it now, while the main loop runs, instead of after it.
+        const int QW0 = DN / a.splits;
+        const bool pre = (EPI == W_ELE) && a.splits > 1 && QW0 <= 64;
+        float em0[32], em1[32];
+        int fk0[8];
+        if (pre) {
+            const int c0 = nt * DN + (int)cluster_cta_rank() * QW0;
+            if (c0 < a.B) wide_gather_em(a, i, r0, row, c0, em0, fk0);
+            if (QW0 == 64 && c0 + 32 < a.B) wide_gather_em(a, i, r0, row, c0 + 32, em1, fk0);
+        }
         bool ok = mbar_wait(&s_done, 0u, 1u << 24);
         if (!ok) s_fail = 3;
         ok = ok && (s_fail == 0);
@@ -389,7 +439,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
                             for (int j = 0; j < 32; ++j) v[j] += mine[((q * QW) + cb + j) * BM + row];
                         }
                     }
-                    wide_finish<EPI, DN>(a, i, r0, row, nt, (int)me * QW + cb, v);
+                    if (pre) wide_finish<EPI, DN>(a, i, r0, row, nt, (int)me * QW + cb, v, cb == 0 ? em0 : em1, fk0);
+                    else wide_finish<EPI, DN>(a, i, r0, row, nt, (int)me * QW + cb, v);
                 }
             }
         }
@@ -613,7 +664,7 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
         }
         uint8_t* tile = a.tiles + ((size_t)(r / BM) * a.n_chunks_total + cc) * (2 * A_TILE);
         uint8_t* dst = tile + sg * (BM * 16) + (r % BM) * 16;
-        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + A_TILE), v);
+        store_split8_streaming(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + A_TILE), v);
     }
     constexpr int EN = 256;
     const int e_per = (a.Kfw + a.cs - 1) / a.cs;
@@ -655,7 +706,7 @@ __global__ void __launch_bounds__(W_PREP_THREADS) wide_prep_par_kernel(const Wid
             v[s] = (!live || em[s] == PCX_NEG_INF || sh[s] == PCX_NEG_INF) ? 0.0f : fminf(__expf(em[s] + sh[s]), 3.0e38f);
         uint8_t* tile = a.y_tiles + ((size_t)(e / EN) * a.n_chunks_total + cc) * (2 * 8 * EN * 16);
         uint8_t* dst = tile + sg * (EN * 16) + (e % EN) * 16;
-        store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + 8 * EN * 16), v);
+        store_split8_streaming(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + 8 * EN * 16), v);
     }
 }
 

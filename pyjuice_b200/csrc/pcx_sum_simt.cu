@@ -189,6 +189,70 @@ sum_fwd_rows(float* __restrict__ node_mars, const float* __restrict__ element_ma
     }
 }
 
+// The same for few rows with very many edges (the root of a wide circuit: one row, thousands of children), where the
+// kernel above leaves the machine to a handful of CTAs that each walk hundreds of dependent loads.  CTA = (node
+// block, 8 samples); thread = (sample, one of 32 edge lanes); four edges per round, all of their loads issued before
+// any is used.
+template <int BS>
+__global__ void __launch_bounds__(NT)
+sum_fwd_rows_deep(float* __restrict__ node_mars, const float* __restrict__ element_mars,
+                  const float* __restrict__ params, const int32_t* __restrict__ nids,
+                  const int32_t* __restrict__ cids, const int32_t* __restrict__ pids, int K, int B) {
+    constexpr int EL = NT / 8;
+    __shared__ float s_mx[EL][8];
+    __shared__ float s_acc[EL][BS][8];
+    const int s = threadIdx.x & 7, el = threadIdx.x >> 3;
+    const int64_t i = blockIdx.x;
+    const int b = blockIdx.y * 8 + s;
+    const int bc = b < B ? b : B - 1;
+    float mx = PCX_NEG_INF, acc[BS];
+#pragma unroll
+    for (int m = 0; m < BS; ++m) acc[m] = 0.0f;
+    for (int e0 = el; e0 < K; e0 += 4 * EL) {
+        int cid[4];
+        int64_t pid[4];
+        float v[4], th[4][BS];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int e = e0 + q * EL;
+            cid[q] = e < K ? cids[i * K + e] : 0;
+            pid[q] = e < K ? pids[i * K + e] : 0;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            v[q] = element_mars[(int64_t)cid[q] * B + bc];           // row 0 exists (-inf)
+#pragma unroll
+            for (int m = 0; m < BS; ++m) th[q][m] = params[pid[q] + m];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (cid[q] == 0 || v[q] == PCX_NEG_INF) continue;
+            float scale = 1.0f, x = 1.0f;
+            if (v[q] > mx) { scale = expf(mx - v[q]); mx = v[q]; } else { x = expf(v[q] - mx); }
+#pragma unroll
+            for (int m = 0; m < BS; ++m) acc[m] = acc[m] * scale + th[q][m] * x;
+        }
+    }
+    s_mx[el][s] = mx;
+#pragma unroll
+    for (int m = 0; m < BS; ++m) s_acc[el][m][s] = acc[m];
+    __syncthreads();
+    if (threadIdx.x < 8 && b < B) {
+        float gm = PCX_NEG_INF;
+        for (int q = 0; q < EL; ++q) gm = fmaxf(gm, s_mx[q][s]);
+        const int64_t nid = nids[i];
+#pragma unroll
+        for (int m = 0; m < BS; ++m) {
+            float tot = 0.0f;
+            for (int q = 0; q < EL; ++q) {
+                const float qm = s_mx[q][s];
+                if (qm != PCX_NEG_INF) tot += s_acc[q][m][s] * expf(qm - gm);
+            }
+            node_mars[(nid + m) * B + b] = (gm == PCX_NEG_INF) ? PCX_NEG_INF : logf(fmaxf(tot, 1e-24f)) + gm;
+        }
+    }
+}
+
 // -------------------------------------------------------------------------------------------------
 // Element flows:  eflows[chid+c, b] = emars[chid+c, b] + log sum_{p,n} params[parpid_p + c*bs + n] * exp(nflow - nmar)
 // -------------------------------------------------------------------------------------------------
@@ -564,6 +628,11 @@ int pcx_sum_fwd(float* node_mars, const float* element_mars, const float* params
             grid.x = (unsigned)n_blocks;
             sum_fwd_tiled<8, 1, 2><<<grid, NT, 0, st>>>(node_mars, element_mars, params, nids, cids, pids, K, block_size, B);
         }
+    } else if (K >= 512 && n_blocks * pcx_cdiv(B, 32) < 148) {          // few rows, very many edges: spread the edges
+        dim3 grid((unsigned)n_blocks, (unsigned)pcx_cdiv(B, 8));
+        if (block_size == 4) sum_fwd_rows_deep<4><<<grid, NT, 0, st>>>(node_mars, element_mars, params, nids, cids, pids, K, B);
+        else if (block_size == 2) sum_fwd_rows_deep<2><<<grid, NT, 0, st>>>(node_mars, element_mars, params, nids, cids, pids, K, B);
+        else sum_fwd_rows_deep<1><<<grid, NT, 0, st>>>(node_mars, element_mars, params, nids, cids, pids, K, B);
     } else {
         dim3 grid((unsigned)n_blocks, (unsigned)pcx_cdiv(B, 32));
         if (block_size == 4) sum_fwd_rows<4><<<grid, NT, 0, st>>>(node_mars, element_mars, params, nids, cids, pids, K, B);
