@@ -96,11 +96,6 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
 // Streaming (evict-first) variant of store_split8 for operands that are written once and read much later.
 __device__ __forceinline__ void store_split8_streaming(uint4* hi, uint4* lo, const float* x) {
     uint32_t h[4], l[4];
@@ -298,8 +293,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
     if (warp == 0) {
         // ---- copy warp: lane 0 waits for the stage and arms its barrier, four lanes move one piece each -------------
         int armed = 0;
-        // parameter tiles: keep; staged operands of the parameter-flow product (a gigabyte, read once): do not
-        const uint64_t keep = (EPI == W_PAR) ? l2_policy_evict_first() : l2_policy_evict_last();
+        const uint64_t keep = l2_policy_evict_last();
         for (int t = 0; t < n_steps; ++t) {
             const int s = t % C::STAGES;
             int stop = 0;
@@ -312,15 +306,17 @@ __global__ void __launch_bounds__(W_THREADS, 1) wide_gemm_kernel(const WideArgs 
             if (stop) break;
             const int c = t / (KC / W_STEP), h = t % (KC / W_STEP);
             uint8_t* dst = smem + s * C::STAGE;
-            if (lane == 0) bulk_copy_g2s_hint(dst, a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
-            if (lane == 1) bulk_copy_g2s_hint(dst + W_A_HALF, a_src + (size_t)c * (2 * A_TILE) + A_TILE + h * W_A_HALF, W_A_HALF, &s_full[s], keep);
-            if (EPI == W_PAR) {
-                if (lane == 2) bulk_copy_g2s_hint(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s], keep);
-                if (lane == 3) bulk_copy_g2s_hint(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s], keep);
-            } else {
-                if (lane == 2) bulk_copy_g2s(dst + 2 * W_A_HALF, b_src + (size_t)c * C::B_TILE + h * C::B_HALF, C::B_HALF, &s_full[s]);
-                if (lane == 3) bulk_copy_g2s(dst + 2 * W_A_HALF + C::B_HALF, b_src + (size_t)c * C::B_TILE + C::B_TILE / 2 + h * C::B_HALF, C::B_HALF, &s_full[s]);
+            const uint8_t* a_at = a_src + (size_t)c * (2 * A_TILE) + h * W_A_HALF;
+            const uint8_t* b_at = b_src + (size_t)c * C::B_TILE + h * C::B_HALF;
+            if (EPI == W_PAR) {                      // staged operands, shared by the CTAs of a wave only: default policy
+                if (lane == 0) bulk_copy_g2s(dst, a_at, W_A_HALF, &s_full[s]);
+                if (lane == 1) bulk_copy_g2s(dst + W_A_HALF, a_at + A_TILE, W_A_HALF, &s_full[s]);
+            } else {                                 // parameter tiles: keep them for the next (tied) layer
+                if (lane == 0) bulk_copy_g2s_hint(dst, a_at, W_A_HALF, &s_full[s], keep);
+                if (lane == 1) bulk_copy_g2s_hint(dst + W_A_HALF, a_at + A_TILE, W_A_HALF, &s_full[s], keep);
             }
+            if (lane == 2) bulk_copy_g2s(dst + 2 * W_A_HALF, b_at, C::B_HALF, &s_full[s]);
+            if (lane == 3) bulk_copy_g2s(dst + 2 * W_A_HALF + C::B_HALF, b_at + C::B_TILE / 2, C::B_HALF, &s_full[s]);
             armed = t + 1;
         }
         if (lane == 0 && s_fail) {
