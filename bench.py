@@ -234,14 +234,20 @@ def family_work(stats, B, elsize):
     }
 
 
-# DRAM bytes (read + write) of ONE launch of the named family's dominant kernel, from ncu captures of the same
-# kernels on one B200 (summaries under profiles/); None = not captured.  (config, family) -> bytes per launch
+# DRAM bytes (read + write) of ONE launch of the named family's dominant kernel, from `ncu` captures of the same
+# kernels on one B200 (dram__bytes_read.sum + dram__bytes_write.sum); None = not captured.  (config, family) -> bytes
 TRAFFIC_PER_LAUNCH = {
     # configs[1], B = 512: one dataflow launch each for the forward pass and the element flows, one batched launch
     # for the parameter flows
     ("cfg1", "pcx_sum_fwd"): 389.0e6,
     ("cfg1", "pcx_sum_bwd_ele"): 801.4e6,
     ("cfg1", "pcx_sum_bwd_par"): 636.3e6,
+    # configs[4], B = 256: the GEMM of one 4096 x 4096 transition layer (captured without cache flushes between
+    # kernels: the tied parameter tiles stay in L2 from layer to layer); parameter flows: the capture of a 7-layer
+    # circuit scaled to the 127 layers of the one product (traffic grows with the contraction depth)
+    ("cfg4", "pcx_sum_fwd"): 31.7e6,
+    ("cfg4", "pcx_sum_bwd_ele"): 51.0e6,
+    ("cfg4", "pcx_sum_bwd_par"): 449.2e6 * 127 / 7,
 }
 
 
