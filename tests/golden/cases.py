@@ -306,3 +306,17 @@ def dump_tables(pc) -> dict:
                 if getattr(ns, name, None) is not None:
                     put(f"ns{ni}/{name}", getattr(ns, name))
     return out
+
+
+def tables_digest(pc):
+    """(number of arrays, SHA-256 over names, dtypes, shapes and bytes of every compiled table of the parity set)."""
+    import hashlib
+    tables = dump_tables(pc)
+    h = hashlib.sha256()
+    for key in sorted(tables):
+        a = np.ascontiguousarray(tables[key])
+        h.update(key.encode())
+        h.update(str(a.dtype).encode())
+        h.update(str(a.shape).encode())
+        h.update(a.tobytes())
+    return len(tables), h.hexdigest()

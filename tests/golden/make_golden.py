@@ -7,7 +7,8 @@ The reference imports matplotlib (absent here) and touches CUDA in three places 
 neutralised below, in this script only, so that its table compiler runs on the host
 (``disable_gpu_compilation=True``).  Nothing else of the reference is modified, and the fixtures are plain
 NumPy archives of int64 tables.  It also writes one checkpoint with the reference's own ``save``
-(``ref_hmm_blocks.jpc``) for the loader test.
+(``ref_hmm_blocks.jpc``) for the loader test, and, with ``--full``, ``full_tables.json``: a SHA-256 over all tables the
+reference compiler emits for the benchmark configurations 1-4 at FULL size (too large to store as arrays).
 """
 import contextlib
 import os
@@ -55,6 +56,24 @@ def main():
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **tables)
         print(f"{name}: {len(tables)} arrays, num_nodes={pc.num_nodes}, num_edges={pc.num_edges}")
     checkpoint_fixture(api)
+    if "--full" in sys.argv:
+        full_size_digests()
+
+
+def full_size_digests():
+    import json
+    import pyjuice as juice
+    import bench
+    from cases import tables_digest
+    out = {}
+    for cfg in ("cfg1", "cfg2", "cfg3", "cfg4"):
+        ns, _ = bench.build_workload(cfg, 8, lib=bench.ReferenceStructures(juice))
+        pc = juice.compile(ns, disable_gpu_compilation=True, verbose=False)
+        n, digest = tables_digest(pc)
+        out[cfg] = {"arrays": n, "sha256": digest, "num_nodes": int(pc.num_nodes), "num_edges": int(pc.num_edges)}
+        print(cfg, out[cfg], flush=True)
+    with open(os.path.join(HERE, "full_tables.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
 
 
 def checkpoint_fixture(api):
