@@ -408,6 +408,15 @@ int pcx_em_input_cat(float* params, const float* param_flows, const int32_t* sou
                      const int32_t* s_pids, const int32_t* s_pfids, const int32_t* node_cats,
                      int64_t n_source, int max_cats, float step, float pseudo, int keep_zero, void* stream);
 
+/* Flows of unobserved categorical leaves: param_flows[s_pfids[n] + c] += scale * source_flow[k] * params[s_pids[n] + c]
+ * for the k-th source node n = source_nids[k] and every category c (source_flow: the linear flow of the node plus
+ * that of the nodes tied to it).  Used by the top-down probabilities of the rescaled EM update.  Replaces
+ * InputLayer.add_missing_flows / Categorical.bk_flow_mask_fn (layer/input_layer.py:894-968,
+ * nodes/distributions/categorical.py:123-160). */
+int pcx_input_cat_missing(float* param_flows, const float* params, const float* source_flow,
+                          const int32_t* source_nids, const int32_t* s_pids, const int32_t* s_pfids,
+                          const int32_t* node_cats, int64_t n_source, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

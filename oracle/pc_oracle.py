@@ -280,6 +280,68 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
     return st
 
 
+def top_down(pc, params: torch.Tensor, input_params, scale: float = 1.0, tables=None, dtype=torch.float64):
+    """Top-down probabilities of a normalised circuit and the parameter flows they induce
+    (model/backend/top_down_prob.py:15-402, layer/input_layer.py:894-968): td(root) = scale; an element receives
+    sum_n td(n) theta(n, e); a node the sum of its parent elements; parameter flow theta(n, e) td(n); a leaf's td,
+    plus that of the leaves tied to it, spreads over its categories in proportion to its parameters.
+    Returns (td [num_nodes], sum parameter flows, [input parameter flows])."""
+    t = tables or _tables(pc)
+    params = params.detach().cpu().to(dtype)
+    nn_, ne_ = t["num_nodes"], t["num_elements"]
+    td = torch.zeros(nn_, dtype=dtype)
+    td[t["root"][0]:t["root"][1]] = scale
+    pf = torch.zeros(t["num_param_flows"], dtype=dtype)
+    inner = t["inner"]
+    for gi in range(len(inner) - 1, -1, -1):
+        kind, layers = inner[gi]
+        if kind == "prod":
+            for layer in layers:
+                j = torch.arange(layer["bs"])
+                for u_cids, parids in zip(layer["u_cids"], layer["parids"]):
+                    rows = parids[:, :, None] + j[None, None, :]
+                    inc = torch.where((parids == 0)[:, :, None], torch.zeros((), dtype=dtype), etd[rows]).sum(dim=1)
+                    tgt = (u_cids[:, None] + j[None, :]).reshape(-1)
+                    td[tgt] += inc.reshape(-1)
+        else:
+            etd = torch.zeros(ne_, dtype=dtype)
+            for layer in layers:
+                m = torch.arange(layer["bs"])
+                for nids, cids, pids, pfids in zip(layer["nids"], layer["cids"], layer["pids"], layer["pfids"]):
+                    th = params[pids[:, :, None] + m[None, None, :]]                    # [n, K, bs]
+                    flow = th * td[nids[:, None] + m[None, :]][:, None, :]               # theta(n, e) td(n)
+                    flow = torch.where((cids == 0)[:, :, None], torch.zeros((), dtype=dtype), flow)
+                    etd.index_add_(0, cids.reshape(-1), flow.sum(dim=2).reshape(-1))
+                    pf.index_add_(0, (pfids[:, :, None] + m[None, None, :]).reshape(-1), flow.reshape(-1))
+            etd[0] = 0.0
+    ipfs = []
+    for lt, ip in zip(t["inputs"], input_params):
+        ip = ip.detach().cpu().to(dtype)
+        out = torch.zeros(lt["num_param_flows"], dtype=dtype)
+        r0, r1 = lt["rng"]
+        flow = td[r0:r1].clone()
+        n2s = pc.input_layer_group[len(ipfs)].node_id2source_id.cpu()
+        tied = n2s >= 0
+        flow.index_add_(0, n2s[tied], td[r0:r1][tied])
+        for n in lt["source_nids"].tolist():
+            C = int(lt["metadata"][lt["s_mids"][n]])
+            a, b = int(lt["s_pids"][n]), int(lt["s_pfids"][n])
+            out[b:b + C] += flow[n] * ip[a:a + C]
+        ipfs.append(out)
+    return td, pf, ipfs
+
+
+def em_update_rescaled(pc, params, input_params, st: OracleState, step_size: float, pseudocount: float, cum_flow: float):
+    """The rescaled mini-batch EM update (model/tensorcircuit.py:1363-1387): flows * step_size / cum_flow, plus the
+    top-down flows of the current parameters at (1 - step_size), then the update with step size one."""
+    _, pf, ipfs = top_down(pc, params, input_params, scale=1.0 - step_size, tables=st.tables, dtype=st.param_flows.dtype)
+    st2 = OracleState()
+    st2.tables = st.tables
+    st2.param_flows = st.param_flows * (step_size / cum_flow) + pf
+    st2.input_param_flows = [a * (step_size / cum_flow) + b for a, b in zip(st.input_param_flows, ipfs)]
+    return em_update(pc, params, input_params, st2, 1.0, pseudocount)
+
+
 def em_update(pc, params: torch.Tensor, input_params, st: OracleState, step_size: float, pseudocount: float = 0.0,
               reference_compat: bool = False):
     """Returns ``(new_params, [new_input_params])``; flows are taken from ``st``.

@@ -114,9 +114,36 @@ em_input_cat_kernel(float* __restrict__ params, const float* __restrict__ flows,
     }
 }
 
+// Flow of a leaf whose variable is not observed: its (linear) flow f spreads over the categories in proportion to the
+// parameters, flows[s_pfids + c] += scale * f * params[s_pids + c].  One CTA per source node.
+__global__ void __launch_bounds__(NT)
+input_cat_missing_kernel(float* __restrict__ flows, const float* __restrict__ params,
+                         const float* __restrict__ source_flow, const int32_t* __restrict__ source_nids,
+                         const int32_t* __restrict__ s_pids, const int32_t* __restrict__ s_pfids,
+                         const int32_t* __restrict__ node_cats, float scale) {
+    const int64_t sidx = blockIdx.x;
+    const float f = scale * source_flow[sidx];
+    if (f == 0.0f) return;
+    const int n = source_nids[sidx];
+    const float* p = params + (int64_t)s_pids[n];
+    float* out = flows + (int64_t)s_pfids[n];
+    const int num_cats = node_cats[n];
+    for (int c = threadIdx.x; c < num_cats; c += NT) out[c] += f * p[c];      // one writer per (source node, category)
+}
+
 }  // namespace
 
 extern "C" {
+
+int pcx_input_cat_missing(float* param_flows, const float* params, const float* source_flow,
+                          const int32_t* source_nids, const int32_t* s_pids, const int32_t* s_pfids,
+                          const int32_t* node_cats, int64_t n_source, float scale, void* stream) {
+    if (n_source <= 0) return 0;
+    input_cat_missing_kernel<<<(unsigned)n_source, NT, 0, (cudaStream_t)stream>>>(param_flows, params, source_flow,
+                                                                                 source_nids, s_pids, s_pfids, node_cats, scale);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
 
 int pcx_tied_accum(float* flows, int64_t start, int64_t n, const int64_t* ch_starts, int n_chs, void* stream) {
     if (n <= 0 || n_chs <= 0) return 0;

@@ -357,6 +357,25 @@ class InputLayer(Layer, nn.Module):
                   self._dev["s_pids"], self._dev["s_pfids"], self._dev["node_cats"], int(self.source_nids.numel()), self.max_cats,
                   float(step_size), float(pseudocount), int(bool(keep_zero_params)))
 
+    def add_missing_flows(self, node_flows: torch.Tensor, scale: float = 1.0, **kwargs):
+        """``node_flows``: one LINEAR flow per node of the circuit (``[num_nodes]``).  Every leaf's flow, plus that of
+        the leaves tied to it, is spread over its categories in proportion to its parameters and added to the
+        parameter flows (layer/input_layer.py:894-968)."""
+        self._require_cuda()
+        if self._param_flows is None:
+            self.init_param_flows()
+        s, e = self._output_ind_range
+        td = node_flows[s:e].to(torch.float32)
+        n2s = self.node_id2source_id.to(self.device)                # -1 for source nodes, else the source's node id
+        src_flow = td.clone()
+        tied = n2s >= 0
+        if bool(tied.any()):
+            src_flow.index_add_(0, n2s[tied], td[tied])
+        src_flow = src_flow[self.source_nids.to(self.device)].contiguous()
+        _lib.call("pcx_input_cat_missing", self._param_flows, self.params.data, src_flow, self._dev["source_nids"],
+                  self._dev["s_pids"], self._dev["s_pfids"], self._dev["node_cats"], int(self.source_nids.numel()),
+                  float(scale))
+
     def update_parameters(self):
         params = self.params.detach().cpu()
         for ns in self.nodes:

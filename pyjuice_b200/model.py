@@ -998,13 +998,72 @@ class TensorCircuit(nn.Module):
     def zero_param_flows(self):
         self.init_param_flows(flows_memory=0.0)
 
+    def eval_top_down_probs(self, update_pflow: bool = True, scale: float = 1.0):
+        """Top-down probability of every node of a normalised circuit — the probability that a top-down sample passes
+        through it: 1 for the root, parameter-weighted through sum nodes, copied through product nodes — and, with
+        ``update_pflow``, ``scale * td(n) * theta(n, c)`` added to every parameter flow
+        (model/backend/top_down_prob.py:290-402).
+
+        This is the backward pass of a circuit whose every node has value one (log-value 0), with linear flows and a
+        root flow of ``scale``, so it runs on the same kernels: eight identical columns (the tensor-core tiles want a
+        batch that is a multiple of eight) that carry ``scale / 8`` each.  Returns the top-down probabilities
+        ``[num_nodes]`` (times ``scale``)."""
+        self._require_cuda()
+        COLS = 8
+        with torch.no_grad():
+            t = self.__dict__.get("_tdp")
+            if t is None:
+                em = torch.zeros(self.num_elements, COLS, device=self.device)
+                em[:self.num_dummy_eles] = NEG_INF
+                t = dict(nm=torch.zeros(self.num_nodes, COLS, device=self.device), em=em,
+                         nf=torch.empty(self.num_nodes, COLS, device=self.device),
+                         ef=torch.empty(self.num_elements, COLS, device=self.device),
+                         w=torch.empty(self.num_root_nodes, COLS, device=self.device))
+                self._tdp = t
+            if self.param_flows is None:
+                self.init_param_flows()
+            saved = (self.node_mars, self.element_mars, self.node_flows, self.element_flows, self._eflow_mode)
+            self.node_mars, self.element_mars, self.node_flows, self.element_flows = t["nm"], t["em"], t["nf"], t["ef"]
+            try:
+                _fill(self.node_flows, 0.0)
+                _fill(self.element_flows, 0.0)
+                t["w"].fill_(float(scale) / COLS)
+                r0, r1 = self._root_node_range
+                _lib.call("pcx_set_root_flows", self.node_flows, t["w"], r0, r1 - r0, COLS, 0)
+                if _lib.SUM_MODE != 0:
+                    self._packer.refresh(self.params.data)
+                key = ("bk-tdp", COLS, bool(update_pflow), 0, self._launch_cfg(), self.params.data_ptr(),
+                       self.param_flows.data_ptr() if update_pflow else 0)
+                self._batched_par_pending = self._bk_par_pending.get(key, False)
+                self._run_inner(key, partial(self._backward_inner, bool(update_pflow), False))
+                self._bk_par_pending[key] = self._batched_par_pending
+                if update_pflow and self._batched_par_pending:
+                    self._launch_batched_par(False)
+                td = self.node_flows.sum(dim=1)
+                if update_pflow:
+                    for layer in self.input_layer_group:
+                        layer.add_missing_flows(td, scale=1.0)       # `td` already carries the scale
+            finally:
+                self.node_mars, self.element_mars, self.node_flows, self.element_flows, self._eflow_mode = saved
+        return td
+
     def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False,
                       step_size_rescaling: bool = False, **kwargs):
         """theta <- (1 - step_size) theta + step_size * (F + pseudocount / nch) / (sum F + pseudocount), for every
-        sum node and every categorical leaf, from the accumulated flows F."""
+        sum node and every categorical leaf, from the accumulated flows F.
+
+        ``step_size_rescaling`` (model/tensorcircuit.py:1363-1375): the flows are first scaled to
+        ``step_size / (total flow of the window)``, the current parameters enter as ``(1 - step_size)`` times their
+        top-down probabilities, and the update is then made with step size one."""
         assert 0.0 < step_size <= 1.0, "`step_size` should be between 0 and 1."
-        _unsupported(step_size_rescaling=step_size_rescaling)
         self._require_cuda()
+        if step_size_rescaling:
+            cum = self._cum_flow
+            assert cum > 0.0, "Please perform a backward pass before calling `mini_batch_em`."
+            self.init_param_flows(flows_memory=step_size / cum)
+            self.eval_top_down_probs(update_pflow=True, scale=1.0 - step_size)
+            self._cum_flow = 0.0
+            step_size = 1.0
         with torch.no_grad():
             def sum_update():
                 head = self.param_flows[:2048].clone() if (self._reference_compat and self._fusing_dev) else None

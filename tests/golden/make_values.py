@@ -97,6 +97,20 @@ def run_case(api, name, seed, B, dev):
                 floor = 1e-6 * max(np.abs(ref).max(), 1e-30)
                 dev.append(float((np.abs(v - ref) / np.maximum(np.abs(ref), floor)).max()))
             out["default_dev"] = np.asarray(dev)
+    # the rescaled update (model/tensorcircuit.py:1363-1375): flows * step / total + (1 - step) * top-down flows
+    pc.params.data.copy_(p0)
+    for layer, p in zip(pc.input_layer_group, ip0):
+        layer.params.data.copy_(p)
+    pc.init_param_flows(flows_memory=0.0)
+    pc._cum_flow = 0.0
+    with torch.no_grad():
+        pc(xd, force_use_fp32=True)
+    pc.backward(xd, flows_memory=1.0, force_use_fp32=True)
+    pc.mini_batch_em(step_size=0.25, pseudocount=PSEUDOCOUNT, step_size_rescaling=True)
+    torch.cuda.synchronize()
+    out["params1_rescaled"] = pc.params.detach().cpu().numpy()
+    for i, layer in enumerate(pc.input_layer_group):
+        out[f"iparams1_rescaled_{i}"] = layer.params.detach().cpu().numpy()
     return out
 
 

@@ -38,7 +38,25 @@ def test_full_size_step_matches_oracle(cfg, batch):
     pc = pj.compile(ns).to(DEV)
     magnitude = pc(_to_tensor(x).to(DEV)).abs().max().item()
     errs = check_against_oracle(pc, _to_tensor(x), rtol=1e-3 + 4 * 1.1920929e-07 * magnitude)
-    print(cfg, magnitude, errs)
+    print("full size", cfg, f"max |LL| {magnitude:.0f}", {k: f"{v:.2e}" for k, v in errs.items()})
+    _lib.check_status()
+
+
+def test_cfg4_layer_shape_matches_oracle():
+    """configs[4] at its full WIDTH (4096 states in blocks of 1024, 32768 tokens: the wide dense kernels with folded
+    products and direct flow stores, the transposed leaf tables, tied parameters) on a sequence short enough for the
+    fp64 oracle: log-likelihood within 1e-3 nats, flows and post-EM parameters within 1e-3 relative."""
+    import numpy as np
+    torch.manual_seed(4)
+    ns = pj.structures.HMM(seq_length=4, num_latents=4096, num_emits=32768, homogeneous=True)
+    ns.init_parameters()
+    pc = pj.compile(ns).to(DEV)
+    assert any(f.get("dense") for f in pc._fused.values()) and pc.input_layer_group[0]._shadow is not None
+    x = torch.from_numpy(np.random.default_rng(4).integers(0, 32768, size=(64, 4)))
+    x[:, 0] = x[0, 0]                                    # one token shared by all samples: many flows into one row
+    for rep in range(2):
+        errs = check_against_oracle(pc, x, fold_input_flows=True)
+    print("cfg4 width", {k: f"{v:.2e}" for k, v in errs.items()})
     _lib.check_status()
 
 

@@ -80,3 +80,37 @@ def test_decaying_flows_over_several_steps(name):
         ref.update(0.3, 0.1, zero_flows=False)
         print(name, i, ref.check_params(pc))
     assert abs(pc._cum_flow - 32 * (1 + 0.5 + 0.25 + 0.125)) < 1e-3
+
+
+@pytest.mark.parametrize("name", ["simple_model", "hmm_blocks", "tied_sums", "hclt_b128", "pd_small", "hmm_b128"])
+def test_top_down_probabilities_and_rescaled_update(name):
+    """`eval_top_down_probs` against the oracle's recursion, and `mini_batch_em(step_size_rescaling=True)`
+    (flows * step / total flow + (1 - step) * top-down flows, then an update with step one) against the same
+    schedule on the CPU.  Reference: model/backend/top_down_prob.py:290-402, model/tensorcircuit.py:1363-1387."""
+    from oracle import pc_oracle as orc
+    from helpers import oracle_step, rel_close
+    pc = _build(name, seed=14).to(DEV)
+    p0 = pc.params.data.double().cpu()
+    ip0 = [l.params.data.double().cpu() for l in pc.input_layer_group]
+    td_ref, _, _ = orc.top_down(pc, p0, ip0, 1.0)
+    td = pc.eval_top_down_probs(update_pflow=False, scale=1.0)
+    ok, err = rel_close(td[pc.num_dummy_nodes:], td_ref[pc.num_dummy_nodes:])
+    assert ok, f"top-down probabilities rel err {err}"
+
+    x = data_for(pc, 40, seed=3)
+    for rep in range(2):                                     # second round: captured / replayed launches
+        p0 = pc.params.data.double().cpu()
+        ip0 = [l.params.data.double().cpu() for l in pc.input_layer_group]
+        _, st, _ = oracle_step(pc, x, None, params=p0, input_params=ip0)
+        ref_p, ref_ip = orc.em_update_rescaled(pc, p0, ip0, st, 0.25, 0.1, cum_flow=40.0)
+        pc.init_param_flows(flows_memory=0.0)
+        pc(x.to(DEV))
+        pc.backward(x.to(DEV))
+        pc.mini_batch_em(step_size=0.25, pseudocount=0.1, step_size_rescaling=True)
+        assert pc._cum_flow == 0.0
+        ok, err = rel_close(pc.params.data[pc.num_dummy_params:], ref_p[pc.num_dummy_params:])
+        assert ok, f"rescaled update, sum parameters rel err {err}"
+        for layer, ref in zip(pc.input_layer_group, ref_ip):
+            ok, err = rel_close(layer.params.data, ref)
+            assert ok, f"rescaled update, input parameters rel err {err}"
+    _lib.check_status(DEV)

@@ -77,6 +77,13 @@ def test_oracle_matches_the_reference_itself(name):
     orc.backward(pc, x, p0, ip0, st, reference_compat=compat)
     new_p, new_ip = orc.em_update(pc, p0, ip0, st, float(v["step_size"]), float(v["pseudocount"]), reference_compat=compat)
     errs = _compare(name, pc, t, n_in, tol, lls, st.node_flows.exp(), st.param_flows, st.input_param_flows, new_p, new_ip)
+    if "params1_rescaled" in v.files and not compat:
+        rp, rip = orc.em_update_rescaled(pc, p0, ip0, st, 0.25, float(v["pseudocount"]), cum_flow=float(x.size(0)))
+        ok, errs["rescaled"] = rel_close(rp[pc.num_dummy_params:], t("params1_rescaled")[pc.num_dummy_params:], tol[1])
+        assert ok, f"{name}: rescaled update differs from the reference's by {errs['rescaled']}"
+        for i in range(n_in):
+            ok, e = rel_close(rip[i], t(f"iparams1_rescaled_{i}"), tol[1])
+            assert ok, f"{name}: rescaled update (input parameters) differs from the reference's by {e}"
     print(name, {k: f"{e:.1e}" for k, e in errs.items()})
 
 
@@ -105,5 +112,19 @@ def test_cuda_path_matches_the_reference_itself(name):
         pc.mini_batch_em(step_size=float(v["step_size"]), pseudocount=float(v["pseudocount"]))
         errs = _compare(name, pc, t, n_in, tol, lls, flows, pf, ipf, pc.params.data,
                         [layer.params.data for layer in pc.input_layer_group])
+    if "params1_rescaled" in v.files and name not in COMPAT:
+        pc.params.data.copy_(t("params0"))
+        pc._packer.invalidate()
+        for i, layer in enumerate(pc.input_layer_group):
+            layer.params.data.copy_(t(f"iparams0_{i}"))
+        pc.init_param_flows(flows_memory=0.0)
+        pc(x)
+        pc.backward(x)
+        pc.mini_batch_em(step_size=0.25, pseudocount=float(v["pseudocount"]), step_size_rescaling=True)
+        ok, errs["rescaled"] = rel_close(pc.params.data[pc.num_dummy_params:], t("params1_rescaled")[pc.num_dummy_params:], tol[1])
+        assert ok, f"{name}: rescaled update differs from the reference's by {errs['rescaled']}"
+        for i, layer in enumerate(pc.input_layer_group):
+            ok, e = rel_close(layer.params.data, t(f"iparams1_rescaled_{i}"), tol[1])
+            assert ok, f"{name}: rescaled update (input parameters) differs from the reference's by {e}"
     print(name, {k: f"{e:.1e}" for k, e in errs.items()})
     _lib.check_status("cuda:0")
