@@ -28,7 +28,8 @@ extern "C" {
 /* Library / build identification: returns the compute capability it was built for (100). */
 int pcx_build_arch(void);
 
-/* Arithmetic of the sum-layer contractions (process-wide): 0 = fp32 CUDA cores everywhere; 1 (default) = tensor
+/* Arithmetic of the sum-layer contractions, held PER CALLING HOST THREAD (two threads that drive two circuits never
+ * change each other's arithmetic; the Python host sets it before every call from the circuit's own attribute): 0 = fp32 CUDA cores everywhere; 1 (default) = tensor
  * cores (tcgen05, fp32 accumulate) with every fp32 factor split into bf16 hi + lo (three products) wherever the
  * block sizes allow a 128-row tile, fp32 CUDA cores elsewhere; 2 = as 1 with a single bf16 product.
  * Takes over the role of the reference's force_use_bf16 / force_use_fp32 switches (layer/sum_layer.py:752-771). */

@@ -7,8 +7,10 @@ into CUDA graphs.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
+import threading
 from ctypes import c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
@@ -70,7 +72,40 @@ SIGNATURES = {
 PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_set_dependent_launch": [I], "pcx_get_status": [], "pcx_clear_status": [],
          "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I],
          "pcx_sm_packed_bytes": [L, I, I], "pcx_dense2_scratch_bytes": [I, I, I]}
-SUM_MODE = 1        # mirror of the library's arithmetic mode (see set_sum_mode)
+SUM_MODE = 1        # the process default of the arithmetic mode (see set_sum_mode / use_sum_mode)
+_tls = threading.local()   # .mode: this thread's override (use_sum_mode); .c_mode: what the library holds for this thread
+
+
+def sum_mode() -> int:
+    """The arithmetic mode of launches made by the calling thread: the override of an enclosing `use_sum_mode`, else
+    the process default.  The library keeps the mode per host thread, so two circuits driven from two threads (or
+    one circuit inside `use_sum_mode`) never change each other's arithmetic."""
+    m = getattr(_tls, "mode", None)
+    return SUM_MODE if m is None else m
+
+
+def _sync_mode(lib) -> None:
+    want = sum_mode()
+    if getattr(_tls, "c_mode", 1) != want:
+        if lib.pcx_set_sum_mode(want) != 0:
+            raise PcxError(f"invalid sum mode {want}")
+        _tls.c_mode = want
+
+
+@contextlib.contextmanager
+def use_sum_mode(mode: Optional[int]):
+    """Run the enclosed calls of this thread in arithmetic mode ``mode`` (None: leave as is)."""
+    if mode is None:
+        yield
+        return
+    if mode not in (0, 1, 2):
+        raise PcxError(f"invalid sum mode {mode}")
+    prev = getattr(_tls, "mode", None)
+    _tls.mode = int(mode)
+    try:
+        yield
+    finally:
+        _tls.mode = prev
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -125,6 +160,7 @@ def call(name: str, *args) -> None:
             conv.append(a)
     global COUNT
     COUNT += 1
+    _sync_mode(lib)
     if dev is not None and dev.index != torch.cuda.current_device():
         with torch.cuda.device(dev):             # the C side reads per-device state (SM count, built-in scratch)
             rc = _invoke(lib, name, conv, args, dev)
@@ -151,9 +187,10 @@ def _invoke(lib, name, conv, args, dev) -> int:
 
 
 def set_sum_mode(mode: int) -> None:
-    """0 = fp32 CUDA cores, 1 = tensor cores with bf16 hi/lo split (default), 2 = tensor cores, single bf16."""
+    """Process default: 0 = fp32 CUDA cores, 1 = tensor cores with bf16 hi/lo split (default), 2 = tensor cores,
+    single bf16.  A circuit's own ``sum_mode`` attribute, or `use_sum_mode`, overrides it per call."""
     global SUM_MODE
-    if load().pcx_set_sum_mode(int(mode)) != 0:
+    if int(mode) not in (0, 1, 2):
         raise PcxError(f"invalid sum mode {mode}")
     SUM_MODE = int(mode)
 

@@ -1132,7 +1132,7 @@ constexpr int kMaxDevices = 64;
 // call on one device at the same time both resolve the same address and store the same value.
 unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
 
-int g_sum_mode = 1;      // 0: fp32 CUDA cores only, 1: tensor cores with bf16 hi/lo split, 2: tensor cores, single bf16
+thread_local int g_sum_mode = 1;      // per host thread; 0: fp32 CUDA cores only, 1: tensor cores with bf16 hi/lo split, 2: tensor cores, single bf16
 
 template <typename Kern>
 int configure_once(Kern kern, bool* done) {

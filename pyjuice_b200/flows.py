@@ -24,6 +24,19 @@ def _round_up(n: int) -> int:
     return (n + _ALIGN - 1) // _ALIGN * _ALIGN
 
 
+class _CastBack:
+    """Work handle of a reduced-precision all-reduce: ``wait()`` orders the current stream after the collective and
+    copies the result back into the fp32 arena."""
+
+    def __init__(self, works, dst, low):
+        self.works, self.dst, self.low = works, dst, low
+
+    def wait(self):
+        for w in self.works:
+            w.wait()
+        self.dst.copy_(self.low)
+
+
 class FlowArena:
     def __init__(self, sizes: Sequence[int], device):
         self.sizes = [int(s) for s in sizes]
@@ -79,12 +92,27 @@ class FlowArena:
             hi = float(int(cum_flow // _SPLIT))
             self.buf[:2].copy_(torch.tensor([hi, float(cum_flow - hi * _SPLIT)], dtype=torch.float32), non_blocking=True)
 
-    def all_reduce_range_async(self, begin: int, end: int, group=None):
-        """Start the fp32 SUM all-reduce of arena[begin:end] and return its work handle: the collective runs on the
+    def all_reduce_range_async(self, begin: int, end: int, group=None, dtype: Optional[torch.dtype] = None):
+        """Start the SUM all-reduce of arena[begin:end] and return a handle with ``wait()``: the collective runs on the
         backend's own stream after the work already enqueued on the current stream, and later kernels on the
-        current stream overlap with it until ``wait()`` is called on the handle."""
+        current stream overlap with it until ``wait()`` is called.  With ``dtype`` (e.g. bfloat16) the range is
+        reduced in that precision and copied back by ``wait()`` — half the bytes on the wire, as the reference's
+        ``sync_param_flows(dtype=...)`` (model/tensorcircuit.py:1456-1460); the header (the flow total) always
+        travels in fp32."""
         import torch.distributed as dist
-        return dist.all_reduce(self.buf[begin:end], op=dist.ReduceOp.SUM, group=group, async_op=True)
+        part = self.buf[begin:end]
+        if dtype is None or dtype == torch.float32:
+            return dist.all_reduce(part, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        works = []
+        lo = begin
+        if begin < _ALIGN:                              # the range starts inside the header: keep that part fp32
+            head = self.buf[begin:min(end, _ALIGN)]
+            works.append(dist.all_reduce(head, op=dist.ReduceOp.SUM, group=group, async_op=True))
+            lo = min(end, _ALIGN)
+        body = self.buf[lo:end]
+        low = body.to(dtype)
+        works.append(dist.all_reduce(low, op=dist.ReduceOp.SUM, group=group, async_op=True))
+        return _CastBack(works, body, low)
 
     @staticmethod
     def decode_total(head: torch.Tensor) -> float:

@@ -565,7 +565,7 @@ class SumLayer(Layer, nn.Module):
     DENSE_MIN_DEPTH = 512
 
     def _dense_ok(self, p: int, B: int, backward: bool) -> bool:
-        if not self.use_dense_kernels or B % 64 != 0 or _lib.SUM_MODE == 0:
+        if not self.use_dense_kernels or B % 64 != 0 or _lib.sum_mode() == 0:
             return False
         if backward:
             return self._packed_bk[p] is not None and self._dev["bk"][p][1].size(1) * self.block_size >= self.DENSE_MIN_DEPTH
@@ -580,7 +580,7 @@ class SumLayer(Layer, nn.Module):
     use_wide_dense = True
 
     def _wide_ok(self, p: int, B: int, backward: bool) -> bool:
-        if not (self.use_dense_kernels and self.use_wide_dense) or B % 8 != 0 or _lib.SUM_MODE == 0 or self._packer is None:
+        if not (self.use_dense_kernels and self.use_wide_dense) or B % 8 != 0 or _lib.sum_mode() == 0 or self._packer is None:
             return False
         if backward:
             depth = self._dev["bk"][p][1].size(1) * self.block_size
@@ -616,7 +616,7 @@ class SumLayer(Layer, nn.Module):
     use_sample_major = True          # tensor-core tiles of 128 samples x 32/64 nodes for small node blocks
 
     def _use_packed(self, params):
-        if self._packer is None or _lib.SUM_MODE == 0:
+        if self._packer is None or _lib.sum_mode() == 0:
             return False
         self._packer.refresh(params)
         return True

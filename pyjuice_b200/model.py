@@ -16,6 +16,7 @@ Buffers (fp32, batch innermost):
 """
 from __future__ import annotations
 
+import functools
 from functools import partial
 from typing import Optional, Sequence, Union
 
@@ -43,6 +44,17 @@ def _pc_model_backward_hook(grad, pc, inputs, **kwargs):
     return None
 
 
+def _in_own_mode(fn):
+    """Run a public method in the circuit's own arithmetic mode (``self.sum_mode``; None = the process default)."""
+    @functools.wraps(fn)
+    def wrapper(self, *args, **kwargs):
+        if self.sum_mode is None:
+            return fn(self, *args, **kwargs)
+        with _lib.use_sum_mode(self.sum_mode):
+            return fn(self, *args, **kwargs)
+    return wrapper
+
+
 class TensorCircuit(nn.Module):
     def __init__(self, root_ns, layer_sparsity_tol: float = 0.5, max_num_partitions: Optional[int] = None,
                  disable_gpu_compilation: bool = False, force_gpu_compilation: bool = False,
@@ -62,6 +74,7 @@ class TensorCircuit(nn.Module):
         self.use_cuda_graphs = True
         self.use_dataflow_launch = True       # runs of folded depths as one launch (tiles wait on counters)
         self.use_side_stream = True           # independent kernels of a step share the device (two streams)
+        self.sum_mode = None                  # this circuit's arithmetic (0, 1 or 2 as `_lib.set_sum_mode`); None = default
         self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
         self.dense_par_max_bytes = 16 << 30   # operand buffers of the dense parameter-flow product (all groups)
         self.default_propagation_alg = "LL"
@@ -472,7 +485,7 @@ class TensorCircuit(nn.Module):
     def _fusion_on(self, gi: int, backward: bool = False) -> bool:
         """Whether depth `gi` (a sum group) runs with its product layer folded in.  The folded parameter-flow kernel
         reads eight samples per vector load, so the backward sweep only folds when the batch is a multiple of 8."""
-        if not (self.fuse_product_layers and _lib.SUM_MODE != 0 and gi in self._fused):
+        if not (self.fuse_product_layers and _lib.sum_mode() != 0 and gi in self._fused):
             return False
         if self._fused[gi]["sm"] and not SumLayer.use_sample_major:
             return False
@@ -485,7 +498,7 @@ class TensorCircuit(nn.Module):
 
     def _launch_cfg(self):
         """Everything that changes which kernels a pass launches (part of the key of a captured graph)."""
-        return (_lib.SUM_MODE, self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
+        return (_lib.sum_mode(), self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
                 SumLayer.use_dense_kernels, SumLayer.use_wide_dense, SumLayer.use_sample_major,
                 getattr(self._packer, "grown", 0),
                 self._reference_compat)
@@ -579,6 +592,7 @@ class TensorCircuit(nn.Module):
             else:
                 group.forward(self.node_mars, self.element_mars, self.params.data)
 
+    @_in_own_mode
     def forward(self, inputs: torch.Tensor, input_layer_fn=None, cache=None, return_cache: bool = False,
                 propagation_alg: Optional[str] = None, pflow_temperature: float = 1.0, **kwargs):
         """Per-sample log-likelihoods ``[B, num_roots]`` of ``inputs`` (``[B, num_vars]``, integer)."""
@@ -595,12 +609,12 @@ class TensorCircuit(nn.Module):
             # the operand tiles of the tensor-core kernels are re-packed (when the parameters changed) on a second
             # stream, beside the input layer: neither reads what the other writes
             cur = torch.cuda.current_stream(self.device)
-            forked = _lib.SUM_MODE != 0 and self.use_side_stream
+            forked = _lib.sum_mode() != 0 and self.use_side_stream
             if forked:
                 self._side_stream.wait_stream(cur)
                 with torch.cuda.stream(self._side_stream):
                     self._packer.refresh(self.params.data)   # outside any graph capture
-            elif _lib.SUM_MODE != 0:
+            elif _lib.sum_mode() != 0:
                 self._packer.refresh(self.params.data)
             for layer in self.input_layer_group:
                 layer.forward(data, self.node_mars)
@@ -619,7 +633,7 @@ class TensorCircuit(nn.Module):
     def _par_jobs(self, B: int):
         """Device job tables (one per child-table width) that let ONE launch compute the parameter flows of every
         depth whose product layer is folded in; cached per batch size."""
-        key = (B, _lib.SUM_MODE, self.fuse_product_layers)
+        key = (B, _lib.sum_mode(), self.fuse_product_layers)
         cache = self.__dict__.setdefault("_par_job_cache", {})
         if key in cache:
             return cache[key]
@@ -798,6 +812,7 @@ class TensorCircuit(nn.Module):
             _lib.call("pcx_sum_bwd_par_batched", self.param_flows, self.node_flows, self.node_mars, self.params.data,
                       jobs, n_jobs, n_items, fc, B, chunks_per_cta, int(bool(logspace_flows)))
 
+    @_in_own_mode
     def backward(self, inputs: Optional[torch.Tensor] = None, ll_weights: Optional[torch.Tensor] = None,
                  compute_param_flows: bool = True, flows_memory: float = 1.0, input_layer_fn=None, cache=None,
                  return_cache: bool = False, allow_modify_flows: bool = False, propagation_alg: str = "LL",
@@ -858,7 +873,7 @@ class TensorCircuit(nn.Module):
                     s = w.sum(dtype=torch.float64)
                     self._cum_flow_dev = s if self._cum_flow_dev is None else self._cum_flow_dev + s
 
-            if _lib.SUM_MODE != 0:
+            if _lib.sum_mode() != 0:
                 self._packer.refresh(self.params.data)
             key = ("bk", B, bool(compute_param_flows), ls, self._launch_cfg(), self.params.data_ptr(),
                    self.param_flows.data_ptr() if compute_param_flows else 0)
@@ -888,12 +903,13 @@ class TensorCircuit(nn.Module):
         return None
 
     # ---- data-parallel flow synchronisation overlapped with the tail of the step ---------------------------------
-    def enable_flow_sync_overlap(self, group=None):
+    def enable_flow_sync_overlap(self, group=None, dtype: Optional[torch.dtype] = None):
         """Called by an optimizer that synchronises after EVERY backward pass (``ddp=True``, one mini-batch per
         update, fp32): the all-reduce is then split in two and overlapped — the input-layer flows are reduced while
         the sum layers' parameter flows are computed, the sum-layer flows (and the flow total in the arena header)
         while the input-layer parameters are updated."""
         self._overlap_group = (group,)
+        self._overlap_dtype = dtype                      # e.g. bfloat16: both parts travel in reduced precision
 
     def _overlap_ready(self) -> bool:
         import torch.distributed as dist
@@ -929,7 +945,8 @@ class TensorCircuit(nn.Module):
         self._finish_late_sync()
         arena = self._flow_arena
         self._early_sync = arena.all_reduce_range_async(arena.offsets[1], self._input_reduce_end(),
-                                                        group=self._overlap_group[0])
+                                                        group=self._overlap_group[0],
+                                                        dtype=getattr(self, "_overlap_dtype", None))
 
     def _finish_late_sync(self):
         """Make the current stream wait for the second part of the overlapped all-reduce (header + sum-layer flows)
@@ -998,6 +1015,7 @@ class TensorCircuit(nn.Module):
     def zero_param_flows(self):
         self.init_param_flows(flows_memory=0.0)
 
+    @_in_own_mode
     def eval_top_down_probs(self, update_pflow: bool = True, scale: float = 1.0):
         """Top-down probability of every node of a normalised circuit — the probability that a top-down sample passes
         through it: 1 for the root, parameter-weighted through sum nodes, copied through product nodes — and, with
@@ -1030,7 +1048,7 @@ class TensorCircuit(nn.Module):
                 t["w"].fill_(float(scale) / COLS)
                 r0, r1 = self._root_node_range
                 _lib.call("pcx_set_root_flows", self.node_flows, t["w"], r0, r1 - r0, COLS, 0)
-                if _lib.SUM_MODE != 0:
+                if _lib.sum_mode() != 0:
                     self._packer.refresh(self.params.data)
                 key = ("bk-tdp", COLS, bool(update_pflow), 0, self._launch_cfg(), self.params.data_ptr(),
                        self.param_flows.data_ptr() if update_pflow else 0)
@@ -1047,6 +1065,7 @@ class TensorCircuit(nn.Module):
                 self.node_mars, self.element_mars, self.node_flows, self.element_flows, self._eflow_mode = saved
         return td
 
+    @_in_own_mode
     def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False,
                       step_size_rescaling: bool = False, **kwargs):
         """theta <- (1 - step_size) theta + step_size * (F + pseudocount / nch) / (sum F + pseudocount), for every
@@ -1125,7 +1144,8 @@ class TensorCircuit(nn.Module):
                 _ = self._cum_flow                          # fold a pending total of an earlier sync into the host part
             total = self._cum_flow_host if self._cum_flow_dev is None else self._cum_flow_dev + self._cum_flow_host
             arena.write_total(total)
-            self._late_sync = arena.all_reduce_range_async(0, arena.segment_end(0), group=group)
+            self._late_sync = arena.all_reduce_range_async(0, arena.segment_end(0), group=group,
+                                                           dtype=getattr(self, "_overlap_dtype", None))
             self._late_head = bool(sync_cum_flow)
             early.wait()
             if not _lazy:
@@ -1168,6 +1188,7 @@ class TensorCircuit(nn.Module):
     # ------------------------------------------------------------------------------------------
     # accessors
     # ------------------------------------------------------------------------------------------
+    @_in_own_mode
     def update_parameters(self, clone: bool = True):
         if self.device.type == "cuda":
             _lib.check_status(self.device)                  # parameters computed after a timed-out wait are wrong

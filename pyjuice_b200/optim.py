@@ -64,8 +64,8 @@ class MiniBatchEM(CircuitOptimizer):
         self.step_size = step_size
         self.niters_per_update = niters_per_update
         self._iter = 0
-        if ddp and sync_every == 1 and niters_per_update == 1 and ddp_dtype in (None, torch.float32):
-            pc.enable_flow_sync_overlap(ddp_group)       # every backward pass is followed by a sync: overlap it
+        if ddp and sync_every == 1 and niters_per_update == 1:
+            pc.enable_flow_sync_overlap(ddp_group, ddp_dtype)     # every backward pass is followed by a sync: overlap it
         else:
             pc._overlap_group = None
 

@@ -149,3 +149,50 @@ def test_local_sgd_two_ranks(tmp_path):
             assert torch.allclose(r[k]["snaps"][step][1], pcs[k].input_layer_group[0].params.data.cpu(), rtol=1e-4, atol=1e-7)
     for k in range(2):
         assert torch.allclose(r[k]["lls"], pcs[k](x[k * 32:(k + 1) * 32]).cpu(), rtol=1e-5, atol=1e-4)
+
+
+def _bf16_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device(dev))
+    try:
+        import pyjuice_b200 as pj
+        pc = _build().to(dev)
+        x = _data(pc, 64)
+        shard = x[rank * 32:(rank + 1) * 32].to(dev)
+        opt = pj.optim.MiniBatchEM(pc, step_size=0.2, pseudocount=0.1, ddp=True, ddp_dtype=torch.bfloat16)
+        assert pc._overlap_ready(), "a reduced-precision exchange keeps the overlapped two-part all-reduce"
+        for _ in range(5):
+            pc(shard).mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        torch.save(dict(params=pc.params.data.cpu(), iparams=pc.input_layer_group[0].params.data.cpu()),
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_bf16_flow_exchange_two_ranks(tmp_path):
+    """`ddp_dtype=torch.bfloat16` (the reference's `sync_param_flows(dtype=...)`, model/tensorcircuit.py:1456-1460):
+    the flows cross the link in bf16, through the same overlapped two-part all-reduce as fp32; the ranks stay
+    identical and the parameters stay within bf16's 2^-8 relative rounding of the fp32 single-GPU result."""
+    import torch.multiprocessing as mp
+    import pyjuice_b200 as pj
+    port = 37700 + (os.getpid() % 2000)
+    mp.spawn(_bf16_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(2))
+    assert torch.equal(r0["params"], r1["params"]) and torch.equal(r0["iparams"], r1["iparams"])
+    pc = _build().to("cuda:0")
+    x = _data(pc, 64).to("cuda:0")
+    opt = pj.optim.MiniBatchEM(pc, step_size=0.2, pseudocount=0.1)
+    for _ in range(5):
+        pc(x).mean().backward()
+        opt.step()
+    err = ((r0["params"] - pc.params.data.cpu()).abs() / pc.params.data.cpu().clamp_min(1e-3)).max().item()
+    ierr = (r0["iparams"] - pc.input_layer_group[0].params.data.cpu()).abs().max().item()
+    print(f"bf16 exchange: worst relative parameter difference {err:.2e}, leaf parameters {ierr:.2e}")
+    assert err < 2e-2 and ierr < 2e-2

@@ -419,3 +419,40 @@ def test_allow_modify_flows_is_accepted_and_changes_nothing():
     assert torch.equal(pc.param_flows, want)
     with pytest.raises(AssertionError):
         pc.backward(x, logspace_flows=True, allow_modify_flows=True)
+
+
+def test_arithmetic_mode_belongs_to_the_circuit_and_the_calling_thread():
+    """Two circuits in one process keep their own arithmetic (`pc.sum_mode`): interleaved steps of an fp32
+    CUDA-core circuit and a tensor-core circuit give what each gives alone, and a step driven from a second host
+    thread under another process default does not change the first thread's results."""
+    import threading
+    from pyjuice_b200 import _lib
+    pc_a, pc_b, pc_c = (_build("hmm_b128", seed=3).to(DEV) for _ in range(3))
+    x = _data_for(pc_a, 64, seed=3).to(DEV)
+    pc_a.sum_mode, pc_b.sum_mode = 0, 2
+
+    def step(pc):
+        lls = pc(x)
+        pc.backward(x, flows_memory=0.0)
+        return lls.clone(), pc.param_flows.clone()
+
+    alone_a, alone_b = step(pc_a), step(pc_b)
+    assert not torch.equal(alone_a[0], alone_b[0]), "fp32 and single-bf16 arithmetic must differ somewhere"
+    for _ in range(2):                                   # interleaved: graphs and launch plans are keyed by the mode
+        got_b, got_a = step(pc_b), step(pc_a)
+        assert torch.equal(got_a[0], alone_a[0]) and torch.equal(got_a[1], alone_a[1])
+        assert torch.equal(got_b[0], alone_b[0]) and torch.equal(got_b[1], alone_b[1])
+    ref_c = step(pc_c)                                   # the process default (split bf16)
+    out = {}
+
+    def other_thread():
+        with _lib.use_sum_mode(0):
+            out["c_fp32"] = step(pc_c)
+        out["c_default"] = step(pc_c)
+
+    t = threading.Thread(target=other_thread)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert torch.equal(out["c_fp32"][0], alone_a[0]) and torch.equal(out["c_default"][0], ref_c[0])
+    assert torch.equal(step(pc_c)[0], ref_c[0]) and _lib.sum_mode() == 1
