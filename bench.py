@@ -55,6 +55,8 @@ CONFIGS = {
     # profiling case: the layer shape of cfg4 (4096 x 4096 tied transitions, 256 samples) in a circuit small enough
     # for multi-pass profiler captures (8 tokens, 2048-word vocabulary: well under 1 GB on the device)
     "cfg4-short": ("HMM 4096 states vocab2048 T=8 tied (profiling case)", 256),
+    # profiling case: the circuit of cfg2 at a quarter of its batch (a few GB on the device instead of 15)
+    "cfg2-b128": ("PD-28x28 256cats K=64 splits[4,7,14] (profiling case: batch 128)", 128),
 }
 
 
@@ -124,7 +126,7 @@ def build_workload(name: str, num_samples: int, lib=None):
         torch.manual_seed(1)
         x, tree, root = pdata.grid_gaussian_bn_samples(num_samples, 28, 28, seed=1)
         ns = lib.hclt_from_tree(tree, root, 128, 256)
-    elif name == "cfg2":
+    elif name in ("cfg2", "cfg2-b128"):
         torch.manual_seed(2)
         random.seed(2)
         pts = sorted(set(range(4, 28, 4)) | set(range(7, 28, 7)) | set(range(14, 28, 14)))

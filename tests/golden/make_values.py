@@ -35,6 +35,10 @@ sys.path.insert(0, os.path.join(HERE, "..", ".."))
 sys.path.insert(0, HERE)
 
 STEP_SIZE, PSEUDOCOUNT = 0.1, 0.1
+# The rescaled update (`step_size_rescaling=True`) is recorded for these cases only: on `sparse_sum` the reference's
+# own top-down pass made an illegal memory access on a B200 (the CUDA context is lost after it), so it is not run
+# again there, nor on the cases after it that were never reached.
+RESCALED_CASES = ("hclt_cfg0", "simple_model", "simple_model_bs1", "simple_model_bs4")
 # case -> (seed, batch)
 VALUE_CASES = {
     "hclt_cfg0": (0, 256), "simple_model": (0, 64), "simple_model_bs1": (0, 33), "simple_model_bs4": (0, 64),
@@ -97,6 +101,8 @@ def run_case(api, name, seed, B, dev):
                 floor = 1e-6 * max(np.abs(ref).max(), 1e-30)
                 dev.append(float((np.abs(v - ref) / np.maximum(np.abs(ref), floor)).max()))
             out["default_dev"] = np.asarray(dev)
+    if name not in RESCALED_CASES:
+        return out
     # the rescaled update (model/tensorcircuit.py:1363-1375): flows * step / total + (1 - step) * top-down flows
     pc.params.data.copy_(p0)
     for layer, p in zip(pc.input_layer_group, ip0):
