@@ -4,6 +4,7 @@
 // Layout: every value buffer is [rows, B] fp32 with the batch innermost, so a warp that walks the
 // batch dimension reads and writes whole 128-byte lines.  Product rows are handled four samples per
 // thread (float4) whenever B is a multiple of 4.
+#include <algorithm>
 #include "pcx_common.cuh"
 #include "../../include/pcx_b200.h"
 
@@ -298,19 +299,31 @@ inline int stage_group(int max_cats) {
     return g > 16 ? 16 : g;
 }
 
+// Index arithmetic of the product kernels: thread t = (row r, vector column bc) with r = (block i, node j).  The
+// divisors are launch constants and almost always powers of two, so the split is two shifts (or two 32-bit
+// divisions); launches are cut on the host so that t fits in 32 bits.
+struct ProdDiv {
+    uint32_t bv, bs;            // vector columns per row, nodes per block
+    int lg_bv, lg_bs;           // log2 when a power of two, else -1
+};
+__device__ __forceinline__ void prod_split(const ProdDiv d, uint32_t t, uint32_t& i, uint32_t& j, uint32_t& bc) {
+    const uint32_t r = d.lg_bv >= 0 ? (t >> d.lg_bv) : (t / d.bv);
+    bc = t - r * d.bv;
+    i = d.lg_bs >= 0 ? (r >> d.lg_bs) : (r / d.bs);
+    j = r - i * d.bs;
+}
+
 // Product forward.  Thread = (row block i, node j of the block, VEC consecutive samples).
 template <int VEC>
 __global__ void prod_fwd_kernel(float* __restrict__ element_mars, const float* __restrict__ node_mars,
                                 const int32_t* __restrict__ nids, const int32_t* __restrict__ cids,
-                                int64_t n_blocks, int n_chs, int block_size, int B) {
-    const int bv = B / VEC;
-    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    int64_t total = n_blocks * block_size * bv;
+                                uint32_t total, int64_t block0, ProdDiv d, int n_chs, int B) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= total) return;
-    int b = (int)(t % bv) * VEC;
-    int64_t r = t / bv;
-    int j = (int)(r % block_size);
-    int64_t i = r / block_size;
+    uint32_t il, j, bc;
+    prod_split(d, t, il, j, bc);
+    const int64_t i = block0 + il;
+    const int b = (int)bc * VEC;
     float acc[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
@@ -335,16 +348,22 @@ __global__ void prod_fwd_kernel(float* __restrict__ element_mars, const float* _
 template <int VEC>
 __global__ void prod_bwd_kernel(float* __restrict__ node_flows, const float* __restrict__ element_flows,
                                 const int32_t* __restrict__ u_cids, const int32_t* __restrict__ parids,
-                                int64_t n_blocks, int n_pars, int block_size, int B, int logspace) {
-    const int bv = B / VEC;
-    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    int64_t total = n_blocks * block_size * bv;
+                                uint32_t total, int64_t block0, ProdDiv d, int n_pars, int B, int logspace) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= total) return;
-    int b = (int)(t % bv) * VEC;
-    int64_t r = t / bv;
-    int j = (int)(r % block_size);
-    int64_t i = r / block_size;
+    uint32_t il, j, bc;
+    prod_split(d, t, il, j, bc);
+    const int64_t i = block0 + il;
+    const int b = (int)bc * VEC;
     const int32_t* prow = parids + i * n_pars;
+    float* dst = node_flows + ((int64_t)u_cids[i] + j) * B + b;
+    float cur[VEC];                                     // requested first: its latency overlaps the parents' loads
+    if (VEC == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(dst);
+        cur[0] = q.x; cur[1] = q.y; cur[2] = q.z; cur[3] = q.w;
+    } else {
+        cur[0] = dst[0];
+    }
 
     float mx[VEC], sum[VEC];
 #pragma unroll
@@ -364,23 +383,44 @@ __global__ void prod_bwd_kernel(float* __restrict__ node_flows, const float* __r
         for (int v = 0; v < VEC; ++v) {
             if (!logspace) { sum[v] += x[v]; continue; }
             if (x[v] == PCX_NEG_INF) continue;
-            if (x[v] > mx[v]) { sum[v] = sum[v] * expf(mx[v] - x[v]) + 1.0f; mx[v] = x[v]; }
-            else sum[v] += expf(x[v] - mx[v]);
+            if (x[v] > mx[v]) { sum[v] = sum[v] * __expf(mx[v] - x[v]) + 1.0f; mx[v] = x[v]; }
+            else sum[v] += __expf(x[v] - mx[v]);
         }
     }
-    float* dst = node_flows + ((int64_t)u_cids[i] + j) * B + b;
     float out[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
         if (logspace) {
-            float inc = (mx[v] == PCX_NEG_INF) ? PCX_NEG_INF : mx[v] + logf(sum[v]);
-            out[v] = pcx_logaddexp(dst[v], inc);
+            // log(exp(cur) + exp(mx) * sum) around the larger of the two exponents
+            const float hi = fmaxf(cur[v], mx[v]);
+            const float s = __expf(cur[v] - hi) + sum[v] * __expf(mx[v] - hi);
+            out[v] = (hi == PCX_NEG_INF) ? PCX_NEG_INF : hi + __logf(s);
         } else {
-            out[v] = dst[v] + sum[v];
+            out[v] = cur[v] + sum[v];
         }
     }
     if (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
     else dst[0] = out[0];
+}
+
+inline int lg2_or_neg(uint32_t v) {
+    if (v == 0 || (v & (v - 1)) != 0) return -1;
+    int l = 0;
+    while ((1u << l) < v) ++l;
+    return l;
+}
+// Cuts `n_blocks` row blocks into launches of fewer than 2^31 threads; `launch(first block, blocks, threads, div)`.
+template <typename F>
+inline void prod_launches(int64_t n_blocks, int block_size, int bv, F launch) {
+    ProdDiv d;
+    d.bv = (uint32_t)bv; d.bs = (uint32_t)block_size;
+    d.lg_bv = lg2_or_neg(d.bv); d.lg_bs = lg2_or_neg(d.bs);
+    const int64_t per_block = (int64_t)block_size * bv;
+    const int64_t max_blocks = std::max<int64_t>(1, ((int64_t)1 << 31) / per_block - 1);
+    for (int64_t b0 = 0; b0 < n_blocks; b0 += max_blocks) {
+        const int64_t nb = std::min(max_blocks, n_blocks - b0);
+        launch(b0, (uint32_t)(nb * per_block), d);
+    }
 }
 
 inline int grid_for(int64_t work) {
@@ -516,11 +556,15 @@ int pcx_prod_fwd(float* element_mars, const float* node_mars, const int32_t* nid
                  int64_t n_blocks, int n_chs, int block_size, int B, void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
     if (B % 4 == 0) {
-        prod_fwd_kernel<4><<<grid_for(n_blocks * block_size * (B / 4)), kThreads, 0, (cudaStream_t)stream>>>(
-            element_mars, node_mars, nids, cids, n_blocks, n_chs, block_size, B);
+        prod_launches(n_blocks, block_size, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
+            prod_fwd_kernel<4><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                element_mars, node_mars, nids, cids, total, b0, d, n_chs, B);
+        });
     } else {
-        prod_fwd_kernel<1><<<grid_for(n_blocks * block_size * B), kThreads, 0, (cudaStream_t)stream>>>(
-            element_mars, node_mars, nids, cids, n_blocks, n_chs, block_size, B);
+        prod_launches(n_blocks, block_size, B, [&](int64_t b0, uint32_t total, ProdDiv d) {
+            prod_fwd_kernel<1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                element_mars, node_mars, nids, cids, total, b0, d, n_chs, B);
+        });
     }
     PCX_LAUNCH_CHECK();
     return 0;
@@ -530,11 +574,15 @@ int pcx_prod_bwd(float* node_flows, const float* element_flows, const int32_t* u
                  int64_t n_blocks, int n_pars, int block_size, int B, int logspace, void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
     if (B % 4 == 0) {
-        prod_bwd_kernel<4><<<grid_for(n_blocks * block_size * (B / 4)), kThreads, 0, (cudaStream_t)stream>>>(
-            node_flows, element_flows, u_cids, parids, n_blocks, n_pars, block_size, B, logspace);
+        prod_launches(n_blocks, block_size, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
+            prod_bwd_kernel<4><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                node_flows, element_flows, u_cids, parids, total, b0, d, n_pars, B, logspace);
+        });
     } else {
-        prod_bwd_kernel<1><<<grid_for(n_blocks * block_size * B), kThreads, 0, (cudaStream_t)stream>>>(
-            node_flows, element_flows, u_cids, parids, n_blocks, n_pars, block_size, B, logspace);
+        prod_launches(n_blocks, block_size, B, [&](int64_t b0, uint32_t total, ProdDiv d) {
+            prod_bwd_kernel<1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                node_flows, element_flows, u_cids, parids, total, b0, d, n_pars, B, logspace);
+        });
     }
     PCX_LAUNCH_CHECK();
     return 0;

@@ -54,16 +54,16 @@ __device__ __forceinline__ float folded2(const int2 r, const float* nmars_col, i
 // One CTA walks tiles m * n_st + st (static round-robin: tiles do not depend on each other).
 template <int NB, bool ELE>
 __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
-    constexpr int TCOLS = NB < 32 ? 32 : NB;
+    constexpr int TCOLS = 2 * NB;                      // two accumulators (one per stage)
     constexpr int TH_TILE = 2 * KG * NB * 16;          // bytes of one parameter tile (hi + lo)
     constexpr int HC = NB / 2;                         // epilogue: node columns per thread
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t s_bar[STAGES];
     __shared__ uint32_t s_tmem;
-    __shared__ float s_part[2][SM_SAMPLES];
-    __shared__ float s_max[SM_SAMPLES];
+    __shared__ float s_part[STAGES][2 * SM_SAMPLES];   // per stage: the two partial maxima of every sample
     __shared__ int s_fail;
+    static_assert(STAGES == 2, "two stages, two accumulators");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
             uint8_t* dst = st + g * (SM_SAMPLES * 16) + ls * 16;
             store_split8(reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst + SM_E_TILE), v);
         };
-        auto issue = [&](uint8_t* st, bool first) {
+        auto issue = [&](uint8_t* st, uint32_t acc_tmem) {       // one chunk into a fresh accumulator
             const uint32_t sa = smem_u32(st), sb = sa + 2 * SM_E_TILE;
 #pragma unroll
             for (int ks = 0; ks < KC / 16; ++ks) {
@@ -166,90 +166,100 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
                 const uint64_t dEl = smem_desc(sa + SM_E_TILE + ks * 2 * (SM_SAMPLES * 16), SM_SAMPLES * 16, 128);
                 const uint64_t dTh = smem_desc(sb + ks * 2 * (NB * 16), NB * 16, 128);
                 const uint64_t dTl = smem_desc(sb + KG * NB * 16 + ks * 2 * (NB * 16), NB * 16, 128);
-                mma_bf16_ss(tmem, dEh, dTh, idesc, (!first || ks > 0) ? 1u : 0u);
+                mma_bf16_ss(acc_tmem, dEh, dTh, idesc, ks > 0 ? 1u : 0u);
                 if (a.terms == 3) {
-                    mma_bf16_ss(tmem, dEh, dTl, idesc, 1u);
-                    mma_bf16_ss(tmem, dEl, dTh, idesc, 1u);
+                    mma_bf16_ss(acc_tmem, dEh, dTl, idesc, 1u);
+                    mma_bf16_ss(acc_tmem, dEl, dTh, idesc, 1u);
                 }
             }
         };
 
-        // ---- pass 1: per-sample maximum (tables this deep are read twice; the second read hits L2) -----------------
-        float mx = PCX_NEG_INF;
-        for (int c = 0; c < n_chunks; ++c) {                    // groups h, h + 2, h + 4, h + 6 of every chunk
+        // ---- one pass over the table, 64 entries at a time -------------------------------------------------------
+        // Every chunk is scaled by ITS OWN per-sample maximum m_c and multiplied into a fresh accumulator (two
+        // accumulators alternate); the threads take chunk c - 1 out of tensor memory while the tensor core works on
+        // chunk c and fold it into a running sum held in registers:
+        //     M' = max(M, m_c),   acc = acc * exp(M - M') + D_c * exp(m_c - M').
+        // The children are therefore gathered once (the gathers are what this kernel spends its time on), and long
+        // sums are carried in fp32 registers with round-to-nearest additions.
+        const int lq = warp & 3, c0 = (warp >> 2) * HC;
+        float acc[HC];
+#pragma unroll
+        for (int j = 0; j < HC; ++j) acc[j] = 0.0f;
+        float M = PCX_NEG_INF;                                   // running maximum of this thread's sample
+        float m_prev = PCX_NEG_INF;                              // maximum of the chunk that is still in tensor memory
+        bool failed = false;
+        auto drain = [&](int c, float m_c) {                     // fold chunk c (accumulator c & 1) into acc
+            if (!failed && !mbar_wait(&s_bar[c & 1], (ph[c & 1] + c / STAGES) & 1)) { failed = true; s_fail = 1; }
+            tc_fence_after_sync();
+            if (failed) return;
+            const float Mn = fmaxf(M, m_c);
+            const float so = (Mn == PCX_NEG_INF) ? 0.0f : __expf(M - Mn);
+            const float sn = (Mn == PCX_NEG_INF) ? 0.0f : __expf(m_c - Mn);
+#pragma unroll
+            for (int p = 0; p < HC / 8; ++p) {
+                float v[8];
+                tmem_ld<8>(tmem + (uint32_t)((c & 1) * NB) + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[8 * p + j] = acc[8 * p + j] * so + v[j] * sn;
+            }
+            M = Mn;
+            tc_fence_before_sync();
+        };
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % STAGES;
+            uint8_t* st = smem + s * SM_STAGE;
+            // stage s and accumulator s are free: chunk c - 2 was drained by every thread during iteration c - 1
+            copy_theta(c, st);
             float v[4][8];
             load_groups4(c * KC + h * 8, v);
+            float mx = PCX_NEG_INF;
 #pragma unroll
             for (int t = 0; t < 4; ++t)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[t][j]);
-        }
-        s_part[h][ls] = mx;
-        __syncthreads();
-        mx = fmaxf(s_part[0][ls], s_part[1][ls]);
-        if (h == 0) s_max[ls] = mx;
-
-        // ---- pass 2: exponentials -> operand tiles, multiply ------------------------------------------------
-        bool failed = false;
-        for (int c = 0; c < n_chunks; ++c) {
-            const int s = c % STAGES, use = c / STAGES;
-            uint8_t* st = smem + s * SM_STAGE;
-            if (c >= STAGES && !failed && !mbar_wait(&s_bar[s], (ph[s] + use - 1) & 1)) { failed = true; s_fail = 1; }
-            copy_theta(c, st);
-            {
-                float v[4][8];
-                load_groups4(c * KC + h * 8, v);
+            s_part[s][h * SM_SAMPLES + ls] = mx;
+            __syncthreads();
+            mx = fmaxf(s_part[s][ls], s_part[s][SM_SAMPLES + ls]);
 #pragma unroll
-                for (int t = 0; t < 4; ++t) store_group(st, h + 2 * t, v[t], mx);
-            }
+            for (int t = 0; t < 4; ++t) store_group(st, h + 2 * t, v[t], mx);
             cp_async_wait_all();
             fence_async_smem();
             __syncthreads();
             failed = failed || (s_fail != 0);
             if (tid == 0 && !failed) {
                 tc_fence_after_sync();
-                issue(st, c == 0);
+                issue(st, tmem + (uint32_t)(s * NB));
                 mma_commit(&s_bar[s]);
             }
+            if (c > 0) drain(c - 1, m_prev);
+            m_prev = mx;
         }
-        {
-            const int cl = n_chunks - 1;
-            if (tid == 0 && !failed && !mbar_wait(&s_bar[cl % STAGES], (ph[cl % STAGES] + cl / STAGES) & 1)) s_fail = 2;
+        drain(n_chunks - 1, m_prev);
 #pragma unroll
-            for (int s = 0; s < STAGES; ++s) ph[s] += (n_chunks - s + STAGES - 1) / STAGES;
-        }
-        __syncthreads();
+        for (int s = 0; s < STAGES; ++s) ph[s] += (n_chunks - s + STAGES - 1) / STAGES;
         failed = failed || (s_fail != 0);
-        tc_fence_after_sync();
 
         // ---- epilogue: lane = sample, column = node; warps w and w + 4 split the nodes ----------------------------
         if (!failed) {
-            const int lq = warp & 3, c0 = (warp >> 2) * HC;
-            const int es = lq * 32 + lane;                       // sample of this thread within the tile
+            const int es = lq * 32 + lane;                       // sample of this thread within the tile (= ls)
             const int b = b0 + es;
-            const float m_s = s_max[es];
             const int64_t base_row = (int64_t)a.rows[i0];        // merged rows are consecutive in the value buffer
+            if (b < B) {
 #pragma unroll
-            for (int p = 0; p < HC / 8; ++p) {
-                float v[8];
-                tmem_ld<8>(tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(c0 + 8 * p), v);
-                if (b >= B) continue;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int64_t off = (base_row + c0 + 8 * p + j) * B + b;
+                for (int j = 0; j < HC; ++j) {
+                    const int64_t off = (base_row + c0 + j) * B + b;
                     float o;
-                    if (!ELE) o = __logf(fmaxf(v[j], 1e-24f)) + m_s;
+                    if (!ELE) o = __logf(fmaxf(acc[j], 1e-24f)) + M;
                     else {
                         const float em = (a.fk != nullptr)
-                            ? folded2(a.fk[(int64_t)i0 * a.cbs + c0 + 8 * p + j], a.nmars + b, B) : a.emars[off];
-                        o = __logf(v[j]) + m_s + em;
+                            ? folded2(a.fk[(int64_t)i0 * a.cbs + c0 + j], a.nmars + b, B) : a.emars[off];
+                        o = __logf(acc[j]) + M + em;
                         if (!a.logspace) o = __expf(o);
                     }
                     a.out[off] = o;
                 }
             }
         }
-        tc_fence_before_sync();
         __syncthreads();
         if (s_fail != 0) break;
     }
@@ -259,15 +269,26 @@ __global__ void __launch_bounds__(NTH, 2) sum_sm_kernel(const SmArgs a) {
 }
 
 // Tables at most 64 deep (the common case for small blocks): one thread per sample, one chunk, no cross-thread
-// reduction, 24 - 48 KB of shared memory -- so that four to six CTAs share an SM and hide each other's latency.
-template <int NB, bool ELE>
-__global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArgs a, const int ng) {
+// reduction, 21 - 48 KB of shared memory.  A tile is a chain of dependent round trips (index table -> child rows ->
+// tensor core -> stores), so the kernel is built to keep many tiles in flight per SM and to shorten the chain:
+//  * NG (K groups of 8 held in registers: 4 for tables up to 32 deep, else 8) is a template parameter, so that the
+//    32-deep forward instantiation fits eight CTAs on an SM (64 registers), the 32-deep element-flow ones five or
+//    six (they also hold the NB element values), and the 64-deep ones four;
+//  * the index pairs of a folded product layer are fetched ONE TILE AHEAD into shared memory (every thread of a
+//    tile needs the same pairs), which takes their L2 round trip off the chain.
+template <int NB, bool ELE, int NG>
+constexpr int sm_small_ctas() { return (NG == 4 && !ELE) ? 8 : 4; }     // resident CTAs per SM (registers)
+
+template <int NB, bool ELE, int NG>
+__global__ void __launch_bounds__(SM_SAMPLES, sm_small_ctas<NB, ELE, NG>()) sum_sm_small_kernel(const SmArgs a, const int ng) {
     constexpr int TCOLS = NB < 32 ? 32 : NB;
+    constexpr int NIDX = 64;                           // index pairs per tile: the table (FWD) or the NB outputs (ELE)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
+    __shared__ int2 s_fk[2][NIDX];
 
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) {
@@ -276,29 +297,43 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
         s_fail = 0;
     }
     if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = s_tmem;
-    uint32_t phase = 0;
 
     const int B = a.B;
     const int KK = ELE ? a.K * a.par_block : a.K;
     const int lg_pb = ELE ? (31 - __clz(a.par_block)) : 0;
     const uint32_t idesc = idesc_bf16_f32(SM_SAMPLES, NB);
+    const bool folded = a.fk != nullptr;
+    const int n_idx = ELE ? NB : KK;                   // pairs per tile
+    const int idx_stride = ELE ? a.cbs : a.K;
     // shared memory: E hi [ng][128][16 B], E lo, theta hi [ng][NB][16 B], theta lo
     uint8_t* e_hi = smem;
     uint8_t* e_lo = smem + ng * (SM_SAMPLES * 16);
     uint8_t* t_hi = smem + 2 * ng * (SM_SAMPLES * 16);
     uint8_t* t_lo = t_hi + ng * (NB * 16);
 
-    for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+    if (folded && blockIdx.x < a.n_tiles && tid < n_idx)
+        s_fk[0][tid] = a.fk[(int64_t)a.first_row[blockIdx.x / a.n_st] * idx_stride + tid];
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    uint32_t phase = 0;
+    int cur = 0;
+
+    for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, cur ^= 1) {
         const int64_t m = tile / a.n_st;
         const int b0 = (int)(tile % a.n_st) * SM_SAMPLES;
         const int i0 = a.first_row[m];
         const int col = b0 + tid;
         const bool col_ok = col < B;
         const int colc = col_ok ? col : 0;
+        const int2* fk = s_fk[cur];
+
+        // the next tile's index pairs: requested now, parked in shared memory at the end of this tile
+        const int64_t tile_n = tile + gridDim.x;
+        int2 fk_next = make_int2(0, 0);
+        const bool pre = folded && tile_n < a.n_tiles && tid < n_idx;
+        if (pre) fk_next = a.fk[(int64_t)a.first_row[tile_n / a.n_st] * idx_stride + tid];
 
         // parameter tile: the first ng K groups of the hi half and of the lo half
         {
@@ -311,18 +346,18 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
         // Values of this thread's sample for every table entry.  Entries without a child / parent (id 0) read row 0,
         // the dummy row, which holds "probability zero" by the buffers' contract (element_mars: -inf); no per-value
         // masking is needed there.  A sample beyond the batch reads column 0 and is never stored.
-        float keep[8][8];
+        float keep[NG][8];
         float mx = PCX_NEG_INF;
         const float* src_col = a.src + colc;
         const float* src2_col = ELE ? a.src2 + colc : nullptr;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < NG; ++g) {
             if (g < ng) {
                 const int kb = g * 8;
-                if (!ELE && a.fk != nullptr) {
+                if (!ELE && folded) {
                     int2 r[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) r[j] = (kb + j < KK) ? a.fk[(int64_t)i0 * a.K + kb + j] : make_int2(0, 0);
+                    for (int j = 0; j < 8; ++j) r[j] = (kb + j < KK) ? fk[kb + j] : make_int2(0, 0);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) keep[g][j] = folded2(r[j], a.nmars + colc, B);
                 } else if (!ELE) {
@@ -351,7 +386,7 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
         }
         const float mxc = (mx == PCX_NEG_INF) ? 0.0f : mx;          // exp(-inf - 0) = 0: no per-value masking either
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < NG; ++g) {
             if (g < ng) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) keep[g][j] = __expf(keep[g][j] - mxc);
@@ -377,6 +412,7 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
             }
             mma_commit(&s_bar);
         }
+        const int64_t base = (int64_t)a.rows[i0] * B + colc;
         // one thread waits for the tensor core, the others sleep in the barrier (128 spinning threads would take
         // issue slots from the other CTAs of the SM)
         if (tid == 0 && !mbar_wait(&s_bar, phase & 1)) s_fail = 2;
@@ -385,16 +421,15 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
         const bool failed = s_fail != 0;
         tc_fence_after_sync();
         if (!failed) {
-            const int64_t base = (int64_t)a.rows[i0] * B + colc;
             float* out_col = a.out + base;
             const float* em_col = ELE ? a.emars + base : nullptr;
 #pragma unroll
             for (int p = 0; p < NB / 8; ++p) {
                 float v[8], em[8];
                 if (ELE) {
-                    if (a.fk != nullptr) {
+                    if (folded) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) em[j] = folded2(a.fk[(int64_t)i0 * a.cbs + 8 * p + j], a.nmars + colc, B);
+                        for (int j = 0; j < 8; ++j) em[j] = folded2(fk[8 * p + j], a.nmars + colc, B);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) em[j] = em_col[(int64_t)(8 * p + j) * B];
@@ -415,6 +450,7 @@ __global__ void __launch_bounds__(SM_SAMPLES, 4) sum_sm_small_kernel(const SmArg
                 }
             }
         }
+        if (pre) s_fk[cur ^ 1][tid] = fk_next;
         tc_fence_before_sync();
         __syncthreads();
         if (s_fail != 0) break;
@@ -666,6 +702,194 @@ __global__ void __launch_bounds__(PNTH, 4) sum_sm_par_kernel(const SmParArgs a) 
     if (warp == 0) tmem_dealloc(tmem, TCOLS);
 }
 
+// Parameter flows of 32-node blocks whose tables are at most 32 deep (one child block per sum block: the bulk of a
+// block-sparse Poon-Domingos layer).  One such table fills a quarter of the 128 edge rows of an MMA tile, so FOUR
+// merged rows share a tile: edge rows 32 j .. 32 j + 31 are the edges of row j, node columns 32 j .. 32 j + 31 its
+// nodes, and only the four diagonal 32 x 32 blocks of the 128 x 128 product are read back.  The tensor core does
+// four times the useful multiplications (it idles anyway); the threads, whose loads and exponentials are what this
+// kernel spends its time on, fill both operand tiles completely instead of a quarter of one.
+__global__ void __launch_bounds__(PNTH, 3) sum_sm_par_quad_kernel(const SmParArgs a, const int64_t n_merged) {
+    constexpr int QN = 32;                             // nodes (and at most edges) per merged row
+    constexpr int STAGE = 4 * X_TILE;                  // edge side hi, lo; node side hi, lo (128 rows each)
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t s_bar[STAGES];
+    __shared__ uint32_t s_tmem;
+    __shared__ __align__(16) float s_part[PNTH / 32][4][PKC];      // [warp][row j][sample of the slice]
+    __shared__ int s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t m0 = (int64_t)blockIdx.x * 4;
+    const int B = a.B;
+    const int total_chunks = (B + PKC - 1) / PKC;
+    const int c_begin = blockIdx.z * a.chunks_per_cta;
+    const int c_end = min(total_chunks, c_begin + a.chunks_per_cta);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[s], 1);
+        fence_mbar_init();
+        s_fail = 0;
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, 128);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+
+    const int g = tid & (PKG - 1), rb = tid / PKG;     // 8-sample group g of the slice; edge rb / node rb of every row j
+    const uint32_t idesc = idesc_bf16_f32(BM, 128);
+    int2 ch[4];                                        // this thread's edge of the four rows (folded: two child rows)
+    int cid[4];
+    int64_t nrow[4];                                   // this thread's node of the four rows
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const bool ok = m0 + j < n_merged;
+        const int i0 = ok ? a.first_row[m0 + j] : 0;
+        cid[j] = (ok && rb < a.K) ? a.cids[(int64_t)i0 * a.K + rb] : 0;
+        ch[j] = (a.fk != nullptr && cid[j] != 0) ? a.fk[(int64_t)i0 * a.K + rb] : make_int2(0, 0);
+        nrow[j] = ok ? (int64_t)a.nids[i0] + rb : -1;
+    }
+    bool failed = false;
+
+    for (int c = c_begin; c < c_end; ++c) {
+        const int it = c - c_begin, s = it % STAGES, use = it / STAGES;
+        uint8_t* st = smem + s * STAGE;
+        const int bb = c * PKC + g * 8;
+        const bool b_ok = bb < B;                      // B is a multiple of 8 here
+        const int bbc = b_ok ? bb : 0;
+
+        float y[4][8], x[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {                   // edge side
+            if (a.fk != nullptr) {                      // folded: sum of the product's two child rows
+                const float* r0p = a.node_mars + (int64_t)ch[j].x * B + bbc;
+                const float* r1p = a.node_mars + (int64_t)ch[j].y * B + bbc;
+                const float4 p0 = *reinterpret_cast<const float4*>(r0p), p1 = *reinterpret_cast<const float4*>(r0p + 4);
+                const float4 q0 = *reinterpret_cast<const float4*>(r1p), q1 = *reinterpret_cast<const float4*>(r1p + 4);
+                const bool any = (ch[j].x | ch[j].y) != 0;
+                y[j][0] = any ? p0.x + q0.x : PCX_NEG_INF; y[j][1] = any ? p0.y + q0.y : PCX_NEG_INF;
+                y[j][2] = any ? p0.z + q0.z : PCX_NEG_INF; y[j][3] = any ? p0.w + q0.w : PCX_NEG_INF;
+                y[j][4] = any ? p1.x + q1.x : PCX_NEG_INF; y[j][5] = any ? p1.y + q1.y : PCX_NEG_INF;
+                y[j][6] = any ? p1.z + q1.z : PCX_NEG_INF; y[j][7] = any ? p1.w + q1.w : PCX_NEG_INF;
+            } else {                                    // element values (row 0 = dummy = -inf)
+                const float4 q0 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc);
+                const float4 q1 = *reinterpret_cast<const float4*>(a.element_mars + (int64_t)cid[j] * B + bbc + 4);
+                y[j][0] = q0.x; y[j][1] = q0.y; y[j][2] = q0.z; y[j][3] = q0.w;
+                y[j][4] = q1.x; y[j][5] = q1.y; y[j][6] = q1.z; y[j][7] = q1.w;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {                   // node side: log(flow / value)
+            const bool ok = nrow[j] >= 0 && b_ok;
+            const int64_t off = (nrow[j] >= 0 ? nrow[j] : 0) * B + bbc;
+            const float4 f0 = *reinterpret_cast<const float4*>(a.node_flows + off);
+            const float4 f1 = *reinterpret_cast<const float4*>(a.node_flows + off + 4);
+            const float4 m0v = *reinterpret_cast<const float4*>(a.node_mars + off);
+            const float4 m1v = *reinterpret_cast<const float4*>(a.node_mars + off + 4);
+            const float nf[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+            const float nm[8] = {m0v.x, m0v.y, m0v.z, m0v.w, m1v.x, m1v.y, m1v.z, m1v.w};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                float f = nf[t];
+                if (!a.logspace) f = __logf(f);
+                x[j][t] = ok ? f - fmaxf(nm[t], -3.0e38f) : PCX_NEG_INF;
+            }
+        }
+        // shift of row j and sample t: the maximum over the row's 32 nodes (eight per warp, then across the warps)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float pm[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                float mm = x[j][t];
+#pragma unroll
+                for (int o = PKG; o < 32; o <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+                pm[t] = mm;
+            }
+            if (lane < PKG) {
+                float4* dst = reinterpret_cast<float4*>(&s_part[warp][j][lane * 8]);
+                dst[0] = make_float4(pm[0], pm[1], pm[2], pm[3]);
+                dst[1] = make_float4(pm[4], pm[5], pm[6], pm[7]);
+            }
+        }
+        if (it >= STAGES && !failed && !mbar_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) { failed = true; s_fail = 1; }
+        __syncthreads();
+        uint8_t* yhi = st;
+        uint8_t* ylo = st + X_TILE;
+        uint8_t* xhi = st + 2 * X_TILE;
+        uint8_t* xlo = st + 3 * X_TILE;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float sh[8];
+            {
+                const float4 p0 = *reinterpret_cast<const float4*>(&s_part[0][j][g * 8]);
+                const float4 p1 = *reinterpret_cast<const float4*>(&s_part[0][j][g * 8 + 4]);
+                sh[0] = p0.x; sh[1] = p0.y; sh[2] = p0.z; sh[3] = p0.w; sh[4] = p1.x; sh[5] = p1.y; sh[6] = p1.z; sh[7] = p1.w;
+#pragma unroll
+                for (int w = 1; w < PNTH / 32; ++w) {
+                    const float4 q0 = *reinterpret_cast<const float4*>(&s_part[w][j][g * 8]);
+                    const float4 q1 = *reinterpret_cast<const float4*>(&s_part[w][j][g * 8 + 4]);
+                    sh[0] = fmaxf(sh[0], q0.x); sh[1] = fmaxf(sh[1], q0.y); sh[2] = fmaxf(sh[2], q0.z); sh[3] = fmaxf(sh[3], q0.w);
+                    sh[4] = fmaxf(sh[4], q1.x); sh[5] = fmaxf(sh[5], q1.y); sh[6] = fmaxf(sh[6], q1.z); sh[7] = fmaxf(sh[7], q1.w);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {     // a sample without any flow (shift -inf) contributes nothing
+                y[j][t] = (sh[t] == PCX_NEG_INF || !b_ok) ? 0.0f : fminf(__expf(y[j][t] + sh[t]), 3.0e38f);
+                x[j][t] = (sh[t] == PCX_NEG_INF) ? 0.0f : __expf(x[j][t] - sh[t]);
+            }
+            const int o = g * XSLAB + (rb + 32 * j) * 16;
+            store_split8(reinterpret_cast<uint4*>(yhi + o), reinterpret_cast<uint4*>(ylo + o), y[j]);
+            store_split8(reinterpret_cast<uint4*>(xhi + o), reinterpret_cast<uint4*>(xlo + o), x[j]);
+        }
+        fence_async_smem();
+        __syncthreads();
+        failed = failed || (s_fail != 0);
+        if (tid == 0 && !failed) {
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(st);
+            issue_stage<XSLAB, XSLAB, PKC>(tmem, sa, sa + 2 * X_TILE, idesc, it == 0, a.terms);
+            mma_commit(&s_bar[s]);
+        }
+    }
+
+    const int n_it = c_end - c_begin;
+    if (n_it > 0) {
+        const int il = n_it - 1;
+        if (tid == 0 && !failed && !mbar_wait(&s_bar[il % STAGES], (uint32_t)((il / STAGES) & 1))) s_fail = 2;
+    }
+    __syncthreads();
+    failed = failed || (s_fail != 0);
+    tc_fence_after_sync();
+    if (!failed && n_it > 0) {
+        // TMEM lane = edge row: warp w holds the edges of row w; its diagonal block is columns 32 w .. 32 w + 31
+        const int e = lane;
+        const bool row_ok = m0 + warp < n_merged;
+        const int i0 = row_ok ? a.first_row[m0 + warp] : 0;
+        const bool e_ok = row_ok && e < a.K && a.cids[(int64_t)i0 * a.K + min(e, a.K - 1)] != 0;
+#pragma unroll 1
+        for (int p = 0; p < QN / 8; ++p) {
+            float v[8];
+            tmem_ld<8>(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(warp * QN + 8 * p), v);    // warp-wide
+            if (!e_ok) continue;
+            const int n0 = 8 * p;                       // eight consecutive nodes lie in one block (blocks >= 8 nodes)
+            const int64_t i = (int64_t)i0 + n0 / a.block;
+            const int nn = n0 % a.block;
+            const float* par = a.params + (int64_t)a.pids[i * a.K + e] + nn;
+            float* pf = a.param_flows + (int64_t)a.pfids[i * a.K + e] + nn;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = par[j] * v[j];
+                if (f != 0.0f) atomicAdd(pf + j, f);
+            }
+        }
+    }
+    if (failed && tid == 0) atomicCAS(&g_tc_status, 0, 530 + s_fail);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
 // All sample-major tables of a circuit in one launch: a device array of jobs, the job of a vector is found by binary
 // search over vec_begin (the running sum of the jobs' vector counts).
 struct SmPackJob {
@@ -724,7 +948,9 @@ int launch_sm(const SmArgs& a, cudaStream_t st) {
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(sum_sm_kernel<NB, ELE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(sum_sm_small_kernel<NB, ELE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+            e = cudaFuncSetAttribute(sum_sm_small_kernel<NB, ELE, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(sum_sm_small_kernel<NB, ELE, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
         if (e != cudaSuccess) return (int)e;
         int dev = 0;
         e = cudaGetDevice(&dev);
@@ -736,9 +962,10 @@ int launch_sm(const SmArgs& a, cudaStream_t st) {
     if (depth <= KC) {
         const int ng = 2 * (int)pcx_cdiv(depth, 16);                    // K groups actually used (pairs: one MMA step)
         const int bytes = 2 * ng * (SM_SAMPLES * 16) + 2 * ng * (NB * 16) + 1024;
-        const int per_sm = bytes <= 36 * 1024 ? 6 : 4;
+        const int per_sm = ng <= 4 ? sm_small_ctas<NB, ELE, 4>() : sm_small_ctas<NB, ELE, 8>();
         const int64_t grid = a.n_tiles < per_sm * (int64_t)sms ? a.n_tiles : per_sm * (int64_t)sms;
-        sum_sm_small_kernel<NB, ELE><<<(unsigned)grid, SM_SAMPLES, bytes, st>>>(a, ng);
+        if (ng <= 4) sum_sm_small_kernel<NB, ELE, 4><<<(unsigned)grid, SM_SAMPLES, bytes, st>>>(a, ng);
+        else sum_sm_small_kernel<NB, ELE, 8><<<(unsigned)grid, SM_SAMPLES, bytes, st>>>(a, ng);
         PCX_LAUNCH_CHECK();
         return 0;
     }
@@ -780,8 +1007,26 @@ int pcx_sum_bwd_par_sm(float* param_flows, const float* node_flows, const float*
     if (fk == nullptr && element_mars == nullptr) return -1;
     SmParArgs a{param_flows, node_flows, node_mars, element_mars, params, first_row, nids, cids, pids, pfids,
                 K, block, B, logspace, (g_sum_mode == 2) ? 1 : 3, 1, reinterpret_cast<const int2*>(fk)};
-    const int64_t base = n_merged * pcx_cdiv(K, BM);
     const int total_chunks = (int)pcx_cdiv(B, PKC);
+    if (nb == 32 && K <= 32) {                                  // four merged rows per tile
+        const int64_t quads = pcx_cdiv(n_merged, 4);
+        int64_t splits = pcx_cdiv(6 * 148, quads);              // about two waves of three CTAs per SM
+        if (splits > total_chunks) splits = total_chunks;
+        if (splits < 1) splits = 1;
+        a.chunks_per_cta = (int)pcx_cdiv(total_chunks, splits);
+        dim3 grid((unsigned)quads, 1, (unsigned)pcx_cdiv(total_chunks, a.chunks_per_cta));
+        const int smem = STAGES * 4 * X_TILE + 1024;
+        static PcxOnce doneq;
+        if (!doneq) {
+            cudaError_t e = cudaFuncSetAttribute(sum_sm_par_quad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return (int)e;
+            doneq = true;
+        }
+        sum_sm_par_quad_kernel<<<grid, PNTH, smem, (cudaStream_t)stream>>>(a, n_merged);
+        PCX_LAUNCH_CHECK();
+        return 0;
+    }
+    const int64_t base = n_merged * pcx_cdiv(K, BM);
     int64_t splits = pcx_cdiv(8 * 148, base);                  // about two waves of four CTAs per SM
     if (splits > total_chunks) splits = total_chunks;
     if (splits < 1) splits = 1;
