@@ -445,6 +445,8 @@ def measure_ours(config: str, args, rank: int, world: int, dev, K: int, W: int, 
     pc = pj.compile(ns).to(dev)
     pc.use_cuda_graphs = not args.no_graphs
     pc.use_dataflow_launch = not args.no_dataflow
+    if args.no_fold:
+        pc.fuse_product_layers = False
     pc.use_side_stream = not args.no_side_stream
     pc.chain_tile = args.chain_tile
     max_cats = max(l.max_cats for l in pc.input_layer_group)
@@ -602,6 +604,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=512, help="samples per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-fold", action="store_true", help="product layers as kernels of their own (not folded into the sum kernels)")
     ap.add_argument("--no-dataflow", action="store_true", help="per-layer launches instead of one launch per run of layers")
     ap.add_argument("--no-side-stream", action="store_true", help="every kernel of a step on one stream")
     ap.add_argument("--no-dependent-launch", action="store_true",

@@ -313,8 +313,8 @@ __device__ __forceinline__ void prod_split(const ProdDiv d, uint32_t t, uint32_t
     j = r - i * d.bs;
 }
 
-// Product forward.  Thread = (row block i, node j of the block, VEC consecutive samples).
-template <int VEC>
+// Product forward.  Thread = (row block i, ROWS nodes j (and j + block / 2) of the block, VEC consecutive samples).
+template <int VEC, int ROWS>
 __global__ void prod_fwd_kernel(float* __restrict__ element_mars, const float* __restrict__ node_mars,
                                 const int32_t* __restrict__ nids, const int32_t* __restrict__ cids,
                                 uint32_t total, int64_t block0, ProdDiv d, int n_chs, int B) {
@@ -324,28 +324,39 @@ __global__ void prod_fwd_kernel(float* __restrict__ element_mars, const float* _
     prod_split(d, t, il, j, bc);
     const int64_t i = block0 + il;
     const int b = (int)bc * VEC;
-    float acc[VEC];
+    const int64_t jstep = (int64_t)d.bs * B;
+    float acc[ROWS][VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[r][v] = 0.0f;
     const int32_t* crow = cids + i * n_chs;
     for (int c = 0; c < n_chs; ++c) {
         int32_t cid = crow[c];
         if (cid == 0) continue;
         const float* src = node_mars + ((int64_t)cid + j) * B + b;
-        if (VEC == 4) {
-            float4 x = *reinterpret_cast<const float4*>(src);
-            acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-        } else {
-            acc[0] += src[0];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (VEC == 4) {
+                float4 x = *reinterpret_cast<const float4*>(src + r * jstep);
+                acc[r][0] += x.x; acc[r][1] += x.y; acc[r][2] += x.z; acc[r][3] += x.w;
+            } else {
+                acc[r][0] += src[r * jstep];
+            }
         }
     }
     float* dst = element_mars + ((int64_t)nids[i] + j) * B + b;
-    if (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    else dst[0] = acc[0];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        if (VEC == 4) *reinterpret_cast<float4*>(dst + r * jstep) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        else dst[r * jstep] = acc[r][0];
+    }
 }
 
-// Product backward: log-sum-exp over the parents, then logaddexp into the child's flow.
-template <int VEC>
+// Product backward: log-sum-exp over the parents, then logaddexp into the child's flow.  A thread owns VEC samples of
+// ROWS nodes of one block (nodes j and j + block / 2 when ROWS = 2): they share the block's parent list, and the
+// thread has twice as many independent loads in flight.  `d.bs` is then half the block size.
+template <int VEC, int ROWS>
 __global__ void prod_bwd_kernel(float* __restrict__ node_flows, const float* __restrict__ element_flows,
                                 const int32_t* __restrict__ u_cids, const int32_t* __restrict__ parids,
                                 uint32_t total, int64_t block0, ProdDiv d, int n_pars, int B, int logspace) {
@@ -356,51 +367,66 @@ __global__ void prod_bwd_kernel(float* __restrict__ node_flows, const float* __r
     const int64_t i = block0 + il;
     const int b = (int)bc * VEC;
     const int32_t* prow = parids + i * n_pars;
+    const int64_t jstep = (int64_t)d.bs * B;            // distance between the thread's rows
     float* dst = node_flows + ((int64_t)u_cids[i] + j) * B + b;
-    float cur[VEC];                                     // requested first: its latency overlaps the parents' loads
-    if (VEC == 4) {
-        const float4 q = *reinterpret_cast<const float4*>(dst);
-        cur[0] = q.x; cur[1] = q.y; cur[2] = q.z; cur[3] = q.w;
-    } else {
-        cur[0] = dst[0];
+    float cur[ROWS][VEC];                               // requested first: its latency overlaps the parents' loads
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        if (VEC == 4) {
+            const float4 q = *reinterpret_cast<const float4*>(dst + r * jstep);
+            cur[r][0] = q.x; cur[r][1] = q.y; cur[r][2] = q.z; cur[r][3] = q.w;
+        } else {
+            cur[r][0] = dst[r * jstep];
+        }
     }
 
-    float mx[VEC], sum[VEC];
+    float mx[ROWS][VEC], sum[ROWS][VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) { mx[v] = PCX_NEG_INF; sum[v] = 0.0f; }
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { mx[r][v] = PCX_NEG_INF; sum[r][v] = 0.0f; }
     for (int p = 0; p < n_pars; ++p) {
         int32_t pid = prow[p];
         if (pid == 0) continue;
         const float* src = element_flows + ((int64_t)pid + j) * B + b;
-        float x[VEC];
-        if (VEC == 4) {
-            float4 q = *reinterpret_cast<const float4*>(src);
-            x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
-        } else {
-            x[0] = src[0];
+        float x[ROWS][VEC];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (VEC == 4) {
+                float4 q = *reinterpret_cast<const float4*>(src + r * jstep);
+                x[r][0] = q.x; x[r][1] = q.y; x[r][2] = q.z; x[r][3] = q.w;
+            } else {
+                x[r][0] = src[r * jstep];
+            }
         }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                const float xv = x[r][v];
+                if (!logspace) { sum[r][v] += xv; continue; }
+                if (xv == PCX_NEG_INF) continue;
+                if (xv > mx[r][v]) { sum[r][v] = sum[r][v] * __expf(mx[r][v] - xv) + 1.0f; mx[r][v] = xv; }
+                else sum[r][v] += __expf(xv - mx[r][v]);
+            }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        float out[VEC];
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-            if (!logspace) { sum[v] += x[v]; continue; }
-            if (x[v] == PCX_NEG_INF) continue;
-            if (x[v] > mx[v]) { sum[v] = sum[v] * __expf(mx[v] - x[v]) + 1.0f; mx[v] = x[v]; }
-            else sum[v] += __expf(x[v] - mx[v]);
+            if (logspace) {
+                // log(exp(cur) + exp(mx) * sum) around the larger of the two exponents
+                const float hi = fmaxf(cur[r][v], mx[r][v]);
+                const float s = __expf(cur[r][v] - hi) + sum[r][v] * __expf(mx[r][v] - hi);
+                out[v] = (hi == PCX_NEG_INF) ? PCX_NEG_INF : hi + __logf(s);
+            } else {
+                out[v] = cur[r][v] + sum[r][v];
+            }
         }
+        if (VEC == 4) *reinterpret_cast<float4*>(dst + r * jstep) = make_float4(out[0], out[1], out[2], out[3]);
+        else dst[r * jstep] = out[0];
     }
-    float out[VEC];
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) {
-        if (logspace) {
-            // log(exp(cur) + exp(mx) * sum) around the larger of the two exponents
-            const float hi = fmaxf(cur[v], mx[v]);
-            const float s = __expf(cur[v] - hi) + sum[v] * __expf(mx[v] - hi);
-            out[v] = (hi == PCX_NEG_INF) ? PCX_NEG_INF : hi + __logf(s);
-        } else {
-            out[v] = cur[v] + sum[v];
-        }
-    }
-    if (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
-    else dst[0] = out[0];
 }
 
 inline int lg2_or_neg(uint32_t v) {
@@ -411,7 +437,7 @@ inline int lg2_or_neg(uint32_t v) {
 }
 // Cuts `n_blocks` row blocks into launches of fewer than 2^31 threads; `launch(first block, blocks, threads, div)`.
 template <typename F>
-inline void prod_launches(int64_t n_blocks, int block_size, int bv, F launch) {
+inline void prod_launches(int64_t n_blocks, int block_size, int bv, F launch) {   // block_size: rows per block per thread set
     ProdDiv d;
     d.bv = (uint32_t)bv; d.bs = (uint32_t)block_size;
     d.lg_bv = lg2_or_neg(d.bv); d.lg_bs = lg2_or_neg(d.bs);
@@ -556,13 +582,19 @@ int pcx_prod_fwd(float* element_mars, const float* node_mars, const int32_t* nid
                  int64_t n_blocks, int n_chs, int block_size, int B, void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
     if (B % 4 == 0) {
-        prod_launches(n_blocks, block_size, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
-            prod_fwd_kernel<4><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
-                element_mars, node_mars, nids, cids, total, b0, d, n_chs, B);
-        });
+        if (block_size % 2 == 0)
+            prod_launches(n_blocks, block_size / 2, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
+                prod_fwd_kernel<4, 2><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                    element_mars, node_mars, nids, cids, total, b0, d, n_chs, B);
+            });
+        else
+            prod_launches(n_blocks, block_size, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
+                prod_fwd_kernel<4, 1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                    element_mars, node_mars, nids, cids, total, b0, d, n_chs, B);
+            });
     } else {
         prod_launches(n_blocks, block_size, B, [&](int64_t b0, uint32_t total, ProdDiv d) {
-            prod_fwd_kernel<1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+            prod_fwd_kernel<1, 1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
                 element_mars, node_mars, nids, cids, total, b0, d, n_chs, B);
         });
     }
@@ -574,13 +606,19 @@ int pcx_prod_bwd(float* node_flows, const float* element_flows, const int32_t* u
                  int64_t n_blocks, int n_pars, int block_size, int B, int logspace, void* stream) {
     if (n_blocks <= 0 || B <= 0) return 0;
     if (B % 4 == 0) {
-        prod_launches(n_blocks, block_size, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
-            prod_bwd_kernel<4><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
-                node_flows, element_flows, u_cids, parids, total, b0, d, n_pars, B, logspace);
-        });
+        if (block_size % 2 == 0)
+            prod_launches(n_blocks, block_size / 2, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
+                prod_bwd_kernel<4, 2><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                    node_flows, element_flows, u_cids, parids, total, b0, d, n_pars, B, logspace);
+            });
+        else
+            prod_launches(n_blocks, block_size, B / 4, [&](int64_t b0, uint32_t total, ProdDiv d) {
+                prod_bwd_kernel<4, 1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+                    node_flows, element_flows, u_cids, parids, total, b0, d, n_pars, B, logspace);
+            });
     } else {
         prod_launches(n_blocks, block_size, B, [&](int64_t b0, uint32_t total, ProdDiv d) {
-            prod_bwd_kernel<1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
+            prod_bwd_kernel<1, 1><<<grid_for(total), kThreads, 0, (cudaStream_t)stream>>>(
                 node_flows, element_flows, u_cids, parids, total, b0, d, n_pars, B, logspace);
         });
     }
