@@ -238,6 +238,7 @@ def family_work(stats, B, elsize):
 
 # DRAM bytes (read + write) of ONE launch of the named family's dominant kernel, from `ncu` captures of the same
 # kernels on one B200 (dram__bytes_read.sum + dram__bytes_write.sum); None = not captured.  (config, family) -> bytes
+# Sources: profiles/ncu_full_cfg1_chain_par.md, profiles/ncu_full_cfg4_wide_gemm.md, profiles/launch_list_cfg2_pd_b512.md
 TRAFFIC_PER_LAUNCH = {
     # configs[1], B = 512: one dataflow launch each for the forward pass and the element flows, one batched launch
     # for the parameter flows
@@ -250,6 +251,9 @@ TRAFFIC_PER_LAUNCH = {
     ("cfg4", "pcx_sum_fwd"): 31.7e6,
     ("cfg4", "pcx_sum_bwd_ele"): 51.0e6,
     ("cfg4", "pcx_sum_bwd_par"): 449.2e6 * 127 / 7,
+    # configs[2], B = 512: mean over the 29 parameter-flow launches of a step, captured at B = 128 and scaled by 4
+    # (every operand is a row of B samples)
+    ("cfg2", "pcx_sum_bwd_par"): 1536.0e6 * 4 / 29,
 }
 
 

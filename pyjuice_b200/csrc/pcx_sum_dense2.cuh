@@ -742,7 +742,10 @@ int wide_launch_prep(Kern kern, const WidePrepArgs& p, dim3 grid, size_t smem, c
     return 0;
 }
 
-inline int wide_dn(int B) { return B > 128 ? 256 : (B > 64 ? 128 : 64); }
+// Tile width in samples.  Batches of 64 and fewer also take 128-column tiles (the rest is padding): a 64-column tile can
+// only be split two ways along the contraction (a CTA finishes at least 32 columns), which leaves 64 CTAs to stream
+// the parameter image of a 4096-row layer, and that stream, not the padded multiplications, is what the time goes into.
+inline int wide_dn(int B) { return B > 128 ? 256 : 128; }
 
 // CTAs per output tile along the contraction (= cluster size): enough to fill the machine, a power of two that divides
 // the chunks and leaves every CTA at least 32 columns of the tile to finish.
