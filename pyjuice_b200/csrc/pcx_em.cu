@@ -114,6 +114,63 @@ em_input_cat_kernel(float* __restrict__ params, const float* __restrict__ flows,
     }
 }
 
+// Categorical EM on the transposed shadow of a large table (`flows_t`, `logp_t`: [category, row]; `params`: [row,
+// category]; every row is a source vector with C categories).  One kernel replaces three passes over the table (move
+// the flows into the [row, category] accumulators, update, rebuild the transposed log-parameter table): a CTA owns 32
+// rows; its warps stride over blocks of 32 categories, first for the rows' flow totals, then for the update, in which
+// the parameter tile goes through a per-warp shared-memory transpose so that both layouts are read and written with
+// coalesced accesses.  The flows are left as they are (the caller clears or moves them later).  (A two-kernel version
+// with a four times larger grid -- totals first, then the update -- was measured and was no faster.)
+constexpr int EMT_WARPS = 16;
+__global__ void __launch_bounds__(EMT_WARPS * 32)
+em_input_cat_t_kernel(float* __restrict__ params, float* __restrict__ logp_t, const float* __restrict__ flows_t,
+                      int64_t R, int C, float step, float pseudo) {
+    extern __shared__ float s_emt[];                     // [EMT_WARPS][32][33] transpose tiles, one per warp
+    __shared__ float s_tot[EMT_WARPS][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = (int64_t)blockIdx.x * 32;
+    const int64_t r = r0 + lane;
+    const bool r_ok = r < R;
+    const float add = pseudo / (float)C;
+
+    float tot = 0.0f;
+    for (int c0 = warp * 32; c0 < C; c0 += EMT_WARPS * 32) {
+        float f[32];
+#pragma unroll
+        for (int cc = 0; cc < 32; ++cc) f[cc] = (r_ok && c0 + cc < C) ? flows_t[(int64_t)(c0 + cc) * R + r] : 0.0f;
+#pragma unroll
+        for (int cc = 0; cc < 32; ++cc) tot += f[cc];
+    }
+    s_tot[warp][lane] = tot;
+    __syncthreads();
+    tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < EMT_WARPS; ++w) tot += s_tot[w][lane];
+    const float denom = tot + pseudo;
+
+    float (*tile)[33] = reinterpret_cast<float (*)[33]>(s_emt + warp * 32 * 33);
+    for (int c0 = warp * 32; c0 < C; c0 += EMT_WARPS * 32) {
+        float f[32];
+#pragma unroll
+        for (int cc = 0; cc < 32; ++cc) f[cc] = (r_ok && c0 + cc < C) ? flows_t[(int64_t)(c0 + cc) * R + r] : 0.0f;
+        const int c = c0 + lane;
+#pragma unroll 8
+        for (int rr = 0; rr < 32; ++rr) tile[rr][lane] = (r0 + rr < R && c < C) ? params[(r0 + rr) * C + c] : 0.0f;
+        __syncwarp();
+#pragma unroll
+        for (int cc = 0; cc < 32; ++cc) {
+            const float upd = (1.0f - step) * tile[lane][cc] + step * (f[cc] + add) / denom;
+            tile[lane][cc] = upd;
+            if (r_ok && c0 + cc < C) logp_t[(int64_t)(c0 + cc) * R + r] = logf(upd);
+        }
+        __syncwarp();
+#pragma unroll 8
+        for (int rr = 0; rr < 32; ++rr)
+            if (r0 + rr < R && c < C) params[(r0 + rr) * C + c] = tile[rr][lane];
+        __syncwarp();
+    }
+}
+
 // Flow of a leaf whose variable is not observed: its (linear) flow f spreads over the categories in proportion to the
 // parameters, flows[s_pfids + c] += scale * f * params[s_pids + c].  One CTA per source node.
 __global__ void __launch_bounds__(NT)
@@ -182,6 +239,22 @@ int pcx_em_input_cat(float* params, const float* param_flows, const int32_t* sou
     } else {
         em_input_cat_kernel<32><<<(unsigned)pcx_cdiv(n_source, NT / 32), NT, 0, st>>>(params, param_flows, source_nids, s_pids, s_pfids, node_cats, n_source, step, pseudo, keep_zero);
     }
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_em_input_cat_t(float* params, float* logp_t, const float* flows_t, int64_t n_rows, int num_cats, float step,
+                       float pseudo, void* stream) {
+    if (n_rows <= 0 || num_cats <= 0) return 0;
+    const int smem = EMT_WARPS * 32 * 33 * (int)sizeof(float);
+    static PcxOnce done;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(em_input_cat_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    em_input_cat_t_kernel<<<(unsigned)pcx_cdiv(n_rows, 32), EMT_WARPS * 32, smem, (cudaStream_t)stream>>>(
+        params, logp_t, flows_t, n_rows, num_cats, step, pseudo);
     PCX_LAUNCH_CHECK();
     return 0;
 }

@@ -185,6 +185,7 @@ class InputLayer(Layer, nn.Module):
         self.params = nn.Parameter(torch.empty([max(self.num_parameters, 1)], dtype=torch.float32), requires_grad=False)
         self._shadow = None
         self._param_epoch = 0
+        self._arena_zero = False                 # True while the [row, category] flow accumulators are known to be all zero
         self.param_flows = None
         self._dev = {}
 
@@ -195,10 +196,12 @@ class InputLayer(Layer, nn.Module):
     # shadow ([category, row] instead of [row, category]); flows are accumulated in the same layout and moved into
     # `param_flows` (the reference's layout) whenever that tensor is read.
     SHADOW_MIN_CATS = 8193
+    use_fused_shadow_em = True
 
     @property
     def param_flows(self):
         self._flush_shadow()
+        self._arena_zero = False                 # the caller may write through the tensor
         return self._param_flows
 
     @param_flows.setter
@@ -232,6 +235,7 @@ class InputLayer(Layer, nn.Module):
             return
         _lib.call("pcx_input_cat_flush_t", self._param_flows, sh["flows"], sh["touched"], sh["row_pfid"], sh["R"], sh["C"])
         sh["dirty"] = False
+        self._arena_zero = False
 
     def _zero_shadow(self):
         sh = self._shadow
@@ -278,6 +282,7 @@ class InputLayer(Layer, nn.Module):
         elif flows_memory == 0.0:
             self._zero_shadow()
             _fill(self._param_flows, 0.0)
+            self._arena_zero = True
         elif flows_memory < 1.0:
             _scale(self.param_flows, flows_memory)            # (reading the property moves shadow flows in first)
         self._tied_folded = False
@@ -327,6 +332,7 @@ class InputLayer(Layer, nn.Module):
             sh["dirty"] = True                            # every flow lands in its source row: replicas stay as they are
             return
         self._tied_folded = False                         # replica accumulators receive new flows
+        self._arena_zero = False
         _lib.call("pcx_input_cat_bwd", self._param_flows, node_flows, data, data.element_size(),
                   self._dev["vids"], self._dev["s_pfids"], self._dev["node_cats"], self.max_cats,
                   self.num_nodes, self._output_ind_range[0], B, int(bool(logspace_flows)))
@@ -351,6 +357,17 @@ class InputLayer(Layer, nn.Module):
 
     def mini_batch_em(self, step_size: float, pseudocount: float = 0.0, keep_zero_params: bool = False):
         self._require_cuda()
+        sh = self._shadow
+        if (sh is not None and sh["dirty"] and self._arena_zero and not keep_zero_params and sh["logp"] is not None
+                and self.use_fused_shadow_em):
+            # every flow of this update sits in the transposed shadow and the accumulators proper are empty: update
+            # the parameters and the transposed log-parameter table straight from it.  The flows stay in
+            # the shadow (still "dirty"): whoever reads `param_flows` later gets them moved over as usual.
+            self._param_epoch += 1
+            _lib.call("pcx_em_input_cat_t", self.params.data, sh["logp"], sh["flows"], sh["R"], sh["C"],
+                      float(step_size), float(pseudocount))
+            sh["stamp"] = (self.params.data_ptr(), self.params._version, self._param_epoch)
+            return
         self.fold_tied_flows()
         self._param_epoch += 1                            # the kernel below writes the parameters behind torch's back
         _lib.call("pcx_em_input_cat", self.params.data, self._param_flows, self._dev["source_nids"],
@@ -364,6 +381,7 @@ class InputLayer(Layer, nn.Module):
         self._require_cuda()
         if self._param_flows is None:
             self.init_param_flows()
+        self._arena_zero = False
         s, e = self._output_ind_range
         td = node_flows[s:e].to(torch.float32)
         n2s = self.node_id2source_id.to(self.device)                # -1 for source nodes, else the source's node id

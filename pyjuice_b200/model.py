@@ -993,11 +993,14 @@ class TensorCircuit(nn.Module):
             self.param_flows = self._flow_arena.views[0]
             for layer, view in zip(self.input_layer_group, self._flow_arena.views[1:]):
                 layer.param_flows = view
+                layer._arena_zero = True
             self._graphs = {k: g for k, g in self._graphs.items() if k[0] != "bk"}
         elif flows_memory == 0.0:
             for layer in self.input_layer_group:
                 layer._zero_shadow()
             _fill(self._flow_arena.buf, 0.0)
+            for layer in self.input_layer_group:
+                layer._arena_zero = True
         elif flows_memory != 1.0:
             for layer in self.input_layer_group:
                 layer._flush_shadow()

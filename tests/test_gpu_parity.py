@@ -345,6 +345,57 @@ def _lib_status():
     _lib.check_status()
 
 
+@pytest.mark.parametrize("B", [64, 36])
+@pytest.mark.parametrize("homogeneous", [True, False])
+def test_em_straight_from_the_transposed_shadow(B, homogeneous, monkeypatch):
+    """When all flows of an update sit in the transposed shadow (nobody read `param_flows`, no data-parallel
+    exchange), the leaf parameters and the transposed log-parameter table are updated straight from it.  Same
+    parameters, same likelihoods afterwards and the same flows on a later read as the three-kernel path (move the
+    flows, update, rebuild the shadow), and as the oracle."""
+    from pyjuice_b200 import _lib
+    from helpers import OracleTrainer
+    calls = []
+    orig = _lib.call
+    monkeypatch.setattr(_lib, "call", lambda name, *a: (calls.append(name), orig(name, *a))[1])
+    pcs = []
+    for fused in (True, False):
+        torch.manual_seed(8)
+        ns = pj.structures.HMM(seq_length=6, num_latents=32, num_emits=9000, homogeneous=homogeneous, block_size=8)
+        ns.init_parameters()
+        pc = pj.compile(ns, max_tied_ns_per_parflow_block=2).to(DEV)
+        pc.input_layer_group[0].use_fused_shadow_em = fused
+        pcs.append(pc)
+    ref = OracleTrainer(pcs[0])
+    opts = [pj.optim.MiniBatchEM(pc, step_size=0.3, pseudocount=0.1) for pc in pcs]
+    for i in range(3):
+        xi = torch.randint(0, 9000, (B, 6))
+        xi[:, 0] = torch.arange(B) % 5
+        for pc, opt in zip(pcs, opts):
+            calls.clear()
+            pc(xi.to(DEV)).mean().backward()
+            opt.step()
+            fused = pc.input_layer_group[0].use_fused_shadow_em
+            assert ("pcx_em_input_cat_t" in calls) == fused and ("pcx_input_cat_flush_t" in calls) == (not fused)
+        ref.accumulate(xi, flows_memory=0.0)
+        ref.update(0.3, 0.1, zero_flows=True)
+        ref.check_params(pcs[0])
+        a, b = (pc.input_layer_group[0].params.data for pc in pcs)
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-9), (a - b).abs().max()
+    x = torch.randint(0, 9000, (B, 6)).to(DEV)
+    lls = [pc(x) for pc in pcs]
+    assert torch.allclose(lls[0], lls[1], rtol=0, atol=1e-4)
+    # the flows of an update stay readable after the update from the shadow
+    flows = []
+    for pc in pcs:
+        pc.init_param_flows(flows_memory=0.0)
+        pc(x)
+        pc.backward(x)
+        pc.mini_batch_em(step_size=0.3, pseudocount=0.1)
+        flows.append(pc.input_layer_group[0].param_flows.clone())
+    assert torch.allclose(flows[0], flows[1], rtol=1e-5, atol=1e-7) and float(flows[0].sum()) > 0
+    _lib_status()
+
+
 @pytest.mark.parametrize("B", [64, 100, 256])
 @pytest.mark.parametrize("case", ["pd", "rat", "hmm64", "hmm32_tied"])
 def test_small_blocks_on_tensor_cores_match_oracle_and_cuda_core_kernels(case, B):
