@@ -221,6 +221,11 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
  * Replace, like the entry points above: SumLayer._forward_block_sparse / _backward_block_sparse_ele_flows /
  * _backward_block_sparse_par_flows (layer/sum_layer.py:551-929, 1369-1719, 1721-2080), with ProdLayer.forward /
  * backward folded in (layer/prod_layer.py:161-238). */
+/* Measurement hook (per calling host thread): while `event` (a cudaEvent_t created with timing) is set,
+ * pcx_sum_fwd_dense2 and pcx_sum_bwd_ele_dense2 record it on their stream between the operand pre-pass kernel and the
+ * GEMM kernel, so that a benchmark that brackets the call with two events of its own gets the duration of each of
+ * the two kernels.  NULL switches it off (default).  No counterpart in the reference. */
+int pcx_set_stage_event(void* event);
 /* The wide-tile kernels are launched with programmatic stream serialization (a kernel sets itself up while its
  * predecessor drains, then waits for it); 0 switches that off, e.g. to compare timings. */
 int pcx_set_dependent_launch(int on);

@@ -70,7 +70,7 @@ SIGNATURES = {
 }
 
 # entry points without a stream argument
-PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_set_dependent_launch": [I], "pcx_get_status": [], "pcx_clear_status": [],
+PLAIN = {"pcx_build_arch": [], "pcx_set_sum_mode": [I], "pcx_set_dependent_launch": [I], "pcx_set_stage_event": [P], "pcx_get_status": [], "pcx_clear_status": [],
          "pcx_packed_tile_count": [L, I, I, I, I], "pcx_dense_scratch_bytes": [I, I, I],
          "pcx_sm_packed_bytes": [L, I, I], "pcx_dense2_scratch_bytes": [I, I, I]}
 SUM_MODE = 1        # the process default of the arithmetic mode (see set_sum_mode / use_sum_mode)
@@ -114,6 +114,7 @@ _lib: Optional[ctypes.CDLL] = None
 # bracketed by CUDA events on the launching stream and (name, start, end) is appended to it.
 COUNT = 0
 PROFILE = None
+PROFILE_BYTES = {}          # while PROFILE is a list: bytes written by the buffer-clearing entry points, per name
 
 
 class PcxError(RuntimeError):
@@ -179,7 +180,20 @@ def _invoke(lib, name, conv, args, dev) -> int:
     if PROFILE is None:
         return getattr(lib, name)(*conv, stream)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if name in ("pcx_fill_f32", "pcx_scale_f32"):
+        PROFILE_BYTES[name] = PROFILE_BYTES.get(name, 0) + 4 * int(args[1])
     a.record()
+    if name in ("pcx_sum_fwd_dense2", "pcx_sum_bwd_ele_dense2"):
+        # two kernels behind one call: the library records `m` between the operand pre-pass and the GEMM
+        m = torch.cuda.Event(enable_timing=True)
+        m.record()                                       # creates the underlying event (overwritten by the library)
+        lib.pcx_set_stage_event(m.cuda_event)
+        rc = getattr(lib, name)(*conv, stream)
+        lib.pcx_set_stage_event(None)
+        b.record()
+        PROFILE.append((name + "_prep", a, m))
+        PROFILE.append((name, m, b))
+        return rc
     rc = getattr(lib, name)(*conv, stream)
     b.record()
     # the dataflow launch serves two operators: tell them apart by its first argument (0 forward, 1 element flows)

@@ -839,6 +839,10 @@ inline WideScratch wide_scratch(void* base, int n_groups, int depth, int B) {
     return w;
 }
 
+// Measurement hook: when set (per host thread), the two-kernel operators record this event between their operand
+// pre-pass and their GEMM, so that a caller timing the call with events of its own can tell the two kernels apart.
+thread_local cudaEvent_t g_wide_stage_event = nullptr;
+
 // Shared host part of the forward pass and the element flows.
 static int wide_rows_op(int mode, float* out, const float* src, const float* src2, const float* emars, float* nflows,
                         const void* packed, const int32_t* rows, const int32_t* kids, const int32_t* fkids_prep,
@@ -871,6 +875,7 @@ static int wide_rows_op(int mode, float* out, const float* src, const float* src
     else if (pfc == 4) rc = launch_wide_prep_rows<4>(p, pgrid, psmem, st);
     else rc = launch_wide_prep_rows<8>(p, pgrid, psmem, st);
     if (rc != 0) return rc;
+    if (g_wide_stage_event != nullptr) cudaEventRecord(g_wide_stage_event, st);      // measurement hook, see pcx_set_stage_event
 
     WideArgs a{};
     a.a_tiles = reinterpret_cast<const uint8_t*>(packed); a.b_tiles = w.tiles; a.b_group = row_group;
@@ -884,6 +889,11 @@ static int wide_rows_op(int mode, float* out, const float* src, const float* src
 }  // namespace
 
 extern "C" {
+
+int pcx_set_stage_event(void* event) {
+    g_wide_stage_event = reinterpret_cast<cudaEvent_t>(event);
+    return 0;
+}
 
 int pcx_set_dependent_launch(int on) {
     g_wide_pdl = on ? 1 : 0;
