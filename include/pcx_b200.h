@@ -221,6 +221,25 @@ int pcx_sum_par_dense_gemm(float* param_flows, const float* params, const void* 
  * Replace, like the entry points above: SumLayer._forward_block_sparse / _backward_block_sparse_ele_flows /
  * _backward_block_sparse_par_flows (layer/sum_layer.py:551-929, 1369-1719, 1721-2080), with ProdLayer.forward /
  * backward folded in (layer/prod_layer.py:161-238). */
+/* The sum-layer operators under the reference's other propagation rules (`propagation_alg`, layer/sum_layer.py:
+ * 367-412, 414-543; kernels layer/kernels/sum_forward_block_sparse.py:83-160, sum_backward_element_block_sparse.py:
+ * 77-160, sum_backward_param_block_sparse.py:57-134), plain fp32 CUDA-core kernels with the table layout of
+ * pcx_sum_fwd / pcx_sum_bwd_ele / pcx_sum_bwd_par.  alg 0 = "LL" (the ordinary rule), 1 = "MPE" (value = max_k
+ * log theta + child; a parent's flow goes to the children and parameters that attain the maximum, |log theta +
+ * child - value| < 1e-6), 2 = "GeneralLL" (value = (1 / alpha) log sum_k (theta exp(child))^alpha; element flows
+ * weighted by theta^alpha exp(alpha (child - value)), parameter flows by theta exp(child - value)). */
+int pcx_sum_fwd_alg(float* node_mars, const float* element_mars, const float* params, const int32_t* nids,
+                    const int32_t* cids, const int32_t* pids, int64_t n_blocks, int K, int block_size, int B, int alg,
+                    float alpha, void* stream);
+int pcx_sum_bwd_ele_alg(float* element_flows, const float* element_mars, const float* node_flows, const float* node_mars,
+                        const float* params, const int32_t* chids, const int32_t* parids, const int32_t* parpids,
+                        int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace, int alg,
+                        float alpha, void* stream);
+int pcx_sum_bwd_par_alg(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                        const float* params, const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                        const int32_t* pfids, int64_t n_blocks, int K, int block_size, int B, int logspace, int alg,
+                        float alpha, void* stream);
+
 /* Measurement hook (per calling host thread): while `event` (a cudaEvent_t created with timing) is set,
  * pcx_sum_fwd_dense2 and pcx_sum_bwd_ele_dense2 record it on their stream between the operand pre-pass kernel and the
  * GEMM kernel, so that a benchmark that brackets the call with two events of its own gets the duration of each of

@@ -184,6 +184,76 @@ def _sum_backward(layer, st, params, compute_param_flows, cache=None, pending=No
             st.param_flows.index_add_(0, idx, (th * acc).reshape(-1))
 
 
+ALG_IDS = {"LL": 0, "MPE": 1, "GeneralLL": 2}
+
+
+def _sum_forward_alg(layer, node_mars, element_mars, params, alg, alpha):
+    """The reference's other propagation rules (layer/sum_layer.py:1079-1090): "MPE": max_k (log theta + child),
+    "GeneralLL": (1 / alpha) log sum_k (theta exp(child))^alpha."""
+    m = torch.arange(layer["bs"])
+    B = node_mars.size(1)
+    for nids, cids, pids in zip(layer["nids"], layer["cids"], layer["pids"]):
+        K = cids.size(1)
+        for r0, r1 in _row_chunks(nids.numel(), K * layer["bs"] * B):
+            em = element_mars[cids[r0:r1]]                           # [n, K, B]
+            lth = params[pids[r0:r1, :, None] + m[None, None, :]].log()                 # [n, K, bs]
+            lth = torch.where((cids[r0:r1] == 0)[:, :, None], _neg_inf_like(lth), lth)
+            val = lth.permute(0, 2, 1)[:, :, :, None] + em[:, None, :, :]               # [n, bs, K, B]
+            out = val.max(dim=2).values if alg == 1 else _lse(alpha * val, 2) / alpha
+            node_mars[(nids[r0:r1, None] + m[None, :]).reshape(-1)] = out.reshape(-1, B)
+
+
+def _sum_backward_alg(layer, st, params, compute_param_flows, alg, alpha):
+    """Flows under "MPE" (a parent's flow goes to the children and parameters that attain its maximum, within 1e-6:
+    layer/kernels/sum_backward_element_block_sparse.py:89-94, sum_backward_param_block_sparse.py:69-77) and
+    "GeneralLL" (element flows weighted by theta^alpha exp(alpha (child - value)), parameter flows by the ordinary
+    theta exp(child - value): sum_backward_element_block_sparse.py:113-139, sum_backward_param_block_sparse.py:79-134
+    and tests/layer/propagation_algs_test.py:198-236)."""
+    bs = layer["bs"]
+    n = torch.arange(bs)
+    B = st.node_mars.size(1)
+
+    def weight(lth, em, nm, a):                     # log weight of (parent, element): shapes broadcast
+        lw = lth + em - nm
+        lw = torch.where(torch.isnan(lw), _neg_inf_like(lw), lw)
+        if alg == 1:
+            return torch.where(lw.abs() < 1e-6, torch.zeros_like(lw), _neg_inf_like(lw))
+        return a * lw
+
+    for chids, parids, parpids, cbs in zip(layer["chids"], layer["parids"], layer["parpids"], layer["cs_block_sizes"]):
+        c = torch.arange(cbs)
+        P = parids.size(1)
+        for r0, r1 in _row_chunks(chids.numel(), P * bs * cbs * B):
+            pr, pp = parids[r0:r1], parpids[r0:r1]
+            rows = (pr[:, :, None] + n[None, None, :]).reshape(pr.size(0), -1)          # [r, P*bs]
+            nf, nm = st.node_flows[rows], st.node_mars[rows]                            # [r, P*bs, B]
+            pad = (pr == 0)[:, :, None].expand(-1, -1, bs).reshape(pr.size(0), -1)
+            nf = torch.where(pad[:, :, None], _neg_inf_like(nf), nf)
+            lth = params[pp[:, :, None, None] + c[None, None, :, None] * bs + n[None, None, None, :]] \
+                .permute(0, 2, 1, 3).reshape(pr.size(0), cbs, -1).log()                 # [r, cbs, P*bs]
+            tgt = (chids[r0:r1, None] + c[None, :]).reshape(-1)
+            em = st.element_mars[tgt].reshape(pr.size(0), cbs, B)
+            lw = weight(lth[:, :, :, None], em[:, :, None, :], nm[:, None, :, :], alpha)           # [r, cbs, P*bs, B]
+            tot = nf[:, None, :, :] + lw
+            tot = torch.where(torch.isnan(tot), _neg_inf_like(tot), tot)
+            st.element_flows[tgt] = _lse(tot, 2).reshape(-1, B)
+    if not compute_param_flows:
+        return
+    for nids, cids, pids, pfids in zip(layer["nids"], layer["cids"], layer["pids"], layer["pfids"]):
+        K = cids.size(1)
+        for r0, r1 in _row_chunks(nids.numel(), K * bs * B):
+            rows = (nids[r0:r1, None] + n[None, :])
+            nf, nm = st.node_flows[rows], st.node_mars[rows]                            # [r, bs, B]
+            em = st.element_mars[cids[r0:r1]]                                           # [r, K, B]
+            lth = params[pids[r0:r1, None, :] + n[None, :, None]].log()                 # [r, bs, K]
+            lth = torch.where((cids[r0:r1] == 0)[:, None, :], _neg_inf_like(lth), lth)
+            lw = weight(lth[:, :, :, None], em[:, None, :, :], nm[:, :, None, :], 1.0)  # [r, bs, K, B]
+            tot = nf[:, :, None, :] + lw
+            tot = torch.where(torch.isnan(tot), _neg_inf_like(tot), tot)
+            idx = (pfids[r0:r1, None, :] + n[None, :, None]).reshape(-1)
+            st.param_flows.index_add_(0, idx, tot.exp().sum(dim=3).reshape(-1))
+
+
 def _flush_pending_param_flows(pending, st, params):
     for slot in pending.values():
         n = torch.arange(slot["bs"])
@@ -204,7 +274,7 @@ def _prod_backward(layer, st):
 
 
 def forward(pc, x: torch.Tensor, params: torch.Tensor, input_params, dtype=torch.float64, tables=None,
-            state: Optional[OracleState] = None):
+            state: Optional[OracleState] = None, propagation_alg: str = "LL", alpha: float = 0.0):
     """Per-sample log-likelihoods ``[B, num_roots]``; fills ``state.node_mars / element_mars``.
 
     ``x`` is ``[B, V]`` integer, ``params`` the flat sum-parameter vector, ``input_params`` one flat
@@ -224,6 +294,8 @@ def forward(pc, x: torch.Tensor, params: torch.Tensor, input_params, dtype=torch
         for layer in layers:
             if kind == "prod":
                 _prod_forward(layer, st.node_mars, st.element_mars)
+            elif ALG_IDS[propagation_alg] != 0:
+                _sum_forward_alg(layer, st.node_mars, st.element_mars, params, ALG_IDS[propagation_alg], alpha)
             else:
                 _sum_forward(layer, st.node_mars, st.element_mars, params, cache=st.cache)
     st.tables = t
@@ -232,7 +304,8 @@ def forward(pc, x: torch.Tensor, params: torch.Tensor, input_params, dtype=torch
 
 def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: OracleState,
              ll_weights: Optional[torch.Tensor] = None, compute_param_flows: bool = True,
-             param_flows: Optional[torch.Tensor] = None, input_param_flows=None, reference_compat: bool = False):
+             param_flows: Optional[torch.Tensor] = None, input_param_flows=None, reference_compat: bool = False,
+             propagation_alg: str = "LL", alpha: float = 0.0):
     """Log-space node/element flows and (accumulated) parameter flows.  ``st`` comes from
     :func:`forward` on the same inputs.  Existing ``param_flows`` are added to, as the reference does.
 
@@ -265,7 +338,10 @@ def backward(pc, x: torch.Tensor, params: torch.Tensor, input_params, st: Oracle
             if not reference_compat:
                 st.element_flows.fill_(NEG_INF)
             for layer in layers:
-                _sum_backward(layer, st, params, compute_param_flows, cache=st.cache, pending=pending)
+                if ALG_IDS[propagation_alg] != 0:
+                    _sum_backward_alg(layer, st, params, compute_param_flows, ALG_IDS[propagation_alg], alpha)
+                else:
+                    _sum_backward(layer, st, params, compute_param_flows, cache=st.cache, pending=pending)
     _flush_pending_param_flows(pending, st, params)
     st.input_param_flows = []
     for li, lt in enumerate(t["inputs"]):

@@ -33,6 +33,9 @@ SIGNATURES = {
     "pcx_prod_fwd": [P, P, P, P, L, I, I, I],
     "pcx_prod_bwd": [P, P, P, P, L, I, I, I, I],
     "pcx_sum_fwd": [P, P, P, P, P, P, L, I, I, I],
+    "pcx_sum_fwd_alg": [P, P, P, P, P, P, L, I, I, I, I, F],
+    "pcx_sum_bwd_ele_alg": [P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, F],
+    "pcx_sum_bwd_par_alg": [P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, F],
     "pcx_sum_bwd_ele": [P, P, P, P, P, P, P, P, L, I, I, I, I, I],
     "pcx_sum_bwd_par": [P, P, P, P, P, P, P, P, P, L, I, I, I, I],
     "pcx_pack_sum_params": [P, I, L, P],

@@ -599,6 +599,109 @@ sum_par_rows(float* __restrict__ param_flows, const float* __restrict__ node_flo
     }
 }
 
+
+// ---- other propagation rules (plain kernels, one thread per output) ---------------------------------------------------
+// alg 1 "MPE":        value(n) = max_k (log theta[n,k] + child_k);  a parent hands its whole flow to the children that
+//                      attain the maximum (|log theta + child - value| < 1e-6), parameter flows likewise.
+// alg 2 "GeneralLL":  value(n) = (1 / alpha) * log sum_k (theta[n,k] * exp(child_k))^alpha;  element flows carry the
+//                      weights theta^alpha * exp(alpha * (child - value)), parameter flows the ordinary ones.
+// alg 0 is the ordinary rule (kept here so that one kernel serves as the reference for the others in tests).
+// Reference: layer/kernels/sum_forward_block_sparse.py:83-160, sum_backward_element_block_sparse.py:77-160,
+// sum_backward_param_block_sparse.py:57-134.
+__global__ void sum_fwd_alg_kernel(float* __restrict__ node_mars, const float* __restrict__ element_mars,
+                                   const float* __restrict__ params, const int32_t* __restrict__ nids,
+                                   const int32_t* __restrict__ cids, const int32_t* __restrict__ pids,
+                                   int64_t n_blocks, int K, int bs, int B, int alg, float alpha) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_blocks * bs * B) return;
+    const int b = (int)(t % B);
+    const int j = (int)((t / B) % bs);
+    const int64_t i = t / ((int64_t)B * bs);
+    float mx = PCX_NEG_INF, sum = 0.0f;
+    for (int k = 0; k < K; ++k) {
+        const int cid = cids[i * K + k];
+        if (cid == 0) continue;
+        float v = logf(params[(int64_t)pids[i * K + k] + j]) + element_mars[(int64_t)cid * B + b];
+        if (alg == 2) v *= alpha;
+        if (v == PCX_NEG_INF) continue;
+        if (alg == 1) { mx = fmaxf(mx, v); continue; }
+        if (v > mx) { sum = sum * expf(mx - v) + 1.0f; mx = v; }
+        else sum += expf(v - mx);
+    }
+    float out = mx;
+    if (alg != 1 && mx != PCX_NEG_INF) out = mx + logf(sum);
+    if (alg == 2) out /= alpha;
+    node_mars[((int64_t)nids[i] + j) * B + b] = out;
+}
+
+// weight (log domain) with which parent n hands flow to element e; -inf when none
+__device__ __forceinline__ float alg_log_weight(int alg, float alpha, float ltheta, float em, float nm) {
+    if (nm == PCX_NEG_INF || em == PCX_NEG_INF || ltheta == PCX_NEG_INF) return PCX_NEG_INF;
+    if (alg == 1) return (fabsf(ltheta + em - nm) < 1e-6f) ? 0.0f : PCX_NEG_INF;
+    const float w = ltheta + em - nm;
+    return alg == 2 ? alpha * w : w;
+}
+
+__global__ void sum_ele_alg_kernel(float* __restrict__ element_flows, const float* __restrict__ element_mars,
+                                   const float* __restrict__ node_flows, const float* __restrict__ node_mars,
+                                   const float* __restrict__ params, const int32_t* __restrict__ chids,
+                                   const int32_t* __restrict__ parids, const int32_t* __restrict__ parpids,
+                                   int64_t n_blocks, int P, int bs, int cbs, int B, int logspace, int alg, float alpha) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_blocks * cbs * B) return;
+    const int b = (int)(t % B);
+    const int c = (int)((t / B) % cbs);
+    const int64_t i = t / ((int64_t)B * cbs);
+    const int64_t erow = (int64_t)chids[i] + c;
+    const float em = element_mars[erow * B + b];
+    float mx = PCX_NEG_INF, sum = 0.0f;
+    for (int p = 0; p < P; ++p) {
+        const int par = parids[i * P + p];
+        if (par == 0) continue;
+        for (int n = 0; n < bs; ++n) {
+            const float nf = node_flows[((int64_t)par + n) * B + b];
+            const float lf = logspace ? nf : logf(nf);
+            const float lw = alg_log_weight(alg, alpha, logf(params[(int64_t)parpids[i * P + p] + (int64_t)c * bs + n]), em,
+                                            node_mars[((int64_t)par + n) * B + b]);
+            const float v = lf + lw;
+            if (v == PCX_NEG_INF || lf == PCX_NEG_INF) continue;
+            if (v > mx) { sum = sum * expf(mx - v) + 1.0f; mx = v; }
+            else sum += expf(v - mx);
+        }
+    }
+    const float lo = (mx == PCX_NEG_INF) ? PCX_NEG_INF : mx + logf(sum);
+    element_flows[erow * B + b] = logspace ? lo : expf(lo);
+}
+
+__global__ void sum_par_alg_kernel(float* __restrict__ param_flows, const float* __restrict__ node_flows,
+                                   const float* __restrict__ node_mars, const float* __restrict__ element_mars,
+                                   const float* __restrict__ params, const int32_t* __restrict__ nids,
+                                   const int32_t* __restrict__ cids, const int32_t* __restrict__ pids,
+                                   const int32_t* __restrict__ pfids, int64_t n_blocks, int K, int bs, int B,
+                                   int logspace, int alg, float alpha) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_blocks * K * bs) return;
+    const int j = (int)(t % bs);
+    const int k = (int)((t / bs) % K);
+    const int64_t i = t / ((int64_t)bs * K);
+    const int cid = cids[i * K + k];
+    if (cid == 0) return;
+    const float ltheta = logf(params[(int64_t)pids[i * K + k] + j]);
+    const int64_t nrow = (int64_t)nids[i] + j;
+    float acc = 0.0f;
+    for (int b = 0; b < B; ++b) {
+        const float nf = node_flows[nrow * B + b];
+        const float lf = logspace ? nf : logf(nf);
+        // GeneralLL: the reference's parameter flows keep the ordinary weight theta * exp(child - value), with the
+        // GeneralLL values (sum_backward_param_block_sparse.py:79-134; tests/layer/propagation_algs_test.py:224-236)
+        const float lw = alg_log_weight(alg == 2 ? 0 : alg, alpha, ltheta, element_mars[(int64_t)cid * B + b],
+                                        node_mars[nrow * B + b]);
+        if (lf == PCX_NEG_INF || lw == PCX_NEG_INF) continue;
+        acc += expf(lf + lw);
+    }
+    if (acc != 0.0f) atomicAdd(param_flows + (int64_t)pfids[i * K + k] + j, acc);
+}
+
 }  // namespace
 
 // tensor-core dispatch (pcx_sum_tc.cu): returns 1 when it took the call, with the launch status in *rc
@@ -710,5 +813,46 @@ int pcx_sum_bwd_par(float* param_flows, const float* node_flows, const float* no
     PCX_LAUNCH_CHECK();
     return 0;
 }
+
+int pcx_sum_fwd_alg(float* node_mars, const float* element_mars, const float* params, const int32_t* nids,
+                    const int32_t* cids, const int32_t* pids, int64_t n_blocks, int K, int block_size, int B, int alg,
+                    float alpha, void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size <= 0 || K <= 0 || alg < 0 || alg > 2 || (alg == 2 && !(alpha > 0.0f))) return -1;
+    const int64_t total = n_blocks * block_size * B;
+    sum_fwd_alg_kernel<<<(unsigned)pcx_cdiv(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        node_mars, element_mars, params, nids, cids, pids, n_blocks, K, block_size, B, alg, alpha);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_sum_bwd_ele_alg(float* element_flows, const float* element_mars, const float* node_flows, const float* node_mars,
+                        const float* params, const int32_t* chids, const int32_t* parids, const int32_t* parpids,
+                        int64_t n_blocks, int P, int block_size, int ch_block_size, int B, int logspace, int alg,
+                        float alpha, void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size <= 0 || ch_block_size <= 0 || P <= 0 || alg < 0 || alg > 2 || (alg == 2 && !(alpha > 0.0f))) return -1;
+    const int64_t total = n_blocks * ch_block_size * B;
+    sum_ele_alg_kernel<<<(unsigned)pcx_cdiv(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        element_flows, element_mars, node_flows, node_mars, params, chids, parids, parpids, n_blocks, P, block_size,
+        ch_block_size, B, logspace, alg, alpha);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
+int pcx_sum_bwd_par_alg(float* param_flows, const float* node_flows, const float* node_mars, const float* element_mars,
+                        const float* params, const int32_t* nids, const int32_t* cids, const int32_t* pids,
+                        const int32_t* pfids, int64_t n_blocks, int K, int block_size, int B, int logspace, int alg,
+                        float alpha, void* stream) {
+    if (n_blocks <= 0 || B <= 0) return 0;
+    if (block_size <= 0 || K <= 0 || alg < 0 || alg > 2 || (alg == 2 && !(alpha > 0.0f))) return -1;
+    const int64_t total = n_blocks * K * block_size;
+    sum_par_alg_kernel<<<(unsigned)pcx_cdiv(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        param_flows, node_flows, node_mars, element_mars, params, nids, cids, pids, pfids, n_blocks, K, block_size, B,
+        logspace, alg, alpha);
+    PCX_LAUNCH_CHECK();
+    return 0;
+}
+
 
 }  // extern "C"

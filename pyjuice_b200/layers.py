@@ -30,6 +30,20 @@ def _dev_i32(t: torch.Tensor, device) -> torch.Tensor:
     return t.to(device=device, dtype=torch.int32).contiguous()
 
 
+ALG_IDS = {"LL": 0, "MPE": 1, "GeneralLL": 2}
+
+
+def _alg_of(propagation_alg, kwargs):
+    """(id, alpha) of a propagation rule given by name (layer/sum_layer.py: `propagation_alg_mapping`)."""
+    if propagation_alg not in ALG_IDS:
+        raise NotImplementedError(f"Unknown propagation algorithm {propagation_alg}.")
+    alg = ALG_IDS[propagation_alg]
+    alpha = float(kwargs.get("alpha", 0.0)) if alg == 2 else 0.0
+    if alg == 2 and not alpha > 0.0:
+        raise ValueError("`propagation_alg='GeneralLL'` needs `alpha` > 0")
+    return alg, alpha
+
+
 def _unsupported(**flags):
     bad = [k for k, v in flags.items() if v]
     if bad:
@@ -646,8 +660,14 @@ class SumLayer(Layer, nn.Module):
     def forward(self, node_mars: torch.Tensor, element_mars: torch.Tensor, params: torch.Tensor,
                 propagation_alg: str = "LL", pflow_temperature: float = 1.0, **kwargs):
         self._require_cuda()
-        _unsupported(propagation_alg=propagation_alg != "LL", pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6)
+        _unsupported(pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6)
         B = node_mars.size(1)
+        alg, alpha = _alg_of(propagation_alg, kwargs)
+        if alg != 0:                                      # "MPE" / "GeneralLL": plain fp32 kernels
+            for nids, cids, pids, _ in self._dev["fw"]:
+                _lib.call("pcx_sum_fwd_alg", node_mars, element_mars, params, nids, cids, pids, nids.numel(),
+                          cids.size(1), self.block_size, B, alg, alpha)
+            return
         packed = self._use_packed(params)
         for p, (nids, cids, pids, _) in enumerate(self._dev["fw"]):
             if packed and self._wide_ok(p, B, False):
@@ -725,11 +745,21 @@ class SumLayer(Layer, nn.Module):
                  negate_pflows: bool = False, accumulate_ch_flows: bool = False, allow_neg_flows: bool = False,
                  pflow_temperature: float = 1.0, temper_eflow: bool = False, **kwargs):
         self._require_cuda()
-        _unsupported(allow_modify_flows=allow_modify_flows, propagation_alg=propagation_alg != "LL",
+        _unsupported(allow_modify_flows=allow_modify_flows,
                      negate_pflows=negate_pflows, accumulate_ch_flows=accumulate_ch_flows, allow_neg_flows=allow_neg_flows,
                      pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6, temper_eflow=temper_eflow)
         B = node_flows.size(1)
         ls = int(bool(logspace_flows))
+        alg, alpha = _alg_of(propagation_alg, kwargs)
+        if alg != 0:                                      # "MPE" / "GeneralLL": plain fp32 kernels
+            for (chids, parids, parpids), cbs in zip(self._dev["bk"], self.cs_block_sizes):
+                _lib.call("pcx_sum_bwd_ele_alg", element_flows, element_mars, node_flows, node_mars, params, chids, parids,
+                          parpids, chids.numel(), parids.size(1), self.block_size, cbs, B, ls, alg, alpha)
+            if param_flows is not None:
+                for nids, cids, pids, pfids in self._dev["fw"]:
+                    _lib.call("pcx_sum_bwd_par_alg", param_flows, node_flows, node_mars, element_mars, params, nids, cids,
+                              pids, pfids, nids.numel(), cids.size(1), self.block_size, B, ls, alg, alpha)
+            return
         packed = self._use_packed(params)
         for p, ((chids, parids, parpids), cbs) in enumerate(zip(self._dev["bk"], self.cs_block_sizes)):
             if packed and self._wide_ok(p, B, True):

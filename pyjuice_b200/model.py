@@ -26,7 +26,7 @@ import torch.nn as nn
 
 from . import _lib
 from .compiler import _IdDict, compile_cum_par_flows, compile_par_update, create_node_layers
-from .layers import InputLayer, LayerGroup, ParamPacker, ProdLayer, SumLayer, _fill, _scale, _unsupported
+from .layers import InputLayer, LayerGroup, ParamPacker, ProdLayer, SumLayer, _alg_of, _fill, _scale, _unsupported
 from .flows import FlowArena
 from .nodes import as_bitset
 
@@ -45,13 +45,31 @@ def _pc_model_backward_hook(grad, pc, inputs, **kwargs):
 
 
 def _in_own_mode(fn):
-    """Run a public method in the circuit's own arithmetic mode (``self.sum_mode``; None = the process default)."""
+    """Run a public method in the circuit's own arithmetic mode (``self.sum_mode``; None = the process default).
+    A pass under another propagation rule ("MPE", "GeneralLL") runs on the plain fp32 kernels (mode 0: nothing is
+    folded or fused), with the rule kept in ``self._alg`` for the duration of the call."""
     @functools.wraps(fn)
     def wrapper(self, *args, **kwargs):
-        if self.sum_mode is None:
-            return fn(self, *args, **kwargs)
-        with _lib.use_sum_mode(self.sum_mode):
-            return fn(self, *args, **kwargs)
+        mode, prev = self.sum_mode, self._alg
+        if fn.__name__ in ("forward", "backward"):
+            name = kwargs.get("propagation_alg")
+            if name is None:
+                name = self.default_propagation_alg if fn.__name__ == "forward" else "LL"
+                if fn.__name__ == "forward":
+                    kwargs = {**self.propagation_alg_kwargs, **kwargs}
+            if not isinstance(name, str):
+                raise NotImplementedError("one propagation rule per layer is outside the compiled path")
+            self._alg = _alg_of(name, kwargs)
+            kwargs["propagation_alg"] = name
+            if self._alg[0] != 0:
+                mode = 0
+        try:
+            if mode is None:
+                return fn(self, *args, **kwargs)
+            with _lib.use_sum_mode(mode):
+                return fn(self, *args, **kwargs)
+        finally:
+            self._alg = prev
     return wrapper
 
 
@@ -77,7 +95,9 @@ class TensorCircuit(nn.Module):
         self.sum_mode = None                  # this circuit's arithmetic (0, 1 or 2 as `_lib.set_sum_mode`); None = default
         self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
         self.dense_par_max_bytes = 16 << 30   # operand buffers of the dense parameter-flow product (all groups)
-        self.default_propagation_alg = "LL"
+        self.default_propagation_alg = "LL"        # "LL", "MPE" or "GeneralLL" (see `set_propagation_alg`)
+        self.propagation_alg_kwargs = dict()
+        self._alg = (0, 0.0)                        # rule of the pass in progress: (id, alpha)
         self._run_params = {}
         self._cum_flow_host = 0.0
         self._cum_flow_dev = None
@@ -501,7 +521,7 @@ class TensorCircuit(nn.Module):
         return (_lib.sum_mode(), self.fuse_product_layers, self.use_dataflow_launch, self.chain_tile,
                 SumLayer.use_dense_kernels, SumLayer.use_wide_dense, SumLayer.use_sample_major,
                 getattr(self._packer, "grown", 0),
-                self._reference_compat)
+                self._reference_compat, self._alg)
 
     def _chain_plan(self, B: int, mode: int):
         """Job table of the dataflow launch (one launch for a run of consecutive depths) for the forward pass
@@ -590,7 +610,27 @@ class TensorCircuit(nn.Module):
                 for layer in group:
                     layer.forward_fused(self.node_mars)
             else:
-                group.forward(self.node_mars, self.element_mars, self.params.data)
+                group.forward(self.node_mars, self.element_mars, self.params.data, **self._alg_kwargs())
+
+    def _alg_kwargs(self) -> dict:
+        names = ("LL", "MPE", "GeneralLL")
+        return dict(propagation_alg=names[self._alg[0]], **({"alpha": self._alg[1]} if self._alg[0] == 2 else {}))
+
+    def set_propagation_alg(self, propagation_alg: str, **kwargs):
+        """Default propagation rule of `forward` ("LL", "MPE", or "GeneralLL" with ``alpha``), as
+        model/tensorcircuit.py:293-317."""
+        _alg_of(propagation_alg, kwargs)
+        self.default_propagation_alg = propagation_alg
+        self.propagation_alg_kwargs = {"alpha": kwargs["alpha"]} if propagation_alg == "GeneralLL" else {}
+
+    def forward_ll(self, *args, **kwargs):
+        return self.forward(*args, propagation_alg="LL", **kwargs)
+
+    def forward_mpe(self, *args, **kwargs):
+        return self.forward(*args, propagation_alg="MPE", **kwargs)
+
+    def forward_general_ll(self, *args, **kwargs):
+        return self.forward(*args, propagation_alg="GeneralLL", **kwargs)
 
     @_in_own_mode
     def forward(self, inputs: torch.Tensor, input_layer_fn=None, cache=None, return_cache: bool = False,
@@ -598,7 +638,7 @@ class TensorCircuit(nn.Module):
         """Per-sample log-likelihoods ``[B, num_roots]`` of ``inputs`` (``[B, num_vars]``, integer)."""
         self._require_cuda()
         _unsupported(input_layer_fn=input_layer_fn is not None, cache=cache is not None, return_cache=return_cache,
-                     propagation_alg=propagation_alg not in (None, "LL"), pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6,
+                     pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6,
                      missing_mask=kwargs.get("missing_mask") is not None)
         origin_inputs = inputs
         with torch.no_grad():
@@ -624,7 +664,7 @@ class TensorCircuit(nn.Module):
             lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
         if torch.is_grad_enabled():
             lls.requires_grad = True
-            lls.register_hook(partial(_pc_model_backward_hook, pc=self, inputs=origin_inputs))
+            lls.register_hook(partial(_pc_model_backward_hook, pc=self, inputs=origin_inputs, **self._alg_kwargs()))
         return lls
 
     # ------------------------------------------------------------------------------------------
@@ -731,7 +771,7 @@ class TensorCircuit(nn.Module):
         pf = self.param_flows if compute_param_flows else None
         groups = self.inner_layer_groups
         any_fused = False
-        dense = self._dense_par_plan(self.node_mars.size(1)) if pf is not None else None
+        dense = self._dense_par_plan(self.node_mars.size(1)) if (pf is not None and self._alg[0] == 0) else None
 
         def dense_stage(layer, p, node_flows, node_mars, element_mars, ls):
             hit = dense["where"].get((id(layer), p))
@@ -793,7 +833,7 @@ class TensorCircuit(nn.Module):
                 groups[gi - 1].forward(self.node_mars, self.element_mars, _for_backward=True)
                 group.backward(self.node_flows, self.element_flows, self.node_mars, self.element_mars,
                                self.params.data, param_flows=pf, logspace_flows=logspace_flows,
-                               dense_par_stage=dense_stage if dense is not None else None)
+                               dense_par_stage=dense_stage if dense is not None else None, **self._alg_kwargs())
         if dense is not None:
             if forked:
                 side.wait_stream(cur)                        # operands staged on the main stream are complete too
@@ -827,7 +867,6 @@ class TensorCircuit(nn.Module):
         assert not (allow_modify_flows and logspace_flows), \
             "`allow_modify_flows` should be set to `False` when using `logspace_flows`."
         _unsupported(input_layer_fn=input_layer_fn is not None, cache=cache is not None, return_cache=return_cache,
-                     propagation_alg=propagation_alg != "LL",
                      negate_pflows=negate_pflows, pflow_temperature=abs(pflow_temperature - 1.0) > 1e-6,
                      missing_mask=kwargs.get("missing_mask") is not None)
         assert self.node_mars is not None and self.element_mars is not None, "Should run forward path first."
