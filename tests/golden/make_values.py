@@ -117,6 +117,21 @@ def run_case(api, name, seed, B, dev):
     out["params1_rescaled"] = pc.params.detach().cpu().numpy()
     for i, layer in enumerate(pc.input_layer_group):
         out[f"iparams1_rescaled_{i}"] = layer.params.detach().cpu().numpy()
+    # the other propagation rules (model/tensorcircuit.py:322-347, 485-509): values and flows from the initial parameters
+    pc.params.data.copy_(p0)
+    for layer, p in zip(pc.input_layer_group, ip0):
+        layer.params.data.copy_(p)
+    for tag, kw in (("mpe", dict(propagation_alg="MPE")), ("gll2", dict(propagation_alg="GeneralLL", alpha=2.0))):
+        pc.init_param_flows(flows_memory=0.0)
+        with torch.no_grad():
+            lls = pc(xd, force_use_fp32=True, **kw)
+        # linear flows: under "MPE" the reference's log-space element-flow kernel adds log-flows within a tile
+        # (layer/kernels/sum_backward_element_block_sparse.py:94), which is not a quantity to pin anything to
+        pc.backward(xd, flows_memory=1.0, force_use_fp32=True, logspace_flows=False, **kw)
+        torch.cuda.synchronize()
+        out["lls_" + tag] = lls.detach().cpu().numpy()
+        out["param_flows_" + tag] = pc.param_flows.detach().cpu().numpy()
+        out["node_flows_" + tag] = pc.node_flows.detach().cpu().numpy()
     return out
 
 

@@ -84,7 +84,25 @@ def test_oracle_matches_the_reference_itself(name):
         for i in range(n_in):
             ok, e = rel_close(rip[i], t(f"iparams1_rescaled_{i}"), tol[1])
             assert ok, f"{name}: rescaled update (input parameters) differs from the reference's by {e}"
+    for tag, alg, alpha in (("mpe", "MPE", 0.0), ("gll2", "GeneralLL", 2.0)):
+        if "lls_" + tag not in v.files:
+            continue
+        alls, ast = orc.forward(pc, x, p0, ip0, propagation_alg=alg, alpha=alpha)
+        orc.backward(pc, x, p0, ip0, ast, propagation_alg=alg, alpha=alpha)
+        errs["ll_" + tag] = _check_rule(name, tag, pc, t, tol, alls, ast.node_flows.exp(), ast.param_flows)
     print(name, {k: f"{e:.1e}" for k, e in errs.items()})
+
+
+def _check_rule(name, tag, pc, t, tol, lls, node_flows, param_flows):
+    """Values and (linear) flows under another propagation rule against the reference's."""
+    d = (lls.double().cpu() - t("lls_" + tag).double().reshape(lls.shape)).abs().max().item()
+    assert d <= tol[0], f"{name} {tag}: values differ from the reference's by {d}"
+    nd = pc.num_dummy_nodes
+    ok, e = rel_close(node_flows.double().cpu()[nd:], t("node_flows_" + tag).double()[nd:], max(tol[1], 2e-3))
+    assert ok, f"{name} {tag}: node flows differ from the reference's by {e}"
+    ok, e = rel_close(param_flows.double().cpu(), t("param_flows_" + tag).double(), max(tol[1], 2e-3))
+    assert ok, f"{name} {tag}: parameter flows differ from the reference's by {e}"
+    return d
 
 
 @pytest.mark.gpu
@@ -126,5 +144,15 @@ def test_cuda_path_matches_the_reference_itself(name):
         for i, layer in enumerate(pc.input_layer_group):
             ok, e = rel_close(layer.params.data, t(f"iparams1_rescaled_{i}"), tol[1])
             assert ok, f"{name}: rescaled update (input parameters) differs from the reference's by {e}"
+    for tag, kw in (("mpe", dict(propagation_alg="MPE")), ("gll2", dict(propagation_alg="GeneralLL", alpha=2.0))):
+        if "lls_" + tag not in v.files:
+            continue
+        pc.params.data.copy_(t("params0"))
+        pc._packer.invalidate()
+        for i, layer in enumerate(pc.input_layer_group):
+            layer.params.data.copy_(t(f"iparams0_{i}"))
+        alls = pc(x, **kw)
+        pc.backward(x, flows_memory=0.0, logspace_flows=False, **kw)
+        errs["ll_" + tag] = _check_rule(name, tag, pc, t, tol, alls, pc.node_flows, pc.param_flows)
     print(name, {k: f"{e:.1e}" for k, e in errs.items()})
     _lib.check_status("cuda:0")
