@@ -92,6 +92,7 @@ class TensorCircuit(nn.Module):
         self.use_cuda_graphs = True
         self.use_dataflow_launch = True       # runs of folded depths as one launch (tiles wait on counters)
         self.use_side_stream = True           # independent kernels of a step share the device (two streams)
+        self.debug_poison = False             # fill value / flow buffers with NaN before every pass (see `assert_no_poison`)
         self.sum_mode = None                  # this circuit's arithmetic (0, 1 or 2 as `_lib.set_sum_mode`); None = default
         self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
         self.dense_par_max_bytes = 16 << 30   # operand buffers of the dense parameter-flow product (all groups)
@@ -645,6 +646,8 @@ class TensorCircuit(nn.Module):
             B = inputs.size(0)
             data = self._prepare_inputs(inputs)
             self._ensure_buffers(B)
+            if self.debug_poison:               # every row must be rewritten by the layer that owns it
+                _fill(self.node_mars[self.num_dummy_nodes:], float("nan"))
             self._last_data, self._last_inputs = data, origin_inputs
             # the operand tiles of the tensor-core kernels are re-packed (when the parameters changed) on a second
             # stream, beside the input layer: neither reads what the other writes
@@ -881,6 +884,8 @@ class TensorCircuit(nn.Module):
             self._ensure_buffers(B, backward=True)
             ls = int(bool(logspace_flows))
             reset = NEG_INF if logspace_flows else 0.0
+            if self.debug_poison:               # rows outside the reset ranges must be rewritten by direct stores
+                _fill(self.node_flows, float("nan"))
             # the partial reset is only valid while every depth that was counted as "stores flows directly" does so
             ranges = self._flow_reset_ranges if (B % 8 == 0 and not self._reference_compat
                                                  and all(self._fusion_on(gi, True) for gi in self._fused)) else None
@@ -1239,6 +1244,76 @@ class TensorCircuit(nn.Module):
     # accessors
     # ------------------------------------------------------------------------------------------
     @_in_own_mode
+    # ---- debugging aids ---------------------------------------------------------------------------------------------
+    def assert_no_poison(self, backward: bool = False):
+        """With ``debug_poison`` on, the value buffer (and, after a backward pass, the flow buffer) was NaN before the
+        pass: a NaN that is still there marks a row no kernel wrote — a tile skipped by a grid computation, a
+        wrong range.  Raises with the number of such values and the first rows."""
+        bufs = [("node_mars", self.node_mars)] + ([("node_flows", self.node_flows)] if backward else [])
+        for name, buf in bufs:
+            bad = torch.isnan(buf[self.num_dummy_nodes:])
+            if bool(bad.any()):
+                rows = torch.nonzero(bad.any(dim=1)).reshape(-1)[:8] + self.num_dummy_nodes
+                raise AssertionError(f"{name}: {int(bad.sum())} values were not written (first rows {rows.tolist()})")
+
+    def validate_tables(self) -> dict:
+        """Bounds check of every compiled index table against the buffers it indexes (node / element rows, parameter
+        and flow offsets, variables): the static half of what a sanitizer run would check, on the host.  Category
+        ids, the only data-dependent indices, are clamped by the leaf kernels.  Returns the number of indices checked
+        per kind; raises ValueError on the first violations."""
+        errs, counts = [], {}
+
+        def cpu(t):
+            return torch.as_tensor(t).detach().cpu().long()
+
+        def check(what, idx, width, limit, skip_zero=False):
+            idx = cpu(idx).reshape(-1)
+            if skip_zero:
+                idx = idx[idx != 0]
+            counts[what] = counts.get(what, 0) + int(idx.numel())
+            if idx.numel() and (int(idx.min()) < 0 or int(idx.max()) + width > limit):
+                errs.append(f"{what}: index range [{int(idx.min())}, {int(idx.max())} + {width}) exceeds [0, {limit})")
+
+        n_par, n_pf = int(self.params.numel()), int(self.num_param_flows)
+        for layer in self.input_layer_group:
+            check("input vids", layer.vids, 1, self.num_vars)
+            cats = cpu(layer.node_cats)
+            check("input s_pids", cpu(layer.s_pids) + cats, 0, int(layer.params.numel()) + 1)
+            check("input s_pfids", cpu(layer.s_pfids) + cats, 0, int(layer.num_param_flows) + 1)
+            check("input rows", torch.tensor(layer._output_ind_range), 0, self.num_nodes + 1)
+        for group in self.inner_layer_groups:
+            for layer in group:
+                bs = layer.block_size
+                if group.is_prod():
+                    for nids, cids in zip(layer.partitioned_nids, layer.partitioned_cids):
+                        check("prod nids", nids, bs, self.num_elements)
+                        check("prod cids", cids, bs, self.num_nodes, skip_zero=True)
+                    for u, par in zip(layer.partitioned_u_cids, layer.partitioned_parids):
+                        check("prod u_cids", u, bs, self.num_nodes)
+                        check("prod parids", par, bs, self.num_elements, skip_zero=True)
+                    continue
+                for nids, cids, pids, pfids in zip(layer.partitioned_nids, layer.partitioned_cids,
+                                                   layer.partitioned_pids, layer.partitioned_pfids):
+                    live = cpu(cids) != 0
+                    check("sum nids", nids, bs, self.num_nodes)
+                    check("sum cids", cids, 1, self.num_elements)
+                    check("sum pids", cpu(pids)[live], bs, n_par)
+                    check("sum pfids", cpu(pfids)[live], bs, n_pf)
+                for chids, parids, parpids, cbs in zip(layer.partitioned_chids, layer.partitioned_parids,
+                                                       layer.partitioned_parpids, layer.cs_block_sizes):
+                    live = cpu(parids) != 0
+                    check("sum chids", chids, cbs, self.num_elements)
+                    check("sum parids", parids, bs, self.num_nodes, skip_zero=True)
+                    check("sum parpids", cpu(parpids)[live], cbs * bs, n_par)
+                f = getattr(layer, "_fusion", None)
+                if f:                                                       # child rows of folded product layers
+                    for t in list(f.get("fw", [])) + list(f.get("bk", [])):
+                        if t is not None:
+                            check("folded child rows", t, 1, self.num_nodes)
+        if errs:
+            raise ValueError("index tables out of bounds: " + "; ".join(errs[:6]))
+        return counts
+
     def update_parameters(self, clone: bool = True):
         if self.device.type == "cuda":
             _lib.check_status(self.device)                  # parameters computed after a timed-out wait are wrong

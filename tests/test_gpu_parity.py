@@ -508,3 +508,32 @@ def test_arithmetic_mode_belongs_to_the_circuit_and_the_calling_thread():
     torch.cuda.synchronize()
     assert torch.equal(out["c_fp32"][0], alone_a[0]) and torch.equal(out["c_default"][0], ref_c[0])
     assert torch.equal(step(pc_c)[0], ref_c[0]) and _lib.sum_mode() == 1
+
+
+@pytest.mark.parametrize("B", [24, 33, 128])
+@pytest.mark.parametrize("name", ["hclt_b128", "hmm_b128", "pd_small", "rat_small", "hclt_grid", "tied_sums", "sparse_sum"])
+def test_every_row_is_written_and_runs_repeat_bit_for_bit(name, B):
+    """Race / coverage checks that need no sanitizer.  (a) The value buffer and the flow buffer are filled with NaN
+    before each pass (`debug_poison`): every row must be rewritten by the kernel that owns it, whichever kernel family,
+    fold and tile shape the table takes — a NaN that survives is a tile nobody computed.  (b) Likelihoods, values and
+    node flows involve no atomics: two runs on the same inputs are equal bit for bit (eager, captured, replayed), and
+    equal to the run without poison.  Parameter flows are sums of float atomics: equal up to their order."""
+    pc = _build(name, seed=5).to(DEV)
+    pc.validate_tables()
+    x = _data_for(pc, B, seed=B).to(DEV)
+    runs = []
+    for poison in (False, True, True, True):
+        pc.debug_poison = poison
+        pc.init_param_flows(flows_memory=0.0)
+        lls = pc(x)
+        pc.backward(x)
+        torch.cuda.synchronize()
+        if poison:
+            pc.assert_no_poison(backward=True)
+        runs.append((lls.clone(), pc.node_mars.clone(), pc.node_flows.clone(), pc.param_flows.clone()))
+    nd = pc.num_dummy_nodes
+    for r in runs[1:]:
+        assert torch.equal(r[0], runs[0][0]) and torch.equal(r[1][nd:], runs[0][1][nd:])
+        assert torch.equal(r[2][nd:], runs[0][2][nd:])
+        assert torch.allclose(r[3], runs[0][3], rtol=1e-5, atol=1e-7)
+    _lib_status()

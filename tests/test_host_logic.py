@@ -120,3 +120,29 @@ def test_patch_pyjuice_rebinds_the_front_door(monkeypatch):
     assert out is fake
     assert fake.compile is pj.compile and fake.model.TensorCircuit is pj.TensorCircuit
     assert fake.optim.MiniBatchEM is pj.optim.MiniBatchEM and fake.optim.FullBatchEM is pj.optim.FullBatchEM
+
+
+def test_table_validation_accepts_compiled_circuits_and_names_a_bad_index():
+    """`validate_tables` checks every compiled index against the buffer it indexes (the static part of what a
+    sanitizer run would check); a corrupted entry is reported with its table."""
+    import sys, os
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    from cases import CASES, OursApi
+    import pytest
+    api = OursApi()
+    for name in ("hclt_grid", "pd_small", "hmm_blocks", "sparse_sum", "tied_sums"):
+        torch.manual_seed(0)
+        ns, kw = CASES[name](api)
+        ns.init_parameters()
+        pc = api.compile(ns, **kw)
+        counts = pc.validate_tables()
+        assert counts["sum cids"] > 0 and counts["prod cids"] > 0 and counts["input vids"] > 0
+    layer = [l for g in pc.inner_layer_groups for l in g if not g.is_prod()][0]
+    saved = layer.partitioned_cids[0][0, 0].item()
+    layer.partitioned_cids[0][0, 0] = pc.num_elements + 5
+    with pytest.raises(ValueError, match="sum cids"):
+        pc.validate_tables()
+    layer.partitioned_cids[0][0, 0] = saved
+    layer.partitioned_pids[0][0, 0] = pc.params.numel()
+    with pytest.raises(ValueError, match="sum pids"):
+        pc.validate_tables()
