@@ -16,7 +16,9 @@ Buffers (fp32, batch innermost):
 """
 from __future__ import annotations
 
+import contextlib
 import functools
+import os
 from functools import partial
 from typing import Optional, Sequence, Union
 
@@ -93,6 +95,7 @@ class TensorCircuit(nn.Module):
         self.use_dataflow_launch = True       # runs of folded depths as one launch (tiles wait on counters)
         self.use_side_stream = True           # independent kernels of a step share the device (two streams)
         self.debug_poison = False             # fill value / flow buffers with NaN before every pass (see `assert_no_poison`)
+        self.use_nvtx = bool(os.environ.get("PCX_B200_NVTX"))     # NVTX ranges around the phases of a step (profilers)
         self.sum_mode = None                  # this circuit's arithmetic (0, 1 or 2 as `_lib.set_sum_mode`); None = default
         self.chain_tile = None                # tile width of that launch in samples (16 / 32 / 64); None = choose
         self.dense_par_max_bytes = 16 << 30   # operand buffers of the dense parameter-flow product (all groups)
@@ -659,11 +662,13 @@ class TensorCircuit(nn.Module):
                     self._packer.refresh(self.params.data)   # outside any graph capture
             elif _lib.sum_mode() != 0:
                 self._packer.refresh(self.params.data)
-            for layer in self.input_layer_group:
-                layer.forward(data, self.node_mars)
+            with self._nvtx("pcx forward: input layers"):
+                for layer in self.input_layer_group:
+                    layer.forward(data, self.node_mars)
             if forked:
                 cur.wait_stream(self._side_stream)
-            self._run_inner(("fw", B, self._launch_cfg(), self.params.data_ptr()), self._forward_inner)
+            with self._nvtx("pcx forward: inner layers"):
+                self._run_inner(("fw", B, self._launch_cfg(), self.params.data_ptr()), self._forward_inner)
             lls = self.node_mars[self._root_node_range[0]:self._root_node_range[1], :].permute(1, 0).clone()
         if torch.is_grad_enabled():
             lls.requires_grad = True
@@ -922,7 +927,8 @@ class TensorCircuit(nn.Module):
             key = ("bk", B, bool(compute_param_flows), ls, self._launch_cfg(), self.params.data_ptr(),
                    self.param_flows.data_ptr() if compute_param_flows else 0)
             self._batched_par_pending = self._bk_par_pending.get(key, False)
-            self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
+            with self._nvtx("pcx backward: inner layers"):
+                self._run_inner(key, partial(self._backward_inner, compute_param_flows, bool(logspace_flows)))
             self._bk_par_pending[key] = self._batched_par_pending
 
             if compute_param_flows:
@@ -1244,6 +1250,9 @@ class TensorCircuit(nn.Module):
     # accessors
     # ------------------------------------------------------------------------------------------
     @_in_own_mode
+    def _nvtx(self, name: str):
+        return torch.cuda.nvtx.range(name) if self.use_nvtx else contextlib.nullcontext()
+
     # ---- debugging aids ---------------------------------------------------------------------------------------------
     def assert_no_poison(self, backward: bool = False):
         """With ``debug_poison`` on, the value buffer (and, after a backward pass, the flow buffer) was NaN before the

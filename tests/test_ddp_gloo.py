@@ -99,3 +99,50 @@ def test_arena_layout():
     assert all(v.data_ptr() % 256 == a.buf.data_ptr() % 256 for v in a.views)
     a.views[1].fill_(2.0)
     assert a.buf[128:198].sum().item() == 140.0 and a.buf[:128].sum().item() == 0.0
+
+
+def _leaver_worker(rank, world, port, out_dir):
+    """Rank 1 takes part in the first exchange and then leaves between steps; rank 0 goes on to the next exchange."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    from pyjuice_b200.flows import FlowArena
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8))
+    arena = FlowArena([256, 64], "cpu")
+    for v in arena.views:
+        v.fill_(float(rank + 1))
+    arena.all_reduce(1.0)                                          # step 1: both ranks
+    first_ok = bool(torch.all(arena.views[0] == 3.0))
+    if rank == 1:
+        open(os.path.join(out_dir, "rank1.txt"), "w").write("left")
+        os._exit(0)                                                # leaves without a word, between steps
+    before = arena.buf.clone()
+    t0 = time.time()
+    try:
+        arena.all_reduce(1.0)                                      # step 2: the peer is gone
+        outcome = "no error"
+    except Exception as e:                                         # gloo: connection reset, or the group's timeout
+        outcome = f"error:{type(e).__name__}"
+    dt = time.time() - t0
+    open(os.path.join(out_dir, "rank0.txt"), "w").write(f"{first_ok}|{outcome}|{dt:.1f}|{bool(torch.isfinite(arena.buf).all())}|"
+                                                        f"{arena.buf.numel() == before.numel()}")
+    os._exit(0)                                                    # the group cannot be torn down collectively any more
+
+
+def test_a_rank_that_left_ends_the_next_exchange_with_an_error_not_a_hang(tmp_path):
+    """Failure detection on the host: a data-parallel rank that exits between steps makes the survivor's next flow
+    exchange raise (connection reset, or the process group's timeout at the latest) instead of waiting forever; the
+    survivor keeps its flow arena."""
+    port = 31500 + (os.getpid() % 2000)
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+        assert not p.is_alive(), "a rank is still waiting for the one that left"
+    assert open(tmp_path / "rank1.txt").read() == "left"
+    first_ok, outcome, dt, finite, same = open(tmp_path / "rank0.txt").read().split("|")
+    assert first_ok == "True" and outcome.startswith("error:"), outcome
+    assert float(dt) < 60.0 and finite == "True" and same == "True"
