@@ -41,12 +41,25 @@ em_sum_kernel(float* __restrict__ params, const float* __restrict__ flows,
     float* p = params + blk_par[i] + m;
     const float add = pseudo / (float)fan;
 
+    // eight edges per round: their loads are independent, so a thread has eight (sixteen) in flight instead of one
+    constexpr int U = 8;
     float tot = 0.0f;
     if (live) {
-        for (int e = ty; e < fan; e += EL) {
-            float fl = f[(int64_t)e * bs];
-            if (keep_zero) tot += (p[(int64_t)e * bs] < 1e-12f) ? 0.0f : fl + add;
-            else tot += fl;
+        for (int e0 = ty; e0 < fan; e0 += EL * U) {
+            float fl[U], pv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = e0 + u * EL;
+                fl[u] = (e < fan) ? f[(int64_t)e * bs] : 0.0f;
+                pv[u] = (keep_zero && e < fan) ? p[(int64_t)e * bs] : 1.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = e0 + u * EL;
+                if (e >= fan) continue;
+                if (keep_zero) tot += (pv[u] < 1e-12f) ? 0.0f : fl[u] + add;
+                else tot += fl[u];
+            }
         }
     }
     s_red[ty][threadIdx.x % MT] = tot;
@@ -57,12 +70,23 @@ em_sum_kernel(float* __restrict__ params, const float* __restrict__ flows,
     }
     if (!live) return;
     const float denom = keep_zero ? s_red[0][threadIdx.x % MT] : s_red[0][threadIdx.x % MT] + pseudo;
-    for (int e = ty; e < fan; e += EL) {
-        float old = p[(int64_t)e * bs];
-        float nw = (f[(int64_t)e * bs] + add) / denom;
-        float upd = (1.0f - step) * old + step * nw;
-        if (keep_zero && old < 1e-12f) upd = 0.0f;
-        p[(int64_t)e * bs] = upd;
+    for (int e0 = ty; e0 < fan; e0 += EL * U) {
+        float fl[U], old[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int e = e0 + u * EL;
+            fl[u] = (e < fan) ? f[(int64_t)e * bs] : 0.0f;
+            old[u] = (e < fan) ? p[(int64_t)e * bs] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int e = e0 + u * EL;
+            if (e >= fan) continue;
+            const float nw = (fl[u] + add) / denom;
+            float upd = (1.0f - step) * old[u] + step * nw;
+            if (keep_zero && old[u] < 1e-12f) upd = 0.0f;
+            p[(int64_t)e * bs] = upd;
+        }
     }
 }
 
