@@ -892,8 +892,12 @@ class TensorCircuit(nn.Module):
             if self.debug_poison:               # rows outside the reset ranges must be rewritten by direct stores
                 _fill(self.node_flows, float("nan"))
             # the partial reset is only valid while every depth that was counted as "stores flows directly" does so
-            ranges = self._flow_reset_ranges if (B % 8 == 0 and not self._reference_compat
-                                                 and all(self._fusion_on(gi, True) for gi in self._fused)) else None
+            rkey = (B, self._launch_cfg())
+            if getattr(self, "_reset_key", None) != rkey:            # (a hundred depths: decided once per configuration)
+                self._reset_key = rkey
+                self._reset_partial = (B % 8 == 0 and not self._reference_compat
+                                       and all(self._fusion_on(gi, True) for gi in self._fused))
+            ranges = self._flow_reset_ranges if self._reset_partial else None
             if ranges is None:
                 _fill(self.node_flows, reset)
             else:                                            # every other row is rewritten by a direct store
