@@ -60,7 +60,7 @@ SIGNATURES = {
     "pcx_em_sum": [P, P, P, P, P, P, L, I, F, F, I],
     "pcx_em_input_cat": [P, P, P, P, P, P, L, I, F, F, I],
     "pcx_probe_bounded_wait": [I, I],
-    "pcx_em_input_cat_t": [P, P, P, L, I, F, F],
+    "pcx_em_input_cat_t": [P, P, P, P, L, I, F, F],
     "pcx_input_cat_missing": [P, P, P, P, P, P, P, L, F],
     "pcx_input_cat_shadow": [P, P, L, I],
     "pcx_input_cat_fwd_t": [P, P, P, I, P, P, L, I, L, L, I],

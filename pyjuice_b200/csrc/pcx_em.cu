@@ -139,59 +139,124 @@ em_input_cat_kernel(float* __restrict__ params, const float* __restrict__ flows,
 }
 
 // Categorical EM on the transposed shadow of a large table (`flows_t`, `logp_t`: [category, row]; `params`: [row,
-// category]; every row is a source vector with C categories).  One kernel replaces three passes over the table (move
-// the flows into the [row, category] accumulators, update, rebuild the transposed log-parameter table): a CTA owns 32
-// rows; its warps stride over blocks of 32 categories, first for the rows' flow totals, then for the update, in which
-// the parameter tile goes through a per-warp shared-memory transpose so that both layouts are read and written with
-// coalesced accesses.  The flows are left as they are (the caller clears or moves them later).  (A two-kernel version
-// with a four times larger grid -- totals first, then the update -- was measured and was no faster.)
-constexpr int EMT_WARPS = 16;
-__global__ void __launch_bounds__(EMT_WARPS * 32)
-em_input_cat_t_kernel(float* __restrict__ params, float* __restrict__ logp_t, const float* __restrict__ flows_t,
-                      int64_t R, int C, float step, float pseudo) {
-    extern __shared__ float s_emt[];                     // [EMT_WARPS][32][33] transpose tiles, one per warp
-    __shared__ float s_tot[EMT_WARPS][32];
+// category]; every row is a source vector with C categories).  Two kernels replace three passes over the table (move
+// the flows into the [row, category] accumulators, update, rebuild the transposed log-parameter table): the first sums
+// every row's flows over the categories, the second works on tiles of 128 rows x 128 categories — 512 contiguous bytes
+// per row of either layout, which is what DRAM wants — with the parameter tile going through shared memory, so that
+// both layouts are read and written with full-width coalesced accesses.  The flows are left as they are (the caller
+// clears or moves them later).  (Tiles of 32 x 32, one CTA per 32 rows, ran at 3.1 TB/s: 128-byte runs strided by
+// 16 KB and 128 KB.)
+constexpr int EMT = 128;                                 // tile edge
+constexpr int EMT_LD = EMT + 1;                          // row pitch of the shared tile: odd, see emt_update_kernel
+
+// totals[r] += sum over this CTA's categories of flows_t[c, r].  Grid (ceil(R / 128), shares of the categories).
+__global__ void __launch_bounds__(256) emt_totals_kernel(float* __restrict__ totals, const float* __restrict__ flows_t,
+                                                          int64_t R, int C) {
+    __shared__ float s_tot[8][EMT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t r0 = (int64_t)blockIdx.x * 32;
-    const int64_t r = r0 + lane;
-    const bool r_ok = r < R;
-    const float add = pseudo / (float)C;
-
-    float tot = 0.0f;
-    for (int c0 = warp * 32; c0 < C; c0 += EMT_WARPS * 32) {
-        float f[32];
+    const int64_t r = (int64_t)blockIdx.x * EMT + 4 * lane;          // four consecutive rows per lane
+    const bool vec = (R % 4 == 0) && r + 3 < R;
+    float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int c0 = (blockIdx.y * 8 + warp) * 8; c0 < C; c0 += gridDim.y * 64) {
+        float4 v[8];
 #pragma unroll
-        for (int cc = 0; cc < 32; ++cc) f[cc] = (r_ok && c0 + cc < C) ? flows_t[(int64_t)(c0 + cc) * R + r] : 0.0f;
-#pragma unroll
-        for (int cc = 0; cc < 32; ++cc) tot += f[cc];
-    }
-    s_tot[warp][lane] = tot;
-    __syncthreads();
-    tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < EMT_WARPS; ++w) tot += s_tot[w][lane];
-    const float denom = tot + pseudo;
-
-    float (*tile)[33] = reinterpret_cast<float (*)[33]>(s_emt + warp * 32 * 33);
-    for (int c0 = warp * 32; c0 < C; c0 += EMT_WARPS * 32) {
-        float f[32];
-#pragma unroll
-        for (int cc = 0; cc < 32; ++cc) f[cc] = (r_ok && c0 + cc < C) ? flows_t[(int64_t)(c0 + cc) * R + r] : 0.0f;
-        const int c = c0 + lane;
-#pragma unroll 8
-        for (int rr = 0; rr < 32; ++rr) tile[rr][lane] = (r0 + rr < R && c < C) ? params[(r0 + rr) * C + c] : 0.0f;
-        __syncwarp();
-#pragma unroll
-        for (int cc = 0; cc < 32; ++cc) {
-            const float upd = (1.0f - step) * tile[lane][cc] + step * (f[cc] + add) / denom;
-            tile[lane][cc] = upd;
-            if (r_ok && c0 + cc < C) logp_t[(int64_t)(c0 + cc) * R + r] = logf(upd);
+        for (int u = 0; u < 8; ++u) {
+            const int c = c0 + u;
+            v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (c < C) {
+                const float* src = flows_t + (int64_t)c * R + r;
+                if (vec) v[u] = *reinterpret_cast<const float4*>(src);
+                else {
+                    if (r < R) v[u].x = src[0];
+                    if (r + 1 < R) v[u].y = src[1];
+                    if (r + 2 < R) v[u].z = src[2];
+                    if (r + 3 < R) v[u].w = src[3];
+                }
+            }
         }
-        __syncwarp();
-#pragma unroll 8
-        for (int rr = 0; rr < 32; ++rr)
-            if (r0 + rr < R && c < C) params[(r0 + rr) * C + c] = tile[rr][lane];
-        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { t[0] += v[u].x; t[1] += v[u].y; t[2] += v[u].z; t[3] += v[u].w; }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s_tot[warp][4 * lane + i] = t[i];
+    __syncthreads();
+    if (threadIdx.x < EMT) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sum += s_tot[w][threadIdx.x];
+        const int64_t rr = (int64_t)blockIdx.x * EMT + threadIdx.x;
+        if (rr < R && sum != 0.0f) atomicAdd(totals + rr, sum);
+    }
+}
+
+// One tile of 128 rows x 128 categories per CTA (256 threads).  Lane l owns rows l, l + 32, l + 64, l + 96 on the
+// transposed side and categories l, l + 32, ... on the parameter side: every global access of a warp is 128 contiguous
+// bytes (four of them make up the 512-byte run of the tile), and with a row pitch of 129 floats neither side has a
+// shared-memory bank conflict.
+__global__ void __launch_bounds__(256) emt_update_kernel(float* __restrict__ params, float* __restrict__ logp_t,
+                                                          const float* __restrict__ flows_t, const float* __restrict__ totals,
+                                                          int64_t R, int C, float step, float pseudo) {
+    extern __shared__ float s_p[];                       // [128 rows][EMT_LD]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = (int64_t)blockIdx.x * EMT;
+    const int c0 = blockIdx.y * EMT;
+    const float add = pseudo / (float)C;
+    // parameter tile in: warp -> rows warp, warp + 8, ...
+    for (int rr = warp; rr < EMT; rr += 8) {
+        const int64_t r = r0 + rr;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + lane + 32 * j;
+            v[j] = (r < R && c < C) ? params[r * C + c] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s_p[rr * EMT_LD + lane + 32 * j] = v[j];
+    }
+    float inv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t r = r0 + lane + 32 * i;
+        inv[i] = (r < R) ? 1.0f / (totals[r] + pseudo) : 0.0f;
+    }
+    __syncthreads();
+    // transposed side: warp -> categories warp, warp + 8, ...; two categories per round (eight loads in flight)
+    for (int cc0 = warp; cc0 < EMT; cc0 += 16) {
+        float f[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = c0 + cc0 + 8 * u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t r = r0 + lane + 32 * i;
+                f[u][i] = (c < C && r < R) ? flows_t[(int64_t)c * R + r] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int cc = cc0 + 8 * u;
+            const int c = c0 + cc;
+            if (c >= C) continue;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t r = r0 + lane + 32 * i;
+                float* cell = s_p + (lane + 32 * i) * EMT_LD + cc;
+                const float upd = (1.0f - step) * (*cell) + step * (f[u][i] + add) * inv[i];
+                *cell = upd;
+                if (r < R) logp_t[(int64_t)c * R + r] = logf(upd);
+            }
+        }
+    }
+    __syncthreads();
+    // parameter tile out
+    for (int rr = warp; rr < EMT; rr += 8) {
+        const int64_t r = r0 + rr;
+        if (r >= R) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + lane + 32 * j;
+            if (c < C) params[r * C + c] = s_p[rr * EMT_LD + lane + 32 * j];
+        }
     }
 }
 
@@ -267,18 +332,28 @@ int pcx_em_input_cat(float* params, const float* param_flows, const int32_t* sou
     return 0;
 }
 
-int pcx_em_input_cat_t(float* params, float* logp_t, const float* flows_t, int64_t n_rows, int num_cats, float step,
-                       float pseudo, void* stream) {
+int pcx_em_input_cat_t(float* params, float* logp_t, const float* flows_t, float* totals, int64_t n_rows, int num_cats,
+                       float step, float pseudo, void* stream) {
     if (n_rows <= 0 || num_cats <= 0) return 0;
-    const int smem = EMT_WARPS * 32 * 33 * (int)sizeof(float);
+    if (totals == nullptr || (reinterpret_cast<uintptr_t>(flows_t) & 15) != 0) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(totals, 0, (size_t)n_rows * sizeof(float), st);
+    if (e != cudaSuccess) return (int)e;
+    const int64_t row_tiles = pcx_cdiv(n_rows, EMT);
+    int64_t shares = pcx_cdiv(8 * 148, row_tiles);                  // about eight CTAs of 256 threads per SM
+    const int64_t max_shares = pcx_cdiv(num_cats, 64);
+    if (shares > max_shares) shares = max_shares;
+    if (shares < 1) shares = 1;
+    emt_totals_kernel<<<dim3((unsigned)row_tiles, (unsigned)shares), 256, 0, st>>>(totals, flows_t, n_rows, num_cats);
+    const int smem = EMT * EMT_LD * (int)sizeof(float);
     static PcxOnce done;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(em_input_cat_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        e = cudaFuncSetAttribute(emt_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    em_input_cat_t_kernel<<<(unsigned)pcx_cdiv(n_rows, 32), EMT_WARPS * 32, smem, (cudaStream_t)stream>>>(
-        params, logp_t, flows_t, n_rows, num_cats, step, pseudo);
+    emt_update_kernel<<<dim3((unsigned)row_tiles, (unsigned)pcx_cdiv(num_cats, EMT)), 256, smem, st>>>(
+        params, logp_t, flows_t, totals, n_rows, num_cats, step, pseudo);
     PCX_LAUNCH_CHECK();
     return 0;
 }
