@@ -436,8 +436,8 @@ int pcx_em_input_cat(float* params, const float* param_flows, const int32_t* sou
 /* Categorical EM for a layer whose flows were accumulated in the transposed shadow (pcx_input_cat_bwd_t) and whose
  * [row, category] accumulators hold nothing else: params[r, c] <- (1 - step) * params[r, c] + step * (flows_t[c, r] +
  * pseudo / C) / (sum_c flows_t[c, r] + pseudo), and logp_t[c, r] <- log of the new value, in two short kernels (instead of
- * pcx_input_cat_flush_t + pcx_em_input_cat + pcx_input_cat_shadow).  `totals`: caller-owned scratch of n_rows floats
- * (cleared by the call); flows_t 16-byte aligned and left unchanged.  The update itself is
+ * pcx_input_cat_flush_t + pcx_em_input_cat + pcx_input_cat_shadow).  `totals`: caller-owned scratch of 16 * n_rows floats
+ * (partial row totals, added in a fixed order: no atomics, results repeat bit for bit); flows_t 16-byte aligned and left unchanged.  The update itself is
  * that of the reference's categorical EM kernels (nodes/distributions/categorical.py:192-229, 231-272). */
 int pcx_em_input_cat_t(float* params, float* logp_t, const float* flows_t, float* totals, int64_t n_rows, int num_cats,
                        float step, float pseudo, void* stream);

@@ -149,7 +149,10 @@ em_input_cat_kernel(float* __restrict__ params, const float* __restrict__ flows,
 constexpr int EMT = 128;                                 // tile edge
 constexpr int EMT_LD = EMT + 1;                          // row pitch of the shared tile: odd, see emt_update_kernel
 
-// totals[r] += sum over this CTA's categories of flows_t[c, r].  Grid (ceil(R / 128), shares of the categories).
+// part[share, r] = sum over this CTA's categories of flows_t[c, r].  Grid (ceil(R / 128), shares of the categories).
+// (No atomics: the row totals are added up in a fixed order, so that data-parallel ranks, which hold bit-identical
+// flows after the all-reduce, stay bit-identical after the update.)
+constexpr int EMT_MAX_SHARES = 16;
 __global__ void __launch_bounds__(256) emt_totals_kernel(float* __restrict__ totals, const float* __restrict__ flows_t,
                                                           int64_t R, int C) {
     __shared__ float s_tot[8][EMT];
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(256) emt_totals_kernel(float* __restrict__ tot
 #pragma unroll
         for (int w = 0; w < 8; ++w) sum += s_tot[w][threadIdx.x];
         const int64_t rr = (int64_t)blockIdx.x * EMT + threadIdx.x;
-        if (rr < R && sum != 0.0f) atomicAdd(totals + rr, sum);
+        if (rr < R) totals[(int64_t)blockIdx.y * R + rr] = sum;
     }
 }
 
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(256) emt_totals_kernel(float* __restrict__ tot
 // shared-memory bank conflict.
 __global__ void __launch_bounds__(256) emt_update_kernel(float* __restrict__ params, float* __restrict__ logp_t,
                                                           const float* __restrict__ flows_t, const float* __restrict__ totals,
-                                                          int64_t R, int C, float step, float pseudo) {
+                                                          int shares, int64_t R, int C, float step, float pseudo) {
     extern __shared__ float s_p[];                       // [128 rows][EMT_LD]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.x * EMT;
@@ -217,7 +220,10 @@ __global__ void __launch_bounds__(256) emt_update_kernel(float* __restrict__ par
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int64_t r = r0 + lane + 32 * i;
-        inv[i] = (r < R) ? 1.0f / (totals[r] + pseudo) : 0.0f;
+        float tot = 0.0f;
+        if (r < R)
+            for (int sh = 0; sh < shares; ++sh) tot += totals[(int64_t)sh * R + r];
+        inv[i] = (r < R) ? 1.0f / (tot + pseudo) : 0.0f;
     }
     __syncthreads();
     // transposed side: warp -> categories warp, warp + 8, ...; two categories per round (eight loads in flight)
@@ -337,12 +343,12 @@ int pcx_em_input_cat_t(float* params, float* logp_t, const float* flows_t, float
     if (n_rows <= 0 || num_cats <= 0) return 0;
     if (totals == nullptr || (reinterpret_cast<uintptr_t>(flows_t) & 15) != 0) return -1;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemsetAsync(totals, 0, (size_t)n_rows * sizeof(float), st);
-    if (e != cudaSuccess) return (int)e;
+    cudaError_t e;
     const int64_t row_tiles = pcx_cdiv(n_rows, EMT);
     int64_t shares = pcx_cdiv(8 * 148, row_tiles);                  // about eight CTAs of 256 threads per SM
     const int64_t max_shares = pcx_cdiv(num_cats, 64);
     if (shares > max_shares) shares = max_shares;
+    if (shares > EMT_MAX_SHARES) shares = EMT_MAX_SHARES;
     if (shares < 1) shares = 1;
     emt_totals_kernel<<<dim3((unsigned)row_tiles, (unsigned)shares), 256, 0, st>>>(totals, flows_t, n_rows, num_cats);
     const int smem = EMT * EMT_LD * (int)sizeof(float);
@@ -353,7 +359,7 @@ int pcx_em_input_cat_t(float* params, float* logp_t, const float* flows_t, float
         done = true;
     }
     emt_update_kernel<<<dim3((unsigned)row_tiles, (unsigned)pcx_cdiv(num_cats, EMT)), 256, smem, st>>>(
-        params, logp_t, flows_t, totals, n_rows, num_cats, step, pseudo);
+        params, logp_t, flows_t, totals, (int)shares, n_rows, num_cats, step, pseudo);
     PCX_LAUNCH_CHECK();
     return 0;
 }

@@ -37,6 +37,26 @@ class _CastBack:
         self.dst.copy_(self.low)
 
 
+class _Works:
+    """Several collectives waited for as one."""
+
+    def __init__(self, works):
+        self.works = works
+
+    def wait(self):
+        for w in self.works:
+            w.wait()
+
+
+def all_reduce_async(t: torch.Tensor, group=None, dtype: Optional[torch.dtype] = None):
+    """Start the SUM all-reduce of a whole tensor (in ``dtype`` on the wire, if given); returns a handle with ``wait()``."""
+    import torch.distributed as dist
+    if dtype is None or dtype == t.dtype:
+        return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    low = t.to(dtype)
+    return _CastBack([dist.all_reduce(low, op=dist.ReduceOp.SUM, group=group, async_op=True)], t, low)
+
+
 class FlowArena:
     def __init__(self, sizes: Sequence[int], device):
         self.sizes = [int(s) for s in sizes]

@@ -379,7 +379,7 @@ class InputLayer(Layer, nn.Module):
             # the shadow (still "dirty"): whoever reads `param_flows` later gets them moved over as usual.
             self._param_epoch += 1
             if sh.get("totals") is None:
-                sh["totals"] = torch.zeros(sh["R"], dtype=torch.float32, device=self.device)
+                sh["totals"] = torch.zeros(16 * sh["R"], dtype=torch.float32, device=self.device)
             _lib.call("pcx_em_input_cat_t", self.params.data, sh["logp"], sh["flows"], sh["totals"], sh["R"], sh["C"],
                       float(step_size), float(pseudocount))
             sh["stamp"] = (self.params.data_ptr(), self.params._version, self._param_epoch)

@@ -998,9 +998,21 @@ class TensorCircuit(nn.Module):
                                "mini-batch per update); use `niters_per_update` to accumulate over several batches")
         self._finish_late_sync()
         arena = self._flow_arena
+        group, dtype = self._overlap_group[0], getattr(self, "_overlap_dtype", None)
+        layers = list(self.input_layer_group)
+        if all(layer._shadow is not None and layer._shadow["dirty"] and layer._arena_zero for layer in layers):
+            # every input-layer flow of this update sits in a transposed shadow table and the accumulators proper are
+            # empty: exchange the shadow tables themselves, so that the update can go on straight from them
+            from .flows import _Works, all_reduce_async
+            works = []
+            for layer in layers:
+                sh = layer._shadow
+                works.append(all_reduce_async(sh["flows"], group=group, dtype=dtype))
+                sh["touched"].fill_(1)                   # the peers' categories arrive: a later move-over skips nothing
+            self._early_sync = _Works(works)
+            return
         self._early_sync = arena.all_reduce_range_async(arena.offsets[1], self._input_reduce_end(),
-                                                        group=self._overlap_group[0],
-                                                        dtype=getattr(self, "_overlap_dtype", None))
+                                                        group=group, dtype=dtype)
 
     def _finish_late_sync(self):
         """Make the current stream wait for the second part of the overlapped all-reduce (header + sum-layer flows)

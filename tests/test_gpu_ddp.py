@@ -196,3 +196,63 @@ def test_bf16_flow_exchange_two_ranks(tmp_path):
     ierr = (r0["iparams"] - pc.input_layer_group[0].params.data.cpu()).abs().max().item()
     print(f"bf16 exchange: worst relative parameter difference {err:.2e}, leaf parameters {ierr:.2e}")
     assert err < 2e-2 and ierr < 2e-2
+
+
+def _big_vocab():
+    import pyjuice_b200 as pj
+    torch.manual_seed(8)
+    ns = pj.structures.HMM(seq_length=6, num_latents=32, num_emits=9000, homogeneous=True, block_size=8)
+    ns.init_parameters()
+    return pj.compile(ns, max_tied_ns_per_parflow_block=2)
+
+
+def _shadow_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device(dev))
+    try:
+        import pyjuice_b200 as pj
+        from pyjuice_b200 import _lib
+        calls = []
+        orig = _lib.call
+        _lib.call = lambda name, *a: (calls.append(name), orig(name, *a))[1]
+        pc = _big_vocab().to(dev)
+        g = torch.Generator().manual_seed(5)
+        x = torch.randint(0, 9000, (64, 6), generator=g)
+        shard = x[rank * 32:(rank + 1) * 32].to(dev)
+        opt = pj.optim.MiniBatchEM(pc, step_size=0.3, pseudocount=0.1, ddp=True)
+        for _ in range(4):
+            pc(shard).mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        torch.save(dict(params=pc.params.data.cpu(), iparams=pc.input_layer_group[0].params.data.cpu(),
+                        fused="pcx_em_input_cat_t" in calls, flushed="pcx_input_cat_flush_t" in calls),
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_large_vocabulary_flows_are_exchanged_in_their_transposed_table(tmp_path):
+    """Leaves with more than 8192 categories keep their flows in a transposed shadow table.  Under the overlapped
+    data-parallel exchange that table itself is all-reduced (no move into the `[row, category]` accumulators) and the
+    EM update runs straight from it on every rank; the result equals single-GPU training on the full batch."""
+    import torch.multiprocessing as mp
+    import pyjuice_b200 as pj
+    port = 39700 + (os.getpid() % 2000)
+    mp.spawn(_shadow_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(2))
+    assert r0["fused"] and r1["fused"] and not r0["flushed"] and not r1["flushed"]
+    assert torch.equal(r0["params"], r1["params"]) and torch.equal(r0["iparams"], r1["iparams"])
+    pc = _big_vocab().to("cuda:0")
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(0, 9000, (64, 6), generator=g).to("cuda:0")
+    opt = pj.optim.MiniBatchEM(pc, step_size=0.3, pseudocount=0.1)
+    for _ in range(4):
+        pc(x).mean().backward()
+        opt.step()
+    assert torch.allclose(r0["params"], pc.params.data.cpu(), rtol=1e-3, atol=1e-7)
+    assert torch.allclose(r0["iparams"], pc.input_layer_group[0].params.data.cpu(), rtol=1e-3, atol=1e-9)
