@@ -240,7 +240,8 @@ def family_work(stats, B, elsize):
 
 # DRAM bytes (read + write) of ONE launch of the named family's dominant kernel, from `ncu` captures of the same
 # kernels on one B200 (dram__bytes_read.sum + dram__bytes_write.sum); None = not captured.  (config, family) -> bytes
-# Sources: profiles/ncu_full_cfg1_chain_par.md, profiles/ncu_full_cfg4_wide_gemm.md, profiles/launch_list_cfg2_pd_b512.md
+# Sources: profiles/ncu_full_cfg1_chain_par.md, profiles/ncu_full_cfg4_wide_gemm.md, profiles/launch_list_cfg2_pd_b512.md,
+# profiles/traffic_cfg3_rat_spn_b1024.md
 TRAFFIC_PER_LAUNCH = {
     # configs[1], B = 512: one dataflow launch each for the forward pass and the element flows, one batched launch
     # for the parameter flows
@@ -256,6 +257,8 @@ TRAFFIC_PER_LAUNCH = {
     # configs[2], B = 512: mean over the 29 parameter-flow launches of a step, captured at B = 128 and scaled by 4
     # (every operand is a row of B samples)
     ("cfg2", "pcx_sum_bwd_par"): 1536.0e6 * 4 / 29,
+    # configs[3], B = 1024: mean over the product-backward launches of the capture
+    ("cfg3", "pcx_prod_bwd"): (2569.6e6 + 503.2e6) / 29,
 }
 
 
