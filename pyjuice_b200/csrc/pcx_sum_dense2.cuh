@@ -800,8 +800,7 @@ int launch_wide_gemm(const WideArgs& a, dim3 grid, cudaStream_t st) {
 template <int EPI>
 int launch_wide_gemm_dn(const WideArgs& a, int DN, dim3 grid, cudaStream_t st) {
     if (DN == 256) return launch_wide_gemm<EPI, 256>(a, grid, st);
-    if (DN == 128) return launch_wide_gemm<EPI, 128>(a, grid, st);
-    return launch_wide_gemm<EPI, 64>(a, grid, st);
+    return launch_wide_gemm<EPI, 128>(a, grid, st);          // wide_dn() yields 256 or 128
 }
 
 template <int FC>
