@@ -592,7 +592,11 @@ def measure_ours(config: str, args, rank: int, world: int, dev, K: int, W: int, 
                 "last_mean_ll": last},
         "gpu_launches": launches_per_step * K,
         "roofline": roofline,
+        # tflops: algorithmic flops (6 * edges * samples) over the sum-layer time of the instrumented pass (eager, one
+        # stream, an event between every two kernels); tflops_whole_step: the same flops over the live step, leaves
+        # and EM included — a lower bound that needs no instrumentation
         "sum_layers": {"tflops": sum_tflops, "ms_per_step": sum_ms,
+                       "tflops_whole_step": 6.0 * stats["e_sum"] * Bl / (ms_dev / K * 1e-3) / 1e12,
                        "frac_of_bf16_peak": (sum_tflops or 0) / peaks["tensor"],
                        "arith": ["fp32 FMA (CUDA cores)",
                                  "tcgen05 bf16 hi/lo split x3, fp32 accumulate (fwd, element flows, parameter flows)",
