@@ -146,3 +146,20 @@ def test_table_validation_accepts_compiled_circuits_and_names_a_bad_index():
     layer.partitioned_pids[0][0, 0] = pc.params.numel()
     with pytest.raises(ValueError, match="sum pids"):
         pc.validate_tables()
+
+
+def test_public_header_is_plain_c():
+    """`include/pcx_b200.h` is the boundary a non-Python host binds: it must compile as C99 on its own (no C++, no
+    torch or CUDA types in the signatures)."""
+    import os, shutil, subprocess, tempfile
+    import pytest
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "h.c")
+        open(src, "w").write('#include "include/pcx_b200.h"\nint main(void) { return 0; }\n')
+        r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I", root, src],
+                           capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
