@@ -221,6 +221,7 @@ class InputLayer(Layer, nn.Module):
     @param_flows.setter
     def param_flows(self, value):
         self._param_flows = value
+        self._arena_zero = False                 # unknown content (whoever hands over a cleared buffer says so)
 
     def _setup_shadow(self, device):
         self._shadow = None
